@@ -1,0 +1,143 @@
+"""In-tree native build: nvcc for the sm_100a kernel library, g++ for the host runtime.
+
+The shared objects are written next to the Python package (``_lib/``) so that a snapshot of the source tree
+carries them to a machine without a compiler cache.  Objects are rebuilt only when a source or header changed
+(content hash), files are compiled in parallel, and nothing here needs a GPU: nvcc cross-compiles.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+PKG = Path(__file__).resolve().parent
+CSRC = PKG / "csrc"
+LIBDIR = PKG / "_lib"
+OBJDIR = PKG.parent / "build" / "obj"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "--use_fast_math", "-Xptxas", "-v",
+]
+# --use_fast_math is dropped for files whose numerics are compared bit-for-bit with an oracle
+NO_FAST_MATH = {"act_quant.cu"}
+GXX_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-Wall", "-Wextra", "-fno-stack-protector", "-pthread"]
+
+KERNEL_LIB = "libb200_kernels.so"
+HOSTRT_LIB = "libb200_hostrt.so"
+DEVRT_LIB = "libb200_devrt.so"
+
+
+def _nvcc() -> str:
+    for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and Path(cand).exists():
+            return cand
+    raise RuntimeError("nvcc not found")
+
+
+def _digest(paths, extra: str) -> str:
+    h = hashlib.sha256(extra.encode())
+    for p in sorted(paths):
+        h.update(str(p.name).encode())
+        h.update(p.read_bytes())
+    return h.hexdigest()
+
+
+def _run(cmd, log: Path | None = None) -> str:
+    proc = subprocess.run(cmd, capture_output=True, text=True)
+    out = proc.stdout + proc.stderr
+    if log is not None:
+        log.write_text(" ".join(map(str, cmd)) + "\n" + out)
+    if proc.returncode != 0:
+        raise RuntimeError("build step failed:\n" + " ".join(map(str, cmd)) + "\n" + out[-6000:])
+    return out
+
+
+def _stale(stamp: Path, digest: str, product: Path) -> bool:
+    if not product.exists() or not stamp.exists():
+        return True
+    try:
+        return json.loads(stamp.read_text()).get("digest") != digest
+    except Exception:
+        return True
+
+
+def build_kernels(verbose: bool = False) -> Path:
+    """Compile every .cu under csrc/kernels for sm_100a and link libb200_kernels.so."""
+    srcdir = CSRC / "kernels"
+    sources = sorted(srcdir.glob("*.cu"))
+    headers = sorted(list(srcdir.glob("*.cuh")) + list(srcdir.glob("*.h")) + list((CSRC / "fabric").glob("*.h")))
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    OBJDIR.mkdir(parents=True, exist_ok=True)
+    nvcc = _nvcc()
+    hdigest = _digest(headers, " ".join(NVCC_FLAGS))
+
+    def compile_one(src: Path) -> Path:
+        obj = OBJDIR / (src.stem + ".o")
+        stamp = OBJDIR / (src.stem + ".stamp")
+        digest = _digest([src], hdigest)
+        if _stale(stamp, digest, obj):
+            flags = [f for f in NVCC_FLAGS if not (f == "--use_fast_math" and src.name in NO_FAST_MATH)]
+            out = _run([nvcc, *flags, "-I", str(srcdir), "-I", str(CSRC), "-c", str(src), "-o", str(obj)],
+                       OBJDIR / (src.stem + ".log"))
+            if verbose:
+                print(out, file=sys.stderr)
+            stamp.write_text(json.dumps({"digest": digest}))
+        return obj
+
+    with ThreadPoolExecutor(max_workers=min(8, max(1, len(sources)))) as ex:
+        objs = list(ex.map(compile_one, sources))
+    lib = LIBDIR / KERNEL_LIB
+    link_digest = _digest(objs, "link")
+    stamp = OBJDIR / "kernels.link.stamp"
+    if _stale(stamp, link_digest, lib):
+        _run([nvcc, "-shared", "-o", str(lib), *map(str, objs), "-cudart", "static"])
+        stamp.write_text(json.dumps({"digest": link_digest}))
+    return lib
+
+
+def _build_cpp(name: str, subdir: str, extra_flags=(), libs=()) -> Path:
+    srcdir = CSRC / subdir
+    sources = sorted(srcdir.glob("*.cpp"))
+    headers = sorted(list(srcdir.glob("*.hpp")) + list(srcdir.glob("*.h")) + list((CSRC / "fabric").glob("*.h")))
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    OBJDIR.mkdir(parents=True, exist_ok=True)
+    lib = LIBDIR / name
+    digest = _digest(sources + headers, " ".join(GXX_FLAGS) + " ".join(extra_flags))
+    stamp = OBJDIR / (name + ".stamp")
+    if _stale(stamp, digest, lib):
+        _run(["g++", *GXX_FLAGS, *extra_flags, "-shared", "-I", str(srcdir), "-I", str(CSRC), "-o", str(lib),
+              *map(str, sources), *libs])
+        stamp.write_text(json.dumps({"digest": digest}))
+    return lib
+
+
+def build_hostrt() -> Path:
+    """C++ host runtime: raw syscalls, NUMA topology, CPU masks, NUMA arena, clone3 thread pool, futex gates."""
+    return _build_cpp(HOSTRT_LIB, "hostrt")
+
+
+def build_devrt() -> Path:
+    """C++ device runtime: GPU topology, HBM arena (CUDA virtual memory management), device masks."""
+    cuda_inc = Path(_nvcc()).resolve().parent.parent / "include"
+    return _build_cpp(DEVRT_LIB, "devrt", extra_flags=("-I", str(cuda_inc)), libs=("-ldl",))
+
+
+def build_all(verbose: bool = False) -> dict:
+    out = {}
+    if any((CSRC / "hostrt").glob("*.cpp")):
+        out["hostrt"] = build_hostrt()
+    if any((CSRC / "devrt").glob("*.cpp")):
+        out["devrt"] = build_devrt()
+    out["kernels"] = build_kernels(verbose)
+    return out
+
+
+if __name__ == "__main__":
+    for k, v in build_all(verbose="-v" in sys.argv).items():
+        print(f"{k}: {v}")

@@ -1,0 +1,217 @@
+// Activation prologue for every W8A8 linear: (residual add) -> (RMSNorm) | (SwiGLU) -> block-Hadamard
+// rotation (block 128, Sylvester order, scaled 1/sqrt(128)) -> per-token symmetric int8 quantisation.
+//
+//   one CTA per token row, 8 warps; warp w owns 128-blocks w, w+8, ...; inside a block lane l holds the four
+//   consecutive elements 4l..4l+3, so the seven butterfly stages are two in-register stages plus five
+//   warp-shuffle stages.  Rotated values stay in registers between the abs-max pass and the quantise pass,
+//   so the row is read from HBM exactly once and written once (int8 + one fp32 scale).
+#include "ptx.cuh"
+#include "api.h"
+
+namespace b200 {
+
+constexpr int AQ_THREADS = 256;
+constexpr int AQ_WARPS = AQ_THREADS / 32;
+
+enum ActQuantMode : int { AQ_PLAIN = 0, AQ_NORM = 1, AQ_ADD_NORM = 2, AQ_SWIGLU = 3 };
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ void fwht128_lane4(float (&v)[4], int lane) {
+  // stages on index bits 0 and 1 (inside the lane)
+  float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
+  v[0] = a0 + a2; v[1] = a1 + a3; v[2] = a0 - a2; v[3] = a1 - a3;
+  // stages on index bits 2..6 (lane bits 0..4)
+#pragma unroll
+  for (int b = 0; b < 5; ++b) {
+    const int mask = 1 << b;
+    const bool upper = (lane & mask) != 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float o = __shfl_xor_sync(0xffffffffu, v[i], mask);
+      v[i] = upper ? (o - v[i]) : (v[i] + o);
+    }
+  }
+  const float s = 0.08838834764831845f;  // 1/sqrt(128)
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] *= s;
+}
+
+__device__ __forceinline__ void load4_bf16(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  v[0] = __low2float(lo); v[1] = __high2float(lo); v[2] = __low2float(hi); v[3] = __high2float(hi);
+}
+__device__ __forceinline__ void store4_bf16(__nv_bfloat16* p, const float (&v)[4]) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
+  __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&lo);
+  raw.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+template <int MAXB, int MODE>
+__global__ void __launch_bounds__(AQ_THREADS)
+act_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ residual,
+                 long long ldr, const __nv_bfloat16* __restrict__ gamma, float eps, int8_t* __restrict__ q,
+                 long long ldq, float* __restrict__ scale, __nv_bfloat16* __restrict__ xn_out, long long ldn,
+                 int K) {
+  __shared__ float red[AQ_WARPS];
+  __shared__ float bcast;
+  const int row = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nblocks = K >> 7;
+  const __nv_bfloat16* xr = x + static_cast<size_t>(row) * ldx;
+
+  float v[MAXB][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXB; ++i) {
+    const int b = warp + i * AQ_WARPS;
+    if (b < nblocks) {
+      const int k = b * 128 + lane * 4;
+      if constexpr (MODE == AQ_SWIGLU) {
+        float g[4], u[4];
+        load4_bf16(xr + k, g);
+        load4_bf16(xr + K + k, u);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[i][j] = (g[j] / (1.f + __expf(-g[j]))) * u[j];
+      } else {
+        load4_bf16(xr + k, v[i]);
+        if constexpr (MODE == AQ_ADD_NORM) {
+          float r[4];
+          __nv_bfloat16* rp = residual + static_cast<size_t>(row) * ldr + k;
+          load4_bf16(rp, r);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            // the residual stream is kept in bf16: round the sum once, and normalise what was stored
+            v[i][j] = __bfloat162float(__float2bfloat16(v[i][j] + r[j]));
+          }
+          store4_bf16(rp, v[i]);
+        }
+        if constexpr (MODE == AQ_NORM || MODE == AQ_ADD_NORM) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ss += v[i][j] * v[i][j];
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[i][j] = 0.f;
+    }
+  }
+
+  if constexpr (MODE == AQ_NORM || MODE == AQ_ADD_NORM) {
+    ss = warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      float t = 0.f;
+#pragma unroll
+      for (int w = 0; w < AQ_WARPS; ++w) t += red[w];
+      bcast = rsqrtf(t / static_cast<float>(K) + eps);
+    }
+    __syncthreads();
+    const float rstd = bcast;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < MAXB; ++i) {
+      const int b = warp + i * AQ_WARPS;
+      if (b < nblocks) {
+        const int k = b * 128 + lane * 4;
+        float g[4];
+        load4_bf16(gamma + k, g);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[i][j] = v[i][j] * rstd * g[j];
+        if (xn_out) store4_bf16(xn_out + static_cast<size_t>(row) * ldn + k, v[i]);
+      }
+    }
+  }
+
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < MAXB; ++i) {
+    const int b = warp + i * AQ_WARPS;
+    if (b < nblocks) {
+      fwht128_lane4(v[i], lane);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+    }
+  }
+  amax = warp_max(amax);
+  if (lane == 0) red[warp] = amax;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < AQ_WARPS; ++w) t = fmaxf(t, red[w]);
+    const float s = (t > 0.f) ? (t / 127.f) : 1.f;
+    bcast = s;
+    scale[row] = s;
+  }
+  __syncthreads();
+  const float s = bcast;
+  int8_t* qr = q + static_cast<size_t>(row) * ldq;
+#pragma unroll
+  for (int i = 0; i < MAXB; ++i) {
+    const int b = warp + i * AQ_WARPS;
+    if (b < nblocks) {
+      uint32_t packed = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        int qi = __float2int_rn(__fdiv_rn(v[i][j], s));
+        qi = max(-127, min(127, qi));
+        packed |= (static_cast<uint32_t>(qi) & 0xffu) << (8 * j);
+      }
+      *reinterpret_cast<uint32_t*>(qr + b * 128 + lane * 4) = packed;
+    }
+  }
+}
+
+template <int MAXB>
+static void launch_aq(int mode, const __nv_bfloat16* x, long long ldx, __nv_bfloat16* residual, long long ldr,
+                      const __nv_bfloat16* gamma, float eps, int8_t* q, long long ldq, float* scale,
+                      __nv_bfloat16* xn, long long ldn, int M, int K, cudaStream_t st) {
+  switch (mode) {
+    case AQ_PLAIN: act_quant_kernel<MAXB, AQ_PLAIN><<<M, AQ_THREADS, 0, st>>>(x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
+    case AQ_NORM: act_quant_kernel<MAXB, AQ_NORM><<<M, AQ_THREADS, 0, st>>>(x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
+    case AQ_ADD_NORM: act_quant_kernel<MAXB, AQ_ADD_NORM><<<M, AQ_THREADS, 0, st>>>(x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
+    default: act_quant_kernel<MAXB, AQ_SWIGLU><<<M, AQ_THREADS, 0, st>>>(x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// mode: 0 plain, 1 rmsnorm, 2 residual-add + rmsnorm (residual updated in place), 3 swiglu (x is [M, 2K]: gate | up)
+extern "C" int b200_act_quant(const void* x, long long ldx, void* residual, long long ldr, const void* gamma, float eps,
+                              void* q, long long ldq, float* scale, void* xn_out, long long ldn, int M, int K, int mode,
+                              cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (K <= 0 || (K % 128) != 0 || K > 128 * AQ_WARPS * 16) return -1;
+  if (mode < 0 || mode > 3) return -1;
+  if ((mode == AQ_NORM || mode == AQ_ADD_NORM) && !gamma) return -1;
+  if (mode == AQ_ADD_NORM && !residual) return -1;
+  if ((ldx % 4) || (ldq % 4) || (reinterpret_cast<uintptr_t>(x) & 7) || (reinterpret_cast<uintptr_t>(q) & 3)) return -2;
+  const int nb = K / 128;
+  auto X = static_cast<const __nv_bfloat16*>(x);
+  auto R = static_cast<__nv_bfloat16*>(residual);
+  auto G = static_cast<const __nv_bfloat16*>(gamma);
+  auto Q = static_cast<int8_t*>(q);
+  auto XN = static_cast<__nv_bfloat16*>(xn_out);
+  if (nb <= 4 * AQ_WARPS) launch_aq<4>(mode, X, ldx, R, ldr, G, eps, Q, ldq, scale, XN, ldn, M, K, stream);
+  else launch_aq<16>(mode, X, ldx, R, ldr, G, eps, Q, ldq, scale, XN, ldn, M, K, stream);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
+}

@@ -1,0 +1,30 @@
+// C ABI of the sm_100a kernel library (loaded from Python with ctypes; usable from any C/C++ host).
+// Conventions: every function returns 0 on success and a negative value on a rejected argument or a
+// launch error; nothing here synchronises the stream; pointers are device pointers unless noted.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- W8A8 linear -----------------------------------------------------------------------------------
+// Scratch bytes the stream-K path of b200_w8a8_gemm wants for an [M,N] problem (int32 partial sums).
+size_t b200_w8a8_gemm_ws_bytes(int M, int N);
+// y[m,n] = (sum_k xq[m,k]*wq[n,k]) * sx[m] * sw[n] (+ residual[m,n]); y is bf16 (or fp32 when out_fp32).
+// ws/counters must be zero on entry and are left zero on exit; force_mode: -1 auto, 0 whole tiles, 1 stream-K.
+int b200_w8a8_gemm(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
+                   const void* residual, int M, int N, int K, int ldy, int out_fp32,
+                   void* ws, size_t ws_bytes, void* counters, int counters_len, int* status,
+                   int num_sms, int force_mode, cudaStream_t stream);
+
+// ---- activation prologue ---------------------------------------------------------------------------
+int b200_act_quant(const void* x, long long ldx, void* residual, long long ldr, const void* gamma, float eps,
+                   void* q, long long ldq, float* scale, void* xn_out, long long ldn, int M, int K, int mode,
+                   cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

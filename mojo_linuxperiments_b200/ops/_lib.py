@@ -1,0 +1,68 @@
+"""ctypes binding of the sm_100a kernel library (``_lib/libb200_kernels.so``).
+
+The library is built in-tree by ``mojo_linuxperiments_b200._build``.  On a machine with a GPU a missing
+library is an error (there is no PyTorch fallback for the hot ops); on a CPU-only machine importing this
+module works and ``lib()`` raises only when a kernel is actually requested.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_void_p, c_size_t, c_float, c_longlong, c_uint64
+from functools import lru_cache
+from pathlib import Path
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libb200_kernels.so"
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+@lru_cache(maxsize=None)
+def lib() -> ctypes.CDLL:
+    if not _LIB_PATH.exists():
+        raise KernelError(
+            f"{_LIB_PATH} is missing: run `python -m mojo_linuxperiments_b200._build` (needs nvcc, no GPU)")
+    L = ctypes.CDLL(str(_LIB_PATH))
+    for name in dir(_Sig):
+        if name.startswith("b200_"):
+            restype, argtypes = getattr(_Sig, name)
+            try:
+                fn = getattr(L, name)
+            except AttributeError as e:  # stale library
+                raise KernelError(f"{name} not found in {_LIB_PATH}; rebuild the kernel library") from e
+            fn.restype = restype
+            fn.argtypes = argtypes
+    return L
+
+
+P = c_void_p
+I = c_int
+LL = c_longlong
+F = c_float
+
+
+class _Sig:
+    b200_w8a8_gemm_ws_bytes = (c_size_t, [I, I])
+    b200_w8a8_gemm = (I, [P, P, P, P, P, P, I, I, I, I, I, P, c_size_t, P, I, P, I, I, P])
+    b200_act_quant = (I, [P, LL, P, LL, P, F, P, LL, P, P, LL, I, I, I, P])
+
+
+def ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+
+
+@lru_cache(maxsize=None)
+def num_sms(device_index: int) -> int:
+    return torch.cuda.get_device_properties(device_index).multi_processor_count

@@ -1,0 +1,59 @@
+"""W8A8 Hadamard linear: activation prologue (rotate + per-token int8) and the tcgen05 int8 GEMM."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .workspace import Workspace, default_workspace
+
+AQ_PLAIN, AQ_NORM, AQ_ADD_NORM, AQ_SWIGLU = 0, 1, 2, 3
+
+
+def act_quant(x: torch.Tensor, *, mode: int = AQ_PLAIN, gamma: torch.Tensor | None = None, eps: float = 1e-5,
+              residual: torch.Tensor | None = None, want_normed: bool = False,
+              out_q: torch.Tensor | None = None, out_scale: torch.Tensor | None = None):
+    """Rotate (block-128 Hadamard) and quantise rows of ``x`` (bf16 [M, K], last dim contiguous).
+
+    mode AQ_NORM applies RMSNorm(gamma) first; AQ_ADD_NORM first adds ``x`` into ``residual`` (in place);
+    AQ_SWIGLU treats ``x`` as [M, 2K] = gate | up and quantises silu(gate) * up.
+    Returns (q int8 [M,K], scale fp32 [M]) and, if ``want_normed``, the normalised bf16 rows.
+    """
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    M = x.shape[0]
+    K = x.shape[1] // 2 if mode == AQ_SWIGLU else x.shape[1]
+    q = out_q if out_q is not None else torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = out_scale if out_scale is not None else torch.empty((M,), dtype=torch.float32, device=x.device)
+    xn = torch.empty((M, K), dtype=torch.bfloat16, device=x.device) if want_normed else None
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.stride(1) == 1
+    rc = _lib.lib().b200_act_quant(
+        x.data_ptr(), x.stride(0), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
+        _lib.ptr(gamma), float(eps), q.data_ptr(), q.stride(0), s.data_ptr(), _lib.ptr(xn),
+        xn.stride(0) if xn is not None else 0, M, K, mode, _lib.stream())
+    _lib.check(rc, "act_quant")
+    return (q, s, xn) if want_normed else (q, s)
+
+
+def w8a8_gemm(xq: torch.Tensor, sx: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor, *,
+              residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
+              out_dtype: torch.dtype = torch.bfloat16, workspace: Workspace | None = None,
+              force_mode: int = -1) -> torch.Tensor:
+    """y[m,n] = (sum_k xq[m,k] wq[n,k]) * sx[m] * sw[n] (+ residual); int8 operands, int32 accumulate in TMEM."""
+    assert xq.is_cuda and xq.dtype == torch.int8 and wq.dtype == torch.int8
+    assert xq.is_contiguous() and wq.is_contiguous()
+    M, K = xq.shape
+    N, K2 = wq.shape
+    assert K == K2
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=xq.device)
+    assert out.stride(1) == 1 and out.dtype in (torch.bfloat16, torch.float32)
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.stride(0) == out.stride(0) and residual.stride(1) == 1
+    w = workspace or default_workspace(xq.device)
+    rc = _lib.lib().b200_w8a8_gemm(
+        xq.data_ptr(), sx.data_ptr(), wq.data_ptr(), sw.data_ptr(), out.data_ptr(), _lib.ptr(residual),
+        M, N, K, out.stride(0), 1 if out.dtype == torch.float32 else 0,
+        w.ws.data_ptr(), w.ws_bytes, w.counters.data_ptr(), w.counters.numel(), w.status.data_ptr(),
+        _lib.num_sms(xq.device.index), force_mode, _lib.stream())
+    _lib.check(rc, "w8a8_gemm")
+    return out

@@ -1,0 +1,112 @@
+"""W8A8 linear on the GPU against the plain PyTorch reference of the same op."""
+import pytest
+import torch
+
+from mojo_linuxperiments_b200.oracle import quant as Q
+
+pytestmark = pytest.mark.gpu
+
+
+def _mk_x(m, k, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    x = torch.randn((m, k), generator=g)
+    mask = torch.rand((m, k), generator=g) < 1e-3
+    x = torch.where(mask, x * 50, x)
+    return x.to(torch.bfloat16).cuda()
+
+
+def _mk_w(n, k, seed=1):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    wq = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8).cuda()
+    sw = (torch.rand((n,), generator=g) * 9e-3 + 1e-3).cuda()
+    return wq, sw
+
+
+@pytest.mark.parametrize("m,k", [(1, 128), (3, 512), (32, 4096), (257, 1792), (64, 14336)])
+def test_act_quant_plain(m, k):
+    from mojo_linuxperiments_b200.ops import linear as L
+    x = _mk_x(m, k)
+    q, s = L.act_quant(x)
+    torch.cuda.synchronize()
+    q_ref, s_ref = Q.rotate_quantize(x)
+    assert torch.allclose(s, s_ref, rtol=1e-5, atol=0)
+    d = (q.int() - q_ref.int()).abs()
+    assert d.max().item() <= 1
+    assert (d > 0).float().mean().item() < 2e-3
+
+
+@pytest.mark.parametrize("mode", ["norm", "add_norm", "swiglu"])
+def test_act_quant_fused_modes(mode):
+    from mojo_linuxperiments_b200.ops import linear as L
+    m, k = 37, 4096
+    x = _mk_x(m, k, 3)
+    gamma = (torch.rand(k) + 0.5).to(torch.bfloat16).cuda()
+    if mode == "norm":
+        q, s, xn = L.act_quant(x, mode=L.AQ_NORM, gamma=gamma, eps=1e-5, want_normed=True)
+        ref = Q.rmsnorm(x, gamma, 1e-5)
+        assert torch.allclose(xn.float(), ref, rtol=2e-2, atol=2e-2)
+    elif mode == "add_norm":
+        res = _mk_x(m, k, 4)
+        res0 = res.clone()
+        q, s = L.act_quant(x, mode=L.AQ_ADD_NORM, gamma=gamma, eps=1e-5, residual=res)
+        h = (x.float() + res0.float()).to(torch.bfloat16)
+        assert torch.equal(res, h)
+        ref = Q.rmsnorm(h, gamma, 1e-5)
+    else:
+        gu = torch.cat([x, _mk_x(m, k, 5)], dim=1).contiguous()
+        q, s = L.act_quant(gu, mode=L.AQ_SWIGLU)
+        ref = Q.swiglu(gu)
+    torch.cuda.synchronize()
+    q_ref, s_ref = Q.quantize_rows(Q.rotate(ref))
+    assert torch.allclose(s, s_ref, rtol=2e-3)
+    deq = q.float() * s[:, None]
+    deq_ref = q_ref.float() * s_ref[:, None]
+    assert (deq - deq_ref).abs().max().item() <= 2.5 * s_ref.max().item()
+
+
+GEMM_SHAPES = [
+    (16, 128, 128), (1, 128, 128), (1, 256, 512), (7, 384, 1024), (32, 4096, 4096), (32, 6144, 4096),
+    (33, 1024, 512), (100, 4096, 1792), (128, 3584, 4096), (200, 1000, 768), (1024, 3584, 4096),
+    (4096, 1792, 4096), (777, 16032, 1024),
+]
+
+
+@pytest.mark.parametrize("m,n,k", GEMM_SHAPES)
+@pytest.mark.parametrize("force_mode", [-1, 0, 1])
+def test_w8a8_gemm_exact(m, n, k, force_mode):
+    """Integer accumulation is exact, so the bf16 output may differ from the reference only by its rounding."""
+    from mojo_linuxperiments_b200.ops import linear as L
+    from mojo_linuxperiments_b200.ops.workspace import default_workspace
+    if force_mode == 1 and m > 512:
+        pytest.skip("stream-K is the small-M path")
+    g = torch.Generator(device="cpu").manual_seed(m * 31 + n)
+    xq = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int8).cuda()
+    sx = (torch.rand((m,), generator=g) * 0.05 + 0.01).cuda()
+    wq, sw = _mk_w(n, k)
+    y = L.w8a8_gemm(xq, sx, wq, sw, out_dtype=torch.float32, force_mode=force_mode)
+    yb = L.w8a8_gemm(xq, sx, wq, sw, force_mode=force_mode)
+    torch.cuda.synchronize()
+    ws = default_workspace(xq.device)
+    ws.check_status()
+    assert int(ws.ws.abs().max().item()) == 0 and int(ws.counters.abs().max().item()) == 0
+    ref = Q.w8a8_linear(xq, sx, wq, sw)
+    assert torch.allclose(y, ref, rtol=1e-5, atol=1e-5), (y - ref).abs().max().item()
+    assert torch.allclose(yb.float(), ref, rtol=1e-2, atol=1e-2)
+
+
+def test_w8a8_gemm_residual_and_full_op():
+    from mojo_linuxperiments_b200.ops import linear as L
+    m, n, k = 48, 4096, 4096
+    x = _mk_x(m, k)
+    w = torch.randn((n, k), generator=torch.Generator().manual_seed(5)) * 0.02
+    wq, sw = Q.quantize_weight(w.cuda())
+    res = _mk_x(m, n, 9)
+    q, s = L.act_quant(x)
+    y = L.w8a8_gemm(q, s, wq, sw, residual=res)
+    torch.cuda.synchronize()
+    ref_same_q = Q.w8a8_linear(q, s, wq, sw, residual=res)
+    assert torch.allclose(y.float(), ref_same_q, rtol=1e-2, atol=2e-2)
+    # looser: against the unquantised product
+    exact = x.float() @ w.cuda().t() + res.float()
+    rel = (y.float() - exact).norm() / exact.norm()
+    assert rel.item() < 0.05
