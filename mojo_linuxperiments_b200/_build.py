@@ -122,6 +122,24 @@ def build_hostrt() -> Path:
     return _build_cpp(HOSTRT_LIB, "hostrt")
 
 
+def build_hostrt_selftest() -> Path:
+    """Stand-alone executable that runs the reference's twelve integration scenarios (exit code = failures)."""
+    srcdir = CSRC / "hostrt"
+    exe = LIBDIR / "hostrt_selftest"
+    sources = sorted(srcdir.glob("*.cpp"))
+    sources = [s for s in sources if s.name != "capi.cpp"] + [srcdir / "selftest" / "main.cc"]
+    headers = sorted(srcdir.glob("*.hpp"))
+    digest = _digest(sources + headers, "selftest" + " ".join(GXX_FLAGS))
+    stamp = OBJDIR / "hostrt_selftest.stamp"
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    OBJDIR.mkdir(parents=True, exist_ok=True)
+    if _stale(stamp, digest, exe):
+        flags = [f for f in GXX_FLAGS if f != "-fPIC"]
+        _run(["g++", *flags, "-I", str(srcdir), "-I", str(CSRC), "-o", str(exe), *map(str, sources)])
+        stamp.write_text(json.dumps({"digest": digest}))
+    return exe
+
+
 def build_devrt() -> Path:
     """C++ device runtime: GPU topology, HBM arena (CUDA virtual memory management), device masks."""
     cuda_inc = Path(_nvcc()).resolve().parent.parent / "include"
@@ -132,6 +150,7 @@ def build_all(verbose: bool = False) -> dict:
     out = {}
     if any((CSRC / "hostrt").glob("*.cpp")):
         out["hostrt"] = build_hostrt()
+        out["hostrt_selftest"] = build_hostrt_selftest()
     if any((CSRC / "devrt").glob("*.cpp")):
         out["devrt"] = build_devrt()
     out["kernels"] = build_kernels(verbose)

@@ -4,10 +4,11 @@
 //   Wq int8 [N,K] (output channels, stored rotated), sw fp32 [N]
 //
 // Design (Blackwell-first):
-//   * The weight tile is the tcgen05 "A" operand (128 output channels fill the MMA M dimension), the
-//     token tile is the "B" operand (BN in {16,32,64,128,256} tokens fill the MMA N dimension).  The same
-//     kernel therefore serves decode (M = 1..32 tokens: pure weight streaming) and prefill (M in the
-//     thousands) without ever padding tokens up to 128.
+//   * Two orientations of one kernel.  SWAP (M <= 64 tokens, decode): the weight tile is the tcgen05 "A"
+//     operand (128 output channels fill the MMA M dimension) and the token tile is the "B" operand
+//     (BN in {16,32,64} tokens fill the MMA N dimension), so tokens are never padded up to 128 and the
+//     kernel is pure weight streaming.  Normal (prefill): 128 tokens are the A rows and BN (64..256) output
+//     channels the B rows, so each epilogue thread owns one token row and writes contiguous bf16.
 //   * Operands arrive by TMA (2-D tiled, 128-byte swizzle, no cluster broadcast) into a STAGES-deep
 //     ring of shared-memory stages guarded by full/empty mbarriers.
 //   * One elected thread issues tcgen05.mma.kind::i8 (128 x BN x 32 per instruction); the int32
@@ -35,7 +36,7 @@ constexpr int GROUP_M = 8;      // token tiles per rasterisation group
 
 struct GemmParams {
   int M, N, K;
-  int m_tiles, n_tiles, kblocks, num_tiles;
+  int m_tiles, n_tiles, kblocks, num_tiles;   // m_tiles: tiles along tokens, n_tiles: tiles along output channels
   int mode;                     // 0: whole tiles round-robin, 1: stream-K
   long long total_units;
   const float* sx;
@@ -89,9 +90,11 @@ __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& 
   n_tile = r / gsize;
 }
 
-template <int BN, int STAGES>
+// tmap_a covers the operand whose 128-row tiles fill the MMA M dimension (weights when SWAP, tokens otherwise),
+// tmap_b the operand whose BN-row tiles fill the MMA N dimension.
+template <int BN, int STAGES, bool SWAP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
   constexpr int A_BYTES = TILE_N * BLOCK_K;      // 16 KiB
   constexpr int B_BYTES = BN * BLOCK_K;
@@ -136,8 +139,9 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
-      prefetch_tmap(&tmap_w);
-      prefetch_tmap(&tmap_x);
+      prefetch_tmap(&tmap_a);
+      prefetch_tmap(&tmap_b);
+      // weights streamed once (single token tile) should not displace anything; otherwise keep them
       const uint64_t pol_w = (p.m_tiles == 1) ? policy_evict_first() : policy_evict_last();
       WorkIter it(p);
       Seg sg;
@@ -151,8 +155,13 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY, limit)) { ok = false; break; }
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
-          tma_load_2d_hint(a_dst, &tmap_w, full_bar(stage), kb * BLOCK_K, n_tile * TILE_N, pol_w);
-          tma_load_2d(a_dst + A_BYTES, &tmap_x, full_bar(stage), kb * BLOCK_K, m_tile * BN);
+          if constexpr (SWAP) {
+            tma_load_2d_hint(a_dst, &tmap_a, full_bar(stage), kb * BLOCK_K, n_tile * TILE_N, pol_w);
+            tma_load_2d(a_dst + A_BYTES, &tmap_b, full_bar(stage), kb * BLOCK_K, m_tile * BN);
+          } else {
+            tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * BLOCK_K, m_tile * TILE_N);
+            tma_load_2d_hint(a_dst + A_BYTES, &tmap_b, full_bar(stage), kb * BLOCK_K, n_tile * BN, pol_w);
+          }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -213,76 +222,153 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_consta
       tile_coords(p, sg.tile, m_tile, n_tile);
       if (!mbar_wait(tfull_bar(a), aphase, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, limit)) { ok = false; break; }
       tc_fence_after();
-      const int n = n_tile * TILE_N + q * 32 + lane;
-      const bool n_ok = n < p.N;
-      const int m0 = m_tile * BN;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BN;
       const bool whole = (sg.kb0 == 0 && sg.kb1 == p.kblocks);
-      const float swn = n_ok ? __ldg(p.sw + n) : 0.f;
-
       constexpr int CH = (BN >= 32) ? 32 : 16;
+
+      if constexpr (!SWAP) {
+        // ---- normal orientation: this thread owns token row m and walks BN output channels ----
+        const int m = m_tile * TILE_N + q * 32 + lane;
+        const bool m_ok = m < p.M;
+        const float sxm = m_ok ? __ldg(p.sx + m) : 0.f;
+        const int n0 = n_tile * BN;
+        const size_t row_off = static_cast<size_t>(m_ok ? m : 0) * p.ldy;
+        const bool vec_ok = !p.out_fp32 && (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) &&
+                            (!p.residual || (reinterpret_cast<uintptr_t>(p.residual) & 15) == 0);
 #pragma unroll 1
-      for (int c = 0; c < BN / CH; ++c) {
-        uint32_t r[CH];
-        if constexpr (CH == 32) tmem_ld_x32(t_addr + c * CH, r); else tmem_ld_x16(t_addr + c * CH, r);
-        tmem_ld_wait();
-        if (whole) {
-          if (n_ok) {
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_x32(t_addr + c * 32, r);
+          tmem_ld_wait();
+          const int nc = n0 + c * 32;
+          if (vec_ok && nc + 32 <= p.N) {
+            const float4* swp = reinterpret_cast<const float4*>(p.sw + nc);
+            uint4 packed[4];
+            uint32_t* pk = reinterpret_cast<uint32_t*>(packed);
 #pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              const int m = m0 + c * CH + j;
-              if (m < p.M) {
-                float v = static_cast<float>(static_cast<int32_t>(r[j])) * swn * __ldg(p.sx + m);
+            for (int g = 0; g < 8; ++g) {
+              const float4 w4 = __ldg(swp + g);
+              const float f0 = static_cast<float>(static_cast<int32_t>(r[4 * g + 0])) * (w4.x * sxm);
+              const float f1 = static_cast<float>(static_cast<int32_t>(r[4 * g + 1])) * (w4.y * sxm);
+              const float f2 = static_cast<float>(static_cast<int32_t>(r[4 * g + 2])) * (w4.z * sxm);
+              const float f3 = static_cast<float>(static_cast<int32_t>(r[4 * g + 3])) * (w4.w * sxm);
+              __nv_bfloat162 lo = __floats2bfloat162_rn(f0, f1), hi = __floats2bfloat162_rn(f2, f3);
+              pk[2 * g] = *reinterpret_cast<uint32_t*>(&lo);
+              pk[2 * g + 1] = *reinterpret_cast<uint32_t*>(&hi);
+            }
+            if (m_ok) {
+              __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(p.y) + row_off + nc;
+              if (p.residual) {
+                const uint4* rp = reinterpret_cast<const uint4*>(p.residual + row_off + nc);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  const uint4 rv = rp[g];
+                  const __nv_bfloat162* rb = reinterpret_cast<const __nv_bfloat162*>(&rv);
+                  __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&packed[g]);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 x = __bfloat1622float2(ob[e]), y2 = __bfloat1622float2(rb[e]);
+                    ob[e] = __floats2bfloat162_rn(x.x + y2.x, x.y + y2.y);
+                  }
+                }
+              }
+#pragma unroll
+              for (int g = 0; g < 4; ++g) reinterpret_cast<uint4*>(yp)[g] = packed[g];
+            }
+          } else if (m_ok) {
+            for (int j = 0; j < 32; ++j) {
+              const int n = nc + j;
+              if (n >= p.N) break;
+              float v = static_cast<float>(static_cast<int32_t>(r[j])) * sxm * __ldg(p.sw + n);
+              const size_t o = row_off + n;
+              if (p.residual) v += __bfloat162float(p.residual[o]);
+              if (p.out_fp32) reinterpret_cast<float*>(p.y)[o] = v;
+              else reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16(v);
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(a));
+      } else {
+        // ---- swapped orientation: this thread owns output channel n and walks BN tokens ----
+        const int n = n_tile * TILE_N + q * 32 + lane;
+        const bool n_ok = n < p.N;
+        const int m0 = m_tile * BN;
+        const float swn = n_ok ? __ldg(p.sw + n) : 0.f;
+#pragma unroll 1
+        for (int c = 0; c < BN / CH; ++c) {
+          uint32_t r[CH];
+          if constexpr (CH == 32) tmem_ld_x32(t_addr + c * CH, r); else tmem_ld_x16(t_addr + c * CH, r);
+          tmem_ld_wait();
+          const int mc = m0 + c * CH;
+          const int jmax = min(CH, p.M - mc);
+          if (!n_ok || jmax <= 0) continue;
+          if (whole) {
+            const float* sxp = p.sx + mc;
+            const size_t o0 = static_cast<size_t>(mc) * p.ldy + n;
+            if (p.out_fp32) {
+              float* yp = reinterpret_cast<float*>(p.y) + o0;
+#pragma unroll
+              for (int j = 0; j < CH; ++j) {
+                if (j < jmax) {
+                  float v = static_cast<float>(static_cast<int32_t>(r[j])) * swn * __ldg(sxp + j);
+                  if (p.residual) v += __bfloat162float(p.residual[o0 + static_cast<size_t>(j) * p.ldy]);
+                  yp[static_cast<size_t>(j) * p.ldy] = v;
+                }
+              }
+            } else {
+              __nv_bfloat16* yp = reinterpret_cast<__nv_bfloat16*>(p.y) + o0;
+#pragma unroll
+              for (int j = 0; j < CH; ++j) {
+                if (j < jmax) {
+                  float v = static_cast<float>(static_cast<int32_t>(r[j])) * swn * __ldg(sxp + j);
+                  if (p.residual) v += __bfloat162float(p.residual[o0 + static_cast<size_t>(j) * p.ldy]);
+                  yp[static_cast<size_t>(j) * p.ldy] = __float2bfloat16(v);
+                }
+              }
+            }
+          } else {
+            int32_t* wp = p.ws + static_cast<size_t>(mc) * p.ldws + n;
+#pragma unroll
+            for (int j = 0; j < CH; ++j)
+              if (j < jmax) atomicAdd(wp + static_cast<size_t>(j) * p.ldws, static_cast<int32_t>(r[j]));
+          }
+        }
+        // accumulator drained: hand the TMEM buffer back to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(a));
+
+        if (!whole) {
+          __threadfence();
+          named_bar_sync(1, 128);
+          if (et == 0) {
+            const uint32_t add = static_cast<uint32_t>(sg.kb1 - sg.kb0);
+            const uint32_t old = atomicAdd(p.counters + sg.tile, add);
+            *fix_slot = (old + add == static_cast<uint32_t>(p.kblocks)) ? 1 : 0;
+          }
+          named_bar_sync(1, 128);
+          const int last = *fix_slot;
+          named_bar_sync(1, 128);     // everyone has read fix_slot before it can be rewritten
+          if (last) {
+            __threadfence();
+            if (n_ok) {
+              const int jmax = min(BN, p.M - m0);
+              for (int j = 0; j < jmax; ++j) {
+                const int m = m0 + j;
+                int32_t* wp = p.ws + static_cast<size_t>(m) * p.ldws + n;
+                const int32_t acc = __ldcg(wp);
+                *wp = 0;
+                float v = static_cast<float>(acc) * swn * __ldg(p.sx + m);
                 const size_t o = static_cast<size_t>(m) * p.ldy + n;
                 if (p.residual) v += __bfloat162float(p.residual[o]);
                 if (p.out_fp32) reinterpret_cast<float*>(p.y)[o] = v;
                 else reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16(v);
               }
             }
+            if (et == 0) p.counters[sg.tile] = 0;
           }
-        } else {
-          if (n_ok) {
-#pragma unroll
-            for (int j = 0; j < CH; ++j) {
-              const int m = m0 + c * CH + j;
-              if (m < p.M) atomicAdd(p.ws + static_cast<size_t>(m) * p.ldws + n, static_cast<int32_t>(r[j]));
-            }
-          }
-        }
-      }
-      // accumulator drained: hand the TMEM buffer back to the MMA warp
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(a));
-
-      if (!whole) {
-        __threadfence();
-        named_bar_sync(1, 128);
-        if (et == 0) {
-          const uint32_t add = static_cast<uint32_t>(sg.kb1 - sg.kb0);
-          const uint32_t old = atomicAdd(p.counters + sg.tile, add);
-          *fix_slot = (old + add == static_cast<uint32_t>(p.kblocks)) ? 1 : 0;
-        }
-        named_bar_sync(1, 128);
-        const int last = *fix_slot;
-        named_bar_sync(1, 128);     // everyone has read fix_slot before it can be rewritten
-        if (last) {
-          __threadfence();
-          if (n_ok) {
-            for (int j = 0; j < BN; ++j) {
-              const int m = m0 + j;
-              if (m >= p.M) break;
-              int32_t* wp = p.ws + static_cast<size_t>(m) * p.ldws + n;
-              const int32_t acc = __ldcg(wp);
-              *wp = 0;
-              float v = static_cast<float>(acc) * swn * __ldg(p.sx + m);
-              const size_t o = static_cast<size_t>(m) * p.ldy + n;
-              if (p.residual) v += __bfloat162float(p.residual[o]);
-              if (p.out_fp32) reinterpret_cast<float*>(p.y)[o] = v;
-              else reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16(v);
-            }
-          }
-          if (et == 0) p.counters[sg.tile] = 0;
         }
       }
       ++seg_idx;
@@ -330,26 +416,38 @@ int make_tmap_2d_u8(CUtensorMap* out, const void* base, uint64_t cols, uint64_t 
   return r == CUDA_SUCCESS ? 0 : -static_cast<int>(r);
 }
 
-template <int BN, int STAGES>
-static int launch_gemm(const CUtensorMap& tw, const CUtensorMap& tx, const GemmParams& p, int grid, cudaStream_t stream) {
+template <int BN, int STAGES, bool SWAP>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int grid, cudaStream_t stream) {
   constexpr int SMEM = STAGES * (TILE_N * BLOCK_K + BN * BLOCK_K) + 1024 + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(w8a8_gemm_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(w8a8_gemm_kernel<BN, STAGES, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }
-  w8a8_gemm_kernel<BN, STAGES><<<grid, GEMM_THREADS, SMEM, stream>>>(tw, tx, p);
+  w8a8_gemm_kernel<BN, STAGES, SWAP><<<grid, GEMM_THREADS, SMEM, stream>>>(ta, tb, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
 
-int gemm_pick_bn(int M) {
+constexpr int SWAP_MAX_M = 64;     // up to this many tokens the weights fill the MMA M dimension
+
+// token-tile width (swapped) or channel-tile width (normal)
+int gemm_pick_bn(int M, int N, int num_sms) {
   if (M <= 16) return 16;
   if (M <= 32) return 32;
-  if (M <= 64) return 64;
-  if (M <= 128) return 128;
-  return 256;
+  if (M <= SWAP_MAX_M) return 64;
+  const int m_tiles = (M + TILE_N - 1) / TILE_N;
+  // rounds of the persistent grid times the cost of one tile (main loop ~ bn, plus a fixed part)
+  int best = 256;
+  long long best_cost = -1;
+  for (int bn : {256, 128, 64}) {
+    const long long tiles = static_cast<long long>(m_tiles) * ((N + bn - 1) / bn);
+    const long long rounds = (tiles + num_sms - 1) / num_sms;
+    const long long cost = rounds * (bn + 64);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
 }
 
 }  // namespace b200
@@ -357,7 +455,8 @@ int gemm_pick_bn(int M) {
 using namespace b200;
 
 extern "C" size_t b200_w8a8_gemm_ws_bytes(int M, int N) {
-  const int bn = gemm_pick_bn(M);
+  if (M > SWAP_MAX_M) return 0;
+  const int bn = gemm_pick_bn(M, N, 148);
   const size_t m_pad = static_cast<size_t>((M + bn - 1) / bn) * bn;
   const size_t n_pad = static_cast<size_t>((N + TILE_N - 1) / TILE_N) * TILE_N;
   return m_pad * n_pad * sizeof(int32_t);
@@ -369,11 +468,12 @@ extern "C" int b200_w8a8_gemm(const void* xq, const float* sx, const void* wq, c
                               int num_sms, int force_mode, cudaStream_t stream) {
   if (M <= 0 || N <= 0 || K <= 0 || (K % 16) != 0) return -1;
   if ((reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15)) return -2;
-  const int bn = gemm_pick_bn(M);
+  const bool swap = M <= SWAP_MAX_M;
+  const int bn = gemm_pick_bn(M, N, num_sms);
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
-  p.m_tiles = (M + bn - 1) / bn;
-  p.n_tiles = (N + TILE_N - 1) / TILE_N;
+  p.m_tiles = swap ? (M + bn - 1) / bn : (M + TILE_N - 1) / TILE_N;
+  p.n_tiles = swap ? (N + TILE_N - 1) / TILE_N : (N + bn - 1) / bn;
   p.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
   p.num_tiles = p.m_tiles * p.n_tiles;
   p.total_units = static_cast<long long>(p.num_tiles) * p.kblocks;
@@ -385,12 +485,14 @@ extern "C" int b200_w8a8_gemm(const void* xq, const float* sx, const void* wq, c
   p.status = status;
   p.limit_ns = 2000000000ull;
 
-  const size_t need_ws = static_cast<size_t>(p.m_tiles) * bn * p.ldws * sizeof(int32_t);
-  const bool can_split = ws && counters && ws_bytes >= need_ws && counters_len >= p.num_tiles;
   int mode = 0;
-  if (force_mode == 0 || force_mode == 1) mode = force_mode;
-  else mode = (p.num_tiles < 2 * num_sms && p.m_tiles <= 2) ? 1 : 0;
-  if (mode == 1 && !can_split) mode = 0;
+  if (swap) {
+    const size_t need_ws = static_cast<size_t>(p.m_tiles) * bn * p.ldws * sizeof(int32_t);
+    const bool can_split = ws && counters && ws_bytes >= need_ws && counters_len >= p.num_tiles;
+    if (force_mode == 0 || force_mode == 1) mode = force_mode;
+    else mode = (p.num_tiles < 4 * num_sms) ? 1 : 0;
+    if (mode == 1 && !can_split) mode = 0;
+  }
   p.mode = mode;
   int grid;
   if (mode == 0) {
@@ -399,21 +501,23 @@ extern "C" int b200_w8a8_gemm(const void* xq, const float* sx, const void* wq, c
     long long g = p.total_units / 4;          // at least ~4 k-blocks per CTA
     if (g < 1) g = 1;
     if (g > num_sms) g = num_sms;
-    if (g < p.num_tiles && p.num_tiles <= num_sms) g = p.num_tiles;
     grid = static_cast<int>(g);
   }
 
   CUtensorMap tw, tx;
-  int r = make_tmap_2d_u8(&tw, wq, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(K), TILE_N);
-  if (r) return -11;
-  r = make_tmap_2d_u8(&tx, xq, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), bn);
-  if (r) return -12;
+  if (make_tmap_2d_u8(&tw, wq, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(K), swap ? TILE_N : bn)) return -11;
+  if (make_tmap_2d_u8(&tx, xq, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), swap ? bn : TILE_N)) return -12;
 
+  if (swap) {
+    switch (bn) {
+      case 16: return launch_gemm<16, 8, true>(tw, tx, p, grid, stream);
+      case 32: return launch_gemm<32, 8, true>(tw, tx, p, grid, stream);
+      default: return launch_gemm<64, 8, true>(tw, tx, p, grid, stream);
+    }
+  }
   switch (bn) {
-    case 16: return launch_gemm<16, 8>(tw, tx, p, grid, stream);
-    case 32: return launch_gemm<32, 8>(tw, tx, p, grid, stream);
-    case 64: return launch_gemm<64, 8>(tw, tx, p, grid, stream);
-    case 128: return launch_gemm<128, 6>(tw, tx, p, grid, stream);
-    default: return launch_gemm<256, 4>(tw, tx, p, grid, stream);
+    case 64: return launch_gemm<64, 8, false>(tx, tw, p, grid, stream);
+    case 128: return launch_gemm<128, 6, false>(tx, tw, p, grid, stream);
+    default: return launch_gemm<256, 4, false>(tx, tw, p, grid, stream);
   }
 }

@@ -1,0 +1,271 @@
+"""Host runtime (C++): the reference's behaviours (test_linux_threading.mojo) plus unit checks of each component."""
+import ctypes
+import os
+import re
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from mojo_linuxperiments_b200 import hostrt as H
+from mojo_linuxperiments_b200.oracle import philox as P
+
+S = 1_000_000_000
+
+
+def test_syscall_numbers_match_kernel_headers():
+    hdr = Path("/usr/include/x86_64-linux-gnu/asm/unistd_64.h")
+    if not hdr.exists():
+        pytest.skip("no kernel headers")
+    text = hdr.read_text()
+    for name in ["mmap", "mprotect", "munmap", "madvise", "exit", "gettid", "sched_setaffinity", "mbind", "move_pages",
+                 "rseq", "clone3", "futex_waitv", "futex_wake", "futex_wait", "getcpu"]:
+        m = re.search(rf"#define __NR_{name}\s+(\d+)", text)
+        assert m, name
+        assert H.lib().hostrt_syscall_nr(name.encode()) == int(m.group(1)), name
+
+
+def test_abi_struct_sizes_and_flags():
+    L = H.lib()
+    assert L.hostrt_struct_size(b"FutexNuma32") == 8
+    assert L.hostrt_struct_size(b"FutexWaitv") == 24
+    assert L.hostrt_struct_size(b"Clone3Args") == 88
+    assert L.hostrt_struct_size(b"Rseq") == 32
+    flags = L.hostrt_thread_clone_flags()
+    for bit in (0x100, 0x200, 0x400, 0x800, 0x10000, 0x40000, 0x80000, 0x100000):   # VM FS FILES SIGHAND THREAD SYSVSEM SETTLS PARENT_SETTID
+        assert flags & bit
+    assert L.hostrt_slot_total_size(64 * 1024) == 73728     # same slot footprint as the reference's default
+
+
+def test_cpumask_semantics():
+    m = H.CpuMask()
+    assert m.count() == 0 and m.byte_size() == 128
+    m.set(0); m.set(9); m.set(1023); m.set(1024); m.set(-1)          # out of range ignored
+    assert m.count() == 3 and m.test(9) and not m.test(8) and not m.test(1024)
+    raw = m.to_bytes()
+    assert raw[0] == 1 and raw[1] == 2 and raw[127] == 0x80        # cpu_set_t layout
+    m.clear(9)
+    assert not m.test(9) and m.count() == 2
+    m.set_all(); assert m.count() == 1024
+    m.clear_all(); assert m.count() == 0
+    assert H.CpuMask.from_cpu_list([3, 5]).cpus() == [3, 5]
+
+
+def test_cpulist_and_meminfo_parsers():
+    assert H.parse_cpulist("0-3,8,10-11\n") == [0, 1, 2, 3, 8, 10, 11]
+    assert H.parse_cpulist("5") == [5]
+    assert H.parse_cpulist("") == []
+    txt = "Node 0 MemTotal:       65842380 kB\nNode 0 MemFree:        1234 kB\n"
+    assert H.parse_meminfo(txt, "MemTotal") == 65842380
+    assert H.parse_meminfo(txt, "MemFree") == 1234
+    assert H.parse_meminfo(txt, "Nope") == -1
+
+
+def _fake_sysfs(tmp_path, nodes):
+    """nodes: {id: (cpulist, distances, total_kb, free_kb)}"""
+    root = tmp_path / "node"
+    root.mkdir()
+    ids = sorted(nodes)
+    (root / "online").write_text(",".join(str(i) for i in ids) + "\n")
+    for i, (cpus, dist, tot, free) in nodes.items():
+        d = root / f"node{i}"
+        d.mkdir()
+        (d / "cpulist").write_text(cpus + "\n")
+        (d / "distance").write_text(" ".join(map(str, dist)) + "\n")
+        (d / "meminfo").write_text(f"Node {i} MemTotal:  {tot} kB\nNode {i} MemFree:   {free} kB\n")
+    return str(root)
+
+
+def test_numa_info_on_fixture_trees(tmp_path):
+    two = _fake_sysfs(tmp_path, {0: ("0-3", [10, 21], 1000, 500), 1: ("4-7", [21, 10], 2000, 700)})
+    info = H.NumaInfo(two)
+    assert info.ok and info.num_nodes == 2 and info.node_ids == [0, 1]
+    assert info.get_node_cpus(1) == [4, 5, 6, 7]
+    assert info.distance(0, 1) == 21 and info.distance(1, 1) == 10 and info.distance(0, 7) == -1
+    assert info.cpus_per_node() == 4 and info.total_cpus() == 8 and info.cpus_on_node(1) == 4
+    assert info.mem_total_kb(1) == 2000 and info.mem_free_kb(0) == 500
+    assert info.get_node_mask(1).cpus() == [4, 5, 6, 7]
+    assert "node 1" in info.debug_string()
+
+
+def test_numa_info_sparse_ids_and_missing_tree(tmp_path):
+    (tmp_path / "a").mkdir()
+    sparse = _fake_sysfs(tmp_path / "a", {0: ("0-1", [10, 40], 10, 5), 2: ("8-9,12", [40, 10], 20, 6)})
+    info = H.NumaInfo(sparse)
+    assert info.node_ids == [0, 2]
+    assert info.get_node_cpus(2) == [8, 9, 12]          # looked up by id, not by position
+    assert info.distance(2, 0) == 40 and info.get_node_cpus(1) == []
+    bad = H.NumaInfo(str(tmp_path / "does-not-exist"))
+    assert not bad.ok and bad.num_nodes == 0
+
+
+def test_live_topology_and_where_am_i():
+    info = H.NumaInfo()
+    assert info.ok and info.num_nodes >= 1 and info.total_cpus() >= 1
+    cpu, node = H.get_current_cpu_and_node()
+    assert node in info.node_ids and cpu in info.get_node_cpus(node)
+    saved = H.get_thread_affinity()
+    try:
+        target = info.get_node_cpus(info.node_ids[0])[0]
+        assert H.set_thread_affinity(H.CpuMask([target])) == 0
+        assert H.get_current_cpu_and_node()[0] == target
+        rc, rn = H.get_cpu_and_node_rseq()
+        if rc >= 0:      # libc registered an rseq area for this thread
+            assert (rc, rn) == H.get_current_cpu_and_node()
+    finally:
+        H.set_thread_affinity(saved)
+
+
+def test_arena_bump_mark_reset_exhaustion():
+    info = H.NumaInfo()
+    a = H.NumaArena(info.node_ids[0], 4096, alignment=64, page_size=H.PAGE_STANDARD)
+    assert a and a.used() == 0 and a.remaining() == 4096 and a.verify_placement()
+    p1 = a.alloc(10)
+    p2 = a.alloc(10)
+    assert p1 == a.base() and p2 == a.base() + 64            # aligned bump
+    m = a.mark()
+    assert a.alloc(1000) is not None
+    assert a.alloc(4096) is None                              # would overflow: refused, state unchanged
+    used = a.used()
+    a.reset_to(used + 100)                                    # forward resets are ignored
+    assert a.used() == used
+    a.reset_to(m)
+    assert a.used() == m
+    H.lib().hostrt_poke(p1, 42)                               # first touch
+    assert H.lib().hostrt_peek(p1) == 42
+    assert a.verify_placement()
+    assert H.lib().hostrt_move_pages_query(p1) == info.node_ids[0]
+    a.reset()
+    assert a.used() == 0 and a.remaining() == 4096
+
+
+def test_arena_failure_is_a_null_arena():
+    a = H.NumaArena(1000, 4096, page_size=H.PAGE_STANDARD)     # node 1000 cannot be bound
+    assert not a and a.alloc(8) is None and not a.verify_placement()
+
+
+def test_pool_launch_join_and_refusal_when_full():
+    pool = H.ThreadPool(2, stack_size=8192)
+    assert pool and len(pool) == 2
+    buf = (ctypes.c_ulonglong * 4)()
+    base = ctypes.addressof(buf)
+    slow = H.worker_address("hostrt_worker_sleep_store")
+    assert pool.launch(slow, 100, base, 11)
+    assert pool.launch(slow, 100, base + 8, 22)
+    assert not pool.launch(slow, 1, base + 16, 33)             # both slots busy
+    assert pool.wait_all(10 * S) == 0
+    assert list(buf)[:3] == [11, 22, 0]
+    assert pool.launch(H.worker_address("hostrt_worker_store"), base + 16, 33) and pool.wait_all(10 * S) == 0
+    assert buf[2] == 33
+    pool.close()
+
+
+def test_pool_wait_any_order_and_timeouts():
+    pool = H.ThreadPool(3)
+    slow = H.worker_address("hostrt_worker_sleep_store")
+    assert pool.wait_any(S) == H.WAIT_NOTHING_RUNNING
+    for ms in (300, 200, 100):
+        assert pool.launch(slow, ms, 0, 0)
+    assert pool.wait_any(1_000_000) == H.WAIT_TIMED_OUT        # 1 ms: nothing has finished yet
+    assert pool.wait_all(1_000_000) == -H.ETIMEDOUT
+    assert [pool.wait_any(10 * S) for _ in range(3)] == [2, 1, 0]
+    assert pool.wait_all(10 * S) == 0
+    pool.close()
+
+
+def test_pinned_pool_runs_where_asked_and_rseq_agrees():
+    info = H.NumaInfo()
+    node = info.node_ids[0]
+    cpu = info.get_node_cpus(node)[-1]
+    pool = H.ThreadPool(1, H.CpuMask([cpu]), node)
+    out = (ctypes.c_int * 4)()
+    assert pool.launch(H.worker_address("hostrt_worker_where"), ctypes.addressof(out))
+    assert pool.wait_all(10 * S) == 0
+    assert out[0] == cpu and out[1] == node and out[2] == cpu and out[3] == node
+    pool.close()
+
+
+def test_gate_release_wakes_worker_and_timeout_is_reported():
+    info = H.NumaInfo()
+    arena = H.NumaArena(info.node_ids[0], 4096, page_size=H.PAGE_STANDARD)
+    gate_addr = arena.alloc(4)
+    res = (ctypes.c_longlong * 2)()
+    pool = H.ThreadPool(2)
+    waiter = H.worker_address("hostrt_worker_gate_wait_store")
+    assert pool.launch(waiter, gate_addr, 5 * S, ctypes.addressof(res))
+    gate = H.MutexGate.from_addr(gate_addr)
+    assert gate.wait(2_000_000) == -H.ETIMEDOUT                 # nobody released it yet
+    gate.release()
+    assert pool.wait_all(10 * S) == 0 and res[0] == 1
+    assert gate.wait(S) == 0                                     # stays open
+    gate.reset()
+    assert pool.launch(waiter, gate_addr, 20_000_000, ctypes.addressof(res) + 8)   # 20 ms bound, never released
+    assert pool.wait_all(10 * S) == 0 and res[1] == -H.ETIMEDOUT
+    pool.close()
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+def test_chain_reduce(world):
+    st, v = H.chain_reduce(H.NumaInfo(), world)
+    assert st == 0 and v == world * (world + 1) // 2
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_butterfly_allreduce(world):
+    st, out = H.butterfly_allreduce(H.NumaInfo(), world)
+    assert st == 0 and out == [world * (world + 1) // 2] * world
+
+
+def test_butterfly_rejects_non_power_of_two():
+    st, _ = H.butterfly_allreduce(H.NumaInfo(), 3)
+    assert st == -22
+
+
+@pytest.mark.parametrize("world,rounds", [(2, 1), (4, 3), (8, 2)])
+def test_fabric_allreduce_epochs(world, rounds):
+    vals = [float(i) + 0.25 for i in range(world)]
+    st, out = H.fabric_allreduce(H.NumaInfo(), vals, rounds=rounds)
+    want = sum(vals) * (world ** (rounds - 1))
+    assert st == 0 and all(abs(o - want) < 1e-9 * abs(want) for o in out)
+    assert len(set(out)) == 1                                    # bitwise identical on every rank
+
+
+def test_fabric_allreduce_silent_rank_times_out_cleanly():
+    st, _ = H.fabric_allreduce(H.NumaInfo(), [1.0, 2.0, 3.0, 4.0], timeout_ns=50_000_000, drop_rank=2)
+    assert st == -H.ETIMEDOUT
+
+
+def test_philox_matches_numpy_oracle():
+    ref = P.uniform_pm1(64, seed=0)
+    got = np.array([H.philox_uniform(i, 0) for i in range(64)], dtype=np.float32)
+    assert np.array_equal(ref, got)
+    assert ref.min() >= -1.0 and ref.max() < 1.0
+    blk = (ctypes.c_uint * 4)()
+    H.lib().hostrt_philox_block(7, 123456789123, blk)
+    assert list(blk) == P.philox4x32_10(np.array([7], dtype=np.uint64), 123456789123)[0].tolist()
+
+
+def test_fill_reduce_matches_oracle_and_is_split_invariant():
+    info = H.NumaInfo()
+    n = 1 << 20
+    want = float(P.uniform_pm1(n, 0).astype(np.float64).sum())
+    r_all = H.fill_reduce(info, n, 0)
+    r_two = H.fill_reduce(info, n, 0, max_workers_per_node=2)
+    for r in (r_all, r_two):
+        assert r["status"] == 0 and r["misplaced"] == 0
+        assert abs(r["sum"] - want) < 1e-6 * n ** 0.5 + 1e-6
+    assert r_two["workers"] == 2 * info.num_nodes
+
+
+def test_reference_scenarios_all_pass():
+    for name, result, detail in H.run_scenarios():
+        assert result in (H.SC_PASS, H.SC_SKIP), f"{name}: {detail}"
+
+
+def test_selftest_executable_exit_code():
+    from mojo_linuxperiments_b200 import _build
+    exe = _build.build_hostrt_selftest()
+    p = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
+    assert p.returncode == 0, p.stdout
+    assert p.stdout.count("[PASS]") + p.stdout.count("[SKIP]") == 12 and "[FAIL]" not in p.stdout
