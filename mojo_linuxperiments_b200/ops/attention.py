@@ -1,0 +1,134 @@
+"""RoPE + paged-KV write, prefill (tcgen05) and decode (split-KV) attention, embedding gather, greedy argmax."""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from . import _lib
+from .workspace import default_workspace
+
+HEAD_DIM = 128
+
+
+def rope_tables(max_pos: int, theta: float, device, head_dim: int = HEAD_DIM):
+    """cos/sin tables [max_pos, head_dim/2] fp32 for the rotate-half convention (pairs i, i + head_dim/2)."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float64) / head_dim))
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
+    return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
+
+
+class PagedKVCache:
+    """One layer's paged KV storage: [num_pages][2][kv_heads][page_size][128] bf16."""
+
+    def __init__(self, num_pages: int, kv_heads: int, page_size: int, device, storage: torch.Tensor | None = None):
+        shape = (num_pages, 2, kv_heads, page_size, HEAD_DIM)
+        self.data = storage if storage is not None else torch.zeros(shape, dtype=torch.bfloat16, device=device)
+        assert tuple(self.data.shape) == shape
+        self.num_pages, self.kv_heads, self.page_size = num_pages, kv_heads, page_size
+
+
+def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, hq: int, hkv: int, *,
+                  q_out: torch.Tensor | None = None, k_out: torch.Tensor | None = None, v_out: torch.Tensor | None = None,
+                  cache: PagedKVCache | None = None, page_table: torch.Tensor | None = None,
+                  seq_ids: torch.Tensor | None = None, q_norm_w=None, k_norm_w=None, eps: float = 1e-6):
+    """qkv bf16 [M, (hq + 2 hkv) * 128] -> rotated q [M, hq, 128]; k, v appended to ``cache`` at (sequence, position)."""
+    M = qkv.shape[0]
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape[1] == (hq + 2 * hkv) * HEAD_DIM
+    assert positions.dtype == torch.int32
+    if q_out is None:
+        q_out = torch.empty((M, hq, HEAD_DIM), dtype=torch.bfloat16, device=qkv.device)
+    rc = _lib.lib().b200_rope_kv_write(
+        qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), _lib.ptr(seq_ids), cos.data_ptr(), sin.data_ptr(),
+        _lib.ptr(q_norm_w), _lib.ptr(k_norm_w), float(eps), q_out.data_ptr(), _lib.ptr(k_out), _lib.ptr(v_out),
+        cache.data.data_ptr() if cache is not None else None, _lib.ptr(page_table),
+        page_table.shape[1] if page_table is not None else 0, cache.page_size if cache is not None else 0,
+        hq, hkv, M, _lib.stream())
+    _lib.check(rc, "rope_kv_write")
+    return q_out
+
+
+def attn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, max_len: int,
+                 scale: float | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Causal GQA attention over concatenated sequences. q [T, hq, 128], k/v [T, hkv, 128] (token stride free)."""
+    T, hq, d = q.shape
+    hkv = k.shape[1]
+    assert d == HEAD_DIM and q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == d
+    assert k.stride(2) == 1 and k.stride(1) == d and v.stride(2) == 1 and v.stride(1) == d
+    assert cu_seqlens.dtype == torch.int32
+    if out is None:
+        out = torch.empty((T, hq, d), dtype=torch.bfloat16, device=q.device)
+    ws = default_workspace(q.device)
+    rc = _lib.lib().b200_attn_prefill(
+        q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(),
+        cu_seqlens.data_ptr(), cu_seqlens.numel() - 1, T, int(max_len), hq, hkv,
+        float(scale if scale is not None else 1.0 / math.sqrt(d)), ws.status.data_ptr(), _lib.stream())
+    _lib.check(rc, "attn_prefill")
+    return out
+
+
+class DecodeAttnScratch:
+    def __init__(self, B: int, hq: int, hkv: int, splits: int, device):
+        n = _lib.lib().b200_attn_decode_scratch_floats(B, hq, splits)
+        self.buf = torch.empty(max(n, 1), dtype=torch.float32, device=device)
+        self.counters = torch.zeros(B * hkv, dtype=torch.int32, device=device)
+        self.splits = splits
+
+
+def pick_decode_splits(B: int, hkv: int, max_len: int, num_sms: int = 148) -> int:
+    """Enough CTAs to fill the GPU about twice, but at least 128 tokens per split."""
+    want = max(1, (2 * num_sms + B * hkv - 1) // (B * hkv))
+    return max(1, min(want, (max_len + 127) // 128, 32))
+
+
+def attn_decode(q: torch.Tensor, cache: PagedKVCache, page_table: torch.Tensor, seq_lens: torch.Tensor, *,
+                scratch: DecodeAttnScratch | None = None, splits: int = 1, scale: float | None = None,
+                out: torch.Tensor | None = None) -> torch.Tensor:
+    """q [B, hq, 128] against the first seq_lens[b] cached tokens of sequence b."""
+    B, hq, d = q.shape
+    assert d == HEAD_DIM and q.is_contiguous() and page_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
+    if out is None:
+        out = torch.empty_like(q)
+    if splits > 1 and scratch is None:
+        scratch = DecodeAttnScratch(B, hq, cache.kv_heads, splits, q.device)
+    rc = _lib.lib().b200_attn_decode(
+        q.data_ptr(), cache.data.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),
+        scratch.buf.data_ptr() if scratch is not None else None,
+        scratch.counters.data_ptr() if scratch is not None else None,
+        B, hq, cache.kv_heads, cache.page_size, page_table.shape[1], splits,
+        float(scale if scale is not None else 1.0 / math.sqrt(d)), _lib.stream())
+    _lib.check(rc, "attn_decode")
+    return out
+
+
+def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    assert ids.dtype == torch.int64 and table.dtype == torch.bfloat16 and table.is_contiguous()
+    M, d = ids.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty((M, d), dtype=torch.bfloat16, device=table.device)
+    _lib.check(_lib.lib().b200_embed_gather(ids.data_ptr(), table.data_ptr(), out.data_ptr(), M, d, table.shape[0],
+                                            _lib.stream()), "embed_gather")
+    return out
+
+
+def argmax_rows(logits: torch.Tensor, index_offset: int = 0, out_val=None, out_idx=None):
+    """(max value fp32, index int64 + offset) per row of bf16 logits [rows, n]; lowest index wins ties."""
+    rows, n = logits.shape
+    assert logits.dtype == torch.bfloat16 and logits.stride(1) == 1
+    if out_val is None:
+        out_val = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    if out_idx is None:
+        out_idx = torch.empty(rows, dtype=torch.int64, device=logits.device)
+    _lib.check(_lib.lib().b200_argmax_rows(logits.data_ptr(), logits.stride(0), rows, n, index_offset,
+                                           out_val.data_ptr(), out_idx.data_ptr(), _lib.stream()), "argmax_rows")
+    return out_val, out_idx
+
+
+def argmax_merge(cand_val: torch.Tensor, cand_idx: torch.Tensor, out_idx: torch.Tensor | None = None) -> torch.Tensor:
+    """cand_* [world, rows] -> global argmax index per row."""
+    world, rows = cand_val.shape
+    if out_idx is None:
+        out_idx = torch.empty(rows, dtype=torch.int64, device=cand_val.device)
+    _lib.check(_lib.lib().b200_argmax_merge(cand_val.data_ptr(), cand_idx.data_ptr(), world, rows, out_idx.data_ptr(),
+                                            _lib.stream()), "argmax_merge")
+    return out_idx

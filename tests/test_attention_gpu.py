@@ -1,0 +1,127 @@
+"""Attention-side kernels on the GPU against plain PyTorch fp32 references."""
+import math
+
+import pytest
+import torch
+
+from mojo_linuxperiments_b200.oracle import attention as OA
+
+pytestmark = pytest.mark.gpu
+D = 128
+
+
+def _rand(shape, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(torch.bfloat16).cuda()
+
+
+@pytest.mark.parametrize("hq,hkv,qk_norm", [(32, 8, False), (4, 1, False), (8, 1, True)])
+def test_rope_kv_write_and_cache_layout(hq, hkv, qk_norm):
+    from mojo_linuxperiments_b200.ops import attention as A
+    B, S, ps = 3, 37, 16
+    theta = 500000.0
+    M = B * S
+    qkv = _rand((M, (hq + 2 * hkv) * D), 1)
+    pos = torch.arange(S, dtype=torch.int32).repeat(B).cuda()
+    seq = torch.arange(B, dtype=torch.int32).repeat_interleave(S).cuda()
+    max_pages = (S + ps - 1) // ps
+    perm = torch.randperm(B * max_pages, generator=torch.Generator().manual_seed(0)).to(torch.int32)
+    page_table = perm.view(B, max_pages).cuda()
+    cache = A.PagedKVCache(B * max_pages, hkv, ps, qkv.device)
+    cos, sin = A.rope_tables(64, theta, qkv.device)
+    qw = (torch.rand(D) + 0.5).to(torch.bfloat16).cuda() if qk_norm else None
+    kw = (torch.rand(D) + 0.5).to(torch.bfloat16).cuda() if qk_norm else None
+    k_out = torch.empty((M, hkv, D), dtype=torch.bfloat16, device=qkv.device)
+    q = A.rope_kv_write(qkv, pos, cos, sin, hq, hkv, k_out=k_out, cache=cache, page_table=page_table, seq_ids=seq,
+                        q_norm_w=qw, k_norm_w=kw, eps=1e-6)
+    torch.cuda.synchronize()
+    x = qkv.view(M, hq + 2 * hkv, D)
+    q_in, k_in, v_in = x[:, :hq], x[:, hq:hq + hkv], x[:, hq + hkv:]
+    if qk_norm:
+        q_in, k_in = OA.head_rmsnorm(q_in, qw, 1e-6), OA.head_rmsnorm(k_in, kw, 1e-6)
+    q_ref, k_ref = OA.rope(q_in, pos, theta), OA.rope(k_in, pos, theta)
+    assert torch.allclose(q.float(), q_ref, rtol=2e-2, atol=2e-2)
+    assert torch.allclose(k_out.float(), k_ref, rtol=2e-2, atol=2e-2)
+    for b in range(B):
+        for t in (0, 15, 16, S - 1):
+            page = int(page_table[b, t // ps])
+            kc = cache.data[page, 0, :, t % ps]
+            vc = cache.data[page, 1, :, t % ps]
+            assert torch.equal(kc, k_out[b * S + t])
+            assert torch.equal(vc, v_in[b * S + t])
+
+
+@pytest.mark.parametrize("lens,hq,hkv", [([128], 4, 1), ([256], 8, 2), ([1024], 4, 1), ([100, 333, 128], 4, 1), ([1, 129], 8, 1)])
+def test_attn_prefill_matches_reference(lens, hq, hkv):
+    from mojo_linuxperiments_b200.ops import attention as A
+    from mojo_linuxperiments_b200.ops.workspace import default_workspace
+    T = sum(lens)
+    q, k, v = _rand((T, hq, D), 1), _rand((T, hkv, D), 2), _rand((T, hkv, D), 3)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32).cuda()
+    out = A.attn_prefill(q, k, v, cu, max(lens))
+    torch.cuda.synchronize()
+    default_workspace(q.device).check_status()
+    o = 0
+    for L in lens:
+        ref = OA.causal_gqa(q[o:o + L], k[o:o + L], v[o:o + L])
+        got = out[o:o + L].float()
+        assert torch.allclose(got, ref, rtol=3e-2, atol=3e-2), (got - ref).abs().max().item()
+        o += L
+
+
+def test_attn_prefill_reads_strided_qkv():
+    """K and V can be consumed in place from the fused qkv buffer."""
+    from mojo_linuxperiments_b200.ops import attention as A
+    T, hq, hkv = 256, 4, 1
+    qkv = _rand((T, (hq + 2 * hkv) * D), 7)
+    x = qkv.view(T, hq + 2 * hkv, D)
+    q, k, v = x[:, :hq], x[:, hq:hq + hkv], x[:, hq + hkv:]
+    cu = torch.tensor([0, T], dtype=torch.int32).cuda()
+    out = A.attn_prefill(q, k, v, cu, T)
+    torch.cuda.synchronize()
+    ref = OA.causal_gqa(q, k, v)
+    assert torch.allclose(out.float(), ref, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("hq,hkv", [(32, 8), (4, 1), (8, 1), (16, 1), (2, 2)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_attn_decode_paged(hq, hkv, splits):
+    from mojo_linuxperiments_b200.ops import attention as A
+    ps = 16
+    lens = [1, 17, 300, 1280, 64]
+    B = len(lens)
+    max_pages = (max(lens) + ps - 1) // ps
+    n_pages = B * max_pages
+    g = torch.Generator().manual_seed(3)
+    page_table = torch.randperm(n_pages, generator=g).to(torch.int32).view(B, max_pages).cuda()
+    cache = A.PagedKVCache(n_pages, hkv, ps, "cuda")
+    cache.data.copy_(_rand(tuple(cache.data.shape), 5))
+    q = _rand((B, hq, D), 6)
+    seq_lens = torch.tensor(lens, dtype=torch.int32).cuda()
+    out = A.attn_decode(q, cache, page_table, seq_lens, splits=splits)
+    out2 = A.attn_decode(q, cache, page_table, seq_lens, splits=splits)     # scratch counters must self-reset
+    torch.cuda.synchronize()
+    for b, L in enumerate(lens):
+        pages = page_table[b, : (L + ps - 1) // ps].long()
+        kk = cache.data[pages, 0].permute(0, 2, 1, 3).reshape(-1, hkv, D)[:L]
+        vv = cache.data[pages, 1].permute(0, 2, 1, 3).reshape(-1, hkv, D)[:L]
+        ref = OA.decode_gqa(q[b], kk, vv)
+        assert torch.allclose(out[b].float(), ref, rtol=2e-2, atol=2e-2), (out[b].float() - ref).abs().max().item()
+    assert torch.equal(out, out2)
+
+
+def test_embed_and_argmax():
+    from mojo_linuxperiments_b200.ops import attention as A
+    table = _rand((1000, 256), 1)
+    ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int64).cuda()
+    assert torch.equal(A.embed_gather(ids, table), table[ids])
+    logits = _rand((7, 16032), 2)
+    logits[3, 77] = 100.0
+    logits[3, 9000] = 100.0       # tie: lowest index wins
+    val, idx = A.argmax_rows(logits, index_offset=1000)
+    torch.cuda.synchronize()
+    assert torch.equal(idx - 1000, logits.float().argmax(dim=1))
+    assert idx[3].item() == 1077
+    cv = torch.stack([val, val + 1.0, val - 1.0])
+    ci = torch.stack([idx, idx + 5, idx + 9])
+    assert torch.equal(A.argmax_merge(cv, ci), idx + 5)
