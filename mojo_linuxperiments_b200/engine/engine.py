@@ -1,0 +1,107 @@
+"""Per-rank inference engine: admission into the paged KV cache, prefill, CUDA-graph decode steps, greedy sampling.
+
+The decode step of a batch is captured once per batch size as one CUDA graph; replaying it is the analogue of the
+reference's ``ThreadPool.launch`` on every rank and ``wait_all`` is the event the caller synchronises on
+(threading/linux_threading.mojo:103-129).  The host only reads the sampled ids.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..models.config import ModelConfig, RuntimeConfig
+from ..models.decoder import Decoder, KVState
+from ..models import weights as Wt
+from ..ops.workspace import default_workspace
+from ..parallel.comm import Comm
+
+
+class Engine:
+    def __init__(self, cfg: ModelConfig, rt: RuntimeConfig | None = None, weights: dict | None = None, seed: int = 0,
+                 device=None, comm: Comm | None = None):
+        self.cfg = cfg
+        self.rt = rt or RuntimeConfig()
+        self.comm = comm or Comm.single()
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if weights is None:
+            weights = Wt.random_shard(cfg, self.rt.tp, self.comm.rank, self.device, seed)
+        self.model = Decoder(cfg, self.rt, weights, self.comm, self.device)
+        self.kv: KVState | None = None
+        self.batch = 0
+        self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self._stream = torch.cuda.Stream(device=self.device)
+
+    # ------------------------------------------------------------------------------------------------------
+    def start_batch(self, batch: int, max_total_len: int) -> None:
+        if max_total_len > self.rt.max_seq_len:
+            raise ValueError(f"{max_total_len} tokens exceed max_seq_len {self.rt.max_seq_len}")
+        if self.kv is None or self.kv.seq_lens.numel() != batch or self.kv.max_pages * self.rt.page_size < max_total_len:
+            self.kv = KVState(self.cfg, self.rt, self.device, batch, self.rt.max_seq_len)
+            self._graphs.clear()
+        else:
+            for s in list(self.kv.owned):
+                self.kv.release(s)
+        for s in range(batch):
+            self.kv.admit(s, max_total_len)
+        self.batch = batch
+        self.tokens = torch.zeros(batch, dtype=torch.int64, device=self.device)
+        self.positions = torch.zeros(batch, dtype=torch.int32, device=self.device)
+        self._graphs.clear()
+
+    def prefill(self, prompts: torch.Tensor) -> torch.Tensor:
+        """prompts int64 [B, S] (host or device; equal lengths).  Returns the first generated token per sequence
+        (device tensor) and leaves the engine ready for ``decode_step``."""
+        B, S = prompts.shape
+        ids = prompts.to(self.device, non_blocking=True).reshape(-1)
+        positions = torch.arange(S, dtype=torch.int32, device=self.device).repeat(B)
+        seq_ids = torch.arange(B, dtype=torch.int32, device=self.device).repeat_interleave(S)
+        cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=self.device)
+        last = torch.arange(S - 1, B * S, S, dtype=torch.int64, device=self.device)
+        nxt = self.model.forward(ids, positions, self.kv, mode="prefill", cu_seqlens=cu, max_len=S, seq_ids=seq_ids,
+                                 last_idx=last)
+        self.tokens.copy_(nxt)
+        self.positions.fill_(S)
+        self.kv.seq_lens.fill_(S + 1)      # the next decode step attends to the prompt plus its own token
+        return nxt
+
+    def _decode_body(self) -> None:
+        nxt = self.model.forward(self.tokens, self.positions, self.kv, mode="decode", max_len=self.rt.max_seq_len)
+        self.tokens.copy_(nxt)
+        self.positions.add_(1)
+        self.kv.seq_lens.add_(1)
+
+    def decode_step(self, use_graph: bool = True) -> torch.Tensor:
+        """One greedy token for every sequence of the batch; returns the device tensor of new ids [B]."""
+        if not use_graph:
+            self._decode_body()
+            return self.tokens
+        g = self._graphs.get(self.batch)
+        if g is None:
+            # warm up outside capture (lazy kernel attribute set-up, allocator), restoring the state afterwards
+            saved = (self.tokens.clone(), self.positions.clone(), self.kv.seq_lens.clone())
+            self._stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._stream):
+                self._decode_body()
+            torch.cuda.current_stream().wait_stream(self._stream)
+            torch.cuda.synchronize()
+            self.tokens.copy_(saved[0]); self.positions.copy_(saved[1]); self.kv.seq_lens.copy_(saved[2])
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=self._stream):
+                self._decode_body()
+            self.tokens.copy_(saved[0]); self.positions.copy_(saved[1]); self.kv.seq_lens.copy_(saved[2])
+            self._graphs[self.batch] = g
+        g.replay()
+        return self.tokens
+
+    def generate(self, prompts: torch.Tensor, max_new_tokens: int, use_graph: bool = True) -> torch.Tensor:
+        """Greedy generation. prompts int64 [B, S] -> int64 [B, max_new_tokens] on the host."""
+        B, S = prompts.shape
+        self.start_batch(B, S + max_new_tokens)
+        out = torch.empty((max_new_tokens, B), dtype=torch.int64, pin_memory=torch.cuda.is_available())
+        first = self.prefill(prompts)
+        out[0].copy_(first, non_blocking=True)
+        for t in range(1, max_new_tokens):
+            nxt = self.decode_step(use_graph)
+            out[t].copy_(nxt, non_blocking=True)
+        torch.cuda.synchronize()
+        default_workspace(self.device).check_status()
+        return out.t().contiguous()

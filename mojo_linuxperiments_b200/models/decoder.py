@@ -1,0 +1,144 @@
+"""Decoder forward pass (Llama-shaped dense and Qwen3-shaped MoE) as a sequence of sm_100a kernels.
+
+Residual stream convention: ``h`` is the bf16 residual; every block produces a ``delta`` that is folded into ``h``
+by the *next* norm kernel (residual add + RMSNorm + Hadamard rotation + int8 quantisation are one launch).
+With tensor parallelism the delta of a row-parallel linear is a partial sum that is all-reduced first, either
+inside the GEMM kernel over peer memory (fused) or by NCCL between kernels (baseline wiring).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from ..ops import attention as A
+from ..ops import linear as L
+from ..parallel.comm import Comm
+from .config import ModelConfig, RuntimeConfig, kv_heads_per_rank
+
+
+class KVState:
+    """Paged KV cache of all layers of one rank plus the page table / lengths of the running batch."""
+
+    def __init__(self, cfg: ModelConfig, rt: RuntimeConfig, device, num_seqs: int, max_seq_len: int):
+        self.page_size = rt.page_size
+        self.max_pages = (max_seq_len + rt.page_size - 1) // rt.page_size
+        self.num_pages = num_seqs * self.max_pages
+        hkv = kv_heads_per_rank(cfg, rt.tp)
+        self.storage = torch.zeros((cfg.n_layers, self.num_pages, 2, hkv, rt.page_size, cfg.head_dim),
+                                   dtype=torch.bfloat16, device=device)
+        self.layers = [A.PagedKVCache(self.num_pages, hkv, rt.page_size, device, storage=self.storage[l])
+                       for l in range(cfg.n_layers)]
+        self.page_table = torch.zeros((num_seqs, self.max_pages), dtype=torch.int32, device=device)
+        self.seq_lens = torch.zeros((num_seqs,), dtype=torch.int32, device=device)
+        self.free_pages = list(range(self.num_pages - 1, -1, -1))
+        self.owned: dict[int, list[int]] = {}
+
+    def admit(self, seq: int, n_tokens: int) -> None:
+        """Reserve pages for ``n_tokens`` tokens of sequence slot ``seq`` (host-side free list)."""
+        need = (n_tokens + self.page_size - 1) // self.page_size
+        have = self.owned.setdefault(seq, [])
+        if need - len(have) > len(self.free_pages):
+            raise RuntimeError("KV cache exhausted")
+        while len(have) < need:
+            have.append(self.free_pages.pop())
+        row = torch.zeros(self.max_pages, dtype=torch.int32)
+        row[: len(have)] = torch.tensor(have, dtype=torch.int32)
+        self.page_table[seq].copy_(row, non_blocking=True)
+
+    def release(self, seq: int) -> None:
+        self.free_pages.extend(reversed(self.owned.pop(seq, [])))
+
+
+class Decoder:
+    def __init__(self, cfg: ModelConfig, rt: RuntimeConfig, weights: dict, comm: Comm | None = None, device=None):
+        self.cfg, self.rt, self.w = cfg, rt, weights
+        self.comm = comm or Comm.single()
+        self.device = device or weights["embed"].device
+        self.hq = cfg.n_heads // rt.tp
+        self.hkv = kv_heads_per_rank(cfg, rt.tp)
+        self.cos, self.sin = A.rope_tables(rt.max_seq_len, cfg.rope_theta, self.device, cfg.head_dim)
+        self.scale = 1.0 / math.sqrt(cfg.head_dim)
+        self.moe = None
+        if cfg.is_moe:
+            from .moe import MoEBlock
+            self.moe = MoEBlock(cfg, rt, self.comm, self.device)
+        self._decode_scratch: dict[int, A.DecodeAttnScratch] = {}
+
+    # -- building blocks ------------------------------------------------------------------------------------
+    def _norm_quant(self, h, delta, gamma, want_normed=False):
+        if delta is None:
+            return L.act_quant(h, mode=L.AQ_NORM, gamma=gamma, eps=self.cfg.eps, want_normed=want_normed)
+        return L.act_quant(delta, mode=L.AQ_ADD_NORM, gamma=gamma, eps=self.cfg.eps, residual=h, want_normed=want_normed)
+
+    def _row_parallel(self, xq, sx, lw):
+        """Row-parallel linear: local partial product, then the cross-rank sum."""
+        y = L.w8a8_gemm(xq, sx, lw.qweight, lw.scale)
+        return self.comm.all_reduce(y)
+
+    def _attention(self, l, qkv, positions, kv: KVState, mode, cu_seqlens, max_len, seq_ids):
+        W = self.w["layers"][l]
+        M = qkv.shape[0]
+        cache = kv.layers[l]
+        if mode == "prefill":
+            k_rot = torch.empty((M, self.hkv, self.cfg.head_dim), dtype=torch.bfloat16, device=qkv.device)
+            q = A.rope_kv_write(qkv, positions, self.cos, self.sin, self.hq, self.hkv, k_out=k_rot, cache=cache,
+                                page_table=kv.page_table, seq_ids=seq_ids, q_norm_w=W.get("q_norm"),
+                                k_norm_w=W.get("k_norm"), eps=self.cfg.eps)
+            v = qkv.view(M, self.hq + 2 * self.hkv, self.cfg.head_dim)[:, self.hq + self.hkv:]
+            return A.attn_prefill(q, k_rot, v, cu_seqlens, max_len, scale=self.scale)
+        q = A.rope_kv_write(qkv, positions, self.cos, self.sin, self.hq, self.hkv, cache=cache,
+                            page_table=kv.page_table, seq_ids=None, q_norm_w=W.get("q_norm"),
+                            k_norm_w=W.get("k_norm"), eps=self.cfg.eps)
+        splits = A.pick_decode_splits(M, self.hkv, max_len)
+        sc = None
+        if splits > 1:
+            sc = self._decode_scratch.get((M, splits))
+            if sc is None:
+                sc = A.DecodeAttnScratch(M, self.hq, self.hkv, splits, qkv.device)
+                self._decode_scratch[(M, splits)] = sc
+        return A.attn_decode(q, cache, kv.page_table, kv.seq_lens, scratch=sc, splits=splits, scale=self.scale)
+
+    def _mlp(self, l, xq, sx, xn):
+        W = self.w["layers"][l]
+        if self.moe is not None:
+            return self.moe.forward(W, xq, sx, xn)
+        gu = L.w8a8_gemm(xq, sx, W["gate_up"].qweight, W["gate_up"].scale)
+        hq, sh = L.act_quant(gu, mode=L.AQ_SWIGLU)
+        return self._row_parallel(hq, sh, W["down"])
+
+    # -- full forward ------------------------------------------------------------------------------------------
+    def forward(self, token_ids: torch.Tensor, positions: torch.Tensor, kv: KVState, *, mode: str,
+                cu_seqlens: torch.Tensor | None = None, max_len: int = 0, seq_ids: torch.Tensor | None = None,
+                last_idx: torch.Tensor | None = None) -> torch.Tensor:
+        """token_ids int64 [M], positions int32 [M] -> greedy next token per sequence (int64).
+
+        mode "prefill": M = all prompt tokens (concatenated), ``last_idx`` selects each sequence's last row;
+        mode "decode":  M = batch, one token per sequence, kv.seq_lens already counts the current token.
+        """
+        cfg = self.cfg
+        h = A.embed_gather(token_ids, self.w["embed"])
+        delta = None
+        for l in range(cfg.n_layers):
+            W = self.w["layers"][l]
+            xq, sx = self._norm_quant(h, delta, W["attn_norm"])
+            qkv = L.w8a8_gemm(xq, sx, W["qkv"].qweight, W["qkv"].scale)
+            attn = self._attention(l, qkv, positions, kv, mode, cu_seqlens, max_len, seq_ids)
+            aq, sa = L.act_quant(attn.view(attn.shape[0], -1))
+            delta = self._row_parallel(aq, sa, W["o"])
+            if self.moe is not None:
+                xq, sx, xn = self._norm_quant(h, delta, W["mlp_norm"], want_normed=True)
+            else:
+                (xq, sx), xn = self._norm_quant(h, delta, W["mlp_norm"]), None
+            delta = self._mlp(l, xq, sx, xn)
+        if last_idx is not None:
+            h = h.index_select(0, last_idx)
+            delta = delta.index_select(0, last_idx)
+        xq, sx = self._norm_quant(h, delta, self.w["final_norm"])
+        lm = self.w["lm_head"]
+        logits = L.w8a8_gemm(xq, sx, lm.qweight, lm.scale)
+        val, idx = A.argmax_rows(logits, index_offset=self.w["vocab_offset"])
+        if self.comm.world > 1:
+            idx = A.argmax_merge(self.comm.all_gather(val), self.comm.all_gather(idx))
+        self.last_logits = logits
+        return idx
