@@ -28,6 +28,7 @@ class Engine:
         self.kv: KVState | None = None
         self.batch = 0
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self.kernels_per_step = 0
         self._stream = torch.cuda.Stream(device=self.device)
 
     # ------------------------------------------------------------------------------------------------------
@@ -85,12 +86,24 @@ class Engine:
             torch.cuda.synchronize()
             self.tokens.copy_(saved[0]); self.positions.copy_(saved[1]); self.kv.seq_lens.copy_(saved[2])
             g = torch.cuda.CUDAGraph()
+            from ..ops import _lib
+            n0 = _lib.LAUNCHES[0]
             with torch.cuda.graph(g, stream=self._stream):
                 self._decode_body()
+            self.kernels_per_step = _lib.LAUNCHES[0] - n0      # this library's kernels inside one replay
             self.tokens.copy_(saved[0]); self.positions.copy_(saved[1]); self.kv.seq_lens.copy_(saved[2])
             self._graphs[self.batch] = g
         g.replay()
         return self.tokens
+
+    def step_from_host(self, ids_in: torch.Tensor, ids_out: torch.Tensor) -> torch.Tensor:
+        """Serving-loop form of a decode step: token ids arrive in pinned host memory (the previous step's sample,
+        possibly edited by the caller), the new ids are written to pinned host memory; returns after they landed."""
+        self.tokens.copy_(ids_in, non_blocking=True)
+        nxt = self.decode_step()
+        ids_out.copy_(nxt, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return ids_out
 
     def generate(self, prompts: torch.Tensor, max_new_tokens: int, use_graph: bool = True) -> torch.Tensor:
         """Greedy generation. prompts int64 [B, S] -> int64 [B, max_new_tokens] on the host."""

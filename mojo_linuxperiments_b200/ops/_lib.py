@@ -65,9 +65,13 @@ def stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
+LAUNCHES = [0]     # kernels of this library launched (or captured into a CUDA graph) by this process
+
+
 def check(rc: int, what: str) -> None:
     if rc != 0:
         raise KernelError(f"{what} failed with code {rc}")
+    LAUNCHES[0] += 1
 
 
 @lru_cache(maxsize=None)
