@@ -1,0 +1,31 @@
+"""Prefill a batch and run a few eager (un-graphed) decode steps of the Llama-3-8B-shaped model, for profiler captures.
+
+python benchmarks/decode_once.py [--batch 32] [--prompt-len 1024] [--steps 2] [--layers 32]
+"""
+import argparse
+from dataclasses import replace
+
+import torch
+
+from mojo_linuxperiments_b200.engine.engine import Engine
+from mojo_linuxperiments_b200.models import config as C
+from mojo_linuxperiments_b200.ops import _lib
+
+ap = argparse.ArgumentParser()
+ap.add_argument("--batch", type=int, default=32)
+ap.add_argument("--prompt-len", type=int, default=1024)
+ap.add_argument("--steps", type=int, default=2)
+ap.add_argument("--layers", type=int, default=32)
+ap.add_argument("--model", default="llama3-8b")
+a = ap.parse_args()
+cfg = replace(C.PRESETS[a.model](), n_layers=a.layers)
+eng = Engine(cfg, C.RuntimeConfig(max_batch=a.batch, max_seq_len=a.prompt_len + 128), seed=0)
+prompts = torch.randint(0, cfg.vocab, (a.batch, a.prompt_len))
+eng.start_batch(a.batch, a.prompt_len + a.steps + 8)
+eng.prefill(prompts)
+torch.cuda.synchronize()
+n0 = _lib.LAUNCHES[0]
+for _ in range(a.steps):
+    eng.decode_step(use_graph=False)
+torch.cuda.synchronize()
+print("launches before decode:", n0, "per step:", (_lib.LAUNCHES[0] - n0) // a.steps)

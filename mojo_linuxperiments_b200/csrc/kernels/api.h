@@ -12,13 +12,19 @@ extern "C" {
 
 // ---- W8A8 linear -----------------------------------------------------------------------------------
 // Scratch bytes the stream-K path of b200_w8a8_gemm wants for an [M,N] problem (int32 partial sums).
-size_t b200_w8a8_gemm_ws_bytes(int M, int N);
+size_t b200_w8a8_gemm_ws_bytes(int M, int N, int K, int num_sms);
 // y[m,n] = (sum_k xq[m,k]*wq[n,k]) * sx[m] * sw[n] (+ residual[m,n]); y is bf16 (or fp32 when out_fp32).
-// ws/counters must be zero on entry and are left zero on exit; force_mode: -1 auto, 0 whole tiles, 1 stream-K.
+// counters must be zero on entry and are left zero on exit (ws needs no initialisation); force_mode: -1 auto, 0 whole tiles, 1 stream-K.
 int b200_w8a8_gemm(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
                    const void* residual, int M, int N, int K, int ldy, int out_fp32,
                    void* ws, size_t ws_bytes, void* counters, int counters_len, int* status,
                    int num_sms, int force_mode, cudaStream_t stream);
+
+// Decode form (M <= 64): split-K thread-block clusters reduced through distributed shared memory; no scratch.
+// force_splits: 0 auto, else 1/2/4/8 CTAs per cluster along K.
+int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
+                          const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
+                          int num_sms, int force_splits, cudaStream_t stream);
 
 // ---- activation prologue ---------------------------------------------------------------------------
 int b200_act_quant(const void* x, long long ldx, void* residual, long long ldr, const void* gamma, float eps,
@@ -31,7 +37,7 @@ int b200_rope_kv_write(const void* qkv, long long ld_qkv, const int* positions, 
                        float eps, void* q_out, void* k_out, void* v_out, void* cache, const int* page_table,
                        int max_pages, int page_size, int hq, int hkv, int M, cudaStream_t stream);
 int b200_embed_gather(const long long* ids, const void* table, void* out, int M, int d, int vocab, cudaStream_t stream);
-int b200_argmax_rows(const void* logits, long long ld, int rows, int n, int index_offset, float* out_val,
+int b200_argmax_rows(const void* logits, long long ld, int rows, int n, int index_offset, int chunks, float* out_val,
                      long long* out_idx, cudaStream_t stream);
 int b200_argmax_merge(const float* cand_val, const long long* cand_idx, int world, int rows, long long* out_idx,
                       cudaStream_t stream);

@@ -39,8 +39,8 @@ struct RopeParams {
   int hq, hkv, M;
 };
 
-// one CTA per token, 8 warps; a warp handles one head at a time, lane l holds elements l, l+32, l+64, l+96
-__global__ void __launch_bounds__(256) rope_kv_kernel(const RopeParams p) {
+// grid (tokens, ceil(heads / 4)), 4 warps; a warp handles one head, lane l holds elements l, l+32, l+64, l+96
+__global__ void __launch_bounds__(128) rope_kv_kernel(const RopeParams p) {
   const int tok = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = p.positions[tok];
@@ -54,7 +54,8 @@ __global__ void __launch_bounds__(256) rope_kv_kernel(const RopeParams p) {
     cache_row = static_cast<size_t>(page) * 2 * p.hkv * p.page_size + (pos % p.page_size);
   }
   const int nheads = p.hq + 2 * p.hkv;
-  for (int h = warp; h < nheads; h += 8) {
+  const int h = blockIdx.y * 4 + warp;
+  if (h < nheads) {
     const __nv_bfloat16* x = row + static_cast<size_t>(h) * HEAD_DIM;
     float v0 = __bfloat162float(x[lane]), v1 = __bfloat162float(x[lane + 32]);
     float v2 = __bfloat162float(x[lane + 64]), v3 = __bfloat162float(x[lane + 96]);
@@ -99,19 +100,34 @@ __global__ void embed_gather_kernel(const long long* __restrict__ ids, const __n
   for (int i = threadIdx.x; i < d / 8; i += blockDim.x) dst[i] = src[i];
 }
 
-// one CTA per row; ties resolve to the lowest index (matches torch.argmax on a single device)
+// grid (rows, chunks): CTA (r, c) scans columns [c*cs, (c+1)*cs) of row r and writes candidate [c][r];
+// ties resolve to the lowest index (matches torch.argmax on a single device after the merge)
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int n,
-                                                          int index_offset, float* __restrict__ out_val,
+                                                          int chunk, int index_offset, float* __restrict__ out_val,
                                                           long long* __restrict__ out_idx) {
   __shared__ float sv[8];
   __shared__ int si[8];
   const int row = blockIdx.x;
+  const int c0 = blockIdx.y * chunk, c1 = min(n, c0 + chunk);
   const __nv_bfloat16* x = logits + static_cast<size_t>(row) * ld;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const float v = __bfloat162float(x[i]);
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  auto consider = [&](float v, int i) { if (v > best || (v == best && i < bi)) { best = v; bi = i; } };
+  if (((reinterpret_cast<uintptr_t>(x) | static_cast<uintptr_t>(c0 * 2)) & 15) == 0) {
+    const int nv = (c1 - c0) / 8;
+    const uint4* xv = reinterpret_cast<const uint4*>(x + c0);
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      const uint4 raw = __ldg(xv + i);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        consider(__uint_as_float(w[k] << 16), c0 + i * 8 + 2 * k);
+        consider(__uint_as_float(w[k] & 0xffff0000u), c0 + i * 8 + 2 * k + 1);
+      }
+    }
+    for (int i = c0 + nv * 8 + threadIdx.x; i < c1; i += blockDim.x) consider(__bfloat162float(x[i]), i);
+  } else {
+    for (int i = c0 + threadIdx.x; i < c1; i += blockDim.x) consider(__bfloat162float(x[i]), i);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -124,8 +140,9 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* _
   if (threadIdx.x == 0) {
     for (int w = 1; w < 8; ++w)
       if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
-    out_val[row] = best;
-    out_idx[row] = static_cast<long long>(bi) + index_offset;
+    const size_t o = static_cast<size_t>(blockIdx.y) * gridDim.x + row;
+    out_val[o] = best;
+    out_idx[o] = static_cast<long long>(bi) + index_offset;
   }
 }
 
@@ -163,7 +180,7 @@ extern "C" int b200_rope_kv_write(const void* qkv, long long ld_qkv, const int* 
   p.v_out = static_cast<__nv_bfloat16*>(v_out);
   p.cache = static_cast<__nv_bfloat16*>(cache); p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size;
   p.hq = hq; p.hkv = hkv; p.M = M;
-  rope_kv_kernel<<<M, 256, 0, stream>>>(p);
+  rope_kv_kernel<<<dim3(M, (hq + 2 * hkv + 3) / 4), 128, 0, stream>>>(p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
@@ -177,10 +194,13 @@ extern "C" int b200_embed_gather(const long long* ids, const void* table, void* 
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
 
-extern "C" int b200_argmax_rows(const void* logits, long long ld, int rows, int n, int index_offset, float* out_val,
-                                long long* out_idx, cudaStream_t stream) {
+// out_val / out_idx: [chunks][rows] candidates (merge them with b200_argmax_merge, world = chunks)
+extern "C" int b200_argmax_rows(const void* logits, long long ld, int rows, int n, int index_offset, int chunks,
+                                float* out_val, long long* out_idx, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  argmax_rows_kernel<<<rows, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), ld, n, index_offset, out_val, out_idx);
+  if (chunks < 1) chunks = 1;
+  const int chunk = ((n + chunks - 1) / chunks + 7) & ~7;
+  argmax_rows_kernel<<<dim3(rows, chunks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), ld, n, chunk, index_offset, out_val, out_idx);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }

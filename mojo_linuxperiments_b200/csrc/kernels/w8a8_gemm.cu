@@ -18,20 +18,17 @@
 //     (each reads its 32-lane quarter of TMEM with tcgen05.ld).
 //   * Persistent grid.  Work is the list of (tile, k-block) units.  Large problems give each CTA whole
 //     tiles round-robin, rasterised so that concurrently running CTAs share token panels in L2.
-//     Small-M problems (decode) use a stream-K split: every CTA gets an equal share of k-blocks;
-//     partial tiles are summed exactly with int32 atomics into a scratch buffer and the CTA that
-//     completes a tile applies the scales (and re-zeroes the scratch for the next launch).
+//     Small-M problems (decode) use a stream-K split: every CTA gets an equal share of k-blocks; a CTA
+//     that covers only part of a tile's K range stores its int32 partial into its own slab of a scratch
+//     buffer (plain coalesced stores), and the last CTA to arrive for the tile sums the slabs exactly,
+//     applies the scales and writes the output.
 //   * Every mbarrier wait is bounded; on a timeout the CTA records a status code, drains and exits.
 #include "ptx.cuh"
 #include "api.h"
-#include <cuda.h>
+#include "gemm_common.cuh"
 
 namespace b200 {
 
-constexpr int TILE_N = 128;     // output channels per tile  (MMA M)
-constexpr int BLOCK_K = 128;    // int8 elements (= bytes) per k-block: one 128-byte swizzle row
-constexpr int UMMA_K = 32;      // int8 elements per tcgen05.mma
-constexpr int GEMM_THREADS = 192;
 constexpr int GROUP_M = 8;      // token tiles per rasterisation group
 
 struct GemmParams {
@@ -45,9 +42,9 @@ struct GemmParams {
   const __nv_bfloat16* residual;
   int ldy;
   int out_fp32;
-  int32_t* ws;                  // [m_tiles*BN][n_tiles*128] int32, zero between launches (mode 1)
-  int ldws;
-  uint32_t* counters;           // [num_tiles], zero between launches (mode 1)
+  int32_t* ws;                  // stream-K partials: [num_tiles][max_segs][BN][128] int32 (mode 1); needs no zeroing
+  int max_segs;
+  uint32_t* counters;           // [num_tiles], zero between launches (mode 1); the finishing CTA re-zeroes
   int* status;
   unsigned long long limit_ns;
 };
@@ -79,6 +76,13 @@ struct WorkIter {
     return true;
   }
 };
+
+// index of the CTA whose unit range [U*c/G, U*(c+1)/G) contains unit u
+__device__ __forceinline__ int cta_of_unit(long long u, long long total_units, int grid) {
+  int c = static_cast<int>(u * grid / total_units);
+  while (c + 1 < grid && total_units * (c + 1) / grid <= u) ++c;
+  return c;
+}
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& m_tile, int& n_tile) {
   const int per_group = GROUP_M * p.n_tiles;
@@ -296,6 +300,15 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const bool n_ok = n < p.N;
         const int m0 = m_tile * BN;
         const float swn = n_ok ? __ldg(p.sw + n) : 0.f;
+        int nseg = 1;
+        int32_t* slab = nullptr;
+        if (!whole) {
+          const long long u_first = static_cast<long long>(sg.tile) * p.kblocks;
+          const int c_first = cta_of_unit(u_first, p.total_units, gridDim.x);
+          const int c_last = cta_of_unit(u_first + p.kblocks - 1, p.total_units, gridDim.x);
+          nseg = c_last - c_first + 1;
+          slab = p.ws + (static_cast<size_t>(sg.tile) * p.max_segs + (blockIdx.x - c_first)) * (BN * TILE_N);
+        }
 #pragma unroll 1
         for (int c = 0; c < BN / CH; ++c) {
           uint32_t r[CH];
@@ -329,10 +342,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             }
           } else {
-            int32_t* wp = p.ws + static_cast<size_t>(mc) * p.ldws + n;
+            // partial K range: park the int32 partial in this CTA's slab, [token][channel] so warps store 128 B rows
+            int32_t* sp = slab + static_cast<size_t>(c * CH) * TILE_N + (q * 32 + lane);
 #pragma unroll
             for (int j = 0; j < CH; ++j)
-              if (j < jmax) atomicAdd(wp + static_cast<size_t>(j) * p.ldws, static_cast<int32_t>(r[j]));
+              if (j < jmax) __stcg(sp + j * TILE_N, static_cast<int32_t>(r[j]));
           }
         }
         // accumulator drained: hand the TMEM buffer back to the MMA warp
@@ -344,9 +358,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           __threadfence();
           named_bar_sync(1, 128);
           if (et == 0) {
-            const uint32_t add = static_cast<uint32_t>(sg.kb1 - sg.kb0);
-            const uint32_t old = atomicAdd(p.counters + sg.tile, add);
-            *fix_slot = (old + add == static_cast<uint32_t>(p.kblocks)) ? 1 : 0;
+            const uint32_t old = atomicAdd(p.counters + sg.tile, 1u);
+            *fix_slot = (old + 1u == static_cast<uint32_t>(nseg)) ? 1 : 0;
           }
           named_bar_sync(1, 128);
           const int last = *fix_slot;
@@ -355,11 +368,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             __threadfence();
             if (n_ok) {
               const int jmax = min(BN, p.M - m0);
+              const int32_t* s0 = p.ws + static_cast<size_t>(sg.tile) * p.max_segs * (BN * TILE_N) + (q * 32 + lane);
               for (int j = 0; j < jmax; ++j) {
+                int32_t acc = 0;
+                for (int sgi = 0; sgi < nseg; ++sgi) acc += __ldcg(s0 + static_cast<size_t>(sgi) * (BN * TILE_N) + j * TILE_N);
                 const int m = m0 + j;
-                int32_t* wp = p.ws + static_cast<size_t>(m) * p.ldws + n;
-                const int32_t acc = __ldcg(wp);
-                *wp = 0;
                 float v = static_cast<float>(acc) * swn * __ldg(p.sx + m);
                 const size_t o = static_cast<size_t>(m) * p.ldy + n;
                 if (p.residual) v += __bfloat162float(p.residual[o]);
@@ -430,7 +443,6 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
 
-constexpr int SWAP_MAX_M = 64;     // up to this many tokens the weights fill the MMA M dimension
 
 // token-tile width (swapped) or channel-tile width (normal)
 int gemm_pick_bn(int M, int N, int num_sms) {
@@ -454,12 +466,24 @@ int gemm_pick_bn(int M, int N, int num_sms) {
 
 using namespace b200;
 
-extern "C" size_t b200_w8a8_gemm_ws_bytes(int M, int N) {
+// grid and slab count of the stream-K schedule for a swapped-orientation problem
+static void streamk_plan(long long total_units, int kblocks, int num_sms, int* grid, int* max_segs) {
+  long long g = total_units / 4;          // at least ~4 k-blocks per CTA
+  if (g < 1) g = 1;
+  if (g > num_sms) g = num_sms;
+  *grid = static_cast<int>(g);
+  const long long min_units = total_units / g;                 // every CTA gets at least this many units
+  *max_segs = static_cast<int>((kblocks + min_units - 1) / (min_units > 0 ? min_units : 1)) + 1;
+}
+
+extern "C" size_t b200_w8a8_gemm_ws_bytes(int M, int N, int K, int num_sms) {
   if (M > SWAP_MAX_M) return 0;
-  const int bn = gemm_pick_bn(M, N, 148);
-  const size_t m_pad = static_cast<size_t>((M + bn - 1) / bn) * bn;
-  const size_t n_pad = static_cast<size_t>((N + TILE_N - 1) / TILE_N) * TILE_N;
-  return m_pad * n_pad * sizeof(int32_t);
+  const int bn = gemm_pick_bn(M, N, num_sms);
+  const long long tiles = static_cast<long long>((M + bn - 1) / bn) * ((N + TILE_N - 1) / TILE_N);
+  const int kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+  int grid, max_segs;
+  streamk_plan(tiles * kblocks, kblocks, num_sms, &grid, &max_segs);
+  return static_cast<size_t>(tiles) * max_segs * bn * TILE_N * sizeof(int32_t);
 }
 
 extern "C" int b200_w8a8_gemm(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
@@ -480,14 +504,16 @@ extern "C" int b200_w8a8_gemm(const void* xq, const float* sx, const void* wq, c
   p.sx = sx; p.sw = sw; p.y = y; p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.ldy = ldy; p.out_fp32 = out_fp32;
   p.ws = static_cast<int32_t*>(ws);
-  p.ldws = p.n_tiles * TILE_N;
+  p.max_segs = 1;
   p.counters = static_cast<uint32_t*>(counters);
   p.status = status;
   p.limit_ns = 2000000000ull;
 
   int mode = 0;
+  int sk_grid = 1;
   if (swap) {
-    const size_t need_ws = static_cast<size_t>(p.m_tiles) * bn * p.ldws * sizeof(int32_t);
+    streamk_plan(p.total_units, p.kblocks, num_sms, &sk_grid, &p.max_segs);
+    const size_t need_ws = static_cast<size_t>(p.num_tiles) * p.max_segs * bn * TILE_N * sizeof(int32_t);
     const bool can_split = ws && counters && ws_bytes >= need_ws && counters_len >= p.num_tiles;
     if (force_mode == 0 || force_mode == 1) mode = force_mode;
     else mode = (p.num_tiles < 4 * num_sms) ? 1 : 0;
@@ -498,10 +524,7 @@ extern "C" int b200_w8a8_gemm(const void* xq, const float* sx, const void* wq, c
   if (mode == 0) {
     grid = p.num_tiles < num_sms ? p.num_tiles : num_sms;
   } else {
-    long long g = p.total_units / 4;          // at least ~4 k-blocks per CTA
-    if (g < 1) g = 1;
-    if (g > num_sms) g = num_sms;
-    grid = static_cast<int>(g);
+    grid = sk_grid;
   }
 
   CUtensorMap tw, tx;

@@ -1,0 +1,268 @@
+// W8A8 GEMM for decode (M <= 64 tokens): weight streaming with a split-K thread-block cluster.
+//
+//   Y[m,n] = (sum_k Xq[m,k] * Wq[n,k]) * sx[m] * sw[n]  (+ residual[m,n])
+//
+// The op is bound by the bytes of Wq, so the grid is shaped for bandwidth, not for the tensor core:
+//   * one CTA = 128 output channels x (K / S) of the reduction; the S CTAs of a cluster share one output tile;
+//   * S is chosen so that the grid has roughly two CTAs per SM (shared memory is sized for two co-resident CTAs),
+//     which keeps > 150 KB of TMA loads in flight per SM and lets CTAs of different tiles overlap head and tail;
+//   * each CTA runs the usual TMA -> tcgen05.mma.kind::i8 -> TMEM pipeline (weights are the 128-row A operand, the
+//     token tile of BN in {16,32,64} rows is the B operand);
+//   * the S partial accumulators are combined through distributed shared memory: every CTA sends, for each of
+//     the S row slices of the tile, its int32 partial to the CTA that owns the slice (st.shared::cluster), the
+//     cluster synchronises, and each CTA reduces and writes 128/S channels.  No global scratch, no atomics.
+// All mbarrier waits are bounded; a CTA that gives up still reaches both cluster barriers, so peers never hang.
+#include "ptx.cuh"
+#include "api.h"
+#include "gemm_common.cuh"
+
+namespace b200 {
+
+struct DecodeGemmParams {
+  int M, N, K, kblocks, splits;
+  const float* sx;
+  const float* sw;
+  void* y;
+  const __nv_bfloat16* residual;
+  int ldy, out_fp32;
+  int* status;
+  unsigned long long limit_ns;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS)
+w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
+                        const DecodeGemmParams p) {
+  constexpr int A_BYTES = TILE_N * BLOCK_K;
+  constexpr int B_BYTES = BN * BLOCK_K;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  constexpr uint32_t IDESC = umma_idesc_i8(TILE_N, BN);
+  static_assert(STAGES * STAGE_BYTES >= BN * TILE_N * 4, "the exchange buffer aliases the pipeline stages");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);      // full[S], empty[S], tfull
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  const uint32_t tfull_bar = bar_base + 8u * (2 * STAGES);
+
+  const int S = p.splits;
+  const int rank = static_cast<int>(cluster_ctarank());          // == blockIdx.x: position along K
+  const int n_tile = blockIdx.y, m_tile = blockIdx.z;
+  const int kb0 = static_cast<int>(static_cast<long long>(p.kblocks) * rank / S);
+  const int kb1 = static_cast<int>(static_cast<long long>(p.kblocks) * (rank + 1) / S);
+  const uint64_t limit = p.limit_ns;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    mbar_init(tfull_bar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tmap(&tmap_w);
+      prefetch_tmap(&tmap_x);
+      const uint64_t pol_w = policy_evict_first();     // weights are read exactly once per launch
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY, limit)) { ok = false; break; }
+        mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+        const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
+        tma_load_2d_hint(a_dst, &tmap_w, full_bar(stage), kb * BLOCK_K, n_tile * TILE_N, pol_w);
+        tma_load_2d(a_dst + A_BYTES, &tmap_x, full_bar(stage), kb * BLOCK_K, m_tile * BN);
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (!ok) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 2000000ull) { } }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL, limit)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t a_src = smem_base + stage * STAGE_BYTES;
+        const uint64_t a_desc = umma_desc_k_sw128(a_src);
+        const uint64_t b_desc = umma_desc_k_sw128(a_src + A_BYTES);
+#pragma unroll
+        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+          umma_i8_ss(tmem_base, a_desc + 2ull * k, b_desc + 2ull * k, IDESC, (kb > kb0 || k > 0) ? 1u : 0u);
+        umma_commit(empty_bar(stage));
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+      if (ok) umma_commit(tfull_bar);
+    }
+    __syncwarp();
+  }
+
+  // ---------------- epilogue warps: wait for the accumulator ----------------
+  const bool epi = warp >= 2;
+  const int q = warp & 3;
+  const int et = threadIdx.x - 64;
+  const int row = q * 32 + lane;                          // channel inside the tile == TMEM lane
+  const int m0 = m_tile * BN;
+  const int jmax = min(BN, p.M - m0);
+  constexpr int CH = (BN >= 32) ? 32 : 16;
+  bool acc_ok = false;
+  if (epi) {
+    acc_ok = (kb1 > kb0) && mbar_wait(tfull_bar, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, limit);
+    tc_fence_after();
+  }
+
+  if (S == 1) {
+    if (epi && acc_ok) {
+      const int n = n_tile * TILE_N + row;
+      const bool n_ok = n < p.N;
+      const float swn = n_ok ? __ldg(p.sw + n) : 0.f;
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / CH; ++c) {
+        uint32_t r[CH];
+        if constexpr (CH == 32) tmem_ld_x32(t_addr + c * CH, r); else tmem_ld_x16(t_addr + c * CH, r);
+        tmem_ld_wait();
+        const int mc = m0 + c * CH;
+        const int jm = min(CH, p.M - mc);
+        if (!n_ok || jm <= 0) continue;
+        const size_t o0 = static_cast<size_t>(mc) * p.ldy + n;
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          if (j < jm) {
+            float v = static_cast<float>(static_cast<int32_t>(r[j])) * swn * __ldg(p.sx + mc + j);
+            const size_t o = o0 + static_cast<size_t>(j) * p.ldy;
+            if (p.residual) v += __bfloat162float(p.residual[o]);
+            if (p.out_fp32) reinterpret_cast<float*>(p.y)[o] = v;
+            else reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16(v);
+          }
+        }
+      }
+    }
+  } else {
+    // every pipeline of the cluster has drained: stage memory can now hold the exchange buffer
+    cluster_sync_all();
+    const int rows_per = TILE_N / S;                        // channels each CTA of the cluster finishes
+    if (epi) {
+      // exchange buffer in the owner CTA: [sender][token j][channel in slice] int32
+      const int owner = row / rows_per, row_in = row - owner * rows_per;
+      const uint32_t remote = mapa_shared(smem_base, static_cast<uint32_t>(owner));
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / CH; ++c) {
+        uint32_t r[CH];
+        if (acc_ok) {
+          if constexpr (CH == 32) tmem_ld_x32(t_addr + c * CH, r); else tmem_ld_x16(t_addr + c * CH, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < CH; ++j) r[j] = 0u;           // empty K range (or aborted): contributes nothing
+        }
+#pragma unroll
+        for (int j = 0; j < CH; ++j) {
+          const int jj = c * CH + j;
+          if (jj < jmax) st_shared_cluster_u32(remote + 4u * ((rank * BN + jj) * rows_per + row_in), r[j]);
+        }
+      }
+    }
+    tc_fence_before();
+    cluster_sync_all();
+    if (epi) {
+      const int32_t* ex = reinterpret_cast<const int32_t*>(smem);
+      const int total = rows_per * jmax;
+      for (int idx = et; idx < total; idx += 128) {
+        const int j = idx / rows_per, row_in = idx - j * rows_per;
+        int32_t acc = 0;
+        for (int s = 0; s < S; ++s) acc += ex[(s * BN + j) * rows_per + row_in];
+        const int n = n_tile * TILE_N + rank * rows_per + row_in;
+        if (n < p.N) {
+          const int m = m0 + j;
+          float v = static_cast<float>(acc) * __ldg(p.sw + n) * __ldg(p.sx + m);
+          const size_t o = static_cast<size_t>(m) * p.ldy + n;
+          if (p.residual) v += __bfloat162float(p.residual[o]);
+          if (p.out_fp32) reinterpret_cast<float*>(p.y)[o] = v;
+          else reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16(v);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+}
+
+template <int BN, int STAGES>
+static int launch_decode(const CUtensorMap& tw, const CUtensorMap& tx, const DecodeGemmParams& p, dim3 grid, cudaStream_t stream) {
+  constexpr int SMEM = STAGES * (TILE_N * BLOCK_K + BN * BLOCK_K) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(w8a8_gemm_decode_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return -1000 - static_cast<int>(e);
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = grid.x;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, w8a8_gemm_decode_kernel<BN, STAGES>, tw, tx, p);
+  return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
+}
+
+// splits along K: aim for about two CTAs per SM, powers of two up to 8, at least one k-block per CTA
+int decode_pick_splits(int tiles, int kblocks, int num_sms) {
+  int s = 1;
+  while (s < 8 && tiles * s * 2 <= 2 * num_sms + num_sms / 2 && kblocks >= s * 2) s *= 2;
+  return s;
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
+                                     const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
+                                     int num_sms, int force_splits, cudaStream_t stream) {
+  if (M <= 0 || M > SWAP_MAX_M || N <= 0 || K <= 0 || (K % 16) != 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15)) return -2;
+  const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+  DecodeGemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+  const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = (M + bn - 1) / bn;
+  int s = force_splits > 0 ? force_splits : decode_pick_splits(n_tiles * m_tiles, p.kblocks, num_sms);
+  if (s != 1 && s != 2 && s != 4 && s != 8) return -1;
+  p.splits = s;
+  p.sx = sx; p.sw = sw; p.y = y; p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.ldy = ldy; p.out_fp32 = out_fp32; p.status = status; p.limit_ns = 2000000000ull;
+  CUtensorMap tw, tx;
+  if (make_tmap_2d_u8(&tw, wq, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(K), TILE_N)) return -11;
+  if (make_tmap_2d_u8(&tx, xq, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), bn)) return -12;
+  dim3 grid(s, n_tiles, m_tiles);
+  switch (bn) {
+    case 16: return launch_decode<16, 6>(tw, tx, p, grid, stream);
+    case 32: return launch_decode<32, 5>(tw, tx, p, grid, stream);
+    default: return launch_decode<64, 4>(tw, tx, p, grid, stream);
+  }
+}

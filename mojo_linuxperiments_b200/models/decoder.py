@@ -139,6 +139,6 @@ class Decoder:
         logits = L.w8a8_gemm(xq, sx, lm.qweight, lm.scale)
         val, idx = A.argmax_rows(logits, index_offset=self.w["vocab_offset"])
         if self.comm.world > 1:
-            idx = A.argmax_merge(self.comm.all_gather(val), self.comm.all_gather(idx))
+            val, idx = self.comm.all_gather(val), self.comm.all_gather(idx)
         self.last_logits = logits
-        return idx
+        return A.argmax_merge(val, idx)

@@ -45,12 +45,13 @@ F = c_float
 
 
 class _Sig:
-    b200_w8a8_gemm_ws_bytes = (c_size_t, [I, I])
+    b200_w8a8_gemm_ws_bytes = (c_size_t, [I, I, I, I])
     b200_w8a8_gemm = (I, [P, P, P, P, P, P, I, I, I, I, I, P, c_size_t, P, I, P, I, I, P])
+    b200_w8a8_gemm_decode = (I, [P, P, P, P, P, P, I, I, I, I, I, P, I, I, P])
     b200_act_quant = (I, [P, LL, P, LL, P, F, P, LL, P, P, LL, I, I, I, P])
     b200_rope_kv_write = (I, [P, LL, P, P, P, P, P, P, F, P, P, P, P, P, I, I, I, I, I, P])
     b200_embed_gather = (I, [P, P, P, I, I, I, P])
-    b200_argmax_rows = (I, [P, LL, I, I, I, P, P, P])
+    b200_argmax_rows = (I, [P, LL, I, I, I, I, P, P, P])
     b200_argmax_merge = (I, [P, P, I, I, P, P])
     b200_attn_decode_scratch_floats = (c_size_t, [I, I, I])
     b200_attn_decode = (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P])

@@ -111,22 +111,26 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | Non
     return out
 
 
-def argmax_rows(logits: torch.Tensor, index_offset: int = 0, out_val=None, out_idx=None):
-    """(max value fp32, index int64 + offset) per row of bf16 logits [rows, n]; lowest index wins ties."""
+def argmax_rows(logits: torch.Tensor, index_offset: int = 0, chunks: int | None = None):
+    """Candidates (max value fp32, index int64 + offset) per row of bf16 logits [rows, n], one per column chunk:
+    returns ([chunks, rows], [chunks, rows]); ``argmax_merge`` picks the winner (lowest index wins ties)."""
     rows, n = logits.shape
     assert logits.dtype == torch.bfloat16 and logits.stride(1) == 1
-    if out_val is None:
-        out_val = torch.empty(rows, dtype=torch.float32, device=logits.device)
-    if out_idx is None:
-        out_idx = torch.empty(rows, dtype=torch.int64, device=logits.device)
-    _lib.check(_lib.lib().b200_argmax_rows(logits.data_ptr(), logits.stride(0), rows, n, index_offset,
+    if chunks is None:
+        chunks = max(1, min(64, n // 2048, 296 // max(rows, 1) + 1))
+    out_val = torch.empty((chunks, rows), dtype=torch.float32, device=logits.device)
+    out_idx = torch.empty((chunks, rows), dtype=torch.int64, device=logits.device)
+    _lib.check(_lib.lib().b200_argmax_rows(logits.data_ptr(), logits.stride(0), rows, n, index_offset, chunks,
                                            out_val.data_ptr(), out_idx.data_ptr(), _lib.stream()), "argmax_rows")
     return out_val, out_idx
 
 
 def argmax_merge(cand_val: torch.Tensor, cand_idx: torch.Tensor, out_idx: torch.Tensor | None = None) -> torch.Tensor:
-    """cand_* [world, rows] -> global argmax index per row."""
-    world, rows = cand_val.shape
+    """cand_* [..., rows] (any number of leading candidate dims) -> global argmax index per row."""
+    rows = cand_val.shape[-1]
+    cand_val = cand_val.reshape(-1, rows)
+    cand_idx = cand_idx.reshape(-1, rows)
+    world = cand_val.shape[0]
     if out_idx is None:
         out_idx = torch.empty(rows, dtype=torch.int64, device=cand_val.device)
     _lib.check(_lib.lib().b200_argmax_merge(cand_val.data_ptr(), cand_idx.data_ptr(), world, rows, out_idx.data_ptr(),

@@ -34,11 +34,18 @@ def act_quant(x: torch.Tensor, *, mode: int = AQ_PLAIN, gamma: torch.Tensor | No
     return (q, s, xn) if want_normed else (q, s)
 
 
+DECODE_MAX_M = 64
+
+
 def w8a8_gemm(xq: torch.Tensor, sx: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor, *,
               residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
               out_dtype: torch.dtype = torch.bfloat16, workspace: Workspace | None = None,
-              force_mode: int = -1) -> torch.Tensor:
-    """y[m,n] = (sum_k xq[m,k] wq[n,k]) * sx[m] * sw[n] (+ residual); int8 operands, int32 accumulate in TMEM."""
+              force_mode: int = -1, force_splits: int = 0) -> torch.Tensor:
+    """y[m,n] = (sum_k xq[m,k] wq[n,k]) * sx[m] * sw[n] (+ residual); int8 operands, int32 accumulate in TMEM.
+
+    Up to 64 tokens the cluster split-K weight-streaming kernel runs (``force_mode`` -1) unless the problem has
+    enough tiles for the persistent kernel; ``force_mode`` 0 / 1 select the persistent kernel's whole-tile / stream-K
+    schedules, ``force_mode`` 2 the cluster kernel with ``force_splits`` CTAs per cluster."""
     assert xq.is_cuda and xq.dtype == torch.int8 and wq.dtype == torch.int8
     assert xq.is_contiguous() and wq.is_contiguous()
     M, K = xq.shape
@@ -50,6 +57,17 @@ def w8a8_gemm(xq: torch.Tensor, sx: torch.Tensor, wq: torch.Tensor, sw: torch.Te
     if residual is not None:
         assert residual.dtype == torch.bfloat16 and residual.stride(0) == out.stride(0) and residual.stride(1) == 1
     w = workspace or default_workspace(xq.device)
+    n_tiles = (N + 127) // 128
+    use_cluster = M <= DECODE_MAX_M and (force_mode == 2 or (force_mode == -1 and n_tiles < 4 * _lib.num_sms(xq.device.index)))
+    if use_cluster:
+        rc = _lib.lib().b200_w8a8_gemm_decode(
+            xq.data_ptr(), sx.data_ptr(), wq.data_ptr(), sw.data_ptr(), out.data_ptr(), _lib.ptr(residual),
+            M, N, K, out.stride(0), 1 if out.dtype == torch.float32 else 0, w.status.data_ptr(),
+            _lib.num_sms(xq.device.index), force_splits, _lib.stream())
+        _lib.check(rc, "w8a8_gemm_decode")
+        return out
+    if force_mode == 2:
+        force_mode = -1
     rc = _lib.lib().b200_w8a8_gemm(
         xq.data_ptr(), sx.data_ptr(), wq.data_ptr(), sw.data_ptr(), out.data_ptr(), _lib.ptr(residual),
         M, N, K, out.stride(0), 1 if out.dtype == torch.float32 else 0,

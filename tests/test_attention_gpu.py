@@ -118,10 +118,13 @@ def test_embed_and_argmax():
     logits = _rand((7, 16032), 2)
     logits[3, 77] = 100.0
     logits[3, 9000] = 100.0       # tie: lowest index wins
-    val, idx = A.argmax_rows(logits, index_offset=1000)
-    torch.cuda.synchronize()
-    assert torch.equal(idx - 1000, logits.float().argmax(dim=1))
-    assert idx[3].item() == 1077
-    cv = torch.stack([val, val + 1.0, val - 1.0])
-    ci = torch.stack([idx, idx + 5, idx + 9])
-    assert torch.equal(A.argmax_merge(cv, ci), idx + 5)
+    for chunks in (1, 7, None):
+        cv, ci = A.argmax_rows(logits, index_offset=1000, chunks=chunks)
+        idx = A.argmax_merge(cv, ci)
+        torch.cuda.synchronize()
+        assert torch.equal(idx - 1000, logits.float().argmax(dim=1))
+        assert idx[3].item() == 1077
+    val = cv.max(dim=0).values
+    cv3 = torch.stack([val, val + 1.0, val - 1.0])
+    ci3 = torch.stack([idx, idx + 5, idx + 9])
+    assert torch.equal(A.argmax_merge(cv3, ci3), idx + 5)

@@ -1,0 +1,103 @@
+"""Device runtime against a host-memory stand-in for the CUDA driver (CPU), and against the real driver (GPU)."""
+import os
+import subprocess
+from pathlib import Path
+
+import pytest
+
+from mojo_linuxperiments_b200 import devrt as D
+
+FAKE_SRC = Path(__file__).parent / "fake_cuda" / "fake_cuda.c"
+
+
+@pytest.fixture()
+def fake_driver(tmp_path, monkeypatch):
+    so = tmp_path / "libfakecuda.so"
+    subprocess.run(["gcc", "-shared", "-fPIC", "-O1", "-o", str(so), str(FAKE_SRC)], check=True)
+    monkeypatch.setenv("B200RT_LIBCUDA", str(so))
+    D.lib().devrt_reload_driver()
+    yield monkeypatch
+    monkeypatch.delenv("B200RT_LIBCUDA", raising=False)
+    D.lib().devrt_reload_driver()
+
+
+def test_device_mask():
+    m = D.DeviceMask([0, 3, 63, 64, -1])
+    assert m.count() == 3 and m.test(3) and not m.test(64) and m.devices() == [0, 3, 63]
+    m.clear(3)
+    assert not m.test(3)
+    m.clear_all()
+    assert m.count() == 0
+
+
+def test_no_driver_is_reported_not_raised(monkeypatch):
+    monkeypatch.setenv("B200RT_LIBCUDA", "/nonexistent/libcuda.so")
+    D.lib().devrt_reload_driver()
+    t = D.GpuTopology()
+    assert t.status == D.NO_DRIVER and t.num_devices == 0 and not t.fully_connected()
+    a = D.HbmArena(0, 1 << 20)
+    assert not a and a.status == D.NO_DRIVER and a.alloc(16) is None
+    monkeypatch.delenv("B200RT_LIBCUDA")
+    D.lib().devrt_reload_driver()
+
+
+def test_topology_on_fake_driver(fake_driver, tmp_path):
+    pci = tmp_path / "pci"
+    for i, node in enumerate([0, 1, 1, 0]):
+        d = pci / f"0000:{0x10 + i:02x}:00.0"
+        d.mkdir(parents=True)
+        (d / "numa_node").write_text(f"{node}\n")
+    fake_driver.setenv("B200RT_PCI_SYSFS", str(pci))
+    fake_driver.setenv("FAKE_CUDA_DEVICES", "4")
+    t = D.GpuTopology()
+    assert t.status == 0 and t.num_devices == 4 and t.fully_connected()
+    g = t.gpu(2)
+    assert g["sm_count"] == 148 and g["cc"] == 100 and g["multicast"] and g["numa_node"] == 1
+    assert g["mem_total"] == 180 << 30 and g["mem_free"] == (170 - 2) << 30
+    assert t.distance(1, 1) == 0 and t.distance(0, 3) == 1 and t.distance(0, 9) == -1
+    assert t.peers_of(1).devices() == [0, 2, 3]
+    assert "Fake B200 #3" in t.debug_string()
+    fake_driver.setenv("FAKE_CUDA_NO_PEER", "1")
+    t2 = D.GpuTopology()
+    assert not t2.fully_connected() and t2.distance(0, 1) == -1 and t2.peers_of(0).count() == 0
+
+
+def test_hbm_arena_contract_on_fake_driver(fake_driver):
+    a = D.HbmArena(1, 3 << 20, alignment=256)
+    assert a and a.size() == 4 << 20                     # rounded to the 2 MiB granularity
+    assert a.used() == 0 and a.verify_placement()
+    p1, p2 = a.alloc(100), a.alloc(100)
+    assert p1 == a.base() and p2 == a.base() + 256
+    m = a.mark()
+    assert a.alloc(1 << 20) is not None
+    assert a.alloc(4 << 20) is None                      # refused, state unchanged
+    used = a.used()
+    a.reset_to(used + 1)
+    assert a.used() == used
+    a.reset_to(m)
+    assert a.used() == m and a.high_water() == used
+    a.reset()
+    assert a.used() == 0 and a.remaining() == a.size()
+    fake_driver.setenv("FAKE_CUDA_FAIL_CREATE", "1")
+    b = D.HbmArena(0, 1 << 20)
+    assert not b and b.alloc(8) is None
+
+
+@pytest.mark.gpu
+def test_real_topology_and_arena_tensor():
+    import torch
+    D.lib().devrt_reload_driver()
+    t = D.GpuTopology()
+    assert t.status == 0 and t.num_devices == torch.cuda.device_count()
+    g = t.gpu(0)
+    assert g["sm_count"] == torch.cuda.get_device_properties(0).multi_processor_count and g["cc"] == 100
+    a = D.HbmArena(0, 8 << 20)
+    assert a and a.verify_placement()
+    x = a.tensor((1024, 256), torch.float32)
+    x.fill_(3.0)
+    assert float(x.sum()) == 3.0 * 1024 * 256 and x.data_ptr() == a.base()
+    y = a.tensor((16,), torch.int64)
+    assert y.data_ptr() >= a.base() + 1024 * 256 * 4 and a.used() >= 1024 * 256 * 4 + 128
+    del x, y
+    if t.num_devices > 1:
+        assert t.fully_connected() and t.distance(0, 1) == 1
