@@ -49,6 +49,14 @@ int b200_attn_prefill(const void* q, long long ld_q, const void* k, long long ld
                       void* out, const int* cu_seqlens, int B, int total_tokens, int max_len, int hq, int hkv,
                       float scale, int* status, cudaStream_t stream);
 
+// ---- collectives over peer-mapped memory ---------------------------------------------------------------
+// peer_data / peer_flags: host arrays [world] of device pointers (rank r's heap base / flag block as mapped here).
+// algo: 0 one-shot peer loads, 1 one-shot NVLS, 2 two-shot NVLS (in place), 3 chain to rank 0, 4 butterfly.
+int b200_peer_allreduce(void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
+                        size_t in_off, size_t scratch_off, void* out, const void* residual, size_t n, int dtype,
+                        int algo, void* epoch_words, int* status, int limit_ms, int trailing_barrier, int max_ctas,
+                        cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

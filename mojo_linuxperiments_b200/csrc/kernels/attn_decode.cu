@@ -5,7 +5,8 @@
 // tokens with an online softmax.  With more than one split the CTAs write un-normalised partials and the last
 // CTA to arrive for a (sequence, kv_head) merges them in the same launch.
 //
-//   phase 1  thread <-> token: dot products of the K row (16 x 16-byte loads) with the G query vectors in smem
+//   phase 1  four lanes <-> token (each lane 32 dims = 4 x 16-byte loads, so a warp reads eight whole 256-byte
+//            K rows per instruction group), partial dots with the G query vectors in smem, 2-step shuffle reduce
 //   phase 2  warp <-> head: running max / sum, probabilities back to smem
 //   phase 3  thread <-> (8 output dims, token slice): P.V with 16-byte V loads, then a cross-slice reduction
 #include "ptx.cuh"
@@ -41,7 +42,7 @@ __device__ __forceinline__ void bf16x8_to_float(const uint4& raw, float (&f)[8])
 
 template <int G>
 __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeParams p) {
-  __shared__ __align__(16) float q_s[G][AD_D];
+  __shared__ __align__(16) float q_s[G][4 * 36];     // four 32-dim parts, padded so the parts hit different banks
   __shared__ float sc[G][AD_TC];
   __shared__ float alpha_s[G], m_s[G], l_s[G];
   __shared__ __align__(16) float out_s[G][AD_D];
@@ -60,7 +61,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodePar
 
   for (int i = tid; i < G * AD_D; i += AD_THREADS) {
     const int g = i / AD_D, d = i % AD_D;
-    q_s[g][d] = __bfloat162float(p.q[(static_cast<size_t>(b) * p.hq + kvh * G + g) * AD_D + d]) * p.scale_log2;
+    q_s[g][(d >> 5) * 36 + (d & 31)] = __bfloat162float(p.q[(static_cast<size_t>(b) * p.hq + kvh * G + g) * AD_D + d]) * p.scale_log2;
     out_s[g][d] = 0.f;
   }
   if (tid < G) { m_s[tid] = -INFINITY; l_s[tid] = 0.f; }
@@ -76,30 +77,43 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodePar
   for (int c0 = t0; c0 < t1; c0 += AD_TC) {
     const int n = min(AD_TC, t1 - c0);
     // ---- phase 1: scores ----
-    for (int tt = tid; tt < n; tt += AD_THREADS) {
-      const int tok = c0 + tt;
-      const int page = pt[tok / p.page_size];
-      const uint4* kp = reinterpret_cast<const uint4*>(p.cache + static_cast<size_t>(page) * page_stride + k_head_off +
-                                                        static_cast<size_t>(tok % p.page_size) * AD_D);
-      uint4 kr[16];
+    {
+      const int part = lane & 3, tsub = lane >> 2;
+#pragma unroll 2
+      for (int tb = warp * 8; tb < n; tb += (AD_THREADS / 32) * 8) {
+        const int tt = tb + tsub;
+        const int tok = c0 + min(tt, n - 1);
+        const int page = pt[tok / p.page_size];
+        const uint4* kp = reinterpret_cast<const uint4*>(p.cache + static_cast<size_t>(page) * page_stride + k_head_off +
+                                                          static_cast<size_t>(tok % p.page_size) * AD_D + part * 32);
+        uint4 kr[4];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) kr[i] = __ldg(kp + i);
-      float dot[G];
+        for (int i = 0; i < 4; ++i) kr[i] = __ldg(kp + i);
+        float dot[G];
 #pragma unroll
-      for (int g = 0; g < G; ++g) dot[g] = 0.f;
+        for (int g = 0; g < G; ++g) dot[g] = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float kf[8];
-        bf16x8_to_float(kr[i], kf);
+        for (int i = 0; i < 4; ++i) {
+          float kf[8];
+          bf16x8_to_float(kr[i], kf);
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][part * 36 + 8 * i]);
+            const float4 qb = *reinterpret_cast<const float4*>(&q_s[g][part * 36 + 8 * i + 4]);
+            dot[g] += kf[0] * qa.x + kf[1] * qa.y + kf[2] * qa.z + kf[3] * qa.w + kf[4] * qb.x + kf[5] * qb.y + kf[6] * qb.z + kf[7] * qb.w;
+          }
+        }
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-          const float4 qa = *reinterpret_cast<const float4*>(&q_s[g][8 * i]);
-          const float4 qb = *reinterpret_cast<const float4*>(&q_s[g][8 * i + 4]);
-          dot[g] += kf[0] * qa.x + kf[1] * qa.y + kf[2] * qa.z + kf[3] * qa.w + kf[4] * qb.x + kf[5] * qb.y + kf[6] * qb.z + kf[7] * qb.w;
+          dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], 1);
+          dot[g] += __shfl_xor_sync(0xffffffffu, dot[g], 2);
+        }
+        if (tt < n) {
+#pragma unroll
+          for (int g = 0; g < G; ++g)
+            if ((g & 3) == part) sc[g][tt] = dot[g];
         }
       }
-#pragma unroll
-      for (int g = 0; g < G; ++g) sc[g][tt] = dot[g];
     }
     __syncthreads();
     // ---- phase 2: online softmax bookkeeping, one warp per head ----

@@ -1,0 +1,108 @@
+"""Symmetric (peer-mapped) HBM for one rank group: the GPU form of the reference's shared arena that every worker
+can address (test_linux_threading.mojo:426-435) and of its futex gates (threading/linux_threading.mojo:174-198).
+
+Every rank allocates the same number of bytes; after the rendezvous each rank holds a pointer to every other rank's
+block (NVLink / NVSwitch peer mapping) and, where the fabric supports it, one NVLS multicast pointer that addresses all
+copies at once.  The first ``FLAG_BYTES`` of the block are the rank's flag words (epochs written by peers); the rest is
+a bump-allocated data heap whose offsets are identical on every rank.  Allocation and mapping come from
+``torch.distributed._symmetric_memory``; the kernels that read and write peers are this package's own.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+FLAG_BYTES = 4096
+AR_ONE_SHOT_P2P, AR_ONE_SHOT_NVLS, AR_TWO_SHOT_NVLS, AR_CHAIN, AR_BUTTERFLY = 0, 1, 2, 3, 4
+_DTYPES = {torch.bfloat16: 0, torch.float32: 1, torch.float64: 2}
+
+
+class SymmetricHeap:
+    def __init__(self, nbytes: int, group=None, device=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.nbytes = (nbytes + 4095) // 4096 * 4096
+        total = FLAG_BYTES + self.nbytes
+        self.block = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+        self.block.zero_()
+        self.handle = symm_mem.rendezvous(self.block, group=self.group.group_name)
+        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.flag_ptrs = ptrs
+        self.data_ptrs = [p + FLAG_BYTES for p in ptrs]
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        self.mc_data_ptr = mc + FLAG_BYTES if mc else 0
+        self._c_data = (ctypes.c_void_p * self.world)(*self.data_ptrs)
+        self._c_flags = (ctypes.c_void_p * self.world)(*self.flag_ptrs)
+        self.offset = 0
+        # device-resident epoch words of this rank: [epoch, exit counter, stage counters...]
+        self.epoch_words = torch.zeros(8, dtype=torch.int32, device=self.device)
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+
+    @property
+    def has_multicast(self) -> bool:
+        return self.mc_data_ptr != 0
+
+    # -- bump allocation: same offsets on every rank as long as every rank makes the same calls ----------------
+    def alloc(self, nbytes: int, align: int = 256) -> int:
+        start = (self.offset + align - 1) // align * align
+        if start + nbytes > self.nbytes:
+            raise MemoryError(f"symmetric heap exhausted ({start + nbytes} > {self.nbytes})")
+        self.offset = start + nbytes
+        return start
+
+    def mark(self) -> int: return self.offset
+    def reset_to(self, w: int):
+        if w <= self.offset:
+            self.offset = w
+    def remaining(self) -> int: return self.nbytes - self.offset
+    def used(self) -> int: return self.offset
+
+    def tensor(self, offset: int, shape, dtype) -> torch.Tensor:
+        """Local view of this rank's bytes at ``offset``."""
+        n = 1
+        for s in shape:
+            n *= s
+        nb = n * torch.empty((), dtype=dtype).element_size()
+        return self.block[FLAG_BYTES + offset: FLAG_BYTES + offset + nb].view(dtype).view(*shape)
+
+    def alloc_tensor(self, shape, dtype, align: int = 256):
+        n = 1
+        for s in shape:
+            n *= s
+        off = self.alloc(n * torch.empty((), dtype=dtype).element_size(), align)
+        return off, self.tensor(off, shape, dtype)
+
+    def check_status(self):
+        code = int(self.status[0].item())
+        if code != 0:
+            self.status.zero_()
+            raise RuntimeError(f"peer kernel status {code} (5 = a flag from a peer never arrived)")
+
+    # -- collectives --------------------------------------------------------------------------------------------
+    def all_reduce(self, offset: int, n: int, dtype: torch.dtype, out: torch.Tensor | None, *, algo: int | None = None,
+                   residual: torch.Tensor | None = None, scratch_offset: int = 0, trailing_barrier: bool = True,
+                   limit_ms: int = 2000, max_ctas: int = 64) -> torch.Tensor | None:
+        """Sum the ``n`` elements every rank holds at ``offset`` of its heap.  The result goes to ``out`` (any local
+        tensor), or stays in place in every heap for the two-shot NVLS algorithm when ``out`` is None."""
+        if algo is None:
+            nbytes = n * torch.empty((), dtype=dtype).element_size()
+            if self.has_multicast and dtype != torch.float64 and nbytes % 16 == 0:
+                algo = AR_ONE_SHOT_NVLS if nbytes <= (512 << 10) else AR_TWO_SHOT_NVLS
+            else:
+                algo = AR_ONE_SHOT_P2P
+        rc = _lib.lib().b200_peer_allreduce(
+            self._c_data, self._c_flags, self.mc_data_ptr or None, self.world, self.rank, offset, scratch_offset,
+            out.data_ptr() if out is not None else None, _lib.ptr(residual), n, _DTYPES[dtype], algo,
+            self.epoch_words.data_ptr(), self.status.data_ptr(), limit_ms, 1 if trailing_barrier else 0, max_ctas,
+            _lib.stream())
+        _lib.check(rc, "peer_allreduce")
+        return out

@@ -1,0 +1,29 @@
+"""Multi-GPU tests: each case launches one process per GPU with torch.distributed.run over NCCL on 127.0.0.1."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+NGPU = torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def _run(script, nproc, *args, timeout=600, env=None):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29500 + nproc), os.path.join(HERE, script), *args]
+    e = dict(os.environ)
+    e.update(env or {})
+    return subprocess.run(cmd, capture_output=True, text=True, timeout=timeout, env=e)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("nproc", [2, 4, 8])
+def test_peer_allreduce(nproc):
+    if NGPU < nproc:
+        pytest.skip(f"needs {nproc} GPUs, found {NGPU}")
+    p = _run("mp_peer_allreduce.py", nproc)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert "FAILURES 0" in p.stdout
