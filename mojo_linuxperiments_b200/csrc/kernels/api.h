@@ -26,6 +26,13 @@ int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void* wq, const
                           const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
                           int num_sms, int force_splits, cudaStream_t stream);
 
+// Same, fused with the tensor-parallel all-reduce over peer memory (one launch).  -20: grid not co-resident, use
+// b200_w8a8_gemm_decode followed by b200_peer_allreduce instead.
+int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
+                             const void* residual, int M, int N, int K, int ldy, int* status, int num_sms,
+                             void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
+                             size_t part_off0, size_t part_off1, void* words, int limit_ms, cudaStream_t stream);
+
 // ---- activation prologue ---------------------------------------------------------------------------
 int b200_act_quant(const void* x, long long ldx, void* residual, long long ldr, const void* gamma, float eps,
                    void* q, long long ldq, float* scale, void* xn_out, long long ldn, int M, int K, int mode,
@@ -56,6 +63,10 @@ int b200_peer_allreduce(void* const* peer_data, void* const* peer_flags, void* m
                         size_t in_off, size_t scratch_off, void* out, const void* residual, size_t n, int dtype,
                         int algo, void* epoch_words, int* status, int limit_ms, int trailing_barrier, int max_ctas,
                         cudaStream_t stream);
+
+int b200_peer_argmax(void* const* peer_data, void* const* peer_flags, int world, int rank, size_t val_off,
+                     size_t idx_off, int ncand, int rows, long long* out_idx, void* epoch_words, int* status,
+                     int limit_ms, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -246,9 +246,79 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ArParams p) {
   finish_launch(p, 1);
 }
 
+// Greedy sampling across vocabulary shards: every rank has written its candidates (fp32 value, int64 index) for each
+// row into its heap ([ncand][rows] values at val_off, indices at idx_off); after the barrier every rank reads all
+// world*ncand candidates and keeps the largest value (lowest index on ties), so all ranks agree without a broadcast.
+struct ArgmaxParams {
+  PeerTable t;
+  size_t val_off, idx_off;
+  int ncand, rows;
+  long long* out_idx;
+  uint32_t* epoch;
+  int* status;
+  unsigned long long limit_ns;
+};
+
+__global__ void __launch_bounds__(128) peer_argmax_kernel(const ArgmaxParams p) {
+  const PeerTable& t = p.t;
+  const uint32_t e0 = *reinterpret_cast<volatile uint32_t*>(p.epoch) + 1;
+  __shared__ int ok_s;
+  if (threadIdx.x == 0) ok_s = 1;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    signal_all(t, 0, e0, threadIdx.x);
+    if (!wait_all(t, 0, e0, threadIdx.x, p.status, p.limit_ns)) ok_s = 0;
+  }
+  __syncthreads();
+  if (ok_s) {
+    for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
+      float best = -INFINITY;
+      long long bi = 0x7fffffffffffffffll;
+      for (int w = 0; w < t.world; ++w) {
+        const volatile float* v = reinterpret_cast<const volatile float*>(t.data[w] + p.val_off);
+        const volatile long long* ix = reinterpret_cast<const volatile long long*>(t.data[w] + p.idx_off);
+        for (int c = 0; c < p.ncand; ++c) {
+          const float val = v[static_cast<size_t>(c) * p.rows + r];
+          const long long idx = ix[static_cast<size_t>(c) * p.rows + r];
+          if (val > best || (val == best && idx < bi)) { best = val; bi = idx; }
+        }
+      }
+      p.out_idx[r] = bi;
+    }
+  }
+  // nobody rewrites its candidates before everyone has read them
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    signal_all(t, 3, e0, threadIdx.x);
+    wait_all(t, 3, e0, threadIdx.x, p.status, p.limit_ns);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) { __threadfence(); p.epoch[0] = e0; }
+}
+
 }  // namespace b200
 
 using namespace b200;
+
+extern "C" int b200_peer_argmax(void* const* peer_data, void* const* peer_flags, int world, int rank, size_t val_off,
+                                size_t idx_off, int ncand, int rows, long long* out_idx, void* epoch_words, int* status,
+                                int limit_ms, cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS || rows <= 0 || ncand <= 0) return -1;
+  ArgmaxParams p;
+  for (int r = 0; r < MAX_RANKS; ++r) {
+    p.t.data[r] = r < world ? static_cast<uint8_t*>(peer_data[r]) : nullptr;
+    p.t.flags[r] = r < world ? static_cast<uint32_t*>(peer_flags[r]) : nullptr;
+  }
+  p.t.mc = nullptr; p.t.world = world; p.t.rank = rank;
+  p.val_off = val_off; p.idx_off = idx_off; p.ncand = ncand; p.rows = rows; p.out_idx = out_idx;
+  p.epoch = static_cast<uint32_t*>(epoch_words); p.status = status;
+  p.limit_ns = static_cast<unsigned long long>(limit_ms > 0 ? limit_ms : 2000) * 1000000ull;
+  peer_argmax_kernel<<<1, 128, 0, stream>>>(p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
+}
 
 // peer_data / peer_flags: host arrays [world] of device pointers (each rank's heap base and flag block as mapped here)
 extern "C" int b200_peer_allreduce(void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,

@@ -12,11 +12,26 @@
 //     the S row slices of the tile, its int32 partial to the CTA that owns the slice (st.shared::cluster), the
 //     cluster synchronises, and each CTA reduces and writes 128/S channels.  No global scratch, no atomics.
 // All mbarrier waits are bounded; a CTA that gives up still reaches both cluster barriers, so peers never hang.
+//
+// Fused all-reduce (row-parallel layers under tensor parallelism): with an `ArTail` the CTAs write their bf16 tile of
+// the local partial product into this rank's symmetric buffer instead of y, the last CTA of the grid to finish
+// signals every peer, and then *all* CTAs (the host only fuses when the whole grid is co-resident) wait for the
+// peers' signals and sum the eight partials - through the NVSwitch with multimem.ld_reduce when the heap has a
+// multicast mapping, with plain peer loads otherwise - straight into y.  GEMM, reduction and residual add are one
+// launch; the partial buffers alternate between two slots so a fast rank never overwrites what a slow one reads.
 #include "ptx.cuh"
 #include "api.h"
 #include "gemm_common.cuh"
+#include "peer.cuh"
 
 namespace b200 {
+
+struct ArTail {
+  PeerTable t;
+  size_t part_off[2];          // byte offsets of the two partial-product slots inside every heap ([M][N] bf16 each)
+  uint32_t* words;             // device words of this rank: [0] epoch, [1] finished CTAs, [2] exited CTAs
+  int enabled, use_nvls;
+};
 
 struct DecodeGemmParams {
   int M, N, K, kblocks, splits;
@@ -27,6 +42,7 @@ struct DecodeGemmParams {
   int ldy, out_fp32;
   int* status;
   unsigned long long limit_ns;
+  ArTail ar;
 };
 
 template <int BN, int STAGES>
@@ -71,6 +87,22 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+
+  // where a finished output element goes: y, or (fused all-reduce) this rank's slot of the symmetric partial buffer
+  const bool fuse_ar = p.ar.enabled != 0;
+  uint32_t ar_epoch = 0;
+  __nv_bfloat16* part = nullptr;
+  if (fuse_ar) {
+    ar_epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.words) + 1;       // bumped only after every CTA has read it
+    part = reinterpret_cast<__nv_bfloat16*>(p.ar.t.data[p.ar.t.rank] + p.ar.part_off[ar_epoch & 1]);
+  }
+  auto store_out = [&](int m, int n, float v) {
+    if (fuse_ar) { part[static_cast<size_t>(m) * p.N + n] = __float2bfloat16(v); return; }
+    const size_t o = static_cast<size_t>(m) * p.ldy + n;
+    if (p.residual) v += __bfloat162float(p.residual[o]);
+    if (p.out_fp32) reinterpret_cast<float*>(p.y)[o] = v;
+    else reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16(v);
+  };
 
   if (warp == 0) {
     if (lane == 0) {
@@ -139,17 +171,9 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         const int mc = m0 + c * CH;
         const int jm = min(CH, p.M - mc);
         if (!n_ok || jm <= 0) continue;
-        const size_t o0 = static_cast<size_t>(mc) * p.ldy + n;
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          if (j < jm) {
-            float v = static_cast<float>(static_cast<int32_t>(r[j])) * swn * __ldg(p.sx + mc + j);
-            const size_t o = o0 + static_cast<size_t>(j) * p.ldy;
-            if (p.residual) v += __bfloat162float(p.residual[o]);
-            if (p.out_fp32) reinterpret_cast<float*>(p.y)[o] = v;
-            else reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16(v);
-          }
-        }
+        for (int j = 0; j < CH; ++j)
+          if (j < jm) store_out(mc + j, n, static_cast<float>(static_cast<int32_t>(r[j])) * swn * __ldg(p.sx + mc + j));
       }
     }
   } else {
@@ -188,14 +212,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         int32_t acc = 0;
         for (int s = 0; s < S; ++s) acc += ex[(s * BN + j) * rows_per + row_in];
         const int n = n_tile * TILE_N + rank * rows_per + row_in;
-        if (n < p.N) {
-          const int m = m0 + j;
-          float v = static_cast<float>(acc) * __ldg(p.sw + n) * __ldg(p.sx + m);
-          const size_t o = static_cast<size_t>(m) * p.ldy + n;
-          if (p.residual) v += __bfloat162float(p.residual[o]);
-          if (p.out_fp32) reinterpret_cast<float*>(p.y)[o] = v;
-          else reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16(v);
-        }
+        if (n < p.N) store_out(m0 + j, n, static_cast<float>(acc) * __ldg(p.sw + n) * __ldg(p.sx + m0 + j));
       }
     }
   }
@@ -203,6 +220,53 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
+
+  if (fuse_ar) {
+    // ---- all-reduce tail: every CTA of the (co-resident) grid takes part ----
+    const PeerTable& t = p.ar.t;
+    const unsigned total_ctas = gridDim.x * gridDim.y * gridDim.z;
+    const unsigned cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    __shared__ int ar_ok;
+    __threadfence_system();                       // this CTA's part of the partial product is visible to peers
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      ar_ok = 1;
+      const unsigned old = atomicAdd(p.ar.words + 1, 1u);
+      if (old == total_ctas - 1) {                // the whole local partial is complete: tell everyone
+        p.ar.words[1] = 0;
+        __threadfence_system();
+        for (int r = 0; r < t.world; ++r) st_release_sys(flag_ptr(t, r, 0, t.rank), ar_epoch);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) { if (!wait_all(t, 0, ar_epoch, threadIdx.x, p.status, limit)) ar_ok = 0; }
+    __syncthreads();
+    if (ar_ok) {
+      const size_t nvec = static_cast<size_t>(p.M) * p.N / 8;            // N is a multiple of 8
+      const size_t v0 = nvec * cta / total_ctas, v1 = nvec * (cta + 1) / total_ctas;
+      const size_t off = p.ar.part_off[ar_epoch & 1];
+      const int vec_per_row = p.N / 8;
+      for (size_t i = v0 + threadIdx.x; i < v1; i += GEMM_THREADS) {
+        float acc[8];
+        if (p.ar.use_nvls) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+          add_bf16x8_to_f32(multimem_ld_reduce_bf16x8(t.mc + off + i * 16), acc);
+        } else {
+          reduce_p2p_bf16x8(t, off + i * 16, acc);
+        }
+        const size_t m = i / vec_per_row, nv = i - m * vec_per_row;
+        const size_t o = m * p.ldy + nv * 8;
+        if (p.residual) add_bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.residual + o), acc);
+        *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.y) + o) = pack_f32x8_to_bf16(acc);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned old = atomicAdd(p.ar.words + 2, 1u);
+      if (old == total_ctas - 1) { p.ar.words[2] = 0; __threadfence(); p.ar.words[0] = ar_epoch; }
+    }
+  }
 }
 
 template <int BN, int STAGES>
@@ -241,9 +305,9 @@ int decode_pick_splits(int tiles, int kblocks, int num_sms) {
 
 using namespace b200;
 
-extern "C" int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
-                                     const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
-                                     int num_sms, int force_splits, cudaStream_t stream) {
+static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
+                            const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
+                            int num_sms, int force_splits, const ArTail* ar, cudaStream_t stream) {
   if (M <= 0 || M > SWAP_MAX_M || N <= 0 || K <= 0 || (K % 16) != 0) return -1;
   if ((reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15)) return -2;
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
@@ -256,6 +320,12 @@ extern "C" int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void
   p.splits = s;
   p.sx = sx; p.sw = sw; p.y = y; p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.ldy = ldy; p.out_fp32 = out_fp32; p.status = status; p.limit_ns = 2000000000ull;
+  if (ar) p.ar = *ar; else { p.ar = ArTail{}; p.ar.enabled = 0; }
+  if (ar) {
+    // every CTA waits for the peers, so the whole grid has to be resident at once (two CTAs per SM by construction)
+    if (static_cast<long long>(s) * n_tiles * m_tiles > 2ll * num_sms) return -20;
+    if ((N % 8) || (ldy % 8) || out_fp32) return -2;
+  }
   CUtensorMap tw, tx;
   if (make_tmap_2d_u8(&tw, wq, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(K), TILE_N)) return -11;
   if (make_tmap_2d_u8(&tx, xq, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), bn)) return -12;
@@ -265,4 +335,32 @@ extern "C" int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void
     case 32: return launch_decode<32, 5>(tw, tx, p, grid, stream);
     default: return launch_decode<64, 4>(tw, tx, p, grid, stream);
   }
+}
+
+extern "C" int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
+                                     const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
+                                     int num_sms, int force_splits, cudaStream_t stream) {
+  return decode_gemm_impl(xq, sx, wq, sw, y, residual, M, N, K, ldy, out_fp32, status, num_sms, force_splits, nullptr, stream);
+}
+
+// Row-parallel linear fused with its all-reduce: y[m,n] = sum over ranks of (xq_r . wq_r^T * sx_r * sw) (+ residual).
+// part_off0/1: byte offsets (same on every rank) of two [M][N] bf16 slots in the symmetric heap; words: >= 4 zeroed
+// device uint32 of this rank.  Returns -20 when the grid would not be co-resident (use the unfused path then).
+extern "C" int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
+                                        const void* residual, int M, int N, int K, int ldy, int* status, int num_sms,
+                                        void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
+                                        size_t part_off0, size_t part_off1, void* words, int limit_ms, cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS) return -1;
+  ArTail ar;
+  for (int r = 0; r < MAX_RANKS; ++r) {
+    ar.t.data[r] = r < world ? static_cast<uint8_t*>(peer_data[r]) : nullptr;
+    ar.t.flags[r] = r < world ? static_cast<uint32_t*>(peer_flags[r]) : nullptr;
+  }
+  ar.t.mc = static_cast<uint8_t*>(mc_base); ar.t.world = world; ar.t.rank = rank;
+  ar.part_off[0] = part_off0; ar.part_off[1] = part_off1;
+  ar.words = static_cast<uint32_t*>(words);
+  ar.enabled = 1; ar.use_nvls = mc_base != nullptr;
+  if ((part_off0 % 16) || (part_off1 % 16)) return -2;
+  (void)limit_ms;
+  return decode_gemm_impl(xq, sx, wq, sw, y, residual, M, N, K, ldy, 0, status, num_sms, 0, &ar, stream);
 }

@@ -24,7 +24,12 @@ class Engine:
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         if weights is None:
             weights = Wt.random_shard(cfg, self.rt.tp, self.comm.rank, self.device, seed)
-        self.model = Decoder(cfg, self.rt, weights, self.comm, self.device)
+        self.tp_ctx = None
+        if self.comm.world > 1 and self.rt.fused_collectives:
+            from ..parallel.tp import TPContext
+            self.tp_ctx = TPContext(cfg.d_model, max_tokens=self.rt.max_prefill_tokens, group=self.comm.group,
+                                    device=self.device, wait_limit_ms=self.rt.wait_limit_ms)
+        self.model = Decoder(cfg, self.rt, weights, self.comm, self.device, tp_ctx=self.tp_ctx)
         self.kv: KVState | None = None
         self.batch = 0
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
@@ -117,4 +122,6 @@ class Engine:
             out[t].copy_(nxt, non_blocking=True)
         torch.cuda.synchronize()
         default_workspace(self.device).check_status()
+        if self.tp_ctx is not None:
+            self.tp_ctx.heap.check_status()
         return out.t().contiguous()

@@ -87,6 +87,7 @@ class RuntimeConfig:
     page_size: int = 16
     max_batch: int = 32
     max_seq_len: int = 2048
+    max_prefill_tokens: int = 32768     # most tokens one prefill call may carry (sizes the symmetric TP buffers)
     fused_collectives: bool = True      # in-kernel peer-memory collectives; False = NCCL between kernels
     wait_limit_ms: int = 2000           # bound of every device-side wait
     debug: bool = False

@@ -51,9 +51,11 @@ class KVState:
 
 
 class Decoder:
-    def __init__(self, cfg: ModelConfig, rt: RuntimeConfig, weights: dict, comm: Comm | None = None, device=None):
+    def __init__(self, cfg: ModelConfig, rt: RuntimeConfig, weights: dict, comm: Comm | None = None, device=None,
+                 tp_ctx=None):
         self.cfg, self.rt, self.w = cfg, rt, weights
         self.comm = comm or Comm.single()
+        self.tp_ctx = tp_ctx          # parallel.tp.TPContext: peer-memory collectives (None: NCCL between kernels)
         self.device = device or weights["embed"].device
         self.hq = cfg.n_heads // rt.tp
         self.hkv = kv_heads_per_rank(cfg, rt.tp)
@@ -73,6 +75,8 @@ class Decoder:
 
     def _row_parallel(self, xq, sx, lw):
         """Row-parallel linear: local partial product, then the cross-rank sum."""
+        if self.tp_ctx is not None:
+            return self.tp_ctx.row_parallel(xq, sx, lw)
         y = L.w8a8_gemm(xq, sx, lw.qweight, lw.scale)
         return self.comm.all_reduce(y)
 
@@ -138,7 +142,9 @@ class Decoder:
         lm = self.w["lm_head"]
         logits = L.w8a8_gemm(xq, sx, lm.qweight, lm.scale)
         val, idx = A.argmax_rows(logits, index_offset=self.w["vocab_offset"])
+        self.last_logits = logits
+        if self.tp_ctx is not None:
+            return self.tp_ctx.argmax(val, idx)
         if self.comm.world > 1:
             val, idx = self.comm.all_gather(val), self.comm.all_gather(idx)
-        self.last_logits = logits
         return A.argmax_merge(val, idx)

@@ -1,0 +1,83 @@
+"""Tensor-parallel execution context of one rank: the symmetric heap plus the fused compute+collective ops.
+
+Row-parallel linears (o_proj, down) produce partial sums that have to be added across ranks:
+  * up to 64 tokens (decode) the GEMM kernel itself performs the all-reduce over peer memory (one launch);
+  * above that the GEMM writes its bf16 partial straight into the symmetric heap and this package's NVLS two-shot
+    all-reduce kernel finishes it (two launches, no NCCL, no extra copy).
+Greedy sampling merges per-rank arg-max candidates through the heap as well.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import _lib
+from ..ops import attention as A
+from ..ops import linear as L
+from ..ops.workspace import default_workspace
+from .symm import SymmetricHeap, AR_ONE_SHOT_NVLS, AR_ONE_SHOT_P2P, AR_TWO_SHOT_NVLS
+
+FUSED_MAX_M = 64
+
+
+class TPContext:
+    def __init__(self, d_model: int, max_tokens: int, group=None, device=None, use_nvls: bool | None = None,
+                 wait_limit_ms: int = 2000):
+        self.d_model = d_model
+        self.max_tokens = max_tokens
+        small = FUSED_MAX_M * d_model * 2
+        big = max(FUSED_MAX_M, max_tokens) * d_model * 2
+        self.heap = SymmetricHeap(2 * small + big + (1 << 20), group=group, device=device)
+        self.world, self.rank = self.heap.world, self.heap.rank
+        # Fused launches alternate between two small slots by the parity of the device-side epoch, so a rank that runs
+        # ahead never overwrites a partial a slower rank is still summing.  The unfused path owns a third slot and its
+        # all-reduce ends with a barrier, so that slot is free again as soon as the call returns.
+        self.part_off = [self.heap.alloc(small), self.heap.alloc(small)]
+        self.big_off = self.heap.alloc(big)
+        self.cand_val_off = self.heap.alloc(64 * 1024)
+        self.cand_idx_off = self.heap.alloc(128 * 1024)
+        self.use_nvls = self.heap.has_multicast if use_nvls is None else (use_nvls and self.heap.has_multicast)
+        self.limit_ms = wait_limit_ms
+
+    def row_parallel(self, xq: torch.Tensor, sx: torch.Tensor, lw, residual: torch.Tensor | None = None) -> torch.Tensor:
+        """Sum over ranks of this rank's K-shard product; returns the full [M, N] bf16 result on every rank."""
+        M, K = xq.shape
+        N = lw.qweight.shape[0]
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=xq.device)
+        h = self.heap
+        ws = default_workspace(xq.device)
+        if M <= FUSED_MAX_M:
+            rc = _lib.lib().b200_w8a8_gemm_decode_ar(
+                xq.data_ptr(), sx.data_ptr(), lw.qweight.data_ptr(), lw.scale.data_ptr(), out.data_ptr(),
+                _lib.ptr(residual), M, N, K, out.stride(0), ws.status.data_ptr(), _lib.num_sms(xq.device.index),
+                h._c_data, h._c_flags, (h.mc_data_ptr or None) if self.use_nvls else None, h.world, h.rank,
+                self.part_off[0], self.part_off[1], h.epoch_words.data_ptr(), self.limit_ms, _lib.stream())
+            if rc != -20:
+                _lib.check(rc, "w8a8_gemm_decode_ar")
+                return out
+        # unfused: partial into the heap, then the peer all-reduce kernel
+        assert M <= max(self.max_tokens, FUSED_MAX_M), f"{M} tokens exceed the symmetric buffer sized for {self.max_tokens}"
+        off = self.big_off
+        part = h.tensor(off, (M, N), torch.bfloat16)
+        L.w8a8_gemm(xq, sx, lw.qweight, lw.scale, out=part)
+        nbytes = M * N * 2
+        if self.use_nvls and nbytes % 16 == 0:
+            algo = AR_ONE_SHOT_NVLS if nbytes <= (512 << 10) else AR_TWO_SHOT_NVLS
+        else:
+            algo = AR_ONE_SHOT_P2P
+        h.all_reduce(off, M * N, torch.bfloat16, out, algo=algo, residual=residual, trailing_barrier=True,
+                     limit_ms=self.limit_ms, max_ctas=128)
+        return out
+
+    def argmax(self, cand_val: torch.Tensor, cand_idx: torch.Tensor) -> torch.Tensor:
+        """cand_* [ncand, rows] of this rank's vocabulary shard -> global greedy token per row (same on all ranks)."""
+        ncand, rows = cand_val.shape
+        assert ncand * rows * 4 <= 64 * 1024
+        h = self.heap
+        h.tensor(self.cand_val_off, (ncand, rows), torch.float32).copy_(cand_val)
+        h.tensor(self.cand_idx_off, (ncand, rows), torch.int64).copy_(cand_idx)
+        out = torch.empty(rows, dtype=torch.int64, device=cand_val.device)
+        rc = _lib.lib().b200_peer_argmax(h._c_data, h._c_flags, h.world, h.rank, self.cand_val_off, self.cand_idx_off,
+                                         ncand, rows, out.data_ptr(), h.epoch_words.data_ptr(), h.status.data_ptr(),
+                                         self.limit_ms, _lib.stream())
+        _lib.check(rc, "peer_argmax")
+        return out

@@ -27,3 +27,16 @@ def test_peer_allreduce(nproc):
     p = _run("mp_peer_allreduce.py", nproc)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     assert "FAILURES 0" in p.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("nproc", [2, 8])
+@pytest.mark.parametrize("mode", ["fused", "nccl"])
+def test_tensor_parallel_tiny_model(nproc, mode):
+    """TP engine (prefill + graph decode) agrees with the oracle; fused = in-kernel peer-memory all-reduce."""
+    if NGPU < nproc:
+        pytest.skip(f"needs {nproc} GPUs, found {NGPU}")
+    p = _run("mp_tp_model.py", nproc, mode)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert "FAILURES 0" in p.stdout
