@@ -56,6 +56,10 @@ int b200_attn_prefill(const void* q, long long ld_q, const void* k, long long ld
                       void* out, const int* cu_seqlens, int B, int total_tokens, int max_len, int hq, int hkv,
                       float scale, int* status, cudaStream_t stream);
 
+// ---- config-1 workload: counter-RNG fill + sum ------------------------------------------------------------
+int b200_fill_uniform_reduce(float* out, unsigned long long begin, unsigned long long end, unsigned long long seed,
+                             double* partials, int max_ctas, unsigned* counter, double* result, cudaStream_t stream);
+
 // ---- collectives over peer-mapped memory ---------------------------------------------------------------
 // peer_data / peer_flags: host arrays [world] of device pointers (rank r's heap base / flag block as mapped here).
 // algo: 0 one-shot peer loads, 1 one-shot NVLS, 2 two-shot NVLS (in place), 3 chain to rank 0, 4 butterfly.

@@ -1,0 +1,73 @@
+// Config-1 workload on the GPU: fill a float32 buffer with uniform[-1,1) values of a counter-based generator keyed on
+// the *global* element index (any split of the index space over GPUs produces the same elements), and reduce them.
+//   fill_uniform_reduce   grid-stride fill (16-byte stores) with per-thread double accumulation, warp shuffle and
+//                         shared-memory block reduction, one double per CTA; the last CTA to finish adds the CTA
+//                         partials in index order (deterministic) into the result
+// The op is bound by the 4 bytes per element written to HBM; Philox costs ~25 integer ops per element.
+#include "ptx.cuh"
+#include "api.h"
+#include "fabric/philox.h"
+
+namespace b200 {
+
+__global__ void __launch_bounds__(256) fill_uniform_reduce_kernel(float* __restrict__ out, unsigned long long begin,
+                                                                  unsigned long long end, unsigned long long seed,
+                                                                  double* __restrict__ partials, unsigned* __restrict__ counter,
+                                                                  double* __restrict__ result) {
+  __shared__ double red[8];
+  __shared__ int last;
+  // work in whole Philox blocks of four elements; `begin` is a multiple of 4 (checked on the host)
+  const unsigned long long nblk = (end - begin + 3) / 4;
+  double s = 0.0;
+  for (unsigned long long b = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; b < nblk;
+       b += static_cast<unsigned long long>(gridDim.x) * blockDim.x) {
+    const unsigned long long i = begin + 4 * b;
+    const Philox4 r = philox4x32_10(i >> 2, seed);
+    float4 v;
+    v.x = u32_to_uniform_pm1(r.v[0]); v.y = u32_to_uniform_pm1(r.v[1]);
+    v.z = u32_to_uniform_pm1(r.v[2]); v.w = u32_to_uniform_pm1(r.v[3]);
+    if (i + 4 <= end) {
+      *reinterpret_cast<float4*>(out + (i - begin)) = v;
+      s += static_cast<double>(v.x) + static_cast<double>(v.y) + static_cast<double>(v.z) + static_cast<double>(v.w);
+    } else {
+      const float e[4] = {v.x, v.y, v.z, v.w};
+      for (int k = 0; k < 4 && i + k < end; ++k) { out[i - begin + k] = e[k]; s += e[k]; }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double t = 0.0;
+    for (int w = 0; w < 8; ++w) t += red[w];
+    partials[blockIdx.x] = t;
+    __threadfence();
+    const unsigned old = atomicAdd(counter, 1u);
+    last = (old == gridDim.x - 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (last && threadIdx.x == 0) {
+    __threadfence();
+    double t = 0.0;
+    for (unsigned c = 0; c < gridDim.x; ++c) t += *reinterpret_cast<volatile double*>(partials + c);
+    *result = t;
+    *counter = 0;
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// out: float[end - begin]; partials: double[max_ctas]; counter: zeroed unsigned; result: double
+extern "C" int b200_fill_uniform_reduce(float* out, unsigned long long begin, unsigned long long end, unsigned long long seed,
+                                        double* partials, int max_ctas, unsigned* counter, double* result, cudaStream_t stream) {
+  if (end <= begin || (begin & 3) || (reinterpret_cast<uintptr_t>(out) & 15) || max_ctas < 1) return -1;
+  const unsigned long long nblk = (end - begin + 3) / 4;
+  long long ctas = static_cast<long long>((nblk + 255) / 256);
+  if (ctas > max_ctas) ctas = max_ctas;
+  fill_uniform_reduce_kernel<<<static_cast<int>(ctas), 256, 0, stream>>>(out, begin, end, seed, partials, counter, result);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
+}
