@@ -164,6 +164,9 @@ def run(args):
     prompts = torch.randint(0, cfg.vocab, (B, S), generator=g).pin_memory()
     eng.start_batch(B, S + W + K + 8)
     eng.prefill(prompts)
+    torch.cuda.synchronize()
+    if hasattr(eng, "check_status"):
+        eng.check_status()          # stop here, not after minutes of timeouts, if a device-side wait ran out
     for _ in range(W):
         eng.decode_step()
     torch.cuda.synchronize()

@@ -33,6 +33,23 @@ int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const void* wq, co
                              void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
                              size_t part_off0, size_t part_off1, void* words, int limit_ms, cudaStream_t stream);
 
+// Mixture-of-experts grouped forms (device-side offsets / tile tables, no host sync).
+int b200_w8a8_gemm_decode_grouped(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
+                                  int max_tokens, int x_rows, int N, int K, int ldy, int groups,
+                                  const int* grp_offsets, const int* grp_counts, int* status, int num_sms,
+                                  cudaStream_t stream);
+int b200_w8a8_gemm_grouped(const void* xq, const float* sx, const void* wq, const float* sw, void* y, int x_rows,
+                           int N, int K, int ldy, int groups, const void* tiles, const int* num_tiles,
+                           int max_tiles, int* status, int num_sms, cudaStream_t stream);
+int b200_router_topk(const float* logits, long long ld, int M, int E, int k, int renorm, int* ids, float* wts,
+                     cudaStream_t stream);
+int b200_moe_align(const int* ids, int M, int k, int e0, int n_local, int* counts, int* offsets, int* slot_token,
+                   int* inv, void* tiles, int* meta, cudaStream_t stream);
+int b200_moe_gather(const void* xq, const float* sx, int d, const int* slot_token, const int* meta, int max_slots,
+                    void* xq_perm, float* sx_perm, cudaStream_t stream);
+int b200_moe_combine(const void* y, long long ldy, const int* inv, const float* wts, int M, int k, int d, void* out,
+                     long long ldo, cudaStream_t stream);
+
 // ---- activation prologue ---------------------------------------------------------------------------
 int b200_act_quant(const void* x, long long ldx, void* residual, long long ldr, const void* gamma, float eps,
                    void* q, long long ldq, float* scale, void* xn_out, long long ldn, int M, int K, int mode,

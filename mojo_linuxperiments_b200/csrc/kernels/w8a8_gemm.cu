@@ -47,6 +47,10 @@ struct GemmParams {
   uint32_t* counters;           // [num_tiles], zero between launches (mode 1); the finishing CTA re-zeroes
   int* status;
   unsigned long long limit_ns;
+  // grouped (mixture-of-experts) form, normal orientation only: the token tiles come from a device table of
+  // {expert, first row, rows, -}; *grp_meta_tiles of them are valid; expert e uses weight rows [e*N, (e+1)*N)
+  const int4* grp_tiles;
+  const int* grp_num_tiles;
 };
 
 struct Seg { int tile, kb0, kb1; };
@@ -55,7 +59,8 @@ struct WorkIter {
   int mode, next_tile, stride, num_tiles, kblocks;
   long long u, u_end;
   __device__ WorkIter(const GemmParams& p) {
-    mode = p.mode; num_tiles = p.num_tiles; kblocks = p.kblocks;
+    mode = p.mode; kblocks = p.kblocks;
+    num_tiles = p.grp_tiles ? (*p.grp_num_tiles) * p.n_tiles : p.num_tiles;
     next_tile = blockIdx.x; stride = gridDim.x;
     u = p.total_units * blockIdx.x / gridDim.x;
     u_end = p.total_units * (blockIdx.x + 1) / gridDim.x;
@@ -85,6 +90,7 @@ __device__ __forceinline__ int cta_of_unit(long long u, long long total_units, i
 }
 
 __device__ __forceinline__ void tile_coords(const GemmParams& p, int tile, int& m_tile, int& n_tile) {
+  if (p.grp_tiles) { m_tile = tile / p.n_tiles; n_tile = tile - m_tile * p.n_tiles; return; }
   const int per_group = GROUP_M * p.n_tiles;
   const int g = tile / per_group;
   const int first_m = g * GROUP_M;
@@ -155,6 +161,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       while (ok && it.next(sg)) {
         int m_tile, n_tile;
         tile_coords(p, sg.tile, m_tile, n_tile);
+        int row0 = m_tile * TILE_N, wrow0 = 0;
+        if (p.grp_tiles) { const int4 tt = p.grp_tiles[m_tile]; row0 = tt.y; wrow0 = tt.x * p.N; }
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY, limit)) { ok = false; break; }
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
@@ -163,8 +171,8 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tma_load_2d_hint(a_dst, &tmap_a, full_bar(stage), kb * BLOCK_K, n_tile * TILE_N, pol_w);
             tma_load_2d(a_dst + A_BYTES, &tmap_b, full_bar(stage), kb * BLOCK_K, m_tile * BN);
           } else {
-            tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * BLOCK_K, m_tile * TILE_N);
-            tma_load_2d_hint(a_dst + A_BYTES, &tmap_b, full_bar(stage), kb * BLOCK_K, n_tile * BN, pol_w);
+            tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * BLOCK_K, row0);
+            tma_load_2d_hint(a_dst + A_BYTES, &tmap_b, full_bar(stage), kb * BLOCK_K, wrow0 + n_tile * BN, pol_w);
           }
           ++issued;
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -232,8 +240,15 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
       if constexpr (!SWAP) {
         // ---- normal orientation: this thread owns token row m and walks BN output channels ----
-        const int m = m_tile * TILE_N + q * 32 + lane;
-        const bool m_ok = m < p.M;
+        int m = m_tile * TILE_N + q * 32 + lane;
+        bool m_ok = m < p.M;
+        const float* swg = p.sw;
+        if (p.grp_tiles) {
+          const int4 tt = p.grp_tiles[m_tile];
+          m = tt.y + q * 32 + lane;
+          m_ok = (q * 32 + lane) < tt.z;
+          swg = p.sw + static_cast<size_t>(tt.x) * p.N;
+        }
         const float sxm = m_ok ? __ldg(p.sx + m) : 0.f;
         const int n0 = n_tile * BN;
         const size_t row_off = static_cast<size_t>(m_ok ? m : 0) * p.ldy;
@@ -246,7 +261,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           tmem_ld_wait();
           const int nc = n0 + c * 32;
           if (vec_ok && nc + 32 <= p.N) {
-            const float4* swp = reinterpret_cast<const float4*>(p.sw + nc);
+            const float4* swp = reinterpret_cast<const float4*>(swg + nc);
             uint4 packed[4];
             uint32_t* pk = reinterpret_cast<uint32_t*>(packed);
 #pragma unroll
@@ -283,7 +298,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             for (int j = 0; j < 32; ++j) {
               const int n = nc + j;
               if (n >= p.N) break;
-              float v = static_cast<float>(static_cast<int32_t>(r[j])) * sxm * __ldg(p.sw + n);
+              float v = static_cast<float>(static_cast<int32_t>(r[j])) * sxm * __ldg(swg + n);
               const size_t o = row_off + n;
               if (p.residual) v += __bfloat162float(p.residual[o]);
               if (p.out_fp32) reinterpret_cast<float*>(p.y)[o] = v;
@@ -508,6 +523,8 @@ extern "C" int b200_w8a8_gemm(const void* xq, const float* sx, const void* wq, c
   p.counters = static_cast<uint32_t*>(counters);
   p.status = status;
   p.limit_ns = 2000000000ull;
+  p.grp_tiles = nullptr;
+  p.grp_num_tiles = nullptr;
 
   int mode = 0;
   int sk_grid = 1;
@@ -543,4 +560,30 @@ extern "C" int b200_w8a8_gemm(const void* xq, const float* sx, const void* wq, c
     case 128: return launch_gemm<128, 6, false>(tx, tw, p, grid, stream);
     default: return launch_gemm<256, 4, false>(tx, tw, p, grid, stream);
   }
+}
+
+// Grouped form for mixture-of-experts prefill: xq [x_rows][K] holds the tokens in slot order, `tiles` (device, int4
+// {expert, first row, rows <= 128, -}) lists the 128-row token tiles and *num_tiles how many are valid (at most
+// max_tiles); expert e multiplies by wq[e*N : (e+1)*N].  N must be a multiple of 256.  Nothing syncs the host.
+extern "C" int b200_w8a8_gemm_grouped(const void* xq, const float* sx, const void* wq, const float* sw, void* y, int x_rows,
+                                      int N, int K, int ldy, int groups, const void* tiles, const int* num_tiles,
+                                      int max_tiles, int* status, int num_sms, cudaStream_t stream) {
+  if (x_rows <= 0 || N <= 0 || K <= 0 || (K % 16) || (N % 256) || groups <= 0 || max_tiles <= 0) return -1;
+  GemmParams p;
+  p.M = x_rows; p.N = N; p.K = K;
+  p.m_tiles = max_tiles;
+  p.n_tiles = N / 256;
+  p.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
+  p.num_tiles = max_tiles * p.n_tiles;
+  p.total_units = static_cast<long long>(p.num_tiles) * p.kblocks;
+  p.mode = 0;
+  p.sx = sx; p.sw = sw; p.y = y; p.residual = nullptr; p.ldy = ldy; p.out_fp32 = 0;
+  p.ws = nullptr; p.max_segs = 1; p.counters = nullptr; p.status = status; p.limit_ns = 2000000000ull;
+  p.grp_tiles = static_cast<const int4*>(tiles);
+  p.grp_num_tiles = num_tiles;
+  CUtensorMap tw, tx;
+  if (make_tmap_2d_u8(&tw, wq, static_cast<uint64_t>(K), static_cast<uint64_t>(groups) * N, static_cast<uint64_t>(K), 256)) return -11;
+  if (make_tmap_2d_u8(&tx, xq, static_cast<uint64_t>(K), static_cast<uint64_t>(x_rows), static_cast<uint64_t>(K), TILE_N)) return -12;
+  const int grid = p.num_tiles < num_sms ? p.num_tiles : num_sms;
+  return launch_gemm<256, 4, false>(tx, tw, p, grid, stream);
 }

@@ -30,7 +30,7 @@ struct ArTail {
   PeerTable t;
   size_t part_off[2];          // byte offsets of the two partial-product slots inside every heap ([M][N] bf16 each)
   uint32_t* words;             // device words of this rank: [0] epoch, [1] finished CTAs, [2] exited CTAs
-  int enabled, use_nvls;
+  int enabled, use_nvls, limit_ms;
 };
 
 struct DecodeGemmParams {
@@ -43,6 +43,10 @@ struct DecodeGemmParams {
   int* status;
   unsigned long long limit_ns;
   ArTail ar;
+  // grouped (mixture-of-experts) form: blockIdx.z = local expert; its tokens are rows [grp_offsets[e], +grp_counts[e])
+  // of xq / y, its weights are rows [e*N, (e+1)*N) of wq / sw
+  const int* grp_offsets;
+  const int* grp_counts;
 };
 
 template <int BN, int STAGES>
@@ -71,7 +75,14 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 
   const int S = p.splits;
   const int rank = static_cast<int>(cluster_ctarank());          // == blockIdx.x: position along K
-  const int n_tile = blockIdx.y, m_tile = blockIdx.z;
+  const int n_tile = blockIdx.y;
+  int m0 = blockIdx.z * BN, rows_valid = min(BN, p.M - m0), w_base = 0;
+  if (p.grp_counts) {
+    rows_valid = min(BN, p.grp_counts[blockIdx.z]);
+    if (rows_valid <= 0) return;            // same for every CTA of the cluster (they share blockIdx.z)
+    m0 = p.grp_offsets[blockIdx.z];
+    w_base = blockIdx.z * p.N;
+  }
   const int kb0 = static_cast<int>(static_cast<long long>(p.kblocks) * rank / S);
   const int kb1 = static_cast<int>(static_cast<long long>(p.kblocks) * (rank + 1) / S);
   const uint64_t limit = p.limit_ns;
@@ -115,8 +126,8 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY, limit)) { ok = false; break; }
         mbar_expect_tx(full_bar(stage), STAGE_BYTES);
         const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
-        tma_load_2d_hint(a_dst, &tmap_w, full_bar(stage), kb * BLOCK_K, n_tile * TILE_N, pol_w);
-        tma_load_2d(a_dst + A_BYTES, &tmap_x, full_bar(stage), kb * BLOCK_K, m_tile * BN);
+        tma_load_2d_hint(a_dst, &tmap_w, full_bar(stage), kb * BLOCK_K, w_base + n_tile * TILE_N, pol_w);
+        tma_load_2d(a_dst + A_BYTES, &tmap_x, full_bar(stage), kb * BLOCK_K, m0);
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
       if (!ok) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 2000000ull) { } }
@@ -148,8 +159,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   const int q = warp & 3;
   const int et = threadIdx.x - 64;
   const int row = q * 32 + lane;                          // channel inside the tile == TMEM lane
-  const int m0 = m_tile * BN;
-  const int jmax = min(BN, p.M - m0);
+  const int jmax = rows_valid;
   constexpr int CH = (BN >= 32) ? 32 : 16;
   bool acc_ok = false;
   if (epi) {
@@ -161,7 +171,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     if (epi && acc_ok) {
       const int n = n_tile * TILE_N + row;
       const bool n_ok = n < p.N;
-      const float swn = n_ok ? __ldg(p.sw + n) : 0.f;
+      const float swn = n_ok ? __ldg(p.sw + w_base + n) : 0.f;
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / CH; ++c) {
@@ -169,7 +179,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if constexpr (CH == 32) tmem_ld_x32(t_addr + c * CH, r); else tmem_ld_x16(t_addr + c * CH, r);
         tmem_ld_wait();
         const int mc = m0 + c * CH;
-        const int jm = min(CH, p.M - mc);
+        const int jm = min(CH, jmax - c * CH);
         if (!n_ok || jm <= 0) continue;
 #pragma unroll
         for (int j = 0; j < CH; ++j)
@@ -212,7 +222,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         int32_t acc = 0;
         for (int s = 0; s < S; ++s) acc += ex[(s * BN + j) * rows_per + row_in];
         const int n = n_tile * TILE_N + rank * rows_per + row_in;
-        if (n < p.N) store_out(m0 + j, n, static_cast<float>(acc) * __ldg(p.sw + n) * __ldg(p.sx + m0 + j));
+        if (n < p.N) store_out(m0 + j, n, static_cast<float>(acc) * __ldg(p.sw + w_base + n) * __ldg(p.sx + m0 + j));
       }
     }
   }
@@ -294,6 +304,36 @@ static int launch_decode(const CUtensorMap& tw, const CUtensorMap& tx, const Dec
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
 
+// How many clusters of `s` CTAs of this kernel the GPU can hold at once (cached per instantiation and cluster size).
+template <int BN, int STAGES>
+static int max_resident_clusters(int s) {
+  static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+  if (s < 1 || s > 8) return 0;
+  if (cache[s] > 0) return cache[s];
+  constexpr int SMEM = STAGES * (TILE_N * BLOCK_K + BN * BLOCK_K) + 1024 + 256;
+  cudaFuncSetAttribute(w8a8_gemm_decode_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(s, 64, 1);
+  cfg.blockDim = dim3(GEMM_THREADS);
+  cfg.dynamicSmemBytes = SMEM;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = s; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, w8a8_gemm_decode_kernel<BN, STAGES>, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+  cache[s] = n > 0 ? n : -1;
+  return cache[s];
+}
+
+static int resident_clusters(int bn, int s) {
+  switch (bn) {
+    case 16: return max_resident_clusters<16, 6>(s);
+    case 32: return max_resident_clusters<32, 5>(s);
+    default: return max_resident_clusters<64, 4>(s);
+  }
+}
+
 // splits along K: aim for about two CTAs per SM, powers of two up to 8, at least one k-block per CTA
 int decode_pick_splits(int tiles, int kblocks, int num_sms) {
   int s = 1;
@@ -305,30 +345,43 @@ int decode_pick_splits(int tiles, int kblocks, int num_sms) {
 
 using namespace b200;
 
+// groups > 0: M is the bound on tokens per expert and on the rows of xq, wq holds groups*N rows
 static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
                             const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
-                            int num_sms, int force_splits, const ArTail* ar, cudaStream_t stream) {
+                            int num_sms, int force_splits, const ArTail* ar, cudaStream_t stream,
+                            int groups = 0, const int* grp_offsets = nullptr, const int* grp_counts = nullptr,
+                            int x_rows = 0) {
   if (M <= 0 || M > SWAP_MAX_M || N <= 0 || K <= 0 || (K % 16) != 0) return -1;
+  if (groups > 0 && ((N % TILE_N) || !grp_offsets || !grp_counts || ar)) return -1;
   if ((reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15)) return -2;
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
   DecodeGemmParams p;
   p.M = M; p.N = N; p.K = K;
   p.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
-  const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = (M + bn - 1) / bn;
+  const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = groups > 0 ? groups : (M + bn - 1) / bn;
   int s = force_splits > 0 ? force_splits : decode_pick_splits(n_tiles * m_tiles, p.kblocks, num_sms);
   if (s != 1 && s != 2 && s != 4 && s != 8) return -1;
   p.splits = s;
   p.sx = sx; p.sw = sw; p.y = y; p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.ldy = ldy; p.out_fp32 = out_fp32; p.status = status; p.limit_ns = 2000000000ull;
   if (ar) p.ar = *ar; else { p.ar = ArTail{}; p.ar.enabled = 0; }
+  p.grp_offsets = groups > 0 ? grp_offsets : nullptr;
+  p.grp_counts = groups > 0 ? grp_counts : nullptr;
+  const int w_rows = groups > 0 ? groups * N : N;
+  const int xr = groups > 0 ? x_rows : M;
   if (ar) {
-    // every CTA waits for the peers, so the whole grid has to be resident at once (two CTAs per SM by construction)
-    if (static_cast<long long>(s) * n_tiles * m_tiles > 2ll * num_sms) return -20;
+    // Every CTA waits for the peers, so the whole grid has to be resident at once: ask the occupancy calculator how
+    // many clusters of this size fit (clusters are placed per GPC, so this is less than SMs x CTAs-per-SM / size)
+    // and narrow the split until the grid fits, keeping a margin of one cluster.
     if ((N % 8) || (ldy % 8) || out_fp32) return -2;
+    while (s >= 1 && n_tiles * m_tiles + 1 > resident_clusters(bn, s)) s >>= 1;
+    if (s < 1) return -20;
+    p.splits = s;
+    p.limit_ns = static_cast<unsigned long long>(ar->limit_ms > 0 ? ar->limit_ms : 2000) * 1000000ull;
   }
   CUtensorMap tw, tx;
-  if (make_tmap_2d_u8(&tw, wq, static_cast<uint64_t>(K), static_cast<uint64_t>(N), static_cast<uint64_t>(K), TILE_N)) return -11;
-  if (make_tmap_2d_u8(&tx, xq, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), bn)) return -12;
+  if (make_tmap_2d_u8(&tw, wq, static_cast<uint64_t>(K), static_cast<uint64_t>(w_rows), static_cast<uint64_t>(K), TILE_N)) return -11;
+  if (make_tmap_2d_u8(&tx, xq, static_cast<uint64_t>(K), static_cast<uint64_t>(xr), static_cast<uint64_t>(K), bn)) return -12;
   dim3 grid(s, n_tiles, m_tiles);
   switch (bn) {
     case 16: return launch_decode<16, 6>(tw, tx, p, grid, stream);
@@ -341,6 +394,17 @@ extern "C" int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void
                                      const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
                                      int num_sms, int force_splits, cudaStream_t stream) {
   return decode_gemm_impl(xq, sx, wq, sw, y, residual, M, N, K, ldy, out_fp32, status, num_sms, force_splits, nullptr, stream);
+}
+
+// Grouped form for mixture-of-experts decode: `groups` local experts, expert e multiplies rows
+// [grp_offsets[e], +grp_counts[e]) of xq (x_rows rows in total, at most max_tokens per expert, max_tokens <= 64) by
+// wq[e*N : (e+1)*N] and writes the same rows of y.  Offsets and counts are device arrays: nothing syncs the host.
+extern "C" int b200_w8a8_gemm_decode_grouped(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
+                                             int max_tokens, int x_rows, int N, int K, int ldy, int groups,
+                                             const int* grp_offsets, const int* grp_counts, int* status, int num_sms,
+                                             cudaStream_t stream) {
+  return decode_gemm_impl(xq, sx, wq, sw, y, nullptr, max_tokens, N, K, ldy, 0, status, num_sms, 0, nullptr, stream, groups,
+                          grp_offsets, grp_counts, x_rows);
 }
 
 // Row-parallel linear fused with its all-reduce: y[m,n] = sum over ranks of (xq_r . wq_r^T * sx_r * sw) (+ residual).
@@ -359,8 +423,7 @@ extern "C" int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const v
   ar.t.mc = static_cast<uint8_t*>(mc_base); ar.t.world = world; ar.t.rank = rank;
   ar.part_off[0] = part_off0; ar.part_off[1] = part_off1;
   ar.words = static_cast<uint32_t*>(words);
-  ar.enabled = 1; ar.use_nvls = mc_base != nullptr;
+  ar.enabled = 1; ar.use_nvls = mc_base != nullptr; ar.limit_ms = limit_ms;
   if ((part_off0 % 16) || (part_off1 % 16)) return -2;
-  (void)limit_ms;
   return decode_gemm_impl(xq, sx, wq, sw, y, residual, M, N, K, ldy, 0, status, num_sms, 0, &ar, stream);
 }

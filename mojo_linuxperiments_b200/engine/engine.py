@@ -89,6 +89,7 @@ class Engine:
                 self._decode_body()
             torch.cuda.current_stream().wait_stream(self._stream)
             torch.cuda.synchronize()
+            self.check_status()         # a bounded wait that ran out surfaces here, before anything is captured or timed
             self.tokens.copy_(saved[0]); self.positions.copy_(saved[1]); self.kv.seq_lens.copy_(saved[2])
             g = torch.cuda.CUDAGraph()
             from ..ops import _lib
@@ -100,6 +101,12 @@ class Engine:
             self._graphs[self.batch] = g
         g.replay()
         return self.tokens
+
+    def check_status(self) -> None:
+        """Synchronising read of the kernels' status words; raises if a device-side wait timed out."""
+        default_workspace(self.device).check_status()
+        if self.tp_ctx is not None:
+            self.tp_ctx.heap.check_status()
 
     def step_from_host(self, ids_in: torch.Tensor, ids_out: torch.Tensor) -> torch.Tensor:
         """Serving-loop form of a decode step: token ids arrive in pinned host memory (the previous step's sample,
@@ -121,7 +128,5 @@ class Engine:
             nxt = self.decode_step(use_graph)
             out[t].copy_(nxt, non_blocking=True)
         torch.cuda.synchronize()
-        default_workspace(self.device).check_status()
-        if self.tp_ctx is not None:
-            self.tp_ctx.heap.check_status()
+        self.check_status()
         return out.t().contiguous()

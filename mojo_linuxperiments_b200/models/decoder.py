@@ -64,7 +64,7 @@ class Decoder:
         self.moe = None
         if cfg.is_moe:
             from .moe import MoEBlock
-            self.moe = MoEBlock(cfg, rt, self.comm, self.device)
+            self.moe = MoEBlock(cfg, rt, self.comm, self.device, tp_ctx=tp_ctx)
         self._decode_scratch: dict[int, A.DecodeAttnScratch] = {}
 
     # -- building blocks ------------------------------------------------------------------------------------

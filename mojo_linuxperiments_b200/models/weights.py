@@ -71,7 +71,7 @@ def init_master(cfg: ModelConfig, seed: int = 0) -> dict:
             m[p + "k_norm"] = gamma(hd)
         m[p + "mlp_norm"] = gamma(d)
         if cfg.is_moe:
-            m[p + "router"] = torch.randn((cfg.n_experts, d), generator=g) * 0.02
+            m[p + "router"] = torch.randn((cfg.n_experts, d), generator=g) * 0.02 * 8
             for e in range(cfg.n_experts):
                 m[p + f"experts.{e}.gate"] = w(cfg.moe_ffn, d)
                 m[p + f"experts.{e}.up"] = w(cfg.moe_ffn, d)
@@ -83,7 +83,7 @@ def init_master(cfg: ModelConfig, seed: int = 0) -> dict:
     return m
 
 
-LINEAR_SUFFIXES = ("wq", "wk", "wv", "wo", "gate", "up", "down", "lm_head")
+LINEAR_SUFFIXES = ("wq", "wk", "wv", "wo", "gate", "up", "down", "lm_head", "router")
 
 
 def quantize_master(master: dict) -> dict:
@@ -158,7 +158,7 @@ def shard_from_checkpoint(cfg: ModelConfig, ck: dict, tp: int, rank: int, device
             L["q_norm"] = ck[p + "q_norm"].to(device)
             L["k_norm"] = ck[p + "k_norm"].to(device)
         if cfg.is_moe:
-            L["router"] = ck[p + "router"].to(device)
+            L["router"] = _lin(ck, p + "router").to(device)        # replicated: every rank routes identically
             epr = cfg.n_experts // tp
             gu, dn = [], []
             for e in range(rank * epr, (rank + 1) * epr):
@@ -202,7 +202,7 @@ def random_shard(cfg: ModelConfig, tp: int, rank: int, device, seed: int = 0) ->
             L["q_norm"], L["k_norm"] = gamma(hd), gamma(hd)
         if cfg.is_moe:
             epr = cfg.n_experts // tp
-            L["router"] = (torch.randn((cfg.n_experts, d), device=device, generator=shared) * 0.02).to(torch.bfloat16)
+            L["router"] = random_linear(cfg.n_experts, d, device, shared, std=0.02)
             gu = random_linear(epr * 2 * cfg.moe_ffn, d, device, gen, std=d ** -0.5)
             dn = random_linear(epr * d, cfg.moe_ffn, device, gen, std=cfg.moe_ffn ** -0.5)
             L["experts_gate_up"] = LinearW(gu.qweight.view(epr, 2 * cfg.moe_ffn, d), gu.scale.view(epr, 2 * cfg.moe_ffn))

@@ -52,6 +52,12 @@ class _Sig:
     b200_peer_argmax = (I, [P, P, I, I, c_size_t, c_size_t, I, I, P, P, P, I, P])
     b200_w8a8_gemm_decode_ar = (I, [P, P, P, P, P, P, I, I, I, I, P, I, P, P, P, I, I, c_size_t, c_size_t, P, I, P])
     b200_fill_uniform_reduce = (I, [P, c_uint64, c_uint64, c_uint64, P, I, P, P, P])
+    b200_w8a8_gemm_decode_grouped = (I, [P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, P])
+    b200_w8a8_gemm_grouped = (I, [P, P, P, P, P, I, I, I, I, I, P, P, I, P, I, P])
+    b200_router_topk = (I, [P, LL, I, I, I, I, P, P, P])
+    b200_moe_align = (I, [P, I, I, I, I, P, P, P, P, P, P, P])
+    b200_moe_gather = (I, [P, P, I, P, P, I, P, P, P])
+    b200_moe_combine = (I, [P, LL, P, P, I, I, I, P, LL, P])
     b200_act_quant = (I, [P, LL, P, LL, P, F, P, LL, P, P, LL, I, I, I, P])
     b200_rope_kv_write = (I, [P, LL, P, P, P, P, P, P, F, P, P, P, P, P, I, I, I, I, I, P])
     b200_embed_gather = (I, [P, P, P, I, I, I, P])

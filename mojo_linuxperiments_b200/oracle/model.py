@@ -34,15 +34,15 @@ def _linear_from_f32(x_f32, lw_q, lw_s, tp=1):
 
 
 def moe_block(cfg, ck, p, xn_f32):
-    """xn fp32 [T, d] (normalised) -> bf16 [T, d].  Router on the bf16-rounded normalised activations."""
+    """xn fp32 [T, d] (normalised) -> bf16 [T, d].  The router is a W8A8 linear like every other projection (it
+    consumes the same rotated int8 activations); its logits stay in fp32."""
     T = xn_f32.shape[0]
-    xb = xn_f32.to(BF)
-    logits = xb.float() @ ck[p + "router"].float().t()
+    xq, sx = Q.quantize_rows(Q.rotate(xn_f32))
+    logits = Q.w8a8_linear(xq, sx, ck[p + "router.qweight"], ck[p + "router.scale"])
     probs = logits.softmax(-1)
     topv, topi = probs.topk(cfg.top_k, dim=-1)
     if cfg.norm_topk_prob:
         topv = topv / topv.sum(-1, keepdim=True)
-    xq, sx = Q.quantize_rows(Q.rotate(xn_f32))
     out = torch.zeros((T, cfg.d_model), dtype=torch.float32, device=xn_f32.device)
     for e in range(cfg.n_experts):
         sel = (topi == e)
@@ -55,7 +55,7 @@ def moe_block(cfg, ck, p, xn_f32):
         hmid = Q.swiglu(gu)
         y = _linear_from_f32(hmid, ck[p + f"experts.{e}.down.qweight"], ck[p + f"experts.{e}.down.scale"]).float()
         wgt = (topv * sel)[rows].sum(-1, keepdim=True)
-        out[rows] += wgt * y
+        out[rows] += wgt * y          # y is bf16-rounded (the expert GEMM's output), the weighted sum is fp32
     return out.to(BF)
 
 

@@ -68,6 +68,21 @@ class TPContext:
                      limit_ms=self.limit_ms, max_ctas=128)
         return out
 
+    def reduce_partial(self, produce, M: int, N: int) -> torch.Tensor:
+        """``produce(out)`` writes this rank's bf16 [M, N] partial into the symmetric heap; returns the sum over ranks."""
+        h = self.heap
+        part = h.tensor(self.big_off, (M, N), torch.bfloat16)
+        produce(part)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=part.device)
+        nbytes = M * N * 2
+        if self.use_nvls and nbytes % 16 == 0:
+            algo = AR_ONE_SHOT_NVLS if nbytes <= (512 << 10) else AR_TWO_SHOT_NVLS
+        else:
+            algo = AR_ONE_SHOT_P2P
+        h.all_reduce(self.big_off, M * N, torch.bfloat16, out, algo=algo, trailing_barrier=True, limit_ms=self.limit_ms,
+                     max_ctas=128)
+        return out
+
     def argmax(self, cand_val: torch.Tensor, cand_idx: torch.Tensor) -> torch.Tensor:
         """cand_* [ncand, rows] of this rank's vocabulary shard -> global greedy token per row (same on all ranks)."""
         ncand, rows = cand_val.shape
