@@ -254,8 +254,12 @@ def run(args):
     if rank == 0:
         print(json.dumps(result), flush=True)
     if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+        # Leave without tearing down NCCL / symmetric-memory state: destroying a communicator whose collectives sit in
+        # live CUDA graphs has been seen to block for minutes.  Every rank has passed the last barrier and flushed.
+        barrier(world)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 def main():

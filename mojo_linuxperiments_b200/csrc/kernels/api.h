@@ -69,6 +69,9 @@ size_t b200_attn_decode_scratch_floats(int B, int hq, int splits);
 int b200_attn_decode(const void* q, const void* cache, const int* page_table, const int* seq_lens, void* out,
                      float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size, int max_pages,
                      int splits, float scale, cudaStream_t stream);
+int b200_attn_decode_tma(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
+                         void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
+                         int max_pages, int splits, float scale, int* status, cudaStream_t stream);
 int b200_attn_prefill(const void* q, long long ld_q, const void* k, long long ld_k, const void* v, long long ld_v,
                       void* out, const int* cu_seqlens, int B, int total_tokens, int max_len, int hq, int hkv,
                       float scale, int* status, cudaStream_t stream);

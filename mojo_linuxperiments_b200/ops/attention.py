@@ -83,14 +83,28 @@ def pick_decode_splits(B: int, hkv: int, max_len: int, num_sms: int = 148) -> in
 
 def attn_decode(q: torch.Tensor, cache: PagedKVCache, page_table: torch.Tensor, seq_lens: torch.Tensor, *,
                 scratch: DecodeAttnScratch | None = None, splits: int = 1, scale: float | None = None,
-                out: torch.Tensor | None = None) -> torch.Tensor:
-    """q [B, hq, 128] against the first seq_lens[b] cached tokens of sequence b."""
+                out: torch.Tensor | None = None, impl: str = "auto") -> torch.Tensor:
+    """q [B, hq, 128] against the first seq_lens[b] cached tokens of sequence b.
+
+    impl "tma" (page size 16, group size 1/2/4/8): TMA-fed ring, warp-private online softmax; "simple": the general
+    kernel; "auto" picks the first when it applies."""
     B, hq, d = q.shape
     assert d == HEAD_DIM and q.is_contiguous() and page_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
     if out is None:
         out = torch.empty_like(q)
     if splits > 1 and scratch is None:
         scratch = DecodeAttnScratch(B, hq, cache.kv_heads, splits, q.device)
+    G = hq // cache.kv_heads
+    if impl == "tma" or (impl == "auto" and cache.page_size == 16 and G in (1, 2, 4, 8)):
+        rc = _lib.lib().b200_attn_decode_tma(
+            q.data_ptr(), cache.data.data_ptr(), cache.num_pages, page_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),
+            scratch.buf.data_ptr() if scratch is not None else None,
+            scratch.counters.data_ptr() if scratch is not None else None,
+            B, hq, cache.kv_heads, cache.page_size, page_table.shape[1], splits,
+            float(scale if scale is not None else 1.0 / math.sqrt(d)), default_workspace(q.device).status.data_ptr(),
+            _lib.stream())
+        _lib.check(rc, "attn_decode_tma")
+        return out
     rc = _lib.lib().b200_attn_decode(
         q.data_ptr(), cache.data.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),
         scratch.buf.data_ptr() if scratch is not None else None,

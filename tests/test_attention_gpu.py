@@ -85,8 +85,11 @@ def test_attn_prefill_reads_strided_qkv():
 
 @pytest.mark.parametrize("hq,hkv", [(32, 8), (4, 1), (8, 1), (16, 1), (2, 2)])
 @pytest.mark.parametrize("splits", [1, 4])
-def test_attn_decode_paged(hq, hkv, splits):
+@pytest.mark.parametrize("impl", ["simple", "tma"])
+def test_attn_decode_paged(hq, hkv, splits, impl):
     from mojo_linuxperiments_b200.ops import attention as A
+    if impl == "tma" and hq // hkv == 16:
+        pytest.skip("the TMA form covers group sizes up to 8")
     ps = 16
     lens = [1, 17, 300, 1280, 64]
     B = len(lens)
@@ -98,8 +101,8 @@ def test_attn_decode_paged(hq, hkv, splits):
     cache.data.copy_(_rand(tuple(cache.data.shape), 5))
     q = _rand((B, hq, D), 6)
     seq_lens = torch.tensor(lens, dtype=torch.int32).cuda()
-    out = A.attn_decode(q, cache, page_table, seq_lens, splits=splits)
-    out2 = A.attn_decode(q, cache, page_table, seq_lens, splits=splits)     # scratch counters must self-reset
+    out = A.attn_decode(q, cache, page_table, seq_lens, splits=splits, impl=impl)
+    out2 = A.attn_decode(q, cache, page_table, seq_lens, splits=splits, impl=impl)     # scratch counters must self-reset
     torch.cuda.synchronize()
     for b, L in enumerate(lens):
         pages = page_table[b, : (L + ps - 1) // ps].long()
