@@ -7,6 +7,7 @@
 //   so the row is read from HBM exactly once and written once (int8 + one fp32 scale).
 #include "ptx.cuh"
 #include "api.h"
+#include "launch.cuh"
 
 namespace b200 {
 
@@ -67,6 +68,9 @@ act_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat
                  long long ldr, const __nv_bfloat16* __restrict__ gamma, float eps, int8_t* __restrict__ q,
                  long long ldq, float* __restrict__ scale, __nv_bfloat16* __restrict__ xn_out, long long ldn,
                  int K) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   __shared__ float red[AQ_WARPS];
   __shared__ float bcast;
   const int row = blockIdx.x;
@@ -183,10 +187,10 @@ static void launch_aq(int mode, const __nv_bfloat16* x, long long ldx, __nv_bflo
                       const __nv_bfloat16* gamma, float eps, int8_t* q, long long ldq, float* scale,
                       __nv_bfloat16* xn, long long ldn, int M, int K, cudaStream_t st) {
   switch (mode) {
-    case AQ_PLAIN: act_quant_kernel<MAXB, AQ_PLAIN><<<M, AQ_THREADS, 0, st>>>(x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
-    case AQ_NORM: act_quant_kernel<MAXB, AQ_NORM><<<M, AQ_THREADS, 0, st>>>(x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
-    case AQ_ADD_NORM: act_quant_kernel<MAXB, AQ_ADD_NORM><<<M, AQ_THREADS, 0, st>>>(x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
-    default: act_quant_kernel<MAXB, AQ_SWIGLU><<<M, AQ_THREADS, 0, st>>>(x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
+    case AQ_PLAIN: launch_ex(act_quant_kernel<MAXB, AQ_PLAIN>, dim3(M), dim3(AQ_THREADS), 0, st, 0, x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
+    case AQ_NORM: launch_ex(act_quant_kernel<MAXB, AQ_NORM>, dim3(M), dim3(AQ_THREADS), 0, st, 0, x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
+    case AQ_ADD_NORM: launch_ex(act_quant_kernel<MAXB, AQ_ADD_NORM>, dim3(M), dim3(AQ_THREADS), 0, st, 0, x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
+    default: launch_ex(act_quant_kernel<MAXB, AQ_SWIGLU>, dim3(M), dim3(AQ_THREADS), 0, st, 0, x, ldx, residual, ldr, gamma, eps, q, ldq, scale, xn, ldn, K); break;
   }
 }
 

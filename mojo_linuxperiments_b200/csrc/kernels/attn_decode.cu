@@ -11,6 +11,7 @@
 //   phase 3  thread <-> (8 output dims, token slice): P.V with 16-byte V loads, then a cross-slice reduction
 #include "ptx.cuh"
 #include "api.h"
+#include "launch.cuh"
 
 namespace b200 {
 
@@ -42,6 +43,9 @@ __device__ __forceinline__ void bf16x8_to_float(const uint4& raw, float (&f)[8])
 
 template <int G>
 __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodeParams p) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   __shared__ __align__(16) float q_s[G][4 * 36];     // four 32-dim parts, padded so the parts hit different banks
   __shared__ float sc[G][AD_TC];
   __shared__ float alpha_s[G], m_s[G], l_s[G];
@@ -249,11 +253,11 @@ extern "C" int b200_attn_decode(const void* q, const void* cache, const int* pag
   p.scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(hkv, B, splits);
   switch (G) {
-    case 1: attn_decode_kernel<1><<<grid, AD_THREADS, 0, stream>>>(p); break;
-    case 2: attn_decode_kernel<2><<<grid, AD_THREADS, 0, stream>>>(p); break;
-    case 4: attn_decode_kernel<4><<<grid, AD_THREADS, 0, stream>>>(p); break;
-    case 8: attn_decode_kernel<8><<<grid, AD_THREADS, 0, stream>>>(p); break;
-    case 16: attn_decode_kernel<16><<<grid, AD_THREADS, 0, stream>>>(p); break;
+    case 1: launch_ex(attn_decode_kernel<1>, dim3(grid), dim3(AD_THREADS), 0, stream, 0, p); break;
+    case 2: launch_ex(attn_decode_kernel<2>, dim3(grid), dim3(AD_THREADS), 0, stream, 0, p); break;
+    case 4: launch_ex(attn_decode_kernel<4>, dim3(grid), dim3(AD_THREADS), 0, stream, 0, p); break;
+    case 8: launch_ex(attn_decode_kernel<8>, dim3(grid), dim3(AD_THREADS), 0, stream, 0, p); break;
+    case 16: launch_ex(attn_decode_kernel<16>, dim3(grid), dim3(AD_THREADS), 0, stream, 0, p); break;
     default: return -1;
   }
   cudaError_t e = cudaGetLastError();

@@ -13,6 +13,7 @@
 // All mbarrier waits are bounded.
 #include "ptx.cuh"
 #include "api.h"
+#include "launch.cuh"
 #include <cuda.h>
 
 namespace b200 {
@@ -46,6 +47,9 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
 template <int G>
 __global__ void __launch_bounds__(ADT_THREADS) attn_decode_tma_kernel(const __grid_constant__ CUtensorMap tmap_kv,
                                                                       const DecodeTmaParams p) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // [stage][K 4K | V 4K] ... then q, merge buffers, barriers
@@ -237,7 +241,7 @@ static int launch_adt(const CUtensorMap& tm, const DecodeTmaParams& p, dim3 grid
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }
-  attn_decode_tma_kernel<G><<<grid, ADT_THREADS, SMEM, stream>>>(tm, p);
+  launch_ex(attn_decode_tma_kernel<G>, dim3(grid), dim3(ADT_THREADS), SMEM, stream, 0, tm, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }

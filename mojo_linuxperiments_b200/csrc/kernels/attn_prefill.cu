@@ -13,6 +13,7 @@
 // which the causal / length mask removes.  All waits are bounded.
 #include "ptx.cuh"
 #include "api.h"
+#include "launch.cuh"
 #include <cuda.h>
 
 namespace b200 {
@@ -36,6 +37,9 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t cols, uint64_
 __global__ void __launch_bounds__(AP_THREADS, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                     const __grid_constant__ CUtensorMap tmap_v, const PrefillParams p) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   // [Q 32K][K0 32K][K1 32K][V0 32K][V1 32K][P 32K][barriers]
@@ -308,7 +312,7 @@ extern "C" int b200_attn_prefill(const void* q, long long ld_q, const void* k, l
     configured = true;
   }
   dim3 grid((max_len + AP_BM - 1) / AP_BM, hq, B);
-  attn_prefill_kernel<<<grid, AP_THREADS, SMEM, stream>>>(tq, tk, tv, p);
+  launch_ex(attn_prefill_kernel, dim3(grid), dim3(AP_THREADS), SMEM, stream, 0, tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }

@@ -6,6 +6,7 @@
 // The op is bound by the 4 bytes per element written to HBM; Philox costs ~25 integer ops per element.
 #include "ptx.cuh"
 #include "api.h"
+#include "launch.cuh"
 #include "fabric/philox.h"
 
 namespace b200 {
@@ -14,6 +15,9 @@ __global__ void __launch_bounds__(256) fill_uniform_reduce_kernel(float* __restr
                                                                   unsigned long long end, unsigned long long seed,
                                                                   double* __restrict__ partials, unsigned* __restrict__ counter,
                                                                   double* __restrict__ result) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   __shared__ double red[8];
   __shared__ int last;
   // work in whole Philox blocks of four elements; `begin` is a multiple of 4 (checked on the host)
@@ -67,7 +71,7 @@ extern "C" int b200_fill_uniform_reduce(float* out, unsigned long long begin, un
   const unsigned long long nblk = (end - begin + 3) / 4;
   long long ctas = static_cast<long long>((nblk + 255) / 256);
   if (ctas > max_ctas) ctas = max_ctas;
-  fill_uniform_reduce_kernel<<<static_cast<int>(ctas), 256, 0, stream>>>(out, begin, end, seed, partials, counter, result);
+  launch_ex(fill_uniform_reduce_kernel, dim3(static_cast<int>(ctas)), dim3(256), 0, stream, 0, out, begin, end, seed, partials, counter, result);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }

@@ -10,6 +10,7 @@
 //   moe_combine    out[token] = sum_k weight[token,k] * expert_out[slot(token,k)]  (local experts only)
 #include "ptx.cuh"
 #include "api.h"
+#include "launch.cuh"
 
 namespace b200 {
 
@@ -17,6 +18,9 @@ namespace b200 {
 template <int EPL>
 __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restrict__ logits, long long ld, int M, int E, int k,
                                                           int renorm, int* __restrict__ ids, float* __restrict__ wts) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok = blockIdx.x * 4 + warp;
   if (tok >= M) return;
@@ -73,6 +77,9 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
                                                          int* __restrict__ counts, int* __restrict__ offsets,
                                                          int* __restrict__ slot_token, int* __restrict__ inv,
                                                          int4* __restrict__ tiles, int* __restrict__ meta) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   extern __shared__ int sm[];
   int* cnt = sm;                  // [n_local]
   int* off = sm + n_local;        // [n_local + 1]
@@ -117,6 +124,9 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
 __global__ void __launch_bounds__(128) moe_gather_kernel(const int8_t* __restrict__ xq, const float* __restrict__ sx, int d,
                                                          const int* __restrict__ slot_token, const int* __restrict__ meta,
                                                          int8_t* __restrict__ xq_perm, float* __restrict__ sx_perm) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   const int s = blockIdx.x;
   if (s >= meta[0]) return;
   const int t = slot_token[s];
@@ -130,6 +140,9 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const int8_t* __restric
 __global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ y, long long ldy,
                                                           const int* __restrict__ inv, const float* __restrict__ wts, int k,
                                                           int d, __nv_bfloat16* __restrict__ out, long long ldo) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   const int t = blockIdx.x;
   __shared__ int slot_s[32];
   __shared__ float w_s[32];
@@ -168,10 +181,10 @@ extern "C" int b200_router_topk(const float* logits, long long ld, int M, int E,
   if (M <= 0) return 0;
   if (E <= 0 || E > 256 || k <= 0 || k > 32 || k > E) return -1;
   const int grid = (M + 3) / 4;
-  if (E <= 32) router_topk_kernel<1><<<grid, 128, 0, stream>>>(logits, ld, M, E, k, renorm, ids, wts);
-  else if (E <= 64) router_topk_kernel<2><<<grid, 128, 0, stream>>>(logits, ld, M, E, k, renorm, ids, wts);
-  else if (E <= 128) router_topk_kernel<4><<<grid, 128, 0, stream>>>(logits, ld, M, E, k, renorm, ids, wts);
-  else router_topk_kernel<8><<<grid, 128, 0, stream>>>(logits, ld, M, E, k, renorm, ids, wts);
+  if (E <= 32) launch_ex(router_topk_kernel<1>, dim3(grid), dim3(128), 0, stream, 0, logits, ld, M, E, k, renorm, ids, wts);
+  else if (E <= 64) launch_ex(router_topk_kernel<2>, dim3(grid), dim3(128), 0, stream, 0, logits, ld, M, E, k, renorm, ids, wts);
+  else if (E <= 128) launch_ex(router_topk_kernel<4>, dim3(grid), dim3(128), 0, stream, 0, logits, ld, M, E, k, renorm, ids, wts);
+  else launch_ex(router_topk_kernel<8>, dim3(grid), dim3(128), 0, stream, 0, logits, ld, M, E, k, renorm, ids, wts);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
@@ -180,7 +193,7 @@ extern "C" int b200_moe_align(const int* ids, int M, int k, int e0, int n_local,
                               int* inv, void* tiles, int* meta, cudaStream_t stream) {
   if (M <= 0 || n_local <= 0 || n_local > 1024) return -1;
   const size_t smem = static_cast<size_t>(3 * n_local + 1) * sizeof(int);
-  moe_align_kernel<<<1, 1024, smem, stream>>>(ids, M, k, e0, n_local, counts, offsets, slot_token, inv,
+  launch_ex(moe_align_kernel, dim3(1), dim3(1024), smem, stream, 0, ids, M, k, e0, n_local, counts, offsets, slot_token, inv,
                                               static_cast<int4*>(tiles), meta);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
@@ -190,7 +203,7 @@ extern "C" int b200_moe_gather(const void* xq, const float* sx, int d, const int
                                void* xq_perm, float* sx_perm, cudaStream_t stream) {
   if (max_slots <= 0) return 0;
   if (d % 16) return -1;
-  moe_gather_kernel<<<max_slots, 128, 0, stream>>>(static_cast<const int8_t*>(xq), sx, d, slot_token, meta,
+  launch_ex(moe_gather_kernel, dim3(max_slots), dim3(128), 0, stream, 0, static_cast<const int8_t*>(xq), sx, d, slot_token, meta,
                                                    static_cast<int8_t*>(xq_perm), sx_perm);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
@@ -200,7 +213,7 @@ extern "C" int b200_moe_combine(const void* y, long long ldy, const int* inv, co
                                 long long ldo, cudaStream_t stream) {
   if (M <= 0) return 0;
   if (d % 8 || k > 32) return -1;
-  moe_combine_kernel<<<M, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), ldy, inv, wts, k, d,
+  launch_ex(moe_combine_kernel, dim3(M), dim3(256), 0, stream, 0, static_cast<const __nv_bfloat16*>(y), ldy, inv, wts, k, d,
                                             static_cast<__nv_bfloat16*>(out), ldo);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);

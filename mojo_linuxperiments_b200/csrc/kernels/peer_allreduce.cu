@@ -10,6 +10,7 @@
 // captured launch can be replayed without host involvement.
 #include "peer.cuh"
 #include "api.h"
+#include "launch.cuh"
 
 namespace b200 {
 
@@ -43,6 +44,9 @@ __device__ __forceinline__ void finish_launch(const ArParams& p, uint32_t epochs
 template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
 
 __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ArParams p) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   const PeerTable& t = p.t;
   const uint32_t e0 = *reinterpret_cast<volatile uint32_t*>(p.epoch) + 1;     // same on every CTA: bumped only at exit
   const int tid = threadIdx.x;
@@ -260,6 +264,9 @@ struct ArgmaxParams {
 };
 
 __global__ void __launch_bounds__(128) peer_argmax_kernel(const ArgmaxParams p) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   const PeerTable& t = p.t;
   const uint32_t e0 = *reinterpret_cast<volatile uint32_t*>(p.epoch) + 1;
   __shared__ int ok_s;
@@ -315,7 +322,7 @@ extern "C" int b200_peer_argmax(void* const* peer_data, void* const* peer_flags,
   p.val_off = val_off; p.idx_off = idx_off; p.ncand = ncand; p.rows = rows; p.out_idx = out_idx;
   p.epoch = static_cast<uint32_t*>(epoch_words); p.status = status;
   p.limit_ns = static_cast<unsigned long long>(limit_ms > 0 ? limit_ms : 2000) * 1000000ull;
-  peer_argmax_kernel<<<1, 128, 0, stream>>>(p);
+  launch_ex(peer_argmax_kernel, dim3(1), dim3(128), 0, stream, 0, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
@@ -350,7 +357,7 @@ extern "C" int b200_peer_allreduce(void* const* peer_data, void* const* peer_fla
   if (ctas < 1) ctas = 1;
   if (max_ctas < 1) max_ctas = 64;
   if (ctas > max_ctas) ctas = max_ctas;        // every CTA spins on flags: keep the grid well inside one wave
-  peer_allreduce_kernel<<<ctas, 256, 0, stream>>>(p);
+  launch_ex(peer_allreduce_kernel, dim3(ctas), dim3(256), 0, stream, 0, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }

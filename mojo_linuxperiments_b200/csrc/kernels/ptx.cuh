@@ -311,3 +311,15 @@ __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 }  // namespace b200
+
+// ---------------------------------------------------------------------------------------------
+// programmatic dependent launch: the next kernel of the stream may start (and run everything that does not read
+// this kernel's output: barrier set-up, TMEM allocation, weight prefetch) while this one is still running
+// ---------------------------------------------------------------------------------------------
+namespace b200 {
+// allow the dependent grid to be scheduled (takes effect once every CTA of this grid has called it or exited)
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// block until the grid this one depends on has completed and its writes are visible; every kernel calls this once,
+// before its first access to memory another kernel may have produced (which also keeps completion order transitive)
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+}  // namespace b200

@@ -9,6 +9,7 @@
 // contiguous 256-byte rows; a sequence finds its pages through page_table[seq][pos / page_size].
 #include "ptx.cuh"
 #include "api.h"
+#include "launch.cuh"
 
 namespace b200 {
 
@@ -41,6 +42,9 @@ struct RopeParams {
 
 // grid (tokens, ceil(heads / 4)), 4 warps; a warp handles one head, lane l holds elements l, l+32, l+64, l+96
 __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeParams p) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   const int tok = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = p.positions[tok];
@@ -92,6 +96,9 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeParams p) {
 
 __global__ void embed_gather_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
                                     __nv_bfloat16* __restrict__ out, int d, int vocab) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   const int tok = blockIdx.x;
   long long id = ids[tok];
   if (id < 0 || id >= vocab) id = 0;
@@ -105,6 +112,9 @@ __global__ void embed_gather_kernel(const long long* __restrict__ ids, const __n
 __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int n,
                                                           int chunk, int index_offset, float* __restrict__ out_val,
                                                           long long* __restrict__ out_idx) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   __shared__ float sv[8];
   __shared__ int si[8];
   const int row = blockIdx.x;
@@ -149,6 +159,9 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* _
 // cand_val/cand_idx: [world][rows]; out: [rows]
 __global__ void argmax_merge_kernel(const float* __restrict__ cand_val, const long long* __restrict__ cand_idx, int world,
                                     int rows, long long* __restrict__ out_idx) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   float best = cand_val[r];
@@ -180,7 +193,7 @@ extern "C" int b200_rope_kv_write(const void* qkv, long long ld_qkv, const int* 
   p.v_out = static_cast<__nv_bfloat16*>(v_out);
   p.cache = static_cast<__nv_bfloat16*>(cache); p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size;
   p.hq = hq; p.hkv = hkv; p.M = M;
-  rope_kv_kernel<<<dim3(M, (hq + 2 * hkv + 3) / 4), 128, 0, stream>>>(p);
+  launch_ex(rope_kv_kernel, dim3(dim3(M, (hq + 2 * hkv + 3) / 4)), dim3(128), 0, stream, 0, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
@@ -189,7 +202,7 @@ extern "C" int b200_embed_gather(const long long* ids, const void* table, void* 
                                  cudaStream_t stream) {
   if (M <= 0) return 0;
   if (d % 8) return -1;
-  embed_gather_kernel<<<M, 128, 0, stream>>>(ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), d, vocab);
+  launch_ex(embed_gather_kernel, dim3(M), dim3(128), 0, stream, 0, ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), d, vocab);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
@@ -200,7 +213,7 @@ extern "C" int b200_argmax_rows(const void* logits, long long ld, int rows, int 
   if (rows <= 0) return 0;
   if (chunks < 1) chunks = 1;
   const int chunk = ((n + chunks - 1) / chunks + 7) & ~7;
-  argmax_rows_kernel<<<dim3(rows, chunks), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(logits), ld, n, chunk, index_offset, out_val, out_idx);
+  launch_ex(argmax_rows_kernel, dim3(dim3(rows, chunks)), dim3(256), 0, stream, 0, static_cast<const __nv_bfloat16*>(logits), ld, n, chunk, index_offset, out_val, out_idx);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
@@ -208,7 +221,7 @@ extern "C" int b200_argmax_rows(const void* logits, long long ld, int rows, int 
 extern "C" int b200_argmax_merge(const float* cand_val, const long long* cand_idx, int world, int rows, long long* out_idx,
                                  cudaStream_t stream) {
   if (rows <= 0) return 0;
-  argmax_merge_kernel<<<(rows + 127) / 128, 128, 0, stream>>>(cand_val, cand_idx, world, rows, out_idx);
+  launch_ex(argmax_merge_kernel, dim3((rows + 127) / 128), dim3(128), 0, stream, 0, cand_val, cand_idx, world, rows, out_idx);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }

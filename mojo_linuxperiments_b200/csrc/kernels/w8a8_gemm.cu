@@ -25,6 +25,7 @@
 //   * Every mbarrier wait is bounded; on a timeout the CTA records a status code, drains and exits.
 #include "ptx.cuh"
 #include "api.h"
+#include "launch.cuh"
 #include "gemm_common.cuh"
 
 namespace b200 {
@@ -106,6 +107,9 @@ template <int BN, int STAGES, bool SWAP>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmParams p) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
   constexpr int A_BYTES = TILE_N * BLOCK_K;      // 16 KiB
   constexpr int B_BYTES = BN * BLOCK_K;
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -453,7 +457,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }
-  w8a8_gemm_kernel<BN, STAGES, SWAP><<<grid, GEMM_THREADS, SMEM, stream>>>(ta, tb, p);
+  launch_ex(w8a8_gemm_kernel<BN, STAGES, SWAP>, dim3(grid), dim3(GEMM_THREADS), SMEM, stream, 0, ta, tb, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }

@@ -23,6 +23,7 @@
 #include "api.h"
 #include "gemm_common.cuh"
 #include "peer.cuh"
+#include "launch.cuh"
 
 namespace b200 {
 
@@ -60,6 +61,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   constexpr uint32_t IDESC = umma_idesc_i8(TILE_N, BN);
   static_assert(STAGES * STAGE_BYTES >= BN * TILE_N * 4, "the exchange buffer aliases the pipeline stages");
 
+  pdl_launch_dependents();     // the next kernel may be scheduled: it only reads our output after its own pdl_wait
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);      // full[S], empty[S], tfull
@@ -77,7 +79,9 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   const int rank = static_cast<int>(cluster_ctarank());          // == blockIdx.x: position along K
   const int n_tile = blockIdx.y;
   int m0 = blockIdx.z * BN, rows_valid = min(BN, p.M - m0), w_base = 0;
-  if (p.grp_counts) {
+  const bool grouped = p.grp_counts != nullptr;
+  if (grouped) {
+    pdl_wait();                             // the work list comes from an earlier kernel of the stream
     rows_valid = min(BN, p.grp_counts[blockIdx.z]);
     if (rows_valid <= 0) return;            // same for every CTA of the cluster (they share blockIdx.z)
     m0 = p.grp_offsets[blockIdx.z];
@@ -122,7 +126,18 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       const uint64_t pol_w = policy_evict_first();     // weights are read exactly once per launch
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      // Weights never change during inference, so the first ring-full of weight tiles is requested before waiting
+      // for the previous kernel; the activation tiles (its output) are requested after the wait.
+      const int pre = grouped ? 0 : min(STAGES, kb1 - kb0);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(full_bar(i), STAGE_BYTES);
+        tma_load_2d_hint(smem_base + i * STAGE_BYTES, &tmap_w, full_bar(i), (kb0 + i) * BLOCK_K, w_base + n_tile * TILE_N, pol_w);
+      }
+      if (!grouped) pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d(smem_base + i * STAGE_BYTES + A_BYTES, &tmap_x, full_bar(i), (kb0 + i) * BLOCK_K, m0);
+      if (pre == STAGES) phase = 1u; else stage = pre;
+      for (int kb = kb0 + pre; kb < kb1; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY, limit)) { ok = false; break; }
         mbar_expect_tx(full_bar(stage), STAGE_BYTES);
         const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
@@ -153,6 +168,8 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     }
     __syncwarp();
   }
+
+  if (!grouped && !(warp == 0 && lane == 0)) pdl_wait();
 
   // ---------------- epilogue warps: wait for the accumulator ----------------
   const bool epi = warp >= 2;
@@ -288,19 +305,7 @@ static int launch_decode(const CUtensorMap& tw, const CUtensorMap& tx, const Dec
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = grid;
-  cfg.blockDim = dim3(GEMM_THREADS);
-  cfg.dynamicSmemBytes = SMEM;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = grid.x;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, w8a8_gemm_decode_kernel<BN, STAGES>, tw, tx, p);
+  cudaError_t e = launch_ex(w8a8_gemm_decode_kernel<BN, STAGES>, grid, dim3(GEMM_THREADS), SMEM, stream, static_cast<int>(grid.x), tw, tx, p);
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
 
