@@ -21,11 +21,14 @@ a = ap.parse_args()
 cfg = replace(C.PRESETS[a.model](), n_layers=a.layers)
 eng = Engine(cfg, C.RuntimeConfig(max_batch=a.batch, max_seq_len=a.prompt_len + 128), seed=0)
 prompts = torch.randint(0, cfg.vocab, (a.batch, a.prompt_len))
-eng.start_batch(a.batch, a.prompt_len + a.steps + 8)
+eng.start_batch(a.batch, a.prompt_len + a.steps + 9)
 eng.prefill(prompts)
+eng.decode_step(use_graph=False)      # warm-up step (lazy kernel attributes, allocator)
 torch.cuda.synchronize()
 n0 = _lib.LAUNCHES[0]
+torch.cuda.profiler.start()           # with `ncu --profile-from-start off` only the steps below are captured
 for _ in range(a.steps):
     eng.decode_step(use_graph=False)
 torch.cuda.synchronize()
+torch.cuda.profiler.stop()
 print("launches before decode:", n0, "per step:", (_lib.LAUNCHES[0] - n0) // a.steps)

@@ -80,6 +80,25 @@ act_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat
 
   float v[MAXB][4];
   float ss = 0.f;
+  // All global loads of the row are issued first, with no arithmetic in between, so their latencies overlap;
+  // the element-wise math (which contains slow-path divisions / exponentials) runs afterwards.
+  uint2 raw_a[MAXB], raw_b[MAXB];
+#pragma unroll
+  for (int i = 0; i < MAXB; ++i) {
+    const int b = warp + i * AQ_WARPS;
+    raw_a[i] = make_uint2(0u, 0u);
+    raw_b[i] = make_uint2(0u, 0u);
+    if (b < nblocks) {
+      const int k = b * 128 + lane * 4;
+      raw_a[i] = *reinterpret_cast<const uint2*>(xr + k);
+      if constexpr (MODE == AQ_SWIGLU) raw_b[i] = *reinterpret_cast<const uint2*>(xr + K + k);
+      if constexpr (MODE == AQ_ADD_NORM) raw_b[i] = *reinterpret_cast<const uint2*>(residual + static_cast<size_t>(row) * ldr + k);
+    }
+  }
+  auto unpack4 = [](const uint2& r, float (&o)[4]) {
+    o[0] = __uint_as_float(r.x << 16); o[1] = __uint_as_float(r.x & 0xffff0000u);
+    o[2] = __uint_as_float(r.y << 16); o[3] = __uint_as_float(r.y & 0xffff0000u);
+  };
 #pragma unroll
   for (int i = 0; i < MAXB; ++i) {
     const int b = warp + i * AQ_WARPS;
@@ -87,22 +106,21 @@ act_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat
       const int k = b * 128 + lane * 4;
       if constexpr (MODE == AQ_SWIGLU) {
         float g[4], u[4];
-        load4_bf16(xr + k, g);
-        load4_bf16(xr + K + k, u);
+        unpack4(raw_a[i], g);
+        unpack4(raw_b[i], u);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) v[i][j] = (g[j] / (1.f + __expf(-g[j]))) * u[j];
+        for (int j = 0; j < 4; ++j) v[i][j] = __fdividef(g[j], 1.f + __expf(-g[j])) * u[j];
       } else {
-        load4_bf16(xr + k, v[i]);
+        unpack4(raw_a[i], v[i]);
         if constexpr (MODE == AQ_ADD_NORM) {
           float r[4];
-          __nv_bfloat16* rp = residual + static_cast<size_t>(row) * ldr + k;
-          load4_bf16(rp, r);
+          unpack4(raw_b[i], r);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             // the residual stream is kept in bf16: round the sum once, and normalise what was stored
             v[i][j] = __bfloat162float(__float2bfloat16(v[i][j] + r[j]));
           }
-          store4_bf16(rp, v[i]);
+          store4_bf16(residual + static_cast<size_t>(row) * ldr + k, v[i]);
         }
         if constexpr (MODE == AQ_NORM || MODE == AQ_ADD_NORM) {
 #pragma unroll
@@ -115,6 +133,15 @@ act_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat
     }
   }
 
+  uint2 raw_g[MAXB];
+  if constexpr (MODE == AQ_NORM || MODE == AQ_ADD_NORM) {
+#pragma unroll
+    for (int i = 0; i < MAXB; ++i) {
+      const int b = warp + i * AQ_WARPS;
+      raw_g[i] = make_uint2(0u, 0u);
+      if (b < nblocks) raw_g[i] = __ldg(reinterpret_cast<const uint2*>(gamma + b * 128 + lane * 4));
+    }
+  }
   if constexpr (MODE == AQ_NORM || MODE == AQ_ADD_NORM) {
     ss = warp_sum(ss);
     if (lane == 0) red[warp] = ss;
@@ -134,7 +161,7 @@ act_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat
       if (b < nblocks) {
         const int k = b * 128 + lane * 4;
         float g[4];
-        load4_bf16(gamma + k, g);
+        unpack4(raw_g[i], g);
 #pragma unroll
         for (int j = 0; j < 4; ++j) v[i][j] = v[i][j] * rstd * g[j];
         if (xn_out) store4_bf16(xn_out + static_cast<size_t>(row) * ldn + k, v[i]);
@@ -165,6 +192,7 @@ act_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat
   }
   __syncthreads();
   const float s = bcast;
+  const float inv_s = 1.0f / s;
   int8_t* qr = q + static_cast<size_t>(row) * ldq;
 #pragma unroll
   for (int i = 0; i < MAXB; ++i) {
@@ -173,7 +201,7 @@ act_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat
       uint32_t packed = 0;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        int qi = __float2int_rn(__fdiv_rn(v[i][j], s));
+        int qi = __float2int_rn(v[i][j] * inv_s);
         qi = max(-127, min(127, qi));
         packed |= (static_cast<uint32_t>(qi) & 0xffu) << (8 * j);
       }

@@ -23,6 +23,7 @@ constexpr int ADT_STAGES = 6;
 constexpr int ADT_PS = 16;                 // tokens per page
 constexpr int ADT_D = 128;
 constexpr int ADT_BLOCK = ADT_PS * ADT_D * 2;   // 4 KiB: one K or V block
+constexpr int ADT_MAX_PAGES = 256;              // page ids staged in shared memory per CTA (more are read on demand)
 
 struct DecodeTmaParams {
   const __nv_bfloat16* q;
@@ -60,6 +61,7 @@ __global__ void __launch_bounds__(ADT_THREADS) attn_decode_tma_kernel(const __gr
   bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(bars) + 7) & ~uintptr_t(7));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * ADT_STAGES);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
+  int* page_s = last_flag + 1;                       // [ADT_MAX_PAGES] this CTA's slice of the page table
   const uint32_t ring = smem_u32(smem);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
@@ -81,6 +83,8 @@ __global__ void __launch_bounds__(ADT_THREADS) attn_decode_tma_kernel(const __gr
   }
   for (int i = tid; i < G * ADT_D; i += ADT_THREADS)
     q_s[i] = __bfloat162float(p.q[(static_cast<size_t>(b) * p.hq + kvh * G) * ADT_D + i]) * p.scale_log2;
+  // the page ids are read once, in parallel, so the producer never waits on a global load between two TMA issues
+  for (int i = tid; i < min(npages, ADT_MAX_PAGES); i += ADT_THREADS) page_s[i] = pt[pg0 + i];
   __syncthreads();
 
   float m_run[G], l_run[G], acc[G][4];
@@ -95,7 +99,7 @@ __global__ void __launch_bounds__(ADT_THREADS) attn_decode_tma_kernel(const __gr
         const int s = i % ADT_STAGES;
         const uint32_t ph = (i / ADT_STAGES) & 1u;
         if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY, p.limit_ns)) { ok = false; break; }
-        const int page = pt[pg0 + i];
+        const int page = i < ADT_MAX_PAGES ? page_s[i] : pt[pg0 + i];
         // half-row index of the K block of (page, head): ((page*2 + 0)*hkv + head) * 32 ; V block: kv = 1
         const int rk = ((page * 2 + 0) * p.hkv + kvh) * (ADT_PS * 2);
         const int rv = ((page * 2 + 1) * p.hkv + kvh) * (ADT_PS * 2);
@@ -234,7 +238,7 @@ typedef CUresult (*EncodeTiledFn2)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 
 template <int G>
 static int launch_adt(const CUtensorMap& tm, const DecodeTmaParams& p, dim3 grid, cudaStream_t stream) {
-  constexpr int SMEM = ADT_STAGES * 2 * ADT_BLOCK + (G * ADT_D + 4 * G * ADT_D + 4 * G * 2 + 2) * 4 + 2 * ADT_STAGES * 8 + 64 + 1024;
+  constexpr int SMEM = ADT_STAGES * 2 * ADT_BLOCK + (G * ADT_D + 4 * G * ADT_D + 4 * G * 2 + 2) * 4 + 2 * ADT_STAGES * 8 + 64 + ADT_MAX_PAGES * 4 + 1024;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);

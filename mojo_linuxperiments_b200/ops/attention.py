@@ -75,10 +75,18 @@ class DecodeAttnScratch:
         self.splits = splits
 
 
-def pick_decode_splits(B: int, hkv: int, max_len: int, num_sms: int = 148) -> int:
-    """Enough CTAs to fill the GPU about twice, but at least 128 tokens per split."""
-    want = max(1, (2 * num_sms + B * hkv - 1) // (B * hkv))
-    return max(1, min(want, (max_len + 127) // 128, 32))
+def pick_decode_splits(B: int, hkv: int, max_len: int, num_sms: int = 148, ctas_per_sm: int = 3) -> int:
+    """Number of KV splits: the grid is B * hkv * splits CTAs on num_sms * ctas_per_sm slots, and each CTA's work is
+    ~1/splits, so the time is ~ceil(grid / slots) / splits; pick the smallest split count within 5 % of the best,
+    keeping at least 64 tokens per split."""
+    slots = num_sms * ctas_per_sm
+    pairs = max(1, B * hkv)
+    max_splits = max(1, min(32, max_len // 64))
+    best_cost = min(-(-(pairs * s) // slots) / s for s in range(1, max_splits + 1))
+    for s in range(1, max_splits + 1):
+        if -(-(pairs * s) // slots) / s <= best_cost * 1.05:
+            return s
+    return 1
 
 
 def attn_decode(q: torch.Tensor, cache: PagedKVCache, page_table: torch.Tensor, seq_lens: torch.Tensor, *,
