@@ -263,3 +263,69 @@ extern "C" int b200_attn_decode(const void* q, const void* cache, const int* pag
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared and documented in attn_decode_noalloc.h).
+// ---------------------------------------------------------------------------------------------------------------
+#include "attn_decode_noalloc.h"
+#include <cstdio>
+
+namespace b200 {
+
+constexpr size_t ADN_MAX_COUNTERS = 4096;                       // (sequence, kv head) pairs
+constexpr size_t ADN_MAX_FLOATS = 1u << 20;                     // split-KV partials: 4 MiB
+constexpr size_t ADN_COUNTER_BYTES = ADN_MAX_COUNTERS * sizeof(unsigned);
+constexpr size_t ADN_BYTES = ADN_COUNTER_BYTES + ADN_MAX_FLOATS * sizeof(float);
+constexpr int ADN_MAX_DEVICES = 64;
+
+// [counters | partials]; lives in every GPU that loads the library.  On the host this name is only a handle for
+// cudaGetSymbolAddress: it must never be passed to a kernel as if it were a device pointer.
+static __device__ __align__(256) unsigned char g_attn_decode_scratch[ADN_BYTES];
+
+// device address of the array on the current device, looked up once per device
+static int adn_scratch_address(unsigned char** out) {
+  static unsigned char* cached[ADN_MAX_DEVICES] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= ADN_MAX_DEVICES) return -3000 - static_cast<int>(e);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_attn_decode_scratch);        // resolves against the device that is current now
+    if (e != cudaSuccess || !p) {
+      std::fprintf(stderr, "b200_attn_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s\n", dev, cudaGetErrorString(e));
+      return -3000 - static_cast<int>(e);
+    }
+    cached[dev] = static_cast<unsigned char*>(p);
+  }
+  *out = cached[dev];
+  return 0;
+}
+
+}  // namespace b200
+
+extern "C" int b200_attn_decode_noalloc(const void* q, const void* cache, const int* page_table, const int* seq_lens, void* out,
+                                        int B, int hq, int hkv, int page_size, int max_pages, int splits, float scale,
+                                        cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (hq <= 0 || hkv <= 0 || (hq % hkv)) return -1;
+  if (splits < 1) splits = 1;
+  const size_t need_floats = b200_attn_decode_scratch_floats(B, hq, splits);
+  const size_t need_counters = static_cast<size_t>(B) * hkv;
+  if (need_floats > ADN_MAX_FLOATS || need_counters > ADN_MAX_COUNTERS) {
+    std::fprintf(stderr,
+                 "b200_attn_decode_noalloc: B=%d hq=%d hkv=%d splits=%d needs %zu scratch floats and %zu counters; the built-in "
+                 "scratch holds %zu floats and %zu counters. Use fewer splits or b200_attn_decode with caller-owned scratch.\n",
+                 B, hq, hkv, splits, need_floats, need_counters, static_cast<size_t>(ADN_MAX_FLOATS), static_cast<size_t>(ADN_MAX_COUNTERS));
+    return B200_NOALLOC_TOO_LARGE;
+  }
+  unsigned char* base = nullptr;
+  const int rc = adn_scratch_address(&base);
+  if (rc) return rc;
+  unsigned* counters = reinterpret_cast<unsigned*>(base);
+  float* partials = reinterpret_cast<float*>(base + ADN_COUNTER_BYTES);
+  // the arrival counters must start at zero; the array may hold anything a previous (possibly failed) call left
+  cudaError_t e = cudaMemsetAsync(counters, 0, need_counters * sizeof(unsigned), stream);
+  if (e != cudaSuccess) return -2000 - static_cast<int>(e);
+  return b200_attn_decode(q, cache, page_table, seq_lens, out, partials, counters, B, hq, hkv, page_size, max_pages, splits,
+                          scale, stream);
+}

@@ -65,6 +65,7 @@ class _Sig:
     b200_argmax_merge = (I, [P, P, I, I, P, P])
     b200_attn_decode_scratch_floats = (c_size_t, [I, I, I])
     b200_attn_decode = (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P])
+    b200_attn_decode_noalloc = (I, [P, P, P, P, P, I, I, I, I, I, I, F, P])
     b200_attn_decode_tma = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
     b200_attn_prefill = (I, [P, LL, P, LL, P, LL, P, P, I, I, I, I, I, F, P, P])
 
