@@ -64,9 +64,9 @@ __device__ __forceinline__ void store4_bf16(__nv_bfloat16* p, const float (&v)[4
 
 template <int MAXB, int MODE>
 __global__ void __launch_bounds__(AQ_THREADS)
-act_quant_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_bfloat16* __restrict__ residual,
-                 long long ldr, const __nv_bfloat16* __restrict__ gamma, float eps, int8_t* __restrict__ q,
-                 long long ldq, float* __restrict__ scale, __nv_bfloat16* __restrict__ xn_out, long long ldn,
+act_quant_kernel(const __nv_bfloat16* x, long long ldx, __nv_bfloat16* residual,
+                 long long ldr, const __nv_bfloat16* gamma, float eps, int8_t* q,
+                 long long ldq, float* scale, __nv_bfloat16* xn_out, long long ldn,
                  int K) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
   pdl_wait();                // everything before this kernel in the stream has completed

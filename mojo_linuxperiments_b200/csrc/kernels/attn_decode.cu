@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodePar
                                                           static_cast<size_t>(tok % p.page_size) * AD_D + part * 32);
         uint4 kr[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) kr[i] = __ldg(kp + i);
+        for (int i = 0; i < 4; ++i) kr[i] = kp[i];
         float dot[G];
 #pragma unroll
         for (int g = 0; g < G; ++g) dot[g] = 0.f;
@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodePar
     for (int tt = ts; tt < n; tt += 8) {
       const int tok = c0 + tt;
       const int page = pt[tok / p.page_size];
-      const uint4 vr = __ldg(reinterpret_cast<const uint4*>(p.cache + static_cast<size_t>(page) * page_stride + v_head_off +
+      const uint4 vr = *(reinterpret_cast<const uint4*>(p.cache + static_cast<size_t>(page) * page_stride + v_head_off +
                                                              static_cast<size_t>(tok % p.page_size) * AD_D + 8 * dg));
       float vf[8];
       bf16x8_to_float(vr, vf);

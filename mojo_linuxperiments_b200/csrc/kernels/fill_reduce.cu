@@ -11,10 +11,10 @@
 
 namespace b200 {
 
-__global__ void __launch_bounds__(256) fill_uniform_reduce_kernel(float* __restrict__ out, unsigned long long begin,
+__global__ void __launch_bounds__(256) fill_uniform_reduce_kernel(float* out, unsigned long long begin,
                                                                   unsigned long long end, unsigned long long seed,
-                                                                  double* __restrict__ partials, unsigned* __restrict__ counter,
-                                                                  double* __restrict__ result) {
+                                                                  double* partials, unsigned* counter,
+                                                                  double* result) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
   pdl_wait();                // everything before this kernel in the stream has completed
 

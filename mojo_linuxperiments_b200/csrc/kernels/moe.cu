@@ -16,8 +16,8 @@ namespace b200 {
 
 // one warp per token; E <= 256 (each lane holds E/32 logits)
 template <int EPL>
-__global__ void __launch_bounds__(128) router_topk_kernel(const float* __restrict__ logits, long long ld, int M, int E, int k,
-                                                          int renorm, int* __restrict__ ids, float* __restrict__ wts) {
+__global__ void __launch_bounds__(128) router_topk_kernel(const float* logits, long long ld, int M, int E, int k,
+                                                          int renorm, int* ids, float* wts) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
   pdl_wait();                // everything before this kernel in the stream has completed
 
@@ -73,10 +73,10 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float* __restric
 // Single CTA.  counts/offsets: [n_local], [n_local + 1]; slot_token: [M*k] (first offsets[n_local] valid);
 // inv: [M*k] slot of each (token, k) or -1; tiles: int4 {expert, first_row, rows, 0} per 128-row tile; meta: [0] total
 // slots, [1] number of tiles.
-__global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__ ids, int M, int k, int e0, int n_local,
-                                                         int* __restrict__ counts, int* __restrict__ offsets,
-                                                         int* __restrict__ slot_token, int* __restrict__ inv,
-                                                         int4* __restrict__ tiles, int* __restrict__ meta) {
+__global__ void __launch_bounds__(1024) moe_align_kernel(const int* ids, int M, int k, int e0, int n_local,
+                                                         int* counts, int* offsets,
+                                                         int* slot_token, int* inv,
+                                                         int4* tiles, int* meta) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
   pdl_wait();                // everything before this kernel in the stream has completed
 
@@ -121,9 +121,9 @@ __global__ void __launch_bounds__(1024) moe_align_kernel(const int* __restrict__
 }
 
 // grid = max slots; rows beyond meta[0] exit.  xq int8 [M][d] -> xq_perm [slots][d]
-__global__ void __launch_bounds__(128) moe_gather_kernel(const int8_t* __restrict__ xq, const float* __restrict__ sx, int d,
-                                                         const int* __restrict__ slot_token, const int* __restrict__ meta,
-                                                         int8_t* __restrict__ xq_perm, float* __restrict__ sx_perm) {
+__global__ void __launch_bounds__(128) moe_gather_kernel(const int8_t* xq, const float* sx, int d,
+                                                         const int* slot_token, const int* meta,
+                                                         int8_t* xq_perm, float* sx_perm) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
   pdl_wait();                // everything before this kernel in the stream has completed
 
@@ -137,9 +137,9 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const int8_t* __restric
 }
 
 // one CTA per token: out[t][:] = sum over the token's local slots of weight * y[slot][:]   (bf16 in, fp32 sum, bf16 out)
-__global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* __restrict__ y, long long ldy,
-                                                          const int* __restrict__ inv, const float* __restrict__ wts, int k,
-                                                          int d, __nv_bfloat16* __restrict__ out, long long ldo) {
+__global__ void __launch_bounds__(256) moe_combine_kernel(const __nv_bfloat16* y, long long ldy,
+                                                          const int* inv, const float* wts, int k,
+                                                          int d, __nv_bfloat16* out, long long ldo) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
   pdl_wait();                // everything before this kernel in the stream has completed
 

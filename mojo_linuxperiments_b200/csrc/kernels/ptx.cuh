@@ -323,3 +323,7 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 // before its first access to memory another kernel may have produced (which also keeps completion order transitive)
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 }  // namespace b200
+// Note on loads under programmatic dependent launch: a kernel may become resident before its predecessor has written
+// its inputs, so activations must never be read through the non-coherent path (__ldg / const __restrict__): a line
+// cached by an older co-resident kernel can be stale.  Only tensors that never change during inference (weights,
+// scales of weights, norm gains, embedding table) use __ldg in this library.

@@ -94,8 +94,8 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeParams p) {
   }
 }
 
-__global__ void embed_gather_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
-                                    __nv_bfloat16* __restrict__ out, int d, int vocab) {
+__global__ void embed_gather_kernel(const long long* ids, const __nv_bfloat16* table,
+                                    __nv_bfloat16* out, int d, int vocab) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
   pdl_wait();                // everything before this kernel in the stream has completed
 
@@ -109,9 +109,9 @@ __global__ void embed_gather_kernel(const long long* __restrict__ ids, const __n
 
 // grid (rows, chunks): CTA (r, c) scans columns [c*cs, (c+1)*cs) of row r and writes candidate [c][r];
 // ties resolve to the lowest index (matches torch.argmax on a single device after the merge)
-__global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, int n,
-                                                          int chunk, int index_offset, float* __restrict__ out_val,
-                                                          long long* __restrict__ out_idx) {
+__global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* logits, long long ld, int n,
+                                                          int chunk, int index_offset, float* out_val,
+                                                          long long* out_idx) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
   pdl_wait();                // everything before this kernel in the stream has completed
 
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* _
     const int nv = (c1 - c0) / 8;
     const uint4* xv = reinterpret_cast<const uint4*>(x + c0);
     for (int i = threadIdx.x; i < nv; i += blockDim.x) {
-      const uint4 raw = __ldg(xv + i);
+      const uint4 raw = xv[i];
       const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
@@ -157,8 +157,8 @@ __global__ void __launch_bounds__(256) argmax_rows_kernel(const __nv_bfloat16* _
 }
 
 // cand_val/cand_idx: [world][rows]; out: [rows]
-__global__ void argmax_merge_kernel(const float* __restrict__ cand_val, const long long* __restrict__ cand_idx, int world,
-                                    int rows, long long* __restrict__ out_idx) {
+__global__ void argmax_merge_kernel(const float* cand_val, const long long* cand_idx, int world,
+                                    int rows, long long* out_idx) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
   pdl_wait();                // everything before this kernel in the stream has completed
 

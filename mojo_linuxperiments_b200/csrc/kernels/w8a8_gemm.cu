@@ -253,7 +253,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           m_ok = (q * 32 + lane) < tt.z;
           swg = p.sw + static_cast<size_t>(tt.x) * p.N;
         }
-        const float sxm = m_ok ? __ldg(p.sx + m) : 0.f;
+        const float sxm = m_ok ? p.sx[m] : 0.f;
         const int n0 = n_tile * BN;
         const size_t row_off = static_cast<size_t>(m_ok ? m : 0) * p.ldy;
         const bool vec_ok = !p.out_fp32 && (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) &&
@@ -344,7 +344,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
               for (int j = 0; j < CH; ++j) {
                 if (j < jmax) {
-                  float v = static_cast<float>(static_cast<int32_t>(r[j])) * swn * __ldg(sxp + j);
+                  float v = static_cast<float>(static_cast<int32_t>(r[j])) * swn * sxp[j];
                   if (p.residual) v += __bfloat162float(p.residual[o0 + static_cast<size_t>(j) * p.ldy]);
                   yp[static_cast<size_t>(j) * p.ldy] = v;
                 }
@@ -354,7 +354,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
               for (int j = 0; j < CH; ++j) {
                 if (j < jmax) {
-                  float v = static_cast<float>(static_cast<int32_t>(r[j])) * swn * __ldg(sxp + j);
+                  float v = static_cast<float>(static_cast<int32_t>(r[j])) * swn * sxp[j];
                   if (p.residual) v += __bfloat162float(p.residual[o0 + static_cast<size_t>(j) * p.ldy]);
                   yp[static_cast<size_t>(j) * p.ldy] = __float2bfloat16(v);
                 }
@@ -392,7 +392,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 int32_t acc = 0;
                 for (int sgi = 0; sgi < nseg; ++sgi) acc += __ldcg(s0 + static_cast<size_t>(sgi) * (BN * TILE_N) + j * TILE_N);
                 const int m = m0 + j;
-                float v = static_cast<float>(acc) * swn * __ldg(p.sx + m);
+                float v = static_cast<float>(acc) * swn * p.sx[m];
                 const size_t o = static_cast<size_t>(m) * p.ldy + n;
                 if (p.residual) v += __bfloat162float(p.residual[o]);
                 if (p.out_fp32) reinterpret_cast<float*>(p.y)[o] = v;

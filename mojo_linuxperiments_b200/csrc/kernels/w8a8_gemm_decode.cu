@@ -200,7 +200,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if (!n_ok || jm <= 0) continue;
 #pragma unroll
         for (int j = 0; j < CH; ++j)
-          if (j < jm) store_out(mc + j, n, static_cast<float>(static_cast<int32_t>(r[j])) * swn * __ldg(p.sx + mc + j));
+          if (j < jm) store_out(mc + j, n, static_cast<float>(static_cast<int32_t>(r[j])) * swn * p.sx[mc + j]);
       }
     }
   } else {
@@ -239,7 +239,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         int32_t acc = 0;
         for (int s = 0; s < S; ++s) acc += ex[(s * BN + j) * rows_per + row_in];
         const int n = n_tile * TILE_N + rank * rows_per + row_in;
-        if (n < p.N) store_out(m0 + j, n, static_cast<float>(acc) * __ldg(p.sw + w_base + n) * __ldg(p.sx + m0 + j));
+        if (n < p.N) store_out(m0 + j, n, static_cast<float>(acc) * __ldg(p.sw + w_base + n) * p.sx[m0 + j]);
       }
     }
   }

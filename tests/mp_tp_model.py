@@ -16,11 +16,16 @@ from mojo_linuxperiments_b200.parallel.comm import Comm  # noqa: E402
 
 def main():
     fused = sys.argv[1] == "fused"
+    kind = sys.argv[2] if len(sys.argv) > 2 else "dense"
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     rank, world = dist.get_rank(), dist.get_world_size()
-    cfg = C.tiny_dense(n_layers=2, d_model=1024, n_heads=8, n_kv_heads=8 if world > 4 else 4, ffn=2048, vocab=2048)
+    if kind == "moe":
+        # 4 KV heads on up to 8 ranks (heads replicated on rank pairs), 16 experts sharded over the ranks
+        cfg = C.tiny_moe(n_layers=2, d_model=1024, n_heads=8, n_kv_heads=4, n_experts=16, top_k=4, moe_ffn=256, vocab=2048)
+    else:
+        cfg = C.tiny_dense(n_layers=2, d_model=1024, n_heads=8, n_kv_heads=8 if world > 4 else 4, ffn=2048, vocab=2048)
     rt = C.RuntimeConfig(tp=world, ep=world, max_seq_len=256, max_prefill_tokens=512, fused_collectives=fused)
     ck = Wt.quantize_master(Wt.init_master(cfg, 0))
     w = Wt.shard_from_checkpoint(cfg, ck, world, rank, "cuda")

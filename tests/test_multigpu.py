@@ -40,3 +40,15 @@ def test_tensor_parallel_tiny_model(nproc, mode):
     p = _run("mp_tp_model.py", nproc, mode)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     assert "FAILURES 0" in p.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_expert_parallel_tiny_moe(nproc):
+    """Expert parallelism over replicated tokens + TP attention with KV heads replicated on rank pairs."""
+    if NGPU < nproc:
+        pytest.skip(f"needs {nproc} GPUs, found {NGPU}")
+    p = _run("mp_tp_model.py", nproc, "fused", "moe")
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert "FAILURES 0" in p.stdout
