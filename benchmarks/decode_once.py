@@ -17,9 +17,11 @@ ap.add_argument("--prompt-len", type=int, default=1024)
 ap.add_argument("--steps", type=int, default=2)
 ap.add_argument("--layers", type=int, default=32)
 ap.add_argument("--model", default="llama3-8b")
+ap.add_argument("--shard-of", type=int, default=1, help="run rank 0's shard of a tensor-parallel group of this size on one GPU "
+                "(same kernel shapes as that group, partial sums are simply not reduced)")
 a = ap.parse_args()
 cfg = replace(C.PRESETS[a.model](), n_layers=a.layers)
-eng = Engine(cfg, C.RuntimeConfig(max_batch=a.batch, max_seq_len=a.prompt_len + 128), seed=0)
+eng = Engine(cfg, C.RuntimeConfig(tp=a.shard_of, ep=a.shard_of, max_batch=a.batch, max_seq_len=a.prompt_len + 128), seed=0)
 prompts = torch.randint(0, cfg.vocab, (a.batch, a.prompt_len))
 eng.start_batch(a.batch, a.prompt_len + a.steps + 9)
 eng.prefill(prompts)
@@ -31,4 +33,5 @@ for _ in range(a.steps):
     eng.decode_step(use_graph=False)
 torch.cuda.synchronize()
 torch.cuda.profiler.stop()
+eng.check_status()
 print("launches before decode:", n0, "per step:", (_lib.LAUNCHES[0] - n0) // a.steps)

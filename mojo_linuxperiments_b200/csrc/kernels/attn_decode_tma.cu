@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(ADT_THREADS) attn_decode_tma_kernel(const __gr
       for (int i = 0; i < npages && ok; ++i) {
         const int s = i % ADT_STAGES;
         const uint32_t ph = (i / ADT_STAGES) & 1u;
-        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY, p.limit_ns)) { ok = false; break; }
+        if (!mbar_wait(empty_bar(s), ph ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (4 << 8)), p.limit_ns)) { ok = false; break; }
         const int page = i < ADT_MAX_PAGES ? page_s[i] : pt[pg0 + i];
         // half-row index of the K block of (page, head): ((page*2 + 0)*hkv + head) * 32 ; V block: kv = 1
         const int rk = ((page * 2 + 0) * p.hkv + kvh) * (ADT_PS * 2);
@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(ADT_THREADS) attn_decode_tma_kernel(const __gr
     for (int i = warp; i < npages && ok; i += 4) {
       const int s = i % ADT_STAGES;
       const uint32_t ph = (i / ADT_STAGES) & 1u;
-      if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL, p.limit_ns)) { ok = false; break; }
+      if (!mbar_wait(full_bar(s), ph, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (4 << 8)), p.limit_ns)) { ok = false; break; }
       const uint8_t* kblk = smem + s * 2 * ADT_BLOCK;
       const uint8_t* vblk = kblk + ADT_BLOCK;
       // ---- scores ----

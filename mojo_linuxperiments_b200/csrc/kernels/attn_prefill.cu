@@ -88,11 +88,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1u;
         const int row = seq0 + j * AP_BN;
-        if (!mbar_wait(bar(B_KEMPTY + st), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY, limit)) { ok = false; break; }
+        if (!mbar_wait(bar(B_KEMPTY + st), ph ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (3 << 8)), limit)) { ok = false; break; }
         mbar_expect_tx(bar(B_KFULL + st), AP_TILE_BYTES);
         tma_load_2d(sK + st * AP_TILE_BYTES, &tmap_k, bar(B_KFULL + st), kvh * AP_D, row);
         tma_load_2d(sK + st * AP_TILE_BYTES + AP_CHUNK_BYTES, &tmap_k, bar(B_KFULL + st), kvh * AP_D + 64, row);
-        if (!mbar_wait(bar(B_VEMPTY + st), ph ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY, limit)) { ok = false; break; }
+        if (!mbar_wait(bar(B_VEMPTY + st), ph ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (3 << 8)), limit)) { ok = false; break; }
         mbar_expect_tx(bar(B_VFULL + st), AP_TILE_BYTES);
         tma_load_2d(sV + st * AP_TILE_BYTES, &tmap_v, bar(B_VFULL + st), kvh * AP_D, row);
         tma_load_2d(sV + st * AP_TILE_BYTES + AP_CHUNK_BYTES, &tmap_v, bar(B_VFULL + st), kvh * AP_D + 64, row);
@@ -117,19 +117,19 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         umma_commit(bar(B_KEMPTY + st));
         umma_commit(bar(B_SFULL + (j & 1)));
       };
-      bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL, limit) &&
-                mbar_wait(bar(B_KFULL + 0), 0, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL, limit);
+      bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (3 << 8)), limit) &&
+                mbar_wait(bar(B_KFULL + 0), 0, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (3 << 8)), limit);
       if (ok) { tc_fence_after(); issue_s(0); }
       for (int j = 0; j < n_tiles && ok; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1u;
         if (j + 1 < n_tiles) {
-          if (!mbar_wait(bar(B_KFULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL, limit)) { ok = false; break; }
+          if (!mbar_wait(bar(B_KFULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (3 << 8)), limit)) { ok = false; break; }
           tc_fence_after();
           issue_s(j + 1);
         }
-        if (!mbar_wait(bar(B_PFULL), j & 1u, abort_flag, p.status, ST_TIMEOUT_PEER_FLAG, limit)) { ok = false; break; }
-        if (!mbar_wait(bar(B_VFULL + st), ph, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL, limit)) { ok = false; break; }
+        if (!mbar_wait(bar(B_PFULL), j & 1u, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (3 << 8)), limit)) { ok = false; break; }
+        if (!mbar_wait(bar(B_VFULL + st), ph, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (3 << 8)), limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d = tmem_base + 256 + (j & 1) * 128;
 #pragma unroll
@@ -157,7 +157,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int sw = r & 7;
 
     auto o_update = [&](int j, float alpha) -> bool {
-      if (!mbar_wait(bar(B_OFULL + (j & 1)), (j >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, limit)) return false;
+      if (!mbar_wait(bar(B_OFULL + (j & 1)), (j >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (3 << 8)), limit)) return false;
       tc_fence_after();
       const uint32_t t_pv = t_lane + 256 + (j & 1) * 128;
 #pragma unroll
@@ -173,7 +173,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     };
 
     for (int j = 0; j < n_tiles; ++j) {
-      if (!mbar_wait(bar(B_SFULL + (j & 1)), (j >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, limit)) { ok = false; break; }
+      if (!mbar_wait(bar(B_SFULL + (j & 1)), (j >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (3 << 8)), limit)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_s = t_lane + (j & 1) * 128;
       const int kv0 = j * AP_BN;
@@ -197,7 +197,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       // the P buffer is free once the PV MMA of the previous tile has completed
       if (j > 0) {
-        if (!mbar_wait(bar(B_OFULL + ((j - 1) & 1)), ((j - 1) >> 1) & 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, limit)) { ok = false; break; }
+        if (!mbar_wait(bar(B_OFULL + ((j - 1) & 1)), ((j - 1) >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (3 << 8)), limit)) { ok = false; break; }
       }
       // pass 2: probabilities -> bf16 -> swizzled shared memory
       float sum = 0.f;

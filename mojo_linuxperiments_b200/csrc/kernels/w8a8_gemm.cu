@@ -168,7 +168,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         int row0 = m_tile * TILE_N, wrow0 = 0;
         if (p.grp_tiles) { const int4 tt = p.grp_tiles[m_tile]; row0 = tt.y; wrow0 = tt.x * p.N; }
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY, limit)) { ok = false; break; }
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (1 << 8)), limit)) { ok = false; break; }
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
           if constexpr (SWAP) {
@@ -201,11 +201,11 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       while (ok && it.next(sg)) {
         const int a = seg_idx & 1;
         const uint32_t aphase = (seg_idx >> 1) & 1u;
-        if (!mbar_wait(tempty_bar(a), aphase ^ 1u, abort_flag, p.status, ST_TIMEOUT_TMEM_EMPTY, limit)) { ok = false; break; }
+        if (!mbar_wait(tempty_bar(a), aphase ^ 1u, abort_flag, p.status, (ST_TIMEOUT_TMEM_EMPTY | (1 << 8)), limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * BN;
         for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL, limit)) { ok = false; break; }
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (1 << 8)), limit)) { ok = false; break; }
           tc_fence_after();
           const uint32_t a_src = smem_base + stage * STAGE_BYTES;
           const uint64_t a_desc = umma_desc_k_sw128(a_src);
@@ -236,7 +236,7 @@ w8a8_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const uint32_t aphase = (seg_idx >> 1) & 1u;
       int m_tile, n_tile;
       tile_coords(p, sg.tile, m_tile, n_tile);
-      if (!mbar_wait(tfull_bar(a), aphase, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, limit)) { ok = false; break; }
+      if (!mbar_wait(tfull_bar(a), aphase, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (1 << 8)), limit)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BN;
       const bool whole = (sg.kb0 == 0 && sg.kb1 == p.kblocks);

@@ -105,12 +105,8 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 
   // where a finished output element goes: y, or (fused all-reduce) this rank's slot of the symmetric partial buffer
   const bool fuse_ar = p.ar.enabled != 0;
-  uint32_t ar_epoch = 0;
+  uint32_t ar_epoch = 0;              // set after the dependency wait: an earlier launch may still be bumping the word
   __nv_bfloat16* part = nullptr;
-  if (fuse_ar) {
-    ar_epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.words) + 1;       // bumped only after every CTA has read it
-    part = reinterpret_cast<__nv_bfloat16*>(p.ar.t.data[p.ar.t.rank] + p.ar.part_off[ar_epoch & 1]);
-  }
   auto store_out = [&](int m, int n, float v) {
     if (fuse_ar) { part[static_cast<size_t>(m) * p.N + n] = __float2bfloat16(v); return; }
     const size_t o = static_cast<size_t>(m) * p.ldy + n;
@@ -138,7 +134,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         tma_load_2d(smem_base + i * STAGE_BYTES + A_BYTES, &tmap_x, full_bar(i), (kb0 + i) * BLOCK_K, m0);
       if (pre == STAGES) phase = 1u; else stage = pre;
       for (int kb = kb0 + pre; kb < kb1; ++kb) {
-        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, ST_TIMEOUT_SMEM_EMPTY, limit)) { ok = false; break; }
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (2 << 8)), limit)) { ok = false; break; }
         mbar_expect_tx(full_bar(stage), STAGE_BYTES);
         const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
         tma_load_2d_hint(a_dst, &tmap_w, full_bar(stage), kb * BLOCK_K, w_base + n_tile * TILE_N, pol_w);
@@ -153,7 +149,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, ST_TIMEOUT_SMEM_FULL, limit)) { ok = false; break; }
+        if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (2 << 8)), limit)) { ok = false; break; }
         tc_fence_after();
         const uint32_t a_src = smem_base + stage * STAGE_BYTES;
         const uint64_t a_desc = umma_desc_k_sw128(a_src);
@@ -170,6 +166,12 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   }
 
   if (!grouped && !(warp == 0 && lane == 0)) pdl_wait();
+  if (fuse_ar) {
+    // Every thread is past its dependency wait here, so all earlier launches of the stream (which advance the epoch
+    // word when they finish) have completed.  The word is bumped again only after every CTA of this grid has exited.
+    ar_epoch = *reinterpret_cast<volatile uint32_t*>(p.ar.words) + 1;
+    part = reinterpret_cast<__nv_bfloat16*>(p.ar.t.data[p.ar.t.rank] + p.ar.part_off[ar_epoch & 1]);
+  }
 
   // ---------------- epilogue warps: wait for the accumulator ----------------
   const bool epi = warp >= 2;
@@ -180,7 +182,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   constexpr int CH = (BN >= 32) ? 32 : 16;
   bool acc_ok = false;
   if (epi) {
-    acc_ok = (kb1 > kb0) && mbar_wait(tfull_bar, 0, abort_flag, p.status, ST_TIMEOUT_TMEM_FULL, limit);
+    acc_ok = (kb1 > kb0) && mbar_wait(tfull_bar, 0, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (2 << 8)), limit);
     tc_fence_after();
   }
 

@@ -30,7 +30,8 @@ class Workspace:
         code = int(self.status[0].item())
         if code != 0:
             self.status.zero_()
-            raise RuntimeError(f"kernel status {code}: {_STATUS_NAMES.get(code, 'unknown')}")
+            kernel = {0: "?", 1: "w8a8_gemm", 2: "w8a8_gemm_decode", 3: "attn_prefill", 4: "attn_decode_tma"}.get(code >> 8, "?")
+            raise RuntimeError(f"kernel status {code & 255} in {kernel}: {_STATUS_NAMES.get(code & 255, 'unknown')}")
 
 
 _default: dict[int, Workspace] = {}
