@@ -31,7 +31,8 @@ int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void* wq, const
 int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
                              const void* residual, int M, int N, int K, int ldy, int* status, int num_sms,
                              void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
-                             size_t part_off0, size_t part_off1, void* words, int limit_ms, cudaStream_t stream);
+                             size_t part_off0, size_t part_off1, void* words, int limit_ms, int ll,
+                             size_t recv_off0, size_t recv_off1, size_t recv_bytes, cudaStream_t stream);
 
 // Mixture-of-experts grouped forms (device-side offsets / tile tables, no host sync).
 int b200_w8a8_gemm_decode_grouped(const void* xq, const float* sx, const void* wq, const float* sw, void* y,

@@ -56,6 +56,21 @@ __device__ __forceinline__ void multimem_st_16B(void* mc_addr, const uint4& v) {
                ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// 8-byte "LL" words {payload, flag}: one store carries data and its own arrival flag, so no fence or separate
+// signal is needed; the receiver polls the word until the flag equals the epoch it expects.
+__device__ __forceinline__ void st_ll_peer(void* p, uint32_t payload, uint32_t flag) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(payload), "r"(flag) : "memory");
+}
+__device__ __forceinline__ void multimem_st_ll(void* mc_addr, uint32_t payload, uint32_t flag) {
+  asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};"
+               ::"l"(mc_addr), "f"(__uint_as_float(payload)), "f"(__uint_as_float(flag)) : "memory");
+}
+__device__ __forceinline__ uint2 ld_ll(const void* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
 // ---- plain peer loads ----
 __device__ __forceinline__ uint4 ld_peer_16B(const void* p) {
   uint4 v;

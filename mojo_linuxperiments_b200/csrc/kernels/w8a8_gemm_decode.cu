@@ -32,6 +32,11 @@ struct ArTail {
   size_t part_off[2];          // byte offsets of the two partial-product slots inside every heap ([M][N] bf16 each)
   uint32_t* words;             // device words of this rank: [0] epoch, [1] finished CTAs, [2] exited CTAs
   int enabled, use_nvls, limit_ms;
+  // Low-latency form: every rank pushes its partial as 8-byte {2 x bf16, epoch} words into a receive area of every
+  // rank ([source][M][N/2] words, two slots by epoch parity) and then sums the world copies that arrived locally:
+  // one NVLink trip, no fence, no grid-wide counter.  recv_off: byte offsets of the two slots in every heap.
+  int ll;
+  size_t recv_off[2];
 };
 
 struct DecodeGemmParams {
@@ -59,7 +64,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   constexpr uint32_t IDESC = umma_idesc_i8(TILE_N, BN);
-  static_assert(STAGES * STAGE_BYTES >= BN * TILE_N * 4, "the exchange buffer aliases the pipeline stages");
+  static_assert(STAGES * STAGE_BYTES >= 2 * BN * TILE_N * 4, "exchange and staging buffers alias the pipeline stages");
 
   pdl_launch_dependents();     // the next kernel may be scheduled: it only reads our output after its own pdl_wait
   extern __shared__ uint8_t smem_raw[];
@@ -107,7 +112,13 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   const bool fuse_ar = p.ar.enabled != 0;
   uint32_t ar_epoch = 0;              // set after the dependency wait: an earlier launch may still be bumping the word
   __nv_bfloat16* part = nullptr;
+  // low-latency all-reduce: finished values are staged in shared memory (behind the exchange buffer) first
+  const bool ll = fuse_ar && p.ar.ll != 0;
+  float* vals = reinterpret_cast<float*>(smem + BN * TILE_N * 4);
+  const int cw = (S == 1) ? TILE_N : TILE_N / S;                       // channels this CTA finishes
+  const int n_base = n_tile * TILE_N + ((S == 1) ? 0 : rank * (TILE_N / S));
   auto store_out = [&](int m, int n, float v) {
+    if (ll) { vals[(m - m0) * cw + (n - n_base)] = v; return; }
     if (fuse_ar) { part[static_cast<size_t>(m) * p.N + n] = __float2bfloat16(v); return; }
     const size_t o = static_cast<size_t>(m) * p.ldy + n;
     if (p.residual) v += __bfloat162float(p.residual[o]);
@@ -250,7 +261,64 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 
-  if (fuse_ar) {
+  if (ll) {
+    // ---- low-latency all-reduce: push {payload, epoch} words to every rank, then sum what arrived here ----
+    const PeerTable& t = p.ar.t;
+    const int half = cw / 2, words = half * jmax;
+    const size_t slot = p.ar.recv_off[ar_epoch & 1];
+    const size_t src_stride = static_cast<size_t>(p.M) * (p.N / 2) * 8;          // bytes per source rank
+    __syncthreads();                                                             // vals complete
+    if (epi) {
+      for (int w = et; w < words; w += 128) {
+        const int j = w / half, c2 = w - j * half;
+        const int n = n_base + 2 * c2;
+        if (n >= p.N) continue;
+        const __nv_bfloat162 pb = __floats2bfloat162_rn(vals[j * cw + 2 * c2], vals[j * cw + 2 * c2 + 1]);
+        const uint32_t payload = *reinterpret_cast<const uint32_t*>(&pb);
+        const size_t off = slot + t.rank * src_stride + (static_cast<size_t>(m0 + j) * (p.N / 2) + n / 2) * 8;
+        if (p.ar.use_nvls) multimem_st_ll(t.mc + off, payload, ar_epoch);
+        else for (int r = 0; r < t.world; ++r) st_ll_peer(t.data[r] + off, payload, ar_epoch);
+      }
+      const uint8_t* mine = t.data[t.rank] + slot;
+      const uint64_t t_start = globaltimer_ns();
+      bool good = true;
+      for (int w = et; w < words && good; w += 128) {
+        const int j = w / half, c2 = w - j * half;
+        const int n = n_base + 2 * c2;
+        if (n >= p.N) continue;
+        const size_t eoff = (static_cast<size_t>(m0 + j) * (p.N / 2) + n / 2) * 8;
+        float a0 = 0.f, a1 = 0.f;
+        for (int r = 0; r < t.world && good; ++r) {                              // fixed order: same bits on every rank
+          const uint8_t* src = mine + r * src_stride + eoff;
+          uint2 v = ld_ll(src);
+          uint32_t spins = 0;
+          while (v.y != ar_epoch) {
+            if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > limit) {
+              if (p.status) atomicCAS(p.status, 0, (ST_TIMEOUT_PEER_FLAG | (2 << 8)));
+              good = false;
+              break;
+            }
+            v = ld_ll(src);
+          }
+          a0 += __uint_as_float(v.x << 16);
+          a1 += __uint_as_float(v.x & 0xffff0000u);
+        }
+        if (!good) break;
+        const size_t o = static_cast<size_t>(m0 + j) * p.ldy + n;
+        if (p.residual) {
+          const __nv_bfloat162 rb = *reinterpret_cast<const __nv_bfloat162*>(p.residual + o);
+          a0 += __low2float(rb); a1 += __high2float(rb);
+        }
+        *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(p.y) + o) = __floats2bfloat162_rn(a0, a1);
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned total_ctas = gridDim.x * gridDim.y * gridDim.z;
+      const unsigned old = atomicAdd(p.ar.words + 2, 1u);
+      if (old == total_ctas - 1) { p.ar.words[2] = 0; __threadfence(); p.ar.words[0] = ar_epoch; }
+    }
+  } else if (fuse_ar) {
     // ---- all-reduce tail: every CTA of the (co-resident) grid takes part ----
     const PeerTable& t = p.ar.t;
     const unsigned total_ctas = gridDim.x * gridDim.y * gridDim.z;
@@ -420,7 +488,8 @@ extern "C" int b200_w8a8_gemm_decode_grouped(const void* xq, const float* sx, co
 extern "C" int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
                                         const void* residual, int M, int N, int K, int ldy, int* status, int num_sms,
                                         void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
-                                        size_t part_off0, size_t part_off1, void* words, int limit_ms, cudaStream_t stream) {
+                                        size_t part_off0, size_t part_off1, void* words, int limit_ms, int ll,
+                                        size_t recv_off0, size_t recv_off1, size_t recv_bytes, cudaStream_t stream) {
   if (world < 1 || world > MAX_RANKS) return -1;
   ArTail ar;
   for (int r = 0; r < MAX_RANKS; ++r) {
@@ -431,6 +500,11 @@ extern "C" int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const v
   ar.part_off[0] = part_off0; ar.part_off[1] = part_off1;
   ar.words = static_cast<uint32_t*>(words);
   ar.enabled = 1; ar.use_nvls = mc_base != nullptr; ar.limit_ms = limit_ms;
+  ar.ll = ll; ar.recv_off[0] = recv_off0; ar.recv_off[1] = recv_off1;
+  if (ll) {
+    if ((recv_off0 % 8) || (recv_off1 % 8) || (N % 2)) return -2;
+    if (static_cast<size_t>(world) * M * (N / 2) * 8 > recv_bytes) return -21;       // receive slot too small
+  }
   if ((part_off0 % 16) || (part_off1 % 16)) return -2;
   return decode_gemm_impl(xq, sx, wq, sw, y, residual, M, N, K, ldy, 0, status, num_sms, 0, &ar, stream);
 }

@@ -24,10 +24,17 @@ class TPContext:
                  wait_limit_ms: int = 2000):
         self.d_model = d_model
         self.max_tokens = max_tokens
+        import os
+        import torch.distributed as dist
+        world = dist.get_world_size(group)
         small = FUSED_MAX_M * d_model * 2
         big = max(FUSED_MAX_M, max_tokens) * d_model * 2
-        self.heap = SymmetricHeap(2 * small + big + (1 << 20), group=group, device=device)
+        # low-latency all-reduce: per slot, one [M, N/2] array of 8-byte {2 x bf16, epoch} words per source rank
+        self.recv_bytes = world * FUSED_MAX_M * (d_model // 2) * 8
+        self.heap = SymmetricHeap(2 * small + big + 2 * self.recv_bytes + (1 << 20), group=group, device=device)
         self.world, self.rank = self.heap.world, self.heap.rank
+        self.recv_off = [self.heap.alloc(self.recv_bytes), self.heap.alloc(self.recv_bytes)]
+        self.low_latency = os.environ.get("B200RT_AR", "ll") != "barrier"
         # Fused launches alternate between two small slots by the parity of the device-side epoch, so a rank that runs
         # ahead never overwrites a partial a slower rank is still summing.  The unfused path owns a third slot and its
         # all-reduce ends with a barrier, so that slot is free again as soon as the call returns.
@@ -50,7 +57,8 @@ class TPContext:
                 xq.data_ptr(), sx.data_ptr(), lw.qweight.data_ptr(), lw.scale.data_ptr(), out.data_ptr(),
                 _lib.ptr(residual), M, N, K, out.stride(0), ws.status.data_ptr(), _lib.num_sms(xq.device.index),
                 h._c_data, h._c_flags, (h.mc_data_ptr or None) if self.use_nvls else None, h.world, h.rank,
-                self.part_off[0], self.part_off[1], h.epoch_words.data_ptr(), self.limit_ms, _lib.stream())
+                self.part_off[0], self.part_off[1], h.epoch_words.data_ptr(), self.limit_ms,
+                1 if self.low_latency else 0, self.recv_off[0], self.recv_off[1], self.recv_bytes, _lib.stream())
             if rc != -20:
                 _lib.check(rc, "w8a8_gemm_decode_ar")
                 return out
