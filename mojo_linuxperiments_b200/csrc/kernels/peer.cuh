@@ -32,6 +32,11 @@ __device__ __forceinline__ uint32_t* flag_ptr(const PeerTable& t, int receiver, 
 __device__ __forceinline__ void signal_all(const PeerTable& t, int kind, uint32_t epoch, int lane) {
   if (lane < t.world) st_release_sys(flag_ptr(t, lane, kind, t.rank), epoch);
 }
+// Same without the release fence: for signals that publish no data of this kernel ("the buffers an earlier kernel
+// of my stream wrote are ready" - kernel completion already made them visible - or "I have finished reading").
+__device__ __forceinline__ void signal_all_relaxed(const PeerTable& t, int kind, uint32_t epoch, int lane) {
+  if (lane < t.world) st_relaxed_sys(flag_ptr(t, lane, kind, t.rank), epoch);
+}
 // one thread per source rank: wait until every rank reached `epoch`; returns false on timeout (lanes >= world: true)
 __device__ __forceinline__ bool wait_all(const PeerTable& t, int kind, uint32_t epoch, int lane, int* status, uint64_t limit_ns) {
   if (lane >= t.world) return true;

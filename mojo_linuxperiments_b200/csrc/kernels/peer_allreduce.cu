@@ -54,8 +54,9 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ArParams p) {
   if (tid == 0) ok_s = 1;
   __syncthreads();
 
-  // ---- barrier: every rank's contribution is in place ----
-  if (blockIdx.x == 0 && tid < 32) signal_all(t, 0, e0, tid);
+  // ---- barrier: every rank's contribution is in place.  The contribution was written by earlier kernels of this
+  // stream, whose completion made it visible, so the signal needs no fence of its own. ----
+  if (blockIdx.x == 0 && tid < 32) signal_all_relaxed(t, 0, e0, tid);
   if (tid < 32) { if (!wait_all(t, 0, e0, tid, p.status, p.limit_ns)) ok_s = 0; }
   __syncthreads();
   const bool ok = ok_s != 0;
@@ -127,7 +128,17 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ArParams p) {
   } else if (ok && p.algo == 2) {
     // my slice of the vectors: [v0, v1)
     const size_t v0 = nvec * t.rank / t.world, v1 = nvec * (t.rank + 1) / t.world;
-    for (size_t i = v0 + gtid; i < v1; i += gsz) {
+    size_t i = v0 + gtid;
+    if (p.dtype == 0) {
+      for (; i + gsz < v1; i += 2 * gsz) {                 // two independent vectors in flight per thread
+        uint8_t* a = t.mc + p.in_off + i * 16;
+        uint8_t* b = a + gsz * 16;
+        const uint4 va = multimem_ld_reduce_bf16x8(a), vb = multimem_ld_reduce_bf16x8(b);
+        multimem_st_16B(a, va);
+        multimem_st_16B(b, vb);
+      }
+    }
+    for (; i < v1; i += gsz) {
       uint8_t* a = t.mc + p.in_off + i * 16;
       if (p.dtype == 0) {
         multimem_st_16B(a, multimem_ld_reduce_bf16x8(a));
@@ -146,7 +157,7 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ArParams p) {
       if (old == gridDim.x - 1) {
         p.epoch[2] = 0;
         __threadfence_system();
-        for (int r = 0; r < t.world; ++r) st_release_sys(flag_ptr(t, r, 1, t.rank), e0);
+        for (int r = 0; r < t.world; ++r) st_relaxed_sys(flag_ptr(t, r, 1, t.rank), e0);
       }
     }
     if (tid < 32) { if (!wait_all(t, 1, e0, tid, p.status, p.limit_ns)) ok_s = 0; }
@@ -235,14 +246,13 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ArParams p) {
 
   if (p.trailing_barrier) {
     // nobody may overwrite its contribution before every rank has finished reading it
-    __threadfence_system();
     __syncthreads();
     if (tid == 0) {
       __threadfence();
       const uint32_t old = atomicAdd(p.epoch + 3, 1u);
       if (old == gridDim.x - 1) {
         p.epoch[3] = 0;
-        for (int r = 0; r < t.world; ++r) st_release_sys(flag_ptr(t, r, 3, t.rank), e0);
+        for (int r = 0; r < t.world; ++r) st_relaxed_sys(flag_ptr(t, r, 3, t.rank), e0);      // "done reading": no data to publish
       }
     }
     if (blockIdx.x == 0 && tid < 32) wait_all(t, 3, e0, tid, p.status, p.limit_ns);

@@ -287,23 +287,28 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         const int n = n_base + 2 * c2;
         if (n >= p.N) continue;
         const size_t eoff = (static_cast<size_t>(m0 + j) * (p.N / 2) + n / 2) * 8;
-        float a0 = 0.f, a1 = 0.f;
-        for (int r = 0; r < t.world && good; ++r) {                              // fixed order: same bits on every rank
-          const uint8_t* src = mine + r * src_stride + eoff;
-          uint2 v = ld_ll(src);
-          uint32_t spins = 0;
-          while (v.y != ar_epoch) {
-            if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > limit) {
-              if (p.status) atomicCAS(p.status, 0, (ST_TIMEOUT_PEER_FLAG | (2 << 8)));
-              good = false;
-              break;
-            }
-            v = ld_ll(src);
+        // all sources are requested at once so their latencies overlap; words that have not arrived are re-read
+        uint2 v[MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < t.world) v[r] = ld_ll(mine + r * src_stride + eoff);
+        uint32_t spins = 0;
+        while (good) {
+          bool all = true;
+#pragma unroll
+          for (int r = 0; r < MAX_RANKS; ++r)
+            if (r < t.world && v[r].y != ar_epoch) { all = false; v[r] = ld_ll(mine + r * src_stride + eoff); }
+          if (all) break;
+          if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > limit) {
+            if (p.status) atomicCAS(p.status, 0, (ST_TIMEOUT_PEER_FLAG | (2 << 8)));
+            good = false;
           }
-          a0 += __uint_as_float(v.x << 16);
-          a1 += __uint_as_float(v.x & 0xffff0000u);
         }
         if (!good) break;
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)                                      // fixed order: same bits on every rank
+          if (r < t.world) { a0 += __uint_as_float(v[r].x << 16); a1 += __uint_as_float(v[r].x & 0xffff0000u); }
         const size_t o = static_cast<size_t>(m0 + j) * p.ldy + n;
         if (p.residual) {
           const __nv_bfloat162 rb = *reinterpret_cast<const __nv_bfloat162*>(p.residual + o);

@@ -67,11 +67,19 @@ class TPContext:
         off = self.big_off
         part = h.tensor(off, (M, N), torch.bfloat16)
         L.w8a8_gemm(xq, sx, lw.qweight, lw.scale, out=part)
+        return self._reduce_slot(off, part, M, N, out, residual)
+
+    def _reduce_slot(self, off, part, M, N, out, residual):
+        """All-reduce the bf16 [M, N] partial every rank holds at ``off``.  Large messages are reduced in place through
+        the switch (two-shot NVLS) and the heap view itself is returned - no copy; the view stays valid until the next
+        unfused collective of this context, which in a decoder is after its consumer ran."""
+        h = self.heap
         nbytes = M * N * 2
-        if self.use_nvls and nbytes % 16 == 0:
-            algo = AR_ONE_SHOT_NVLS if nbytes <= (512 << 10) else AR_TWO_SHOT_NVLS
-        else:
-            algo = AR_ONE_SHOT_P2P
+        if self.use_nvls and nbytes % 16 == 0 and nbytes > (512 << 10) and residual is None:
+            h.all_reduce(off, M * N, torch.bfloat16, None, algo=AR_TWO_SHOT_NVLS, trailing_barrier=False,
+                         limit_ms=self.limit_ms, max_ctas=128)
+            return part
+        algo = AR_ONE_SHOT_NVLS if (self.use_nvls and nbytes % 16 == 0) else AR_ONE_SHOT_P2P
         h.all_reduce(off, M * N, torch.bfloat16, out, algo=algo, residual=residual, trailing_barrier=True,
                      limit_ms=self.limit_ms, max_ctas=128)
         return out
@@ -82,14 +90,7 @@ class TPContext:
         part = h.tensor(self.big_off, (M, N), torch.bfloat16)
         produce(part)
         out = torch.empty((M, N), dtype=torch.bfloat16, device=part.device)
-        nbytes = M * N * 2
-        if self.use_nvls and nbytes % 16 == 0:
-            algo = AR_ONE_SHOT_NVLS if nbytes <= (512 << 10) else AR_TWO_SHOT_NVLS
-        else:
-            algo = AR_ONE_SHOT_P2P
-        h.all_reduce(self.big_off, M * N, torch.bfloat16, out, algo=algo, trailing_barrier=True, limit_ms=self.limit_ms,
-                     max_ctas=128)
-        return out
+        return self._reduce_slot(self.big_off, part, M, N, out, None)
 
     def argmax(self, cand_val: torch.Tensor, cand_idx: torch.Tensor) -> torch.Tensor:
         """cand_* [ncand, rows] of this rank's vocabulary shard -> global greedy token per row (same on all ranks)."""
