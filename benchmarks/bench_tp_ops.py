@@ -85,11 +85,14 @@ def main():
         x.normal_()
         out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
         r = {"op": "all_reduce bf16", "bytes": nbytes, "world": world}
-        algos = [("p2p_one_shot", S.AR_ONE_SHOT_P2P)] + ([("nvls_one_shot", S.AR_ONE_SHOT_NVLS), ("nvls_two_shot", S.AR_TWO_SHOT_NVLS)] if heap.has_multicast else [])
+        ll_recv = tp.ll_recv_off
+        algos = ([("low_latency", S.AR_LOW_LATENCY)] if nbytes <= (512 << 10) else []) + [("p2p_one_shot", S.AR_ONE_SHOT_P2P)] + ([("nvls_one_shot", S.AR_ONE_SHOT_NVLS), ("nvls_two_shot", S.AR_TWO_SHOT_NVLS)] if heap.has_multicast else [])
         for name, algo in algos:
             if algo == S.AR_ONE_SHOT_P2P and nbytes > (8 << 20):
                 continue
-            r[name + "_us"] = graph_time(lambda: heap.all_reduce(off, n, torch.bfloat16, out, algo=algo, max_ctas=128), iters=10)
+            r[name + "_us"] = graph_time(lambda: heap.all_reduce(off, n, torch.bfloat16, out if algo != S.AR_TWO_SHOT_NVLS else None,
+                                                                 algo=algo, scratch_offset=ll_recv, max_ctas=128,
+                                                                 trailing_barrier=algo not in (S.AR_LOW_LATENCY, S.AR_TWO_SHOT_NVLS)), iters=10)
         y = x.clone()
         r["nccl_us"] = graph_time(lambda: dist.all_reduce(y), iters=10)
         r["busbw_gbs_best_ours"] = 2 * (world - 1) / world * nbytes / (min(v for k, v in r.items() if k.endswith("_us") and k != "nccl_us") * 1e-6) / 1e9

@@ -83,15 +83,16 @@ int b200_fill_uniform_reduce(float* out, unsigned long long begin, unsigned long
 
 // ---- collectives over peer-mapped memory ---------------------------------------------------------------
 // peer_data / peer_flags: host arrays [world] of device pointers (rank r's heap base / flag block as mapped here).
-// algo: 0 one-shot peer loads, 1 one-shot NVLS, 2 two-shot NVLS (in place), 3 chain to rank 0, 4 butterfly.
+// algo: 0 one-shot peer loads, 1 one-shot NVLS, 2 two-shot NVLS (in place), 3 chain to rank 0, 4 butterfly,
+// 5 low-latency push of {payload, epoch} words (bf16, receive area of 2 * world * n * 4 bytes at scratch_off).
 int b200_peer_allreduce(void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
                         size_t in_off, size_t scratch_off, void* out, const void* residual, size_t n, int dtype,
                         int algo, void* epoch_words, int* status, int limit_ms, int trailing_barrier, int max_ctas,
                         cudaStream_t stream);
 
-int b200_peer_argmax(void* const* peer_data, void* const* peer_flags, int world, int rank, size_t val_off,
-                     size_t idx_off, int ncand, int rows, long long* out_idx, void* epoch_words, int* status,
-                     int limit_ms, cudaStream_t stream);
+int b200_peer_argmax(void* const* peer_data, void* const* peer_flags, int world, int rank, size_t recv_off,
+                     const float* cand_val, const long long* cand_idx, int ncand, int rows, long long* out_idx,
+                     void* epoch_words, int* status, int limit_ms, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

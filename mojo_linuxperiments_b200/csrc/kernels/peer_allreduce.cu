@@ -54,6 +54,54 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ArParams p) {
   if (tid == 0) ok_s = 1;
   __syncthreads();
 
+  if (p.algo == 5) {
+    // Low-latency form for small bf16 messages: no barrier at all.  Every rank pushes its contribution as 8-byte
+    // {2 x bf16, epoch} words into slot (epoch & 1) of every rank's receive area ([source][n/2] words at scratch_off)
+    // and sums the world copies that arrive in its own.  The contribution was written by earlier kernels of the stream.
+    const size_t nw = p.n / 2;
+    const size_t src_stride = nw * 8;
+    const size_t slot = p.scratch_off + static_cast<size_t>(e0 & 1) * t.world * src_stride;
+    const uint32_t* mine_in = reinterpret_cast<const uint32_t*>(t.data[t.rank] + p.in_off);
+    const size_t g0 = static_cast<size_t>(blockIdx.x) * blockDim.x + tid, gs = static_cast<size_t>(gridDim.x) * blockDim.x;
+    for (size_t i = g0; i < nw; i += gs) {
+      const size_t off = slot + t.rank * src_stride + i * 8;
+      const uint32_t payload = mine_in[i];
+      if (t.mc) multimem_st_ll(t.mc + off, payload, e0);
+      else for (int r = 0; r < t.world; ++r) st_ll_peer(t.data[r] + off, payload, e0);
+    }
+    const uint8_t* mine = t.data[t.rank] + slot;
+    const uint64_t t_start = globaltimer_ns();
+    bool good = true;
+    for (size_t i = g0; i < nw && good; i += gs) {
+      uint2 v[MAX_RANKS];
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r) if (r < t.world) v[r] = ld_ll(mine + r * src_stride + i * 8);
+      uint32_t spins = 0;
+      while (good) {
+        bool all = true;
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r)
+          if (r < t.world && v[r].y != e0) { all = false; v[r] = ld_ll(mine + r * src_stride + i * 8); }
+        if (all) break;
+        if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > p.limit_ns) {
+          if (p.status) atomicCAS(p.status, 0, (int)ST_TIMEOUT_PEER_FLAG);
+          good = false;
+        }
+      }
+      if (!good) break;
+      float a0 = 0.f, a1 = 0.f;
+#pragma unroll
+      for (int r = 0; r < MAX_RANKS; ++r) if (r < t.world) { a0 += __uint_as_float(v[r].x << 16); a1 += __uint_as_float(v[r].x & 0xffff0000u); }
+      if (p.residual) {
+        const __nv_bfloat162 rb = reinterpret_cast<const __nv_bfloat162*>(p.residual)[i];
+        a0 += __low2float(rb); a1 += __high2float(rb);
+      }
+      reinterpret_cast<__nv_bfloat162*>(p.out)[i] = __floats2bfloat162_rn(a0, a1);
+    }
+    finish_launch(p, 1);
+    return;
+  }
+
   // ---- barrier: every rank's contribution is in place.  The contribution was written by earlier kernels of this
   // stream, whose completion made it visible, so the signal needs no fence of its own. ----
   if (blockIdx.x == 0 && tid < 32) signal_all_relaxed(t, 0, e0, tid);
@@ -265,7 +313,9 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ArParams p) {
 // world*ncand candidates and keeps the largest value (lowest index on ties), so all ranks agree without a broadcast.
 struct ArgmaxParams {
   PeerTable t;
-  size_t val_off, idx_off;
+  size_t val_off, idx_off;       // val_off: receive area (2 slots x world x rows x 16 bytes); idx_off unused
+  const float* cand_val;         // local candidates [ncand][rows]
+  const long long* cand_idx;
   int ncand, rows;
   long long* out_idx;
   uint32_t* epoch;
@@ -274,42 +324,52 @@ struct ArgmaxParams {
 };
 
 __global__ void __launch_bounds__(128) peer_argmax_kernel(const ArgmaxParams p) {
-  pdl_launch_dependents();   // the next kernel may start its prologue now
-  pdl_wait();                // everything before this kernel in the stream has completed
-
+  pdl_launch_dependents();
+  pdl_wait();
+  // Low-latency exchange: every rank reduces its own candidates to one (value, index) per row, pushes it as two
+  // 8-byte {payload, epoch} words into every rank's receive area and picks the best of the world pairs that arrive
+  // in its own - one NVLink trip, no barrier.  Receive area: val_off, two slots by epoch parity, [source][row][2].
   const PeerTable& t = p.t;
   const uint32_t e0 = *reinterpret_cast<volatile uint32_t*>(p.epoch) + 1;
-  __shared__ int ok_s;
-  if (threadIdx.x == 0) ok_s = 1;
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    signal_all(t, 0, e0, threadIdx.x);
-    if (!wait_all(t, 0, e0, threadIdx.x, p.status, p.limit_ns)) ok_s = 0;
-  }
-  __syncthreads();
-  if (ok_s) {
-    for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
-      float best = -INFINITY;
-      long long bi = 0x7fffffffffffffffll;
-      for (int w = 0; w < t.world; ++w) {
-        const volatile float* v = reinterpret_cast<const volatile float*>(t.data[w] + p.val_off);
-        const volatile long long* ix = reinterpret_cast<const volatile long long*>(t.data[w] + p.idx_off);
-        for (int c = 0; c < p.ncand; ++c) {
-          const float val = v[static_cast<size_t>(c) * p.rows + r];
-          const long long idx = ix[static_cast<size_t>(c) * p.rows + r];
-          if (val > best || (val == best && idx < bi)) { best = val; bi = idx; }
-        }
-      }
-      p.out_idx[r] = bi;
+  const size_t src_stride = static_cast<size_t>(p.rows) * 16;
+  const size_t slot = p.val_off + static_cast<size_t>(e0 & 1) * t.world * src_stride;
+  const uint64_t t_start = globaltimer_ns();
+  for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
+    float best = -INFINITY;
+    long long bi = 0x7fffffffll;
+    for (int c = 0; c < p.ncand; ++c) {
+      const float val = p.cand_val[static_cast<size_t>(c) * p.rows + r];
+      const long long idx = p.cand_idx[static_cast<size_t>(c) * p.rows + r];
+      if (val > best || (val == best && idx < bi)) { best = val; bi = idx; }
+    }
+    const size_t off = slot + t.rank * src_stride + static_cast<size_t>(r) * 16;
+    for (int w = 0; w < t.world; ++w) {
+      st_ll_peer(t.data[w] + off, __float_as_uint(best), e0);
+      st_ll_peer(t.data[w] + off + 8, static_cast<uint32_t>(bi), e0);
     }
   }
-  // nobody rewrites its candidates before everyone has read them
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    signal_all(t, 3, e0, threadIdx.x);
-    wait_all(t, 3, e0, threadIdx.x, p.status, p.limit_ns);
+  for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
+    float best = -INFINITY;
+    long long bi = 0x7fffffffll;
+    bool good = true;
+    for (int w = 0; w < t.world && good; ++w) {
+      const uint8_t* src = t.data[t.rank] + slot + w * src_stride + static_cast<size_t>(r) * 16;
+      uint2 a = ld_ll(src), b = ld_ll(src + 8);
+      uint32_t spins = 0;
+      while (a.y != e0 || b.y != e0) {
+        if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > p.limit_ns) {
+          if (p.status) atomicCAS(p.status, 0, (int)ST_TIMEOUT_PEER_FLAG);
+          good = false;
+          break;
+        }
+        a = ld_ll(src); b = ld_ll(src + 8);
+      }
+      if (!good) break;
+      const float val = __uint_as_float(a.x);
+      const long long idx = static_cast<long long>(b.x);
+      if (val > best || (val == best && idx < bi)) { best = val; bi = idx; }
+    }
+    p.out_idx[r] = bi;
   }
   __syncthreads();
   if (threadIdx.x == 0) { __threadfence(); p.epoch[0] = e0; }
@@ -319,17 +379,19 @@ __global__ void __launch_bounds__(128) peer_argmax_kernel(const ArgmaxParams p) 
 
 using namespace b200;
 
-extern "C" int b200_peer_argmax(void* const* peer_data, void* const* peer_flags, int world, int rank, size_t val_off,
-                                size_t idx_off, int ncand, int rows, long long* out_idx, void* epoch_words, int* status,
-                                int limit_ms, cudaStream_t stream) {
-  if (world < 1 || world > MAX_RANKS || rows <= 0 || ncand <= 0) return -1;
+// cand_val / cand_idx: this rank's local candidates [ncand][rows] (ordinary device memory); recv_off: byte offset of a
+// receive area of 2 * world * rows * 16 bytes in every heap.  Indices must fit 31 bits.
+extern "C" int b200_peer_argmax(void* const* peer_data, void* const* peer_flags, int world, int rank, size_t recv_off,
+                                const float* cand_val, const long long* cand_idx, int ncand, int rows, long long* out_idx,
+                                void* epoch_words, int* status, int limit_ms, cudaStream_t stream) {
+  if (world < 1 || world > MAX_RANKS || rows <= 0 || ncand <= 0 || (recv_off % 8)) return -1;
   ArgmaxParams p;
   for (int r = 0; r < MAX_RANKS; ++r) {
     p.t.data[r] = r < world ? static_cast<uint8_t*>(peer_data[r]) : nullptr;
     p.t.flags[r] = r < world ? static_cast<uint32_t*>(peer_flags[r]) : nullptr;
   }
   p.t.mc = nullptr; p.t.world = world; p.t.rank = rank;
-  p.val_off = val_off; p.idx_off = idx_off; p.ncand = ncand; p.rows = rows; p.out_idx = out_idx;
+  p.val_off = recv_off; p.idx_off = 0; p.cand_val = cand_val; p.cand_idx = cand_idx; p.ncand = ncand; p.rows = rows; p.out_idx = out_idx;
   p.epoch = static_cast<uint32_t*>(epoch_words); p.status = status;
   p.limit_ns = static_cast<unsigned long long>(limit_ms > 0 ? limit_ms : 2000) * 1000000ull;
   launch_ex(peer_argmax_kernel, dim3(1), dim3(128), 0, stream, 0, p);
@@ -343,7 +405,8 @@ extern "C" int b200_peer_allreduce(void* const* peer_data, void* const* peer_fla
                                    int algo, void* epoch_words, int* status, int limit_ms, int trailing_barrier, int max_ctas,
                                    cudaStream_t stream) {
   if (world < 1 || world > MAX_RANKS || rank < 0 || rank >= world || n == 0) return -1;
-  if (dtype < 0 || dtype > 2 || algo < 0 || algo > 4) return -1;
+  if (dtype < 0 || dtype > 2 || algo < 0 || algo > 5) return -1;
+  if (algo == 5 && (dtype != 0 || (n % 2) || !out || (scratch_off % 8))) return -3;
   if ((algo == 1 || algo == 2) && (!mc_base || dtype == 2)) return -3;
   if ((algo == 3 || algo == 4) && dtype == 0) return -3;
   if ((algo == 0 || algo == 1) && !out) return -1;

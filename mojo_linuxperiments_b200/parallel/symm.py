@@ -17,7 +17,7 @@ import torch.distributed as dist
 from ..ops import _lib
 
 FLAG_BYTES = 4096
-AR_ONE_SHOT_P2P, AR_ONE_SHOT_NVLS, AR_TWO_SHOT_NVLS, AR_CHAIN, AR_BUTTERFLY = 0, 1, 2, 3, 4
+AR_ONE_SHOT_P2P, AR_ONE_SHOT_NVLS, AR_TWO_SHOT_NVLS, AR_CHAIN, AR_BUTTERFLY, AR_LOW_LATENCY = 0, 1, 2, 3, 4, 5
 _DTYPES = {torch.bfloat16: 0, torch.float32: 1, torch.float64: 2}
 
 

@@ -14,7 +14,7 @@ from ..ops import _lib
 from ..ops import attention as A
 from ..ops import linear as L
 from ..ops.workspace import default_workspace
-from .symm import SymmetricHeap, AR_ONE_SHOT_NVLS, AR_ONE_SHOT_P2P, AR_TWO_SHOT_NVLS
+from .symm import SymmetricHeap, AR_LOW_LATENCY, AR_ONE_SHOT_NVLS, AR_ONE_SHOT_P2P, AR_TWO_SHOT_NVLS
 
 FUSED_MAX_M = 64
 
@@ -40,8 +40,9 @@ class TPContext:
         # all-reduce ends with a barrier, so that slot is free again as soon as the call returns.
         self.part_off = [self.heap.alloc(small), self.heap.alloc(small)]
         self.big_off = self.heap.alloc(big)
-        self.cand_val_off = self.heap.alloc(64 * 1024)
-        self.cand_idx_off = self.heap.alloc(128 * 1024)
+        self.cand_recv_off = self.heap.alloc(2 * world * 1024 * 16)        # arg-max exchange: up to 1,024 rows
+        self.ll_recv_bytes = 2 * world * (512 << 10) * 2                     # low-latency all-reduce of <= 512 KiB
+        self.ll_recv_off = self.heap.alloc(self.ll_recv_bytes)
         self.use_nvls = self.heap.has_multicast if use_nvls is None else (use_nvls and self.heap.has_multicast)
         self.limit_ms = wait_limit_ms
 
@@ -79,6 +80,10 @@ class TPContext:
             h.all_reduce(off, M * N, torch.bfloat16, None, algo=AR_TWO_SHOT_NVLS, trailing_barrier=False,
                          limit_ms=self.limit_ms, max_ctas=128)
             return part
+        if self.low_latency and nbytes <= (512 << 10) and (M * N) % 2 == 0:
+            h.all_reduce(off, M * N, torch.bfloat16, out, algo=AR_LOW_LATENCY, residual=residual, scratch_offset=self.ll_recv_off,
+                         trailing_barrier=False, limit_ms=self.limit_ms, max_ctas=128)
+            return out
         algo = AR_ONE_SHOT_NVLS if (self.use_nvls and nbytes % 16 == 0) else AR_ONE_SHOT_P2P
         h.all_reduce(off, M * N, torch.bfloat16, out, algo=algo, residual=residual, trailing_barrier=True,
                      limit_ms=self.limit_ms, max_ctas=128)
@@ -95,13 +100,11 @@ class TPContext:
     def argmax(self, cand_val: torch.Tensor, cand_idx: torch.Tensor) -> torch.Tensor:
         """cand_* [ncand, rows] of this rank's vocabulary shard -> global greedy token per row (same on all ranks)."""
         ncand, rows = cand_val.shape
-        assert ncand * rows * 4 <= 64 * 1024
+        assert rows <= 1024 and cand_val.is_contiguous() and cand_idx.is_contiguous()
         h = self.heap
-        h.tensor(self.cand_val_off, (ncand, rows), torch.float32).copy_(cand_val)
-        h.tensor(self.cand_idx_off, (ncand, rows), torch.int64).copy_(cand_idx)
         out = torch.empty(rows, dtype=torch.int64, device=cand_val.device)
-        rc = _lib.lib().b200_peer_argmax(h._c_data, h._c_flags, h.world, h.rank, self.cand_val_off, self.cand_idx_off,
-                                         ncand, rows, out.data_ptr(), h.epoch_words.data_ptr(), h.status.data_ptr(),
-                                         self.limit_ms, _lib.stream())
+        rc = _lib.lib().b200_peer_argmax(h._c_data, h._c_flags, h.world, h.rank, self.cand_recv_off, cand_val.data_ptr(),
+                                         cand_idx.data_ptr(), ncand, rows, out.data_ptr(), h.epoch_words.data_ptr(),
+                                         h.status.data_ptr(), self.limit_ms, _lib.stream())
         _lib.check(rc, "peer_argmax")
         return out

@@ -24,6 +24,7 @@ def main():
         if not cond:
             failures.append(name)
 
+    ll_recv = heap.alloc(2 * world * (512 << 10) * 2)      # receive area of the low-latency algorithm
     # bf16 messages of several sizes, every algorithm that applies
     for n in (8, 4096, 32 * 4096, 1024 * 4096 + 8):
         off, x = heap.alloc_tensor((n,), torch.bfloat16)
@@ -34,11 +35,13 @@ def main():
             dist.all_reduce(ref)
             res = torch.randn(n, device="cuda", generator=g).to(torch.bfloat16)
             algos = [S.AR_ONE_SHOT_P2P] + ([S.AR_ONE_SHOT_NVLS, S.AR_TWO_SHOT_NVLS] if heap.has_multicast else [])
+            if n % 2 == 0 and n * 2 <= (512 << 10):
+                algos.append(S.AR_LOW_LATENCY)
             for algo in algos:
                 if algo == S.AR_TWO_SHOT_NVLS:
                     keep = x.clone()
                 out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
-                heap.all_reduce(off, n, torch.bfloat16, out, algo=algo, residual=res)
+                heap.all_reduce(off, n, torch.bfloat16, out, algo=algo, residual=res, scratch_offset=ll_recv)
                 torch.cuda.synchronize()
                 heap.check_status()
                 want = ref + res.float()
