@@ -31,7 +31,10 @@ class TPContext:
         big = max(FUSED_MAX_M, max_tokens) * d_model * 2
         # low-latency all-reduce: per slot, one [M, N/2] array of 8-byte {2 x bf16, epoch} words per source rank
         self.recv_bytes = world * FUSED_MAX_M * (d_model // 2) * 8
-        self.heap = SymmetricHeap(2 * small + big + 2 * self.recv_bytes + (1 << 20), group=group, device=device)
+        cand_bytes = 2 * world * 1024 * 16                                   # arg-max exchange: up to 1,024 rows
+        self.ll_recv_bytes = 2 * world * (512 << 10) * 2                     # low-latency all-reduce of <= 512 KiB
+        total = 2 * small + big + 2 * self.recv_bytes + cand_bytes + self.ll_recv_bytes
+        self.heap = SymmetricHeap(total + (1 << 20), group=group, device=device)
         self.world, self.rank = self.heap.world, self.heap.rank
         self.recv_off = [self.heap.alloc(self.recv_bytes), self.heap.alloc(self.recv_bytes)]
         self.low_latency = os.environ.get("B200RT_AR", "ll") != "barrier"
@@ -40,8 +43,7 @@ class TPContext:
         # all-reduce ends with a barrier, so that slot is free again as soon as the call returns.
         self.part_off = [self.heap.alloc(small), self.heap.alloc(small)]
         self.big_off = self.heap.alloc(big)
-        self.cand_recv_off = self.heap.alloc(2 * world * 1024 * 16)        # arg-max exchange: up to 1,024 rows
-        self.ll_recv_bytes = 2 * world * (512 << 10) * 2                     # low-latency all-reduce of <= 512 KiB
+        self.cand_recv_off = self.heap.alloc(cand_bytes)
         self.ll_recv_off = self.heap.alloc(self.ll_recv_bytes)
         self.use_nvls = self.heap.has_multicast if use_nvls is None else (use_nvls and self.heap.has_multicast)
         self.limit_ms = wait_limit_ms
