@@ -82,7 +82,7 @@ class TPContext:
             h.all_reduce(off, M * N, torch.bfloat16, None, algo=AR_TWO_SHOT_NVLS, trailing_barrier=False,
                          limit_ms=self.limit_ms, max_ctas=128)
             return part
-        if self.low_latency and nbytes <= (512 << 10) and (M * N) % 2 == 0:
+        if self.low_latency and nbytes <= (16 << 10) and (M * N) % 2 == 0:
             h.all_reduce(off, M * N, torch.bfloat16, out, algo=AR_LOW_LATENCY, residual=residual, scratch_offset=self.ll_recv_off,
                          trailing_barrier=False, limit_ms=self.limit_ms, max_ctas=128)
             return out
