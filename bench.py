@@ -40,6 +40,7 @@ def parse():
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--model", default="llama3-8b")
     ap.add_argument("--skip-extra", action="store_true", help="only the headline number (no bs-1 / TTFT / e2e runs)")
+    ap.add_argument("--layers", type=int, default=0, help="smoke runs only: override the layer count (the line is then marked invalid)")
     return ap.parse_args()
 
 
@@ -142,8 +143,12 @@ def make_engine(args, world, rank, batch):
     from mojo_linuxperiments_b200.models import config as C
     from mojo_linuxperiments_b200.parallel.comm import Comm
     cfg = C.PRESETS[args.model]()
+    if args.layers > 0:
+        from dataclasses import replace
+        cfg = replace(cfg, n_layers=args.layers)
     total = args.prompt_len + args.warmup + args.steps + 16
-    rt = C.RuntimeConfig.from_env(tp=world, ep=world, max_batch=batch, max_seq_len=(total + 127) // 128 * 128)
+    rt = C.RuntimeConfig.from_env(tp=world, ep=world, max_batch=batch, max_seq_len=(total + 127) // 128 * 128,
+                                  max_prefill_tokens=16384)
     if args.impl == "torch_baseline":
         from baseline.torch_baseline import BaselineEngine
         return cfg, rt, BaselineEngine(cfg, rt, seed=0, comm=Comm() if world > 1 else Comm.single())
@@ -188,7 +193,7 @@ def run(args):
         "config": {"model": MODEL if args.model == "llama3-8b" else args.model, "global_batch": B, "seq_len": S,
                    "parallelism": f"tp{world}", "decode_context": f"{S}..{S + W + K}",
                    "l2_note": "every step streams this rank's int8 weights (>= 1 GB) from HBM: inputs larger than the 126 MB L2"},
-        "clocks": clocks, "gpu_launches": int(per_step) * K, "kernels_per_step": int(per_step),
+        "valid": args.layers == 0, "clocks": clocks, "gpu_launches": int(per_step) * K, "kernels_per_step": int(per_step),
     }
 
     extra = {}

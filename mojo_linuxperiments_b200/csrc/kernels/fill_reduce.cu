@@ -22,7 +22,9 @@ __global__ void __launch_bounds__(256) fill_uniform_reduce_kernel(float* out, un
   __shared__ int last;
   // work in whole Philox blocks of four elements; `begin` is a multiple of 4 (checked on the host)
   const unsigned long long nblk = (end - begin + 3) / 4;
-  double s = 0.0;
+  // Every value is k * 2^-23 - 1 with a 24-bit integer k, so the sum is accumulated exactly in integers (cheap) and
+  // converted once: sum = 2^-23 * sum(k) - count.  The result does not depend on how the index space is split.
+  unsigned long long ksum = 0, cnt = 0;
   for (unsigned long long b = static_cast<unsigned long long>(blockIdx.x) * blockDim.x + threadIdx.x; b < nblk;
        b += static_cast<unsigned long long>(gridDim.x) * blockDim.x) {
     const unsigned long long i = begin + 4 * b;
@@ -32,12 +34,14 @@ __global__ void __launch_bounds__(256) fill_uniform_reduce_kernel(float* out, un
     v.z = u32_to_uniform_pm1(r.v[2]); v.w = u32_to_uniform_pm1(r.v[3]);
     if (i + 4 <= end) {
       *reinterpret_cast<float4*>(out + (i - begin)) = v;
-      s += static_cast<double>(v.x) + static_cast<double>(v.y) + static_cast<double>(v.z) + static_cast<double>(v.w);
+      ksum += static_cast<unsigned long long>((r.v[0] >> 8) + (r.v[1] >> 8)) + ((r.v[2] >> 8) + (r.v[3] >> 8));
+      cnt += 4;
     } else {
       const float e[4] = {v.x, v.y, v.z, v.w};
-      for (int k = 0; k < 4 && i + k < end; ++k) { out[i - begin + k] = e[k]; s += e[k]; }
+      for (int k = 0; k < 4 && i + k < end; ++k) { out[i - begin + k] = e[k]; ksum += r.v[k] >> 8; ++cnt; }
     }
   }
+  double s = static_cast<double>(ksum) * (2.0 / 16777216.0) - static_cast<double>(cnt);
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;

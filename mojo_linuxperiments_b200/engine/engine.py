@@ -55,19 +55,25 @@ class Engine:
 
     def prefill(self, prompts: torch.Tensor) -> torch.Tensor:
         """prompts int64 [B, S] (host or device; equal lengths).  Returns the first generated token per sequence
-        (device tensor) and leaves the engine ready for ``decode_step``."""
+        (device tensor) and leaves the engine ready for ``decode_step``.  Long batches are processed in groups of
+        whole sequences so that one call never carries more than ``rt.max_prefill_tokens`` tokens."""
         B, S = prompts.shape
-        ids = prompts.to(self.device, non_blocking=True).reshape(-1)
-        positions = torch.arange(S, dtype=torch.int32, device=self.device).repeat(B)
-        seq_ids = torch.arange(B, dtype=torch.int32, device=self.device).repeat_interleave(S)
-        cu = torch.arange(0, (B + 1) * S, S, dtype=torch.int32, device=self.device)
-        last = torch.arange(S - 1, B * S, S, dtype=torch.int64, device=self.device)
-        nxt = self.model.forward(ids, positions, self.kv, mode="prefill", cu_seqlens=cu, max_len=S, seq_ids=seq_ids,
-                                 last_idx=last)
-        self.tokens.copy_(nxt)
+        ids_all = prompts.to(self.device, non_blocking=True)
+        group = max(1, min(B, self.rt.max_prefill_tokens // S))
+        for b0 in range(0, B, group):
+            b1 = min(B, b0 + group)
+            n = b1 - b0
+            ids = ids_all[b0:b1].reshape(-1)
+            positions = torch.arange(S, dtype=torch.int32, device=self.device).repeat(n)
+            seq_ids = torch.arange(b0, b1, dtype=torch.int32, device=self.device).repeat_interleave(S)
+            cu = torch.arange(0, (n + 1) * S, S, dtype=torch.int32, device=self.device)
+            last = torch.arange(S - 1, n * S, S, dtype=torch.int64, device=self.device)
+            nxt = self.model.forward(ids, positions, self.kv, mode="prefill", cu_seqlens=cu, max_len=S, seq_ids=seq_ids,
+                                     last_idx=last)
+            self.tokens[b0:b1].copy_(nxt)
         self.positions.fill_(S)
         self.kv.seq_lens.fill_(S + 1)      # the next decode step attends to the prompt plus its own token
-        return nxt
+        return self.tokens.clone()
 
     def _decode_body(self) -> None:
         nxt = self.model.forward(self.tokens, self.positions, self.kv, mode="decode", max_len=self.rt.max_seq_len)
