@@ -94,6 +94,32 @@ int b200_peer_argmax(void* const* peer_data, void* const* peer_flags, int world,
                      const float* cand_val, const long long* cand_idx, int ncand, int rows, long long* out_idx,
                      void* epoch_words, int* status, int limit_ms, cudaStream_t stream);
 
+// ---- tensor-parallel prefill linears fused with their collective (token-sharded layout between blocks) ----------
+// All offsets are byte offsets into every rank's symmetric heap (peer_data[r] = rank r's heap as mapped here).
+// Rank r owns token rows [r*rows_per_rank, (r+1)*rows_per_rank) of the M rows.  phase: 7 in production (1 tiles,
+// 2 scatter tail, 4 gather push; subsets only for single-device tests that run virtual ranks as consecutive launches).
+//
+// All-gather -> GEMM: y[M,N] = gathered(xq_local)[M,K] * wq[N,K]^T, scaled.  Gather buffers (two, by epoch parity):
+// int8 [m_cap][K] at q_off*, fp32 [m_cap] at s_off*; flags uint32 [world][blk_cap] at flag_off; done words uint32
+// [world] at done_off; words: 2 local uint32 (epoch, exit counter), row_ctr: blk_cap local uint32, all zero at first.
+// finish != 0 acknowledges the epoch at exit; with 0 the gather buffer stays valid until b200_ag_sync(finish=1).
+int b200_w8a8_gemm_ag(const void* xq_local, const float* sx_local, const void* wq, const float* sw, void* y,
+                      int M, int N, int K, int ldy, int rows_per_rank, void* const* peer_data, void* mc_base,
+                      int world, int rank, size_t q_off0, size_t q_off1, size_t s_off0, size_t s_off1,
+                      size_t flag_off, size_t done_off, int blk_cap, int m_cap, void* words, void* row_ctr,
+                      int finish, int phase, int* status, int limit_ms, int num_sms, cudaStream_t stream);
+// GEMM -> reduce-scatter: out[my rows, N] = sum over ranks of (xq[M,K_shard] * wq^T) (+ residual[my rows]).
+// Receive slots (two, by parity): bf16 [world][r_cap][N] at recv_off*; arrival counters uint32 [2] at ctr_off (zero at
+// first); words: 2 local uint32.
+int b200_w8a8_gemm_rs(const void* xq, const float* sx, const void* wq, const float* sw, void* out,
+                      const void* residual, int M, int N, int K, int ldo, int ldr, int rows_per_rank,
+                      void* const* peer_data, int world, int rank, size_t recv_off0, size_t recv_off1,
+                      size_t ctr_off, int r_cap, void* words, int phase, int* status, int limit_ms, int num_sms,
+                      cudaStream_t stream);
+int b200_ag_sync(void* const* peer_data, int world, int rank, size_t flag_off, size_t done_off, int blk_cap,
+                 int rows_per_rank, int M, void* words, int wait, int finish, int* status, int limit_ms,
+                 cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -12,15 +12,15 @@ def test_stream_pool_launch_wait_any_order_and_reuse():
     pool = StreamPool(3)
     assert pool.wait_any(0.1) == -1
     out = torch.zeros(3, device="cuda")
-    a = torch.randn((4096, 4096), device="cuda", dtype=torch.bfloat16)
+    a = torch.randn((8192, 8192), device="cuda", dtype=torch.bfloat16)
 
     def work(i, reps):
         x = a
-        for _ in range(reps):                         # reps x ~0.1 ms of device work, queued asynchronously
+        for _ in range(reps):                         # reps x ~0.8 ms of device work, queued asynchronously
             x = (x @ a) * 1e-2
         out[i] = i + 1
 
-    for i, reps in enumerate((400, 100, 2)):
+    for i, reps in enumerate((80, 20, 1)):
         assert pool.launch(work, i, reps) == i
     assert pool.launch(work, 0, 1) == -1              # every slot busy
     order = [pool.wait_any(10.0) for _ in range(3)]

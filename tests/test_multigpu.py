@@ -52,3 +52,15 @@ def test_expert_parallel_tiny_moe(nproc):
     p = _run("mp_tp_model.py", nproc, "fused", "moe")
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     assert "FAILURES 0" in p.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("nproc", [2, 8])
+def test_sequence_parallel_fused_linears(nproc):
+    """All-gather->GEMM and GEMM->reduce-scatter kernels over real peer memory (NVLS stores and plain peer stores)."""
+    if NGPU < nproc:
+        pytest.skip(f"needs {nproc} GPUs, found {NGPU}")
+    p = _run("mp_sp_ops.py", nproc)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert "FAILURES 0" in p.stdout
