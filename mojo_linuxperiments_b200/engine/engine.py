@@ -113,6 +113,8 @@ class Engine:
         default_workspace(self.device).check_status()
         if self.tp_ctx is not None:
             self.tp_ctx.heap.check_status()
+            if self.tp_ctx.sp is not None:
+                self.tp_ctx.sp.check_status()
 
     def step_from_host(self, ids_in: torch.Tensor, ids_out: torch.Tensor) -> torch.Tensor:
         """Serving-loop form of a decode step: token ids arrive in pinned host memory (the previous step's sample,

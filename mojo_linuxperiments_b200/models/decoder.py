@@ -121,6 +121,9 @@ class Decoder:
         mode "decode":  M = batch, one token per sequence, kv.seq_lens already counts the current token.
         """
         cfg = self.cfg
+        if (mode == "prefill" and self.moe is None and self.tp_ctx is not None and last_idx is not None
+                and self.tp_ctx.sp_ok(token_ids.shape[0])):
+            return self._forward_prefill_sharded(token_ids, positions, kv, cu_seqlens, max_len, seq_ids, last_idx)
         h = A.embed_gather(token_ids, self.w["embed"])
         delta = None
         for l in range(cfg.n_layers):
@@ -138,6 +141,42 @@ class Decoder:
         if last_idx is not None:
             h = h.index_select(0, last_idx)
             delta = delta.index_select(0, last_idx)
+        return self._sample(h, delta)
+
+    def _forward_prefill_sharded(self, token_ids, positions, kv, cu_seqlens, max_len, seq_ids, last_idx):
+        """Dense tensor-parallel prefill with the residual stream sharded by token: this rank normalises and quantises
+        only the rows it owns, column-parallel linears gather the int8 rows inside the GEMM kernel, row-parallel
+        linears reduce-scatter their partial sums from the GEMM epilogue.  Attention sees all tokens of its own heads
+        exactly as in the replicated path."""
+        cfg, sp = self.cfg, self.tp_ctx.sp
+        M = token_ids.shape[0]
+        a, b = sp.my_rows(M)
+        h = A.embed_gather(token_ids[a:b], self.w["embed"])
+        delta = None
+        for l in range(cfg.n_layers):
+            W = self.w["layers"][l]
+            xq, sx = self._norm_quant(h, delta, W["attn_norm"])
+            qkv = sp.ag_linear(xq, sx, W["qkv"].qweight, W["qkv"].scale, M)
+            attn = self._attention(l, qkv, positions, kv, "prefill", cu_seqlens, max_len, seq_ids)
+            aq, sa = L.act_quant(attn.view(M, -1))
+            delta = sp.rs_linear(aq, sa, W["o"].qweight, W["o"].scale)[: b - a]
+            xq, sx = self._norm_quant(h, delta, W["mlp_norm"])
+            gu = sp.ag_linear(xq, sx, W["gate_up"].qweight, W["gate_up"].scale, M)
+            hq, sh = L.act_quant(gu, mode=L.AQ_SWIGLU)
+            delta = sp.rs_linear(hq, sh, W["down"].qweight, W["down"].scale)[: b - a]
+        # each sequence's last row lives on exactly one rank: the others contribute zeros to a small all-reduce
+        mine = ((last_idx >= a) & (last_idx < b)).unsqueeze(1)
+        loc = (last_idx - a).clamp(0, max(b - a - 1, 0))
+        d = cfg.d_model
+        nb = last_idx.shape[0]
+
+        def produce(buf):
+            buf[:, :d] = torch.where(mine, h.index_select(0, loc), torch.zeros((), dtype=h.dtype, device=h.device))
+            buf[:, d:] = torch.where(mine, delta.index_select(0, loc), torch.zeros((), dtype=h.dtype, device=h.device))
+        both = self.tp_ctx.reduce_partial(produce, nb, 2 * d).clone()
+        return self._sample(both[:, :d].contiguous(), both[:, d:].contiguous())
+
+    def _sample(self, h, delta):
         xq, sx = self._norm_quant(h, delta, self.w["final_norm"])
         lm = self.w["lm_head"]
         logits = L.w8a8_gemm(xq, sx, lm.qweight, lm.scale)

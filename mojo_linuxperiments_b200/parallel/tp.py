@@ -3,7 +3,10 @@
 Row-parallel linears (o_proj, down) produce partial sums that have to be added across ranks:
   * up to 64 tokens (decode) the GEMM kernel itself performs the all-reduce over peer memory (one launch);
   * above that the GEMM writes its bf16 partial straight into the symmetric heap and this package's NVLS two-shot
-    all-reduce kernel finishes it (two launches, no NCCL, no extra copy).
+    all-reduce kernel finishes it (two launches, no NCCL, no extra copy);
+  * dense prefill (at least ``SP_MIN_TOKENS_PER_RANK`` tokens per rank) leaves the replicated layout altogether:
+    ``self.sp`` (``parallel.sp.SPLink``) keeps the residual stream sharded by token and runs all-gather->GEMM and
+    GEMM->reduce-scatter as single kernels.
 Greedy sampling merges per-rank arg-max candidates through the heap as well.
 """
 from __future__ import annotations
@@ -17,6 +20,7 @@ from ..ops.workspace import default_workspace
 from .symm import SymmetricHeap, AR_LOW_LATENCY, AR_ONE_SHOT_NVLS, AR_ONE_SHOT_P2P, AR_TWO_SHOT_NVLS
 
 FUSED_MAX_M = 64
+SP_MIN_TOKENS_PER_RANK = 16
 
 
 class TPContext:
@@ -34,6 +38,10 @@ class TPContext:
         cand_bytes = 2 * world * 1024 * 16                                   # arg-max exchange: up to 1,024 rows
         self.ll_recv_bytes = 2 * world * (512 << 10) * 2                     # low-latency all-reduce of <= 512 KiB
         total = 2 * small + big + 2 * self.recv_bytes + cand_bytes + self.ll_recv_bytes
+        from .sp import SPLayout, SPLink
+        want_sp = os.environ.get("B200RT_SP", "1") != "0" and max_tokens >= SP_MIN_TOKENS_PER_RANK * world
+        if want_sp:
+            total += SPLayout(world, max_tokens, d_model, d_model).nbytes + 4096
         self.heap = SymmetricHeap(total + (1 << 20), group=group, device=device)
         self.world, self.rank = self.heap.world, self.heap.rank
         self.recv_off = [self.heap.alloc(self.recv_bytes), self.heap.alloc(self.recv_bytes)]
@@ -47,6 +55,12 @@ class TPContext:
         self.ll_recv_off = self.heap.alloc(self.ll_recv_bytes)
         self.use_nvls = self.heap.has_multicast if use_nvls is None else (use_nvls and self.heap.has_multicast)
         self.limit_ms = wait_limit_ms
+        self.sp = SPLink.on_heap(self.heap, max_tokens, d_model, d_model, use_nvls=self.use_nvls,
+                                 limit_ms=wait_limit_ms) if want_sp else None
+
+    def sp_ok(self, M: int) -> bool:
+        """Whether an M-token call should use the token-sharded path."""
+        return self.sp is not None and SP_MIN_TOKENS_PER_RANK * self.world <= M <= self.sp.layout.m_cap and M > FUSED_MAX_M
 
     def row_parallel(self, xq: torch.Tensor, sx: torch.Tensor, lw, residual: torch.Tensor | None = None) -> torch.Tensor:
         """Sum over ranks of this rank's K-shard product; returns the full [M, N] bf16 result on every rank."""
