@@ -27,6 +27,7 @@ namespace b200 {
 constexpr int TP_THREADS = 256;          // producer, MMA, 4 epilogue warps, 2 comm warps
 constexpr int TP_GROUP_M = 8;
 constexpr int TP_STG_BYTES = 4 * 4096;   // per epilogue warp: 32 rows x 128 bytes
+constexpr int TP_READY_MAX = 1024;       // (source rank, 128-row block) pairs a gather may have
 
 int gemm_pick_bn(int M, int N, int num_sms);
 
@@ -40,6 +41,7 @@ struct TpGemmParams {
   int gather, scatter, finish, phase;
   const int8_t* xq_local;        // gather: this rank's R quantised rows [R][K]
   const float* sx_local;         // gather: their scales
+  int own_lo, own_hi;            // gather: global rows [own_lo, own_hi) are this rank's (read straight from xq_local)
   void* out; int ldo;            // scatter: bf16 [R, N]
   const __nv_bfloat16* residual; int ldr;   // optional addend of the scatter output
   int* status;
@@ -62,7 +64,8 @@ __device__ __forceinline__ void tp_tile_coords(const TpGemmParams& p, int tile, 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(TP_THREADS, 1)
 w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__ CUtensorMap tmap_a1,
-                    const __grid_constant__ CUtensorMap tmap_b, const TpGemmParams p) {
+                    const __grid_constant__ CUtensorMap tmap_loc, const __grid_constant__ CUtensorMap tmap_b,
+                    const TpGemmParams p) {
   pdl_launch_dependents();
   pdl_wait();
 
@@ -79,6 +82,8 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* misc_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);   // [0] comm go-ahead, [1] tail go-ahead
+  volatile uint32_t* mbox = reinterpret_cast<volatile uint32_t*>(tmem_slot + 4);   // [4] tiles stored so far, per epilogue warp
+  volatile uint8_t* ready = reinterpret_cast<volatile uint8_t*>(tmem_slot + 8);    // [TP_READY_MAX] gather blocks seen complete
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -94,8 +99,10 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
     for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
     *abort_flag = 0;
     misc_slot[0] = 0; misc_slot[1] = 0;
+    for (int i = 0; i < 4; ++i) mbox[i] = 0;
     mbar_fence_init();
   }
+  for (int i = threadIdx.x; i < TP_READY_MAX; i += TP_THREADS) ready[i] = 0;
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
     tmem_relinquish();
@@ -120,33 +127,51 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
     if (lane == 0) {
       const CUtensorMap* ta = (p.gather && ag_par) ? &tmap_a1 : &tmap_a0;
       prefetch_tmap(ta);
+      if (p.gather) prefetch_tmap(&tmap_loc);
       prefetch_tmap(&tmap_b);
       const uint64_t pol_w = policy_evict_last();
-      const uint32_t* flags = p.gather ? reinterpret_cast<const uint32_t*>(p.ag.t.data[p.ag.t.rank] + p.ag.flag_off) : nullptr;
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         int m_tile, n_tile;
         tp_tile_coords(p, tile, m_tile, n_tile);
         const int row0 = m_tile * TILE_N;
-        if (p.gather) {
-          // rows [row0, row0+128) come from source ranks s = row / R; each source publishes one flag per 128 of its rows
+        // a tile made only of this rank's rows is read straight from the local operand: nothing to wait for
+        const bool own = p.gather && row0 >= p.own_lo && min(row0 + TILE_N, p.M) <= p.own_hi;
+        if (p.gather && !own) {
+          // rows [row0, row0+128) come from source ranks s = row / R; each source publishes one flag per 128 of its
+          // rows, which the comm warps of this CTA watch and mirror into shared memory
           const int R = p.ag.rows_per_rank;
           const int r_lo = row0, r_hi = min(row0 + TILE_N, p.M) - 1;
           for (int s = r_lo / R; ok && s <= r_hi / R; ++s) {
             const int a = max(r_lo, s * R) - s * R, b = min(r_hi, (s + 1) * R - 1) - s * R;
-            for (int blk = a >> 7; blk <= (b >> 7); ++blk) {
-              if (!wait_flag_ge(flags + s * p.ag.blk_cap + blk, ag_e, p.status, limit)) { *abort_flag = 1; ok = false; break; }
+            for (int blk = a >> 7; ok && blk <= (b >> 7); ++blk) {
+              const int i = s * p.ag.blk_cap + blk;
+              if (ready[i]) continue;
+              const uint64_t t0 = globaltimer_ns();
+              uint32_t spins = 0;
+              while (!ready[i]) {
+                if ((++spins & 63u) == 0u) {
+                  if (*abort_flag) { ok = false; break; }
+                  if (globaltimer_ns() - t0 > limit) {
+                    *abort_flag = 1;
+                    if (p.status) atomicCAS(p.status, 0, (int)ST_TIMEOUT_PEER_FLAG | (3 << 8));
+                    ok = false; break;
+                  }
+                }
+              }
             }
           }
           if (!ok) break;
+          __threadfence_block();
           fence_proxy_async_all();
         }
         for (int kb = 0; kb < p.kblocks; ++kb) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (3 << 8)), limit)) { ok = false; break; }
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
-          tma_load_2d(a_dst, ta, full_bar(stage), kb * BLOCK_K, row0);
+          if (own) tma_load_2d(a_dst, &tmap_loc, full_bar(stage), kb * BLOCK_K, row0 - p.own_lo);
+          else tma_load_2d(a_dst, ta, full_bar(stage), kb * BLOCK_K, row0);
           tma_load_2d_hint(a_dst + A_BYTES, &tmap_b, full_bar(stage), kb * BLOCK_K, n_tile * BN, pol_w);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -203,7 +228,12 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
       const int m = m_tile * TILE_N + q * 32 + lane;
       const bool m_ok = m < p.M;
       // gathered scales were written by peers: read them past the L1
-      const float sxm = m_ok ? (p.gather ? __ldcg(sx + m) : sx[m]) : 0.f;
+      float sxm = 0.f;
+      if (m_ok) {
+        if (!p.gather) sxm = sx[m];
+        else if (m >= p.own_lo && m < p.own_hi) sxm = p.sx_local[m - p.own_lo];
+        else sxm = __ldcg(sx + m);
+      }
       const int n0 = n_tile * BN;
 
       // destination of the 8 rows this lane stores per 64-column chunk (after the re-layout through shared memory,
@@ -268,83 +298,132 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
       if (lane == 0) mbar_arrive(tempty_bar(a));
 
       if (p.scatter) {
-        // tell the owners how many of their rows this warp delivered for this column tile
+        // hand the "stores of this tile are issued" event to the signalling thread of the comm warps: the system-scope
+        // fence that must precede the arrival count then never stalls this warp
         __syncwarp();
-        if (lane == 0) {
-          const int m0 = m_tile * TILE_N + q * 32, m1 = min(m0 + 32, p.M);
-          if (m0 < m1) {
-            __threadfence_system();
-            const int R = p.rs.rows_per_rank;
-            for (int o = m0 / R; o <= (m1 - 1) / R; ++o) {
-              const int cnt = min(m1, (o + 1) * R) - max(m0, o * R);
-              red_release_sys_add(reinterpret_cast<uint32_t*>(p.rs.t.data[o] + p.rs.ctr_off) + rs_par, static_cast<uint32_t>(cnt));
-            }
-          }
-        }
+        if (lane == 0) { __threadfence_block(); mbox[warp - 2] = static_cast<uint32_t>(seg_idx + 1); }
       }
       ++seg_idx;
     }
   } else {
-    // ------------------------------ comm warps (gather push) ------------------------------
-    if (p.gather && (p.phase & 4)) {
+    // ------------------------------ comm warps ------------------------------
+    const int ct = threadIdx.x - 192;                  // 0..63
+    if (p.gather) {
       const AgLink& g = p.ag;
       const PeerTable& t = g.t;
-      const int ct = threadIdx.x - 192;                  // 0..63
       const int R = g.rows_per_rank;
-      const int my_rows = max(0, min(R, p.M - t.rank * R));
-      if (ct == 0) {
-        // the buffer of this parity was last used two calls ago: every consumer must have finished that call
-        const uint32_t* done = reinterpret_cast<const uint32_t*>(t.data[t.rank] + g.done_off);
-        int good = 1;
-        for (int r = 0; r < t.world && good; ++r)
-          if (!wait_flag_ge(done + r, ag_e - 2u, p.status, limit)) good = 0;
-        misc_slot[0] = good;
-      }
-      named_bar_sync(2, 64);
-      const bool go = misc_slot[0] != 0;
-      const size_t vec_per_row = static_cast<size_t>(p.K) / 16;
-      const size_t gtid = static_cast<size_t>(blockIdx.x) * 64 + ct, gsz = static_cast<size_t>(gridDim.x) * 64;
-      const size_t row_base = static_cast<size_t>(t.rank) * R;
-      const int nblk = (my_rows + 127) >> 7;
-      for (int blk = 0; blk < nblk; ++blk) {
-        const int rows_b = min(128, my_rows - blk * 128);
-        if (go) {
-          const size_t v_end = static_cast<size_t>(rows_b) * vec_per_row;
-          const uint4* src = reinterpret_cast<const uint4*>(p.xq_local + static_cast<size_t>(blk) * 128 * p.K);
-          const size_t dst0 = g.q_off[ag_par] + (row_base + static_cast<size_t>(blk) * 128) * p.K;
-          size_t v = gtid;
-          for (; v + 3 * gsz < v_end; v += 4 * gsz) {     // four independent 16-byte copies in flight
-            uint4 x[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) x[u] = src[v + u * gsz];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const size_t off = dst0 + (v + u * gsz) * 16;
-              if (t.mc) multimem_st_16B(t.mc + off, x[u]);
-              else for (int r = 0; r < t.world; ++r) *reinterpret_cast<uint4*>(t.data[r] + off) = x[u];
-            }
-          }
-          for (; v < v_end; v += gsz) {
-            const uint4 x = src[v];
-            const size_t off = dst0 + v * 16;
-            if (t.mc) multimem_st_16B(t.mc + off, x);
-            else for (int r = 0; r < t.world; ++r) *reinterpret_cast<uint4*>(t.data[r] + off) = x;
-          }
-          for (size_t i = gtid; i < static_cast<size_t>(rows_b); i += gsz) {
-            const float s = p.sx_local[blk * 128 + i];
-            const size_t off = g.s_off[ag_par] + (row_base + blk * 128 + i) * 4;
-            for (int r = 0; r < t.world; ++r) *reinterpret_cast<float*>(t.data[r] + off) = s;
-          }
+      if (p.phase & 4) {
+        // ---- push my rows into every rank's gather buffer ----
+        const int my_rows = max(0, min(R, p.M - t.rank * R));
+        if (ct == 0) {
+          // the buffer of this parity was last used two calls ago: every consumer must have finished that call
+          const uint32_t* done = reinterpret_cast<const uint32_t*>(t.data[t.rank] + g.done_off);
+          int good = 1;
+          for (int r = 0; r < t.world && good; ++r)
+            if (!wait_flag_ge(done + r, ag_e - 2u, p.status, limit)) good = 0;
+          misc_slot[0] = good;
         }
         named_bar_sync(2, 64);
-        if (ct == 0 && go) {
-          __threadfence_system();
-          const uint32_t old = atomicAdd(g.row_ctr + blk, 1u);
-          if (old == gridDim.x - 1) {                      // every CTA of this rank has stored its share of the block
-            g.row_ctr[blk] = 0;
-            __threadfence_system();
-            for (int r = 0; r < t.world; ++r)
-              st_release_sys(reinterpret_cast<uint32_t*>(t.data[r] + g.flag_off) + t.rank * g.blk_cap + blk, ag_e);
+        const bool go = misc_slot[0] != 0;
+        const size_t vec_per_row = static_cast<size_t>(p.K) / 16;
+        const size_t row_base = static_cast<size_t>(t.rank) * R;
+        const int nblk = (my_rows + 127) >> 7;
+        // the CTAs split into nblk groups, one per 128-row block, so that each CTA pays for one system-scope fence
+        const int G = static_cast<int>(gridDim.x);
+        const int members = nblk > 0 && nblk <= G ? G / nblk : 1;
+        const int first = nblk <= G ? static_cast<int>(blockIdx.x) / members : static_cast<int>(blockIdx.x);
+        const int step = nblk <= G ? nblk : G;
+        const size_t mtid = static_cast<size_t>(nblk <= G ? static_cast<int>(blockIdx.x) % members : 0) * 64 + ct;
+        const size_t msz = static_cast<size_t>(members) * 64;
+        for (int blk = first; blk < nblk; blk += step) {
+          const int rows_b = min(128, my_rows - blk * 128);
+          if (go) {
+            const size_t v_end = static_cast<size_t>(rows_b) * vec_per_row;
+            const uint4* src = reinterpret_cast<const uint4*>(p.xq_local + static_cast<size_t>(blk) * 128 * p.K);
+            const size_t dst0 = g.q_off[ag_par] + (row_base + static_cast<size_t>(blk) * 128) * p.K;
+            size_t v = mtid;
+            for (; v + 7 * msz < v_end; v += 8 * msz) {     // eight independent 16-byte copies in flight
+              uint4 x[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) x[u] = src[v + u * msz];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const size_t off = dst0 + (v + u * msz) * 16;
+                if (t.mc) multimem_st_16B(t.mc + off, x[u]);
+                else for (int r = 0; r < t.world; ++r) *reinterpret_cast<uint4*>(t.data[r] + off) = x[u];
+              }
+            }
+            for (; v < v_end; v += msz) {
+              const uint4 x = src[v];
+              const size_t off = dst0 + v * 16;
+              if (t.mc) multimem_st_16B(t.mc + off, x);
+              else for (int r = 0; r < t.world; ++r) *reinterpret_cast<uint4*>(t.data[r] + off) = x;
+            }
+            for (size_t i = mtid; i < static_cast<size_t>(rows_b); i += msz) {
+              const float sc = p.sx_local[blk * 128 + i];
+              const size_t off = g.s_off[ag_par] + (row_base + blk * 128 + i) * 4;
+              for (int r = 0; r < t.world; ++r) *reinterpret_cast<float*>(t.data[r] + off) = sc;
+            }
+          }
+          named_bar_sync(2, 64);
+          if (ct == 0 && go) {
+            fence_acq_rel_sys();
+            const uint32_t old = atomicAdd(g.row_ctr + blk, 1u);
+            if (old == static_cast<uint32_t>(members) - 1u) {   // every CTA of the block's group has stored its share
+              g.row_ctr[blk] = 0;
+              fence_acq_rel_sys();
+              for (int r = 0; r < t.world; ++r)
+                st_release_sys(reinterpret_cast<uint32_t*>(t.data[r] + g.flag_off) + t.rank * g.blk_cap + blk, ag_e);
+            }
+          }
+        }
+      }
+      if (do_tiles) {
+        // ---- watch the arrival flags (sources visited starting with this rank) and mirror them into shared memory ----
+        const uint32_t* flags = reinterpret_cast<const uint32_t*>(t.data[t.rank] + g.flag_off);
+        const int total = t.world * g.blk_cap;
+        for (int j = ct; j < total; j += 64) {
+          const int sj = j / g.blk_cap, blk = j - sj * g.blk_cap;
+          int s = sj + t.rank;
+          if (s >= t.world) s -= t.world;
+          const int rows_s = max(0, min(R, p.M - s * R));
+          if (blk * 128 >= rows_s) continue;
+          if (*abort_flag) break;
+          if (!wait_flag_ge(flags + s * g.blk_cap + blk, ag_e, p.status, limit)) { *abort_flag = 1; break; }
+          __threadfence_block();
+          ready[s * g.blk_cap + blk] = 1;
+        }
+      }
+    }
+    if (p.scatter && do_tiles && ct < 4) {
+      // ---- one signalling thread per epilogue warp: fence, then add the delivered rows to the owners' counters ----
+      const int q = (ct + 2) & 3;                        // TMEM lane quarter of epilogue warp ct + 2
+      const int R = p.rs.rows_per_rank;
+      uint32_t seq = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x, ++seq) {
+        const uint64_t t0 = globaltimer_ns();
+        uint32_t spins = 0;
+        while (mbox[ct] <= seq) {
+          if ((++spins & 63u) == 0u) {
+            if (*abort_flag) { ok = false; break; }
+            if (globaltimer_ns() - t0 > limit) {
+              *abort_flag = 1;
+              if (p.status) atomicCAS(p.status, 0, (int)ST_TIMEOUT_DRAIN | (3 << 8));
+              ok = false; break;
+            }
+          }
+        }
+        if (!ok) break;
+        __threadfence_block();
+        int m_tile, n_tile;
+        tp_tile_coords(p, tile, m_tile, n_tile);
+        const int m0 = m_tile * TILE_N + q * 32, m1 = min(m0 + 32, p.M);
+        if (m0 < m1) {
+          // red.release.sys orders the tile's stores (observed through the mailbox) before the count
+          for (int o = m0 / R; o <= (m1 - 1) / R; ++o) {
+            const int cnt = min(m1, (o + 1) * R) - max(m0, o * R);
+            red_release_sys_add(reinterpret_cast<uint32_t*>(p.rs.t.data[o] + p.rs.ctr_off) + rs_par, static_cast<uint32_t>(cnt));
           }
         }
       }
@@ -377,17 +456,32 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
       const size_t total = static_cast<size_t>(my_rows) * vec_per_row;
       const size_t src_stride = static_cast<size_t>(s.r_cap) * p.N * 2;
       const uint8_t* base = t.data[t.rank] + s.recv_off[rs_par];
-      for (size_t v = static_cast<size_t>(blockIdx.x) * TP_THREADS + threadIdx.x; v < total; v += static_cast<size_t>(gridDim.x) * TP_THREADS) {
+      const size_t gsz = static_cast<size_t>(gridDim.x) * TP_THREADS;
+      auto addr = [&](size_t v) { const size_t row = v / vec_per_row, c8 = v - row * vec_per_row; return base + (row * p.N + c8 * 8) * 2; };
+      auto finish = [&](size_t v, const uint4 (&x)[MAX_RANKS]) {
         const size_t row = v / vec_per_row, c8 = v - row * vec_per_row;
-        const uint8_t* a = base + (row * p.N + c8 * 8) * 2;
-        uint4 x[MAX_RANKS];
-#pragma unroll
-        for (int r = 0; r < MAX_RANKS; ++r) if (r < t.world) x[r] = ld_peer_16B(a + r * src_stride);
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int r = 0; r < MAX_RANKS; ++r) if (r < t.world) add_bf16x8_to_f32(x[r], acc);
         if (p.residual) add_bf16x8_to_f32(*reinterpret_cast<const uint4*>(p.residual + row * p.ldr + c8 * 8), acc);
         *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + row * p.ldo + c8 * 8) = pack_f32x8_to_bf16(acc);
+      };
+      size_t v = static_cast<size_t>(blockIdx.x) * TP_THREADS + threadIdx.x;
+      for (; v + gsz < total; v += 2 * gsz) {              // two vectors x world sources in flight per thread
+        const uint8_t* a0 = addr(v);
+        const uint8_t* a1 = addr(v + gsz);
+        uint4 x0[MAX_RANKS], x1[MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r) if (r < t.world) { x0[r] = ld_peer_16B(a0 + r * src_stride); x1[r] = ld_peer_16B(a1 + r * src_stride); }
+        finish(v, x0);
+        finish(v + gsz, x1);
+      }
+      for (; v < total; v += gsz) {
+        const uint8_t* a0 = addr(v);
+        uint4 x0[MAX_RANKS];
+#pragma unroll
+        for (int r = 0; r < MAX_RANKS; ++r) if (r < t.world) x0[r] = ld_peer_16B(a0 + r * src_stride);
+        finish(v, x0);
       }
     }
   }
@@ -446,16 +540,16 @@ __global__ void __launch_bounds__(256) ag_sync_kernel(const AgLink g, int M, int
 }
 
 template <int BN, int STAGES>
-static int launch_tp(const CUtensorMap& ta0, const CUtensorMap& ta1, const CUtensorMap& tb, const TpGemmParams& p, int grid,
-                     cudaStream_t stream) {
-  constexpr int SMEM = STAGES * (TILE_N * BLOCK_K + BN * BLOCK_K) + TP_STG_BYTES + 1024 + 256;
+static int launch_tp(const CUtensorMap& ta0, const CUtensorMap& ta1, const CUtensorMap& tl, const CUtensorMap& tb,
+                     const TpGemmParams& p, int grid, cudaStream_t stream) {
+  constexpr int SMEM = STAGES * (TILE_N * BLOCK_K + BN * BLOCK_K) + TP_STG_BYTES + 1024 + 256 + TP_READY_MAX;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(w8a8_gemm_tp_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }
-  launch_ex(w8a8_gemm_tp_kernel<BN, STAGES>, dim3(grid), dim3(TP_THREADS), SMEM, stream, 0, ta0, ta1, tb, p);
+  launch_ex(w8a8_gemm_tp_kernel<BN, STAGES>, dim3(grid), dim3(TP_THREADS), SMEM, stream, 0, ta0, ta1, tl, tb, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
@@ -468,7 +562,8 @@ static void fill_table(PeerTable& t, void* const* peer_data, void* mc_base, int 
   t.mc = static_cast<uint8_t*>(mc_base); t.world = world; t.rank = rank;
 }
 
-static int run_tp(const CUtensorMap& ta0, const CUtensorMap& ta1, const void* wq, TpGemmParams& p, int num_sms, cudaStream_t stream) {
+static int run_tp(const CUtensorMap& ta0, const CUtensorMap& ta1, const CUtensorMap& tl, const void* wq, TpGemmParams& p, int num_sms,
+                  cudaStream_t stream) {
   const int bn = gemm_pick_bn(p.M, p.N, num_sms);
   p.m_tiles = (p.M + TILE_N - 1) / TILE_N;
   p.n_tiles = (p.N + bn - 1) / bn;
@@ -478,9 +573,9 @@ static int run_tp(const CUtensorMap& ta0, const CUtensorMap& ta1, const void* wq
   if (make_tmap_2d_u8(&tw, wq, static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.K), bn)) return -11;
   // every SM takes part in the push / the tail even when there are fewer tiles than SMs
   switch (bn) {
-    case 64: return launch_tp<64, 8>(ta0, ta1, tw, p, num_sms, stream);
-    case 128: return launch_tp<128, 6>(ta0, ta1, tw, p, num_sms, stream);
-    default: return launch_tp<256, 4>(ta0, ta1, tw, p, num_sms, stream);
+    case 64: return launch_tp<64, 8>(ta0, ta1, tl, tw, p, num_sms, stream);
+    case 128: return launch_tp<128, 6>(ta0, ta1, tl, tw, p, num_sms, stream);
+    default: return launch_tp<256, 4>(ta0, ta1, tl, tw, p, num_sms, stream);
   }
 }
 
@@ -495,7 +590,7 @@ extern "C" int b200_w8a8_gemm_ag(const void* xq_local, const float* sx_local, co
                                  int finish, int phase, int* status, int limit_ms, int num_sms, cudaStream_t stream) {
   if (M <= 64 || N <= 0 || K <= 0 || (K % 128) || (N % 64) || (ldy % 8) || world < 1 || world > MAX_RANKS || rank < 0 || rank >= world) return -1;
   if (rows_per_rank <= 0 || static_cast<long long>(rows_per_rank) * world < M || M > m_cap) return -1;
-  if ((rows_per_rank + 127) / 128 > blk_cap) return -1;
+  if ((rows_per_rank + 127) / 128 > blk_cap || world * blk_cap > TP_READY_MAX) return -1;
   if ((q_off0 | q_off1) % 1024 || (s_off0 | s_off1 | flag_off | done_off) % 16) return -2;
   if ((reinterpret_cast<uintptr_t>(xq_local) | reinterpret_cast<uintptr_t>(wq) | reinterpret_cast<uintptr_t>(y)) & 15) return -2;
   TpGemmParams p = {};
@@ -517,7 +612,13 @@ extern "C" int b200_w8a8_gemm_ag(const void* xq_local, const float* sx_local, co
   const uint8_t* mine = static_cast<const uint8_t*>(peer_data[rank]);
   if (make_tmap_2d_u8(&ta0, mine + q_off0, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), TILE_N)) return -12;
   if (make_tmap_2d_u8(&ta1, mine + q_off1, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), TILE_N)) return -12;
-  return run_tp(ta0, ta1, wq, p, num_sms, stream);
+  // this rank's own rows, read without waiting for anything
+  p.own_lo = rank * rows_per_rank < M ? rank * rows_per_rank : M;
+  p.own_hi = p.own_lo + rows_per_rank < M ? p.own_lo + rows_per_rank : M;
+  CUtensorMap tl = ta0;
+  if (p.own_hi > p.own_lo &&
+      make_tmap_2d_u8(&tl, xq_local, static_cast<uint64_t>(K), static_cast<uint64_t>(p.own_hi - p.own_lo), static_cast<uint64_t>(K), TILE_N)) return -12;
+  return run_tp(ta0, ta1, tl, wq, p, num_sms, stream);
 }
 
 extern "C" int b200_w8a8_gemm_rs(const void* xq, const float* sx, const void* wq, const float* sw, void* out,
@@ -547,7 +648,7 @@ extern "C" int b200_w8a8_gemm_rs(const void* xq, const float* sx, const void* wq
   if (p.m_rot >= m_tiles) p.m_rot = 0;
   CUtensorMap ta;
   if (make_tmap_2d_u8(&ta, xq, static_cast<uint64_t>(K), static_cast<uint64_t>(M), static_cast<uint64_t>(K), TILE_N)) return -12;
-  return run_tp(ta, ta, wq, p, num_sms, stream);
+  return run_tp(ta, ta, ta, wq, p, num_sms, stream);
 }
 
 extern "C" int b200_ag_sync(void* const* peer_data, int world, int rank, size_t flag_off, size_t done_off, int blk_cap,

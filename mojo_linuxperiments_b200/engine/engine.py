@@ -2,7 +2,9 @@
 
 The decode step of a batch is captured once per batch size as one CUDA graph; replaying it is the analogue of the
 reference's ``ThreadPool.launch`` on every rank and ``wait_all`` is the event the caller synchronises on
-(threading/linux_threading.mojo:103-129).  The host only reads the sampled ids.
+(threading/linux_threading.mojo:103-129).  The host only reads the sampled ids.  Prefill is captured too, once per
+(first sequence slot, sequences, prompt length): a prompt's ~400 kernel launches otherwise cost more host time than
+the GPU needs to run them once the model is sharded over several GPUs.
 """
 from __future__ import annotations
 
@@ -33,6 +35,10 @@ class Engine:
         self.kv: KVState | None = None
         self.batch = 0
         self._graphs: dict[int, torch.cuda.CUDAGraph] = {}
+        self._prefill_graphs: dict[tuple, tuple] = {}
+        self._prefill_pool = None
+        self.tokens = None
+        self.positions = None
         self.kernels_per_step = 0
         self._stream = torch.cuda.Stream(device=self.device)
 
@@ -41,39 +47,74 @@ class Engine:
         if max_total_len > self.rt.max_seq_len:
             raise ValueError(f"{max_total_len} tokens exceed max_seq_len {self.rt.max_seq_len}")
         if self.kv is None or self.kv.seq_lens.numel() != batch or self.kv.max_pages * self.rt.page_size < max_total_len:
-            self.kv = KVState(self.cfg, self.rt, self.device, batch, self.rt.max_seq_len)
+            self.kv = None                  # free the old cache before the new one is allocated
             self._graphs.clear()
+            self._prefill_graphs.clear()
+            self.kv = KVState(self.cfg, self.rt, self.device, batch, self.rt.max_seq_len)
+            self.tokens = torch.zeros(batch, dtype=torch.int64, device=self.device)
+            self.positions = torch.zeros(batch, dtype=torch.int32, device=self.device)
         else:
+            # same cache, same static tensors: the captured graphs stay valid
             for s in list(self.kv.owned):
                 self.kv.release(s)
+            self.tokens.zero_()
+            self.positions.zero_()
         for s in range(batch):
             self.kv.admit(s, max_total_len)
         self.batch = batch
-        self.tokens = torch.zeros(batch, dtype=torch.int64, device=self.device)
-        self.positions = torch.zeros(batch, dtype=torch.int32, device=self.device)
-        self._graphs.clear()
 
-    def prefill(self, prompts: torch.Tensor) -> torch.Tensor:
+    def prefill(self, prompts: torch.Tensor, use_graph: bool = True) -> torch.Tensor:
         """prompts int64 [B, S] (host or device; equal lengths).  Returns the first generated token per sequence
         (device tensor) and leaves the engine ready for ``decode_step``.  Long batches are processed in groups of
-        whole sequences so that one call never carries more than ``rt.max_prefill_tokens`` tokens."""
+        whole sequences so that one call never carries more than ``rt.max_prefill_tokens`` tokens; each group's
+        forward pass is one CUDA graph (captured at first use)."""
         B, S = prompts.shape
         ids_all = prompts.to(self.device, non_blocking=True)
         group = max(1, min(B, self.rt.max_prefill_tokens // S))
         for b0 in range(0, B, group):
             b1 = min(B, b0 + group)
-            n = b1 - b0
             ids = ids_all[b0:b1].reshape(-1)
-            positions = torch.arange(S, dtype=torch.int32, device=self.device).repeat(n)
-            seq_ids = torch.arange(b0, b1, dtype=torch.int32, device=self.device).repeat_interleave(S)
-            cu = torch.arange(0, (n + 1) * S, S, dtype=torch.int32, device=self.device)
-            last = torch.arange(S - 1, n * S, S, dtype=torch.int64, device=self.device)
-            nxt = self.model.forward(ids, positions, self.kv, mode="prefill", cu_seqlens=cu, max_len=S, seq_ids=seq_ids,
-                                     last_idx=last)
-            self.tokens[b0:b1].copy_(nxt)
+            if not use_graph:
+                self._prefill_body(ids, b0, b1, S, self._prefill_consts(b0, b1, S))
+                continue
+            key = (b0, b1 - b0, S)
+            entry = self._prefill_graphs.get(key)
+            if entry is None:
+                consts = self._prefill_consts(b0, b1, S)
+                ids_buf = ids.clone()
+                # once eagerly on the side stream (lazy set-up, allocator warm-up, status check), then capture
+                self._stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self._stream):
+                    self._prefill_body(ids_buf, b0, b1, S, consts)
+                torch.cuda.current_stream().wait_stream(self._stream)
+                torch.cuda.synchronize()
+                self.check_status()
+                if self._prefill_pool is None:
+                    self._prefill_pool = torch.cuda.graph_pool_handle()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=self._stream, pool=self._prefill_pool):
+                    self._prefill_body(ids_buf, b0, b1, S, consts)
+                entry = (g, ids_buf, consts)
+                self._prefill_graphs[key] = entry
+            entry[1].copy_(ids, non_blocking=True)
+            entry[0].replay()
         self.positions.fill_(S)
         self.kv.seq_lens.fill_(S + 1)      # the next decode step attends to the prompt plus its own token
         return self.tokens.clone()
+
+    def _prefill_consts(self, b0: int, b1: int, S: int):
+        n = b1 - b0
+        dev = self.device
+        return (torch.arange(S, dtype=torch.int32, device=dev).repeat(n),
+                torch.arange(b0, b1, dtype=torch.int32, device=dev).repeat_interleave(S),
+                torch.arange(0, (n + 1) * S, S, dtype=torch.int32, device=dev),
+                torch.arange(S - 1, n * S, S, dtype=torch.int64, device=dev))
+
+    def _prefill_body(self, ids, b0, b1, S, consts) -> None:
+        positions, seq_ids, cu, last = consts
+        nxt = self.model.forward(ids, positions, self.kv, mode="prefill", cu_seqlens=cu, max_len=S, seq_ids=seq_ids,
+                                 last_idx=last)
+        self.tokens[b0:b1].copy_(nxt)
 
     def _decode_body(self) -> None:
         nxt = self.model.forward(self.tokens, self.positions, self.kv, mode="decode", max_len=self.rt.max_seq_len)
@@ -130,7 +171,7 @@ class Engine:
         B, S = prompts.shape
         self.start_batch(B, S + max_new_tokens)
         out = torch.empty((max_new_tokens, B), dtype=torch.int64, pin_memory=torch.cuda.is_available())
-        first = self.prefill(prompts)
+        first = self.prefill(prompts, use_graph)
         out[0].copy_(first, non_blocking=True)
         for t in range(1, max_new_tokens):
             nxt = self.decode_step(use_graph)

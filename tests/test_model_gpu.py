@@ -30,7 +30,7 @@ def test_tiny_dense_prefill_logits_and_greedy_decode():
     assert out.shape == (B, NEW)
     # prefill logits of the last prompt token against the oracle
     eng.start_batch(B, S + NEW)
-    eng.prefill(prompts)
+    eng.prefill(prompts, use_graph=False)      # eager: `last_logits` is then this call's tensor, not a captured one
     torch.cuda.synchronize()
     got = eng.model.last_logits.float()
     agree = 0

@@ -80,7 +80,7 @@ def test_tiny_moe_model_matches_oracle():
     out_eager = eng.generate(prompts, NEW, use_graph=False)
     assert torch.equal(out, out_eager)
     eng.start_batch(B, S + NEW)
-    eng.prefill(prompts)
+    eng.prefill(prompts, use_graph=False)      # eager: `last_logits` is then this call's tensor, not a captured one
     torch.cuda.synchronize()
     got = eng.model.last_logits.float()
     agree = 0
