@@ -10,6 +10,10 @@ import os
 
 import torch
 
+import os
+import sys as _sys
+_sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
 from mojo_linuxperiments_b200.ops import attention as A
 from mojo_linuxperiments_b200.ops import linear as L
 
@@ -58,13 +62,22 @@ def main():
         pt = torch.arange(B * max_pages, dtype=torch.int32, device=dev).view(B, max_pages)
         lens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
         q = torch.randn((B, hq, 128), device=dev).to(torch.bfloat16)
-        splits = A.pick_decode_splits(B, hkv, ctx + 64)
-        sc = A.DecodeAttnScratch(B, hq, hkv, splits, dev)
         out = torch.empty_like(q)
-        t = graph_time(lambda i: A.attn_decode(q, caches[i % n_layers], pt, lens, scratch=sc, splits=splits, out=out))
         byts = B * ctx * hkv * 512
-        print(json.dumps({"op": "attn_decode", "case": tag, "splits": splits, "us": t * 1e6, "gbs": byts / t / 1e9,
-                          "frac_of_measured_hbm": byts / t / 1e9 / hbm}), flush=True)
+        for impl in ("tc", "tma"):
+            if impl == "tc":
+                splits = A.pick_decode_splits_tc(B, hkv, max_pages * ps)
+            else:
+                splits = A.pick_decode_splits(B, hkv, ctx + 64)
+            sc = A.DecodeAttnScratch(B, hq, hkv, splits, dev)
+            t = graph_time(lambda i: A.attn_decode(q, caches[i % n_layers], pt, lens, scratch=sc, splits=splits, out=out, impl=impl))
+            print(json.dumps({"op": "attn_decode", "impl": impl, "case": tag, "splits": splits, "us": t * 1e6,
+                              "gbs": byts / t / 1e9, "frac_of_measured_hbm": byts / t / 1e9 / hbm}), flush=True)
+        if os.environ.get("SWEEP_SPLITS"):
+            for splits in range(A.tc_min_splits(max_pages * ps), 10):
+                sc = A.DecodeAttnScratch(B, hq, hkv, splits, dev)
+                t = graph_time(lambda i: A.attn_decode(q, caches[i % n_layers], pt, lens, scratch=sc, splits=splits, out=out, impl="tc"))
+                print(json.dumps({"op": "attn_decode", "impl": "tc", "case": tag, "splits": splits, "us": t * 1e6}), flush=True)
         del caches
     for (M, K, mode, tag) in [(32, 4096, L.AQ_ADD_NORM, "add_norm bs32"), (1, 4096, L.AQ_ADD_NORM, "add_norm bs1"),
                               (32, 14336, L.AQ_SWIGLU, "swiglu bs32"), (32, 4096, L.AQ_PLAIN, "plain bs32"),

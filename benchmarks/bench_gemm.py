@@ -9,6 +9,10 @@ import json
 
 import torch
 
+import os
+import sys as _sys
+_sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
 from mojo_linuxperiments_b200.ops import linear as L
 
 SHAPES = [  # (M, N, K, tag)

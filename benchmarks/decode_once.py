@@ -7,6 +7,10 @@ from dataclasses import replace
 
 import torch
 
+import os
+import sys as _sys
+_sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
 from mojo_linuxperiments_b200.engine.engine import Engine
 from mojo_linuxperiments_b200.models import config as C
 from mojo_linuxperiments_b200.ops import _lib

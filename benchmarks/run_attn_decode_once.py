@@ -1,8 +1,12 @@
 """Launch paged decode attention a few times on one shape (for profiler captures).
-python benchmarks/run_attn_decode_once.py [impl=tma|simple] [B=32] [ctx=1024] [hq=32] [hkv=8] [splits=0(auto)]"""
+python benchmarks/run_attn_decode_once.py [impl=tc|tma|simple] [B=32] [ctx=1024] [hq=32] [hkv=8] [splits=0(auto)]"""
 import sys
 
 import torch
+
+import os
+import sys as _sys
+_sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 from mojo_linuxperiments_b200.ops import attention as A
 
@@ -19,7 +23,10 @@ pt = torch.arange(B * max_pages, dtype=torch.int32, device=dev).view(B, max_page
 lens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
 q = torch.randn((B, hq, 128), device=dev).to(torch.bfloat16)
 if splits <= 0:
-    splits = A.pick_decode_splits(B, hkv, ctx + 64)
+    if impl == "tc":
+        splits = A.pick_decode_splits_tc(B, hkv, max_pages * ps)
+    else:
+        splits = A.pick_decode_splits(B, hkv, ctx + 64)
 sc = A.DecodeAttnScratch(B, hq, hkv, splits, dev)
 out = torch.empty_like(q)
 for i in range(3):

@@ -3,6 +3,10 @@ import sys
 
 import torch
 
+import os
+import sys as _sys
+_sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
 from mojo_linuxperiments_b200.ops import linear as L
 from mojo_linuxperiments_b200.ops.workspace import default_workspace
 

@@ -1,0 +1,388 @@
+// Paged-KV decode attention on the tcgen05 tensor cores (page size 16, head dim 128, bf16, fp32 accumulate).
+//
+// The CUDA-core form (attn_decode_tma.cu) is bound by its instruction count (two FMAs per byte of KV for a group of
+// four query heads); here the dot products are MMAs and the kernel is a pure HBM stream.
+//
+// Grid (kv_head, sequence, split), 192 threads, two CTAs per SM.  A CTA owns up to ADC_NB blocks of 128 cached tokens.
+//   warp 0      TMA producer: for each block the 8 pages of K, then (second pass) the 8 pages of V, each page as two
+//               [16 tokens x 64 dims] boxes (3-D tensor map over the cache, 128-byte swizzle) into a two-stage ring of
+//               32 KiB tiles laid out exactly as the MMA wants them ([128 tokens][64 dims] x 2 halves)
+//   warp 1      MMA issuer.  S^T[128 tokens x 16] = K_tile (A, K-major) . Q^T (B: the G query heads of this KV head
+//               padded to 16 rows), one TMEM column block per token block; after the softmax warps have written
+//               P (bf16, [16 heads x 128 tokens], K-major) O^T[128 dims x 16] += V_tile^T (A, MN-major) . P
+//   warps 2..5  softmax, thread <-> token (TMEM lane): scores of all blocks stay in registers, the maximum and the
+//               sum per head are combined across the four warps through shared memory, so P is computed once with
+//               the final maximum and the PV accumulation needs no rescaling; then thread <-> output dim for O^T.
+// Pages beyond the end of the sequence are replaced by the sequence's last valid page (an L2 hit) and masked.
+// With several splits each CTA writes (o, m, l) partials and the last one to finish merges them.  All waits bounded.
+#include "ptx.cuh"
+#include "api.h"
+#include "launch.cuh"
+#include <cuda.h>
+
+namespace b200 {
+
+constexpr int ADC_THREADS = 192;
+constexpr int ADC_NB = 4;                       // token blocks (of 128) per CTA
+constexpr int ADC_D = 128;
+constexpr int ADC_HALF = 128 * 128;             // bytes: 128 tokens x 64 dims bf16
+constexpr int ADC_TILE = 2 * ADC_HALF;          // 32 KiB
+constexpr int ADC_NH = 16;                      // MMA N: query heads padded to 16
+constexpr int ADC_P_TILE = ADC_NH * 128 * 2;    // 4 KiB: P of one block
+constexpr int ADC_Q_TILE = ADC_NH * ADC_D * 2;  // 4 KiB
+constexpr int ADC_TMEM_COLS = 128;              // S: ADC_NB x 16 columns, O: 16 columns at 64
+constexpr int ADC_O_COL = 64;
+
+struct DecodeTcParams {
+  const __nv_bfloat16* q;
+  const int* page_table;
+  const int* seq_lens;
+  __nv_bfloat16* out;
+  float* part_acc;
+  float* part_ml;
+  unsigned* counters;
+  int hq, hkv, max_pages, splits;
+  float scale_log2;
+  int* status;
+  unsigned long long limit_ns;
+};
+
+template <int G>
+__global__ void __launch_bounds__(ADC_THREADS, 2)
+attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeTcParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // [ring 2 x 32K][P ADC_NB x 4K][Q 4K][exchange floats][barriers]
+  uint8_t* pP = smem + 2 * ADC_TILE;
+  uint8_t* pQ = pP + ADC_NB * ADC_P_TILE;
+  float* xch = reinterpret_cast<float*>(pQ + ADC_Q_TILE);          // [2][4 warps][8]: per-warp max, then sum
+  float* ml_s = xch + 64;                                          // [8][2]: final (m, l) per head
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ml_s + 16);
+  enum { B_FULL = 0, B_EMPTY = 2, B_SFULL = 4, B_PFULL = 4 + ADC_NB, B_OFULL = 4 + 2 * ADC_NB, B_XCH = 5 + 2 * ADC_NB, B_COUNT = 6 + 2 * ADC_NB };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* last_flag = const_cast<int*>(abort_flag) + 1;
+  int* page_s = last_flag + 1;                     // [ADC_NB * 8] page ids of this CTA's blocks
+  const uint32_t sRing = smem_u32(smem);
+  const uint32_t sP = smem_u32(pP), sQ = smem_u32(pQ);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+
+  const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int len = p.seq_lens[b];
+  const int total_pages = (len + 15) >> 4;
+  const int total_blocks = (len + 127) >> 7;
+  const int per = (total_blocks + p.splits - 1) / p.splits;
+  const int blk0 = split * per;
+  int nb = min(total_blocks, blk0 + per) - blk0;
+  if (nb < 0) nb = 0;
+  if (nb > ADC_NB) {                       // the host sized `splits` for a shorter maximum length
+    if (tid == 0 && p.status) atomicCAS(p.status, 0, (int)ST_BAD_ARGUMENT | (5 << 8));
+    nb = ADC_NB;
+  }
+  const int* pt = p.page_table + static_cast<size_t>(b) * p.max_pages;
+  const uint64_t limit = p.limit_ns;
+
+  if (tid == 0) {
+    for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i >= B_PFULL && i < B_PFULL + ADC_NB) || i == B_XCH ? 4 : 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), ADC_TMEM_COLS); tmem_relinquish(); }
+  // Q^T operand: rows = heads, K-major, two 64-dim halves of [16 rows x 128 B], 128-byte swizzle.  Only the first G
+  // rows of Q^T and of the P tiles are ever written: row n of a B operand feeds column n of the accumulator alone,
+  // and the columns >= G of S^T and O^T are never read, so whatever the other rows hold is harmless.
+  // Page ids are fetched once, in parallel, so the producer never waits on a global load between two TMA issues;
+  // pages past the end of the sequence are replaced by its last page (already in L2) and masked in the softmax.
+  if (tid < ADC_NB * 8 && total_pages > 0) page_s[tid] = pt[min(blk0 * 8 + tid, total_pages - 1)];
+  for (int i = tid; i < G * 16; i += ADC_THREADS) {
+    const int g = i >> 4, c = i & 15;
+    const uint4 v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(b) * p.hq + kvh * G + g) * ADC_D + c * 8);
+    *reinterpret_cast<uint4*>(pQ + (c >> 3) * 2048 + (g >> 3) * 1024 + (g & 7) * 128 + (((c & 7) ^ (g & 7)) << 4)) = v;
+  }
+  fence_proxy_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0 && nb > 0) {
+      prefetch_tmap(&tmap_kv);
+      bool ok = true;
+      for (int i = 0; i < 2 * nb && ok; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1u;
+        const int blk = i < nb ? i : i - nb;
+        const int kv = i < nb ? 0 : 1;
+        if (!mbar_wait(bar(B_EMPTY + st), ph ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (5 << 8)), limit)) { ok = false; break; }
+        mbar_expect_tx(bar(B_FULL + st), ADC_TILE);
+        const uint32_t dst = sRing + st * ADC_TILE;
+#pragma unroll 1
+        for (int j = 0; j < 8; ++j) {
+          const int page = page_s[blk * 8 + j];
+          const int row = ((page * 2 + kv) * p.hkv + kvh) * 16;  // first token row of the block in the [rows][2][64] view
+          tma_load_3d(dst + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 0, row);
+          tma_load_3d(dst + ADC_HALF + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 1, row);
+        }
+      }
+      if (!ok) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 2000000ull) { } }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0 && nb > 0) {
+      constexpr uint32_t IDESC_S = umma_idesc_bf16(128, ADC_NH, 0, 0);
+      constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, ADC_NH, 1, 0);      // A (= V^T) is MN-major
+      bool ok = true;
+      for (int i = 0; i < nb && ok; ++i) {
+        const int st = i & 1;
+        if (!mbar_wait(bar(B_FULL + st), (i >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (5 << 8)), limit)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d = tmem_base + i * ADC_NH;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t a = umma_desc_k_sw128(sRing + st * ADC_TILE + (kk >> 2) * ADC_HALF) + 2ull * (kk & 3);
+          const uint64_t bd = umma_desc_k_sw128(sQ + (kk >> 2) * 2048) + 2ull * (kk & 3);
+          umma_f16_ss(d, a, bd, IDESC_S, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(bar(B_EMPTY + st));
+        umma_commit(bar(B_SFULL + i));
+      }
+      for (int blk = 0; blk < nb && ok; ++blk) {
+        const int i = nb + blk;
+        const int st = i & 1;
+        if (!mbar_wait(bar(B_PFULL + blk), 0, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (5 << 8)), limit)) { ok = false; break; }
+        if (!mbar_wait(bar(B_FULL + st), (i >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (5 << 8)), limit)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d = tmem_base + ADC_O_COL;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t a = umma_desc_mn_sw128(sRing + st * ADC_TILE + kk * 2048, ADC_HALF, 1024);
+          const uint64_t bd = umma_desc_k_sw128(sP + blk * ADC_P_TILE + (kk >> 2) * 2048) + 2ull * (kk & 3);
+          umma_f16_ss(d, a, bd, IDESC_PV, (blk > 0 || kk > 0) ? 1u : 0u);
+        }
+        umma_commit(bar(B_EMPTY + st));
+        if (blk == nb - 1) umma_commit(bar(B_OFULL));
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ softmax / output warps ------------------------------
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;                    // token inside a block, later output dim: the TMEM lane
+    const int wi = warp - 2;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
+    float s[ADC_NB][G];
+    float mx[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) mx[g] = -INFINITY;
+    bool ok = nb > 0;
+#pragma unroll
+    for (int blk = 0; blk < ADC_NB; ++blk) {
+      if (blk < nb && ok) {
+        if (!mbar_wait(bar(B_SFULL + blk), 0, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (5 << 8)), limit)) { ok = false; }
+        else {
+          tc_fence_after();
+          uint32_t v[16];
+          tmem_ld_x16(t_lane + blk * ADC_NH, v);
+          tmem_ld_wait();
+          const bool valid = (blk0 + blk) * 128 + r < len;
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            s[blk][g] = valid ? __uint_as_float(v[g]) * p.scale_log2 : -INFINITY;
+            mx[g] = fmaxf(mx[g], s[blk][g]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int g = 0; g < G; ++g) s[blk][g] = -INFINITY;
+      }
+    }
+    // ---- maximum per head over the CTA's tokens: warp shuffle, then the four warps through shared memory ----
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xffffffffu, mx[g], o));
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) xch[wi * 8 + g] = mx[g];
+      mbar_arrive(bar(B_XCH));
+    }
+    if (ok && !mbar_wait(bar(B_XCH), 0, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (5 << 8)), limit)) ok = false;
+    float m[G], sum[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      m[g] = fmaxf(fmaxf(xch[g], xch[8 + g]), fmaxf(xch[16 + g], xch[24 + g]));
+      sum[g] = 0.f;
+    }
+    // ---- probabilities with the final maximum -> bf16 -> P tiles (K-major rows = heads, swizzled) ----
+#pragma unroll
+    for (int blk = 0; blk < ADC_NB; ++blk) {
+      if (blk < nb && ok) {
+        uint8_t* pt_blk = pP + blk * ADC_P_TILE + (r >> 6) * 2048;
+        const int c = (r & 63) >> 3, e = (r & 7) * 2;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float pr = (m[g] == -INFINITY) ? 0.f : exp2f(s[blk][g] - m[g]);
+          const __nv_bfloat16 pb = __float2bfloat16(pr);
+          sum[g] += __bfloat162float(pb);                 // what the MMA will actually see
+          *reinterpret_cast<__nv_bfloat16*>(pt_blk + (g >> 3) * 1024 + (g & 7) * 128 + ((c ^ (g & 7)) << 4) + e) = pb;
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_PFULL + blk));
+      }
+    }
+    // ---- sum per head ----
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) sum[g] += __shfl_xor_sync(0xffffffffu, sum[g], o);
+    }
+    if (lane == 0) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) xch[32 + wi * 8 + g] = sum[g];
+      mbar_arrive(bar(B_XCH));
+    }
+    if (ok && !mbar_wait(bar(B_XCH), 1, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (5 << 8)), limit)) ok = false;
+    float l[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) l[g] = xch[32 + g] + xch[40 + g] + xch[48 + g] + xch[56 + g];
+    // ---- output: thread <-> dim ----
+    float o[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) o[g] = 0.f;
+    if (nb > 0 && ok) {
+      if (!mbar_wait(bar(B_OFULL), 0, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (5 << 8)), limit)) ok = false;
+      else {
+        tc_fence_after();
+        uint32_t v[16];
+        tmem_ld_x16(t_lane + ADC_O_COL, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < G; ++g) o[g] = __uint_as_float(v[g]);
+      }
+    }
+    if (nb == 0) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const size_t hrow = static_cast<size_t>(b) * p.hq + kvh * G + g;
+      if (p.splits == 1) {
+        p.out[hrow * ADC_D + r] = __float2bfloat16(l[g] > 0.f ? o[g] / l[g] : 0.f);
+      } else {
+        p.part_acc[(hrow * p.splits + split) * ADC_D + r] = o[g];
+        if (r == 0) { p.part_ml[(hrow * p.splits + split) * 2] = m[g]; p.part_ml[(hrow * p.splits + split) * 2 + 1] = l[g]; }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, ADC_TMEM_COLS); }
+  if (p.splits == 1) return;
+
+  // ---- the last CTA of this (sequence, kv head) merges the splits ----
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    unsigned* ctr = p.counters + static_cast<size_t>(b) * p.hkv + kvh;
+    const unsigned old = atomicAdd(ctr, 1u);
+    *last_flag = (old == static_cast<unsigned>(p.splits - 1)) ? 1 : 0;
+    if (*last_flag) *ctr = 0;
+  }
+  __syncthreads();
+  if (!*last_flag) return;
+  __threadfence();
+  for (int i = tid; i < G * ADC_D; i += ADC_THREADS) {
+    const int g = i / ADC_D, d = i % ADC_D;
+    const size_t base = (static_cast<size_t>(b) * p.hq + kvh * G + g) * p.splits;
+    float m = -INFINITY;
+    for (int sI = 0; sI < p.splits; ++sI) m = fmaxf(m, __ldcg(p.part_ml + (base + sI) * 2));
+    float l = 0.f, o = 0.f;
+    for (int sI = 0; sI < p.splits; ++sI) {
+      const float ms = __ldcg(p.part_ml + (base + sI) * 2);
+      const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+      l += w * __ldcg(p.part_ml + (base + sI) * 2 + 1);
+      o += w * __ldcg(p.part_acc + (base + sI) * ADC_D + d);
+    }
+    p.out[(static_cast<size_t>(b) * p.hq + kvh * G + g) * ADC_D + d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
+  }
+}
+
+typedef CUresult (*EncodeTiledFn3)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+template <int G>
+static int launch_adc(const CUtensorMap& tm, const DecodeTcParams& p, dim3 grid, cudaStream_t stream) {
+  constexpr int SMEM = 2 * ADC_TILE + ADC_NB * ADC_P_TILE + ADC_Q_TILE + (64 + 16) * 4 + (6 + 2 * ADC_NB) * 8 + 64 + ADC_NB * 8 * 4 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return -1000 - static_cast<int>(e);
+    configured = true;
+  }
+  launch_ex(attn_decode_tc_kernel<G>, dim3(grid), dim3(ADC_THREADS), SMEM, stream, 0, tm, p);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Smallest split count this kernel accepts for sequences of up to max_len tokens (each CTA holds at most 4 x 128).
+extern "C" int b200_attn_decode_tc_min_splits(int max_len) {
+  const int blocks = (max_len + 127) / 128;
+  return (blocks + ADC_NB - 1) / ADC_NB > 0 ? (blocks + ADC_NB - 1) / ADC_NB : 1;
+}
+
+// Same contract as b200_attn_decode_tma.  splits must be at least b200_attn_decode_tc_min_splits(longest sequence).
+extern "C" int b200_attn_decode_tc(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
+                                   void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
+                                   int max_pages, int splits, float scale, int* status, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (page_size != 16 || (hq % hkv)) return -3;
+  const int G = hq / hkv;
+  if (G != 1 && G != 2 && G != 4 && G != 8) return -3;
+  if (splits < 1) splits = 1;
+  if (splits > 1 && (!scratch || !counters)) return -1;
+  if ((reinterpret_cast<uintptr_t>(cache) & 127) || (reinterpret_cast<uintptr_t>(q) & 15)) return -2;
+  static EncodeTiledFn3 fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess) return -11;
+    fn = reinterpret_cast<EncodeTiledFn3>(ptr);
+  }
+  // the cache as [token rows][2 halves][64 bf16]: box = 16 token rows of one half
+  CUtensorMap tm;
+  cuuint64_t dims[3] = {64, 2, static_cast<cuuint64_t>(num_pages) * 2 * hkv * 16};
+  cuuint64_t strides[2] = {128, 256};
+  cuuint32_t box[3] = {64, 1, 16};
+  cuuint32_t estr[3] = {1, 1, 1};
+  if (fn(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(cache), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return -12;
+  DecodeTcParams p;
+  p.q = static_cast<const __nv_bfloat16*>(q); p.page_table = page_table; p.seq_lens = seq_lens;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.part_acc = scratch;
+  p.part_ml = scratch ? scratch + static_cast<size_t>(B) * hq * splits * ADC_D : nullptr;
+  p.counters = counters; p.hq = hq; p.hkv = hkv; p.max_pages = max_pages; p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.limit_ns = 2000000000ull;
+  dim3 grid(hkv, B, splits);
+  switch (G) {
+    case 1: return launch_adc<1>(tm, p, grid, stream);
+    case 2: return launch_adc<2>(tm, p, grid, stream);
+    case 4: return launch_adc<4>(tm, p, grid, stream);
+    default: return launch_adc<8>(tm, p, grid, stream);
+  }
+}

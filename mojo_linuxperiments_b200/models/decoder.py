@@ -94,7 +94,11 @@ class Decoder:
         q = A.rope_kv_write(qkv, positions, self.cos, self.sin, self.hq, self.hkv, cache=cache,
                             page_table=kv.page_table, seq_ids=None, q_norm_w=W.get("q_norm"),
                             k_norm_w=W.get("k_norm"), eps=self.cfg.eps)
-        splits = A.pick_decode_splits(M, self.hkv, max_len)
+        impl = A.decode_impl(cache.page_size, self.hq // self.hkv)
+        if impl == "tc":
+            splits = A.pick_decode_splits_tc(M, self.hkv, kv.page_table.shape[1] * cache.page_size)
+        else:
+            splits = A.pick_decode_splits(M, self.hkv, max_len)
         sc = None
         if splits > 1:
             sc = self._decode_scratch.get((M, splits))

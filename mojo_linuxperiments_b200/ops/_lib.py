@@ -70,6 +70,8 @@ class _Sig:
     b200_attn_decode = (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P])
     b200_attn_decode_noalloc = (I, [P, P, P, P, P, I, I, I, I, I, I, F, P])
     b200_attn_decode_tma = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
+    b200_attn_decode_tc = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
+    b200_attn_decode_tc_min_splits = (I, [I])
     b200_attn_prefill = (I, [P, LL, P, LL, P, LL, P, P, I, I, I, I, I, F, P, P])
 
 

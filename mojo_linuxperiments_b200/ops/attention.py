@@ -75,18 +75,52 @@ class DecodeAttnScratch:
         self.splits = splits
 
 
-def pick_decode_splits(B: int, hkv: int, max_len: int, num_sms: int = 148, ctas_per_sm: int = 3) -> int:
+TC_BLOCKS_PER_CTA = 4          # the tensor-core decode kernel holds at most 4 x 128 cached tokens per CTA
+
+
+def tc_min_splits(max_len: int) -> int:
+    """Fewest KV splits the tensor-core decode kernel accepts for sequences of up to ``max_len`` tokens."""
+    blocks = (max_len + 127) // 128
+    return max(1, -(-blocks // TC_BLOCKS_PER_CTA))
+
+
+def decode_impl(page_size: int, group: int) -> str:
+    """Which decode-attention kernel "auto" means: the tcgen05 one where it applies (B200RT_ATTN=tma|simple overrides)."""
+    import os
+    want = os.environ.get("B200RT_ATTN", "tc")
+    if page_size == 16 and group in (1, 2, 4, 8):
+        return want if want in ("tc", "tma", "simple") else "tc"
+    return "simple"
+
+
+def pick_decode_splits_tc(B: int, hkv: int, max_len: int, num_sms: int = 148) -> int:
+    """KV splits for the tensor-core decode kernel.  Measured on B200 its time is close to
+    waves x (128-token blocks per CTA + 1.6) x 2.7 us with two CTAs per SM (the 1.6 is the per-CTA set-up, softmax
+    exchange and partial write), plus a little per split for the merge: few, long CTAs win once the grid fills the GPU."""
+    blocks = max(1, (max_len + 127) // 128)
+    smin = tc_min_splits(max_len)
+    slots = 2 * num_sms
+    best, best_cost = smin, None
+    for s in range(smin, max(smin, min(32, blocks)) + 1):
+        cost = -(-(max(1, B * hkv) * s) // slots) * (-(-blocks // s) + 1.6) + 0.15 * s
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
+
+
+def pick_decode_splits(B: int, hkv: int, max_len: int, num_sms: int = 148, ctas_per_sm: int = 3,
+                       min_splits: int = 1) -> int:
     """Number of KV splits: the grid is B * hkv * splits CTAs on num_sms * ctas_per_sm slots, and each CTA's work is
     ~1/splits, so the time is ~ceil(grid / slots) / splits; pick the smallest split count within 5 % of the best,
-    keeping at least 64 tokens per split."""
+    keeping at least 64 tokens per split (and at least ``min_splits``)."""
     slots = num_sms * ctas_per_sm
     pairs = max(1, B * hkv)
-    max_splits = max(1, min(32, max_len // 64))
-    best_cost = min(-(-(pairs * s) // slots) / s for s in range(1, max_splits + 1))
-    for s in range(1, max_splits + 1):
+    max_splits = max(min_splits, min(32, max_len // 64))
+    best_cost = min(-(-(pairs * s) // slots) / s for s in range(min_splits, max_splits + 1))
+    for s in range(min_splits, max_splits + 1):
         if -(-(pairs * s) // slots) / s <= best_cost * 1.05:
             return s
-    return 1
+    return min_splits
 
 
 def attn_decode(q: torch.Tensor, cache: PagedKVCache, page_table: torch.Tensor, seq_lens: torch.Tensor, *,
@@ -94,24 +128,30 @@ def attn_decode(q: torch.Tensor, cache: PagedKVCache, page_table: torch.Tensor, 
                 out: torch.Tensor | None = None, impl: str = "auto") -> torch.Tensor:
     """q [B, hq, 128] against the first seq_lens[b] cached tokens of sequence b.
 
-    impl "tma" (page size 16, group size 1/2/4/8): TMA-fed ring, warp-private online softmax; "simple": the general
-    kernel; "auto" picks the first when it applies."""
+    impl "tc" (page size 16, group size 1/2/4/8): tcgen05 MMAs for Q.K^T and P.V, scores in TMEM, pages by TMA
+    (raises ``splits`` to what the longest representable sequence needs); "tma": TMA-fed ring with CUDA-core dot
+    products; "simple": the general kernel; "auto" picks the first that applies."""
     B, hq, d = q.shape
     assert d == HEAD_DIM and q.is_contiguous() and page_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
     if out is None:
         out = torch.empty_like(q)
-    if splits > 1 and scratch is None:
-        scratch = DecodeAttnScratch(B, hq, cache.kv_heads, splits, q.device)
     G = hq // cache.kv_heads
-    if impl == "tma" or (impl == "auto" and cache.page_size == 16 and G in (1, 2, 4, 8)):
-        rc = _lib.lib().b200_attn_decode_tma(
+    if impl == "auto":
+        impl = decode_impl(cache.page_size, G)
+    if impl == "tc":
+        splits = max(splits, tc_min_splits(page_table.shape[1] * cache.page_size))
+    if splits > 1 and (scratch is None or scratch.splits != splits):
+        scratch = DecodeAttnScratch(B, hq, cache.kv_heads, splits, q.device)
+    if impl in ("tc", "tma"):
+        fn = _lib.lib().b200_attn_decode_tc if impl == "tc" else _lib.lib().b200_attn_decode_tma
+        rc = fn(
             q.data_ptr(), cache.data.data_ptr(), cache.num_pages, page_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),
             scratch.buf.data_ptr() if scratch is not None else None,
             scratch.counters.data_ptr() if scratch is not None else None,
             B, hq, cache.kv_heads, cache.page_size, page_table.shape[1], splits,
             float(scale if scale is not None else 1.0 / math.sqrt(d)), default_workspace(q.device).status.data_ptr(),
             _lib.stream())
-        _lib.check(rc, "attn_decode_tma")
+        _lib.check(rc, "attn_decode_" + impl)
         return out
     rc = _lib.lib().b200_attn_decode(
         q.data_ptr(), cache.data.data_ptr(), page_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),

@@ -23,8 +23,12 @@ def test_stream_pool_launch_wait_any_order_and_reuse():
     work(0, 1)                                        # first use of a kernel may load its module, which can
     torch.cuda.synchronize()                          # synchronise the device: do that before anything is timed
     out.zero_()
+    import time
     for i, reps in enumerate((80, 20, 1)):
-        assert pool.launch(work, i, reps) == i
+        t0 = time.monotonic()
+        got = pool.launch(work, i, reps)
+        dt = time.monotonic() - t0
+        assert got == i, (got, i, dt, [pool._busy(j) for j in range(3)])
     assert pool.launch(work, 0, 1) == -1              # every slot busy
     order = [pool.wait_any(10.0) for _ in range(3)]
     assert order == [2, 1, 0]
