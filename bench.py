@@ -45,56 +45,110 @@ def parse():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle samples every 200 ms while the timed region runs (read-only query)."""
+    """Clock / throttle-reason samples of one GPU while the timed region runs (read-only queries).
 
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    ``nvidia-smi -lms 50`` is started before the warm-up steps so that it is already printing when the timed region
+    begins; every line carries its own timestamp and only lines between ``mark_start()`` and ``stop()`` count.  A
+    second, in-process sampler reads the same values through NVML every 10 ms during the region, which still yields
+    samples when the region is shorter than nvidia-smi's period.  If neither saw the region (a very short run), the
+    samples taken during the warm-up steps are reported and marked as such."""
+
+    FIELDS = ("timestamp,index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, device_index: int):
+        import datetime
+        import threading
+        self._dt = datetime
         self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         self.proc = None
+        self.t_start = None
+        self.nvml_samples = []          # (in_region, sm_mhz, max_mhz, reasons bitmask)
+        self._stop = threading.Event()
+        self._in_region = False
+        uuid = None
         try:
             uuid = str(torch.cuda.get_device_properties(device_index).uuid)
-            sel = ["-i", uuid if uuid.startswith("GPU-") else "GPU-" + uuid]
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
         except Exception:
-            sel = []
+            pass
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", *sel, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "200"], stdout=self.file, stderr=subprocess.DEVNULL)
+            self.proc = subprocess.Popen(["nvidia-smi", *(["-i", uuid] if uuid else []), f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
+                                         stdout=self.file, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
+        self._thread = threading.Thread(target=self._nvml_loop, args=(uuid,), daemon=True)
+        self._thread.start()
+
+    def _nvml_loop(self, uuid):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if isinstance(uuid, str) else uuid)
+            mx = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            while not self._stop.is_set():
+                sm = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                try:
+                    why = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(h))
+                except Exception:
+                    why = int(pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h))
+                self.nvml_samples.append((self._in_region, float(sm), float(mx), why))
+                self._stop.wait(0.01)
+        except Exception:
+            return
+
+    def mark_start(self):
+        self.t_start = self._dt.datetime.now()
+        self._in_region = True
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        self.file.flush()
-        self.file.seek(0)
-        sm, mx, reasons = [], [], set()
+        t_end = self._dt.datetime.now()
+        self._in_region = False
+        self._stop.set()
+        self._thread.join(timeout=2)
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.file.read().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
+        inside, before = [], []
+        if self.proc is not None:
+            self.proc.terminate()
             try:
-                sm.append(float(parts[1])); mx.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+            self.file.flush()
+            self.file.seek(0)
+            for line in self.file.read().splitlines():
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 10:
+                    continue
+                try:
+                    ts = self._dt.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f")
+                    rec = (float(parts[2]), float(parts[3]),
+                           {n for n, v in zip(names, parts[6:10]) if v.lower().startswith("active")})
+                except ValueError:
+                    continue
+                (inside if (self.t_start is not None and self.t_start <= ts <= t_end) else before).append(rec)
         try:
             os.unlink(self.file.name)
         except OSError:
             pass
-        busy = sorted(sm)[len(sm) // 2:] if sm else []
-        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        # NVML reason bits: 0x4 sw_power_cap, 0x8 hw_slowdown, 0x20 sw_thermal, 0x40 hw_thermal
+        bits = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+        for in_region, sm, mx, why in self.nvml_samples:
+            rec = (sm, mx, {n for b, n in bits.items() if why & b})
+            (inside if in_region else before).append(rec)
+        window = "timed region"
+        use = inside
+        if not use:
+            use, window = before[-20:], "warm-up steps just before the timed region (the region was shorter than a sample period)"
+        if not use:
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["no clock samples available"]}
+        sm = sorted(r[0] for r in use)
+        reasons = set().union(*(r[2] for r in use))
+        busy = sm[len(sm) // 2:]
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(r[1] for r in use), "samples": len(use),
+                "window": window, "reasons": sorted(reasons)}
 
 
 def dist_setup(n: int):
@@ -172,12 +226,14 @@ def run(args):
     torch.cuda.synchronize()
     if hasattr(eng, "check_status"):
         eng.check_status()          # stop here, not after minutes of timeouts, if a device-side wait ran out
+    sampler = ClockSampler(local) if rank == 0 else None      # started early: it is already sampling when timing starts
     for _ in range(W):
         eng.decode_step()
     torch.cuda.synchronize()
     launches_before = _lib.LAUNCHES[0]
     per_step = getattr(eng, "kernels_per_step", None)
-    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.mark_start()
     secs = timed_steps(eng.decode_step, K, world)
     clocks = sampler.stop() if sampler else None
     value = B * K / secs
