@@ -125,6 +125,34 @@ int b200_ag_sync(void* const* peer_data, int world, int rank, size_t flag_off, s
                  int rows_per_rank, int M, void* words, int wait, int finish, int* status, int limit_ms,
                  cudaStream_t stream);
 
+// ---- expert-parallel dispatch / combine for token-sharded prefill (buffers of the all-gather / reduce-scatter links) ----
+// dispatch: this rank's rows go (int8 + scale) to the ranks owning one of their top-k experts, the routing lists
+// (ids / weights padded to 8 per token at ids_off* / wts_off*) to every rank; flags as in b200_w8a8_gemm_ag.
+int b200_ep_dispatch(const void* xq_local, const float* sx_local, const int* ids_local, const float* wts_local,
+                     int M, int K, int k, int experts_per_rank, int rows_per_rank, void* const* peer_data,
+                     int world, int rank, size_t q_off0, size_t q_off1, size_t s_off0, size_t s_off1,
+                     size_t ids_off0, size_t ids_off1, size_t wts_off0, size_t wts_off1, size_t flag_off,
+                     size_t done_off, int blk_cap, void* words, void* row_ctr, int* status, int limit_ms,
+                     cudaStream_t stream);
+// wait for all sources, then copy the routing lists of all M tokens to ids_out / wts_out [M][k]
+int b200_ep_wait(void* const* peer_data, int world, int rank, size_t ids_off0, size_t ids_off1, size_t wts_off0,
+                 size_t wts_off1, size_t flag_off, int blk_cap, int rows_per_rank, int M, int k, void* words,
+                 int* ids_out, float* wts_out, int* status, int limit_ms, cudaStream_t stream);
+// b200_moe_gather over the gather buffer of the current epoch (heap_base: this rank's heap)
+int b200_ep_gather(const void* heap_base, size_t q_off0, size_t q_off1, size_t s_off0, size_t s_off1,
+                   const void* words, int d, const int* slot_token, const int* meta, int max_slots,
+                   void* xq_perm, float* sx_perm, cudaStream_t stream);
+// combine: weighted local expert outputs of each token -> receive slot of the token's owner; blk_ctr: world*blk_cap
+// local uint32, zero at first.  reduce: the owner sums the slots of the ranks its own routing names -> out[my rows][d].
+int b200_ep_combine_scatter(const void* y, long long ldy, const int* inv, const float* wts, int M, int k, int d,
+                            int rows_per_rank, void* const* peer_data, int world, int rank, size_t recv_off0,
+                            size_t recv_off1, size_t ctr_off, int r_cap, void* words, void* blk_ctr, int blk_cap,
+                            int* status, int limit_ms, cudaStream_t stream);
+int b200_ep_combine_reduce(const int* ids_local, int M, int k, int d, int experts_per_rank, int rows_per_rank,
+                           void* const* peer_data, int world, int rank, size_t recv_off0, size_t recv_off1,
+                           size_t ctr_off, int r_cap, void* words, void* out, long long ldo, int* status,
+                           int limit_ms, int num_sms, cudaStream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

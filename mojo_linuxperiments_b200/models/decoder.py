@@ -125,7 +125,7 @@ class Decoder:
         mode "decode":  M = batch, one token per sequence, kv.seq_lens already counts the current token.
         """
         cfg = self.cfg
-        if (mode == "prefill" and self.moe is None and self.tp_ctx is not None and last_idx is not None
+        if (mode == "prefill" and self.tp_ctx is not None and last_idx is not None
                 and self.tp_ctx.sp_ok(token_ids.shape[0])):
             return self._forward_prefill_sharded(token_ids, positions, kv, cu_seqlens, max_len, seq_ids, last_idx)
         h = A.embed_gather(token_ids, self.w["embed"])
@@ -148,10 +148,11 @@ class Decoder:
         return self._sample(h, delta)
 
     def _forward_prefill_sharded(self, token_ids, positions, kv, cu_seqlens, max_len, seq_ids, last_idx):
-        """Dense tensor-parallel prefill with the residual stream sharded by token: this rank normalises and quantises
-        only the rows it owns, column-parallel linears gather the int8 rows inside the GEMM kernel, row-parallel
-        linears reduce-scatter their partial sums from the GEMM epilogue.  Attention sees all tokens of its own heads
-        exactly as in the replicated path."""
+        """Tensor-parallel prefill with the residual stream sharded by token: this rank normalises and quantises only
+        the rows it owns, column-parallel linears gather the int8 rows inside the GEMM kernel, row-parallel linears
+        reduce-scatter their partial sums from the GEMM epilogue, and mixture-of-experts layers dispatch rows to the
+        experts' ranks and combine the outputs back at the owners.  Attention sees all tokens of its own heads exactly
+        as in the replicated path."""
         cfg, sp = self.cfg, self.tp_ctx.sp
         M = token_ids.shape[0]
         a, b = sp.my_rows(M)
@@ -165,6 +166,9 @@ class Decoder:
             aq, sa = L.act_quant(attn.view(M, -1))
             delta = sp.rs_linear(aq, sa, W["o"].qweight, W["o"].scale)[: b - a]
             xq, sx = self._norm_quant(h, delta, W["mlp_norm"])
+            if self.moe is not None:
+                delta = self.moe.forward_sharded(W, xq, sx, M)[: b - a]
+                continue
             gu = sp.ag_linear(xq, sx, W["gate_up"].qweight, W["gate_up"].scale, M)
             hq, sh = L.act_quant(gu, mode=L.AQ_SWIGLU)
             delta = sp.rs_linear(hq, sh, W["down"].qweight, W["down"].scale)[: b - a]

@@ -4,6 +4,11 @@ After the attention all-reduce every rank holds the same normalised, rotated, in
 all tokens (same result everywhere), keeps the (token, expert) pairs whose expert it owns, runs the two grouped expert
 GEMMs on them and produces a partial output per token; the partials are summed across ranks by the same peer-memory
 all-reduce the dense row-parallel layers use.  With one rank this degenerates to a plain local MoE.
+
+Token-sharded prefill (``forward_sharded``) replaces the replication by the expert all-to-all: each rank routes only
+the rows it owns, ``ep_dispatch`` stores a row into the heaps of exactly the ranks that own one of its experts,
+the grouped expert GEMMs run on what arrived, and ``ep_combine`` sends each token's weighted local outputs back to its
+owner, which sums the contributions (``csrc/kernels/moe_ep.cu``).
 """
 from __future__ import annotations
 
@@ -33,3 +38,19 @@ class MoEBlock:
             return self.tp_ctx.reduce_partial(lambda out: MO.moe_combine(yd, work, wts, out=out), M, cfg.d_model)
         out = MO.moe_combine(yd, work, wts)
         return self.comm.all_reduce(out)
+
+    def forward_sharded(self, W: dict, xq_loc: torch.Tensor, sx_loc: torch.Tensor, M: int) -> torch.Tensor:
+        """xq_loc / sx_loc: the normalised, quantised rows this rank owns of an M-token call; returns the MoE output of
+        those rows (bf16 [rows_per_rank, d], the first ``my_rows`` valid)."""
+        cfg, sp = self.cfg, self.tp_ctx.sp
+        logits = L.w8a8_gemm(xq_loc, sx_loc, W["router"].qweight, W["router"].scale, out_dtype=torch.float32)
+        ids_loc, wts_loc = MO.router_topk(logits, cfg.top_k, cfg.norm_topk_prob)
+        sp.ep_dispatch(xq_loc, sx_loc, ids_loc, wts_loc, M, self.n_local)
+        ids, wts = sp.ep_wait(M, cfg.top_k)
+        work = MO.moe_align(ids, self.e0, self.n_local)
+        xp, sp_scale = sp.ep_gather(work, cfg.d_model)
+        sp.ag_sync(M, wait=False, finish=True)        # the gather buffer of this epoch has been consumed
+        gu = MO.grouped_gemm(xp, sp_scale, W["experts_gate_up"].qweight, W["experts_gate_up"].scale, work)
+        hq, sh = L.act_quant(gu, mode=L.AQ_SWIGLU)
+        yd = MO.grouped_gemm(hq, sh, W["experts_down"].qweight, W["experts_down"].scale, work)
+        return sp.ep_combine(yd, work, wts, ids_loc, M, self.n_local)

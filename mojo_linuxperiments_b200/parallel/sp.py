@@ -25,6 +25,7 @@ import torch
 from ..ops import _lib
 
 PHASE_ALL, PHASE_TILES, PHASE_TAIL, PHASE_PUSH = 7, 1, 2, 4
+EP_KMAX = 8                  # routing slots per token in the dispatch buffers
 
 
 def _round_up(x: int, a: int) -> int:
@@ -46,6 +47,8 @@ class SPLayout:
     done_off: int = 0
     recv_off: tuple = ()
     ctr_off: int = 0
+    ids_off: tuple = ()        # expert routing lists of all tokens (int32 / fp32, 8 per token), per parity
+    wts_off: tuple = ()
     nbytes: int = 0
 
     def __post_init__(self):
@@ -64,6 +67,8 @@ class SPLayout:
         self.done_off = take(self.world * 4)
         self.recv_off = (take(self.world * self.r_cap * self.n_cap * 2), take(self.world * self.r_cap * self.n_cap * 2))
         self.ctr_off = take(16)
+        self.ids_off = (take(self.m_cap * EP_KMAX * 4), take(self.m_cap * EP_KMAX * 4))
+        self.wts_off = (take(self.m_cap * EP_KMAX * 4), take(self.m_cap * EP_KMAX * 4))
         self.nbytes = _round_up(off, 1024)
 
 
@@ -87,6 +92,7 @@ class SPLink:
         self._c_data = (ctypes.c_void_p * self.world)(*self.data_ptrs)
         z = lambda n: torch.zeros(n, dtype=torch.int32, device=self.device)
         self.ag_words, self.rs_words, self.row_ctr, self.status = z(4), z(4), z(max(self.layout.blk_cap, 1)), z(4)
+        self.ep_blk_ctr = z(max(self.world * self.layout.blk_cap, 1))
 
     @classmethod
     def on_heap(cls, heap, m_cap: int, k_cap: int, n_cap: int, use_nvls: bool = True, limit_ms: int = 2000) -> "SPLink":
@@ -164,6 +170,72 @@ class SPLink:
                                      1 if wait else 0, 1 if finish else 0, self.status.data_ptr(), self.limit_ms,
                                      _lib.stream())
         _lib.check(rc, "ag_sync")
+
+
+    # ---- expert-parallel dispatch / combine (csrc/kernels/moe_ep.cu) ---------------------------------------------
+    def ep_dispatch(self, xq_local: torch.Tensor, sx_local: torch.Tensor, ids_local: torch.Tensor, wts_local: torch.Tensor,
+                    M: int, experts_per_rank: int) -> None:
+        """Send this rank's token rows to the ranks that own one of their top-k experts and the routing lists to all."""
+        lay, bo = self.layout, self.base_off
+        K, k = xq_local.shape[1], ids_local.shape[1]
+        assert xq_local.is_contiguous() and ids_local.is_contiguous() and wts_local.is_contiguous()
+        assert ids_local.dtype == torch.int32 and wts_local.dtype == torch.float32 and k <= EP_KMAX
+        assert M <= lay.m_cap and K <= lay.k_cap
+        rc = _lib.lib().b200_ep_dispatch(
+            xq_local.data_ptr(), sx_local.data_ptr(), ids_local.data_ptr(), wts_local.data_ptr(), M, K, k,
+            experts_per_rank, self.rows_per_rank(M), self._c_data, self.world, self.rank, bo + lay.q_off[0],
+            bo + lay.q_off[1], bo + lay.s_off[0], bo + lay.s_off[1], bo + lay.ids_off[0], bo + lay.ids_off[1],
+            bo + lay.wts_off[0], bo + lay.wts_off[1], bo + lay.flag_off, bo + lay.done_off, lay.blk_cap,
+            self.ag_words.data_ptr(), self.row_ctr.data_ptr(), self.status.data_ptr(), self.limit_ms, _lib.stream())
+        _lib.check(rc, "ep_dispatch")
+
+    def ep_wait(self, M: int, k: int):
+        """Wait for every rank's dispatch; returns the routing of all M tokens (ids int32 [M,k], weights fp32 [M,k])."""
+        lay, bo = self.layout, self.base_off
+        ids = torch.empty((M, k), dtype=torch.int32, device=self.device)
+        wts = torch.empty((M, k), dtype=torch.float32, device=self.device)
+        rc = _lib.lib().b200_ep_wait(self._c_data, self.world, self.rank, bo + lay.ids_off[0], bo + lay.ids_off[1],
+                                     bo + lay.wts_off[0], bo + lay.wts_off[1], bo + lay.flag_off, lay.blk_cap,
+                                     self.rows_per_rank(M), M, k, self.ag_words.data_ptr(), ids.data_ptr(),
+                                     wts.data_ptr(), self.status.data_ptr(), self.limit_ms, _lib.stream())
+        _lib.check(rc, "ep_wait")
+        return ids, wts
+
+    def ep_gather(self, work, d: int):
+        """Rows of the dispatched tokens in this rank's slot order (the `moe_gather` of the gather buffer)."""
+        lay, bo = self.layout, self.base_off
+        xp = torch.empty((work.max_slots, d), dtype=torch.int8, device=self.device)
+        sp_ = torch.empty((work.max_slots,), dtype=torch.float32, device=self.device)
+        rc = _lib.lib().b200_ep_gather(self.data_ptrs[self.rank], bo + lay.q_off[0], bo + lay.q_off[1], bo + lay.s_off[0],
+                                       bo + lay.s_off[1], self.ag_words.data_ptr(), d, work.slot_token.data_ptr(),
+                                       work.meta.data_ptr(), work.max_slots, xp.data_ptr(), sp_.data_ptr(), _lib.stream())
+        _lib.check(rc, "ep_gather")
+        return xp, sp_
+
+    def ep_combine(self, y: torch.Tensor, work, wts_all: torch.Tensor, ids_local: torch.Tensor, M: int,
+                   experts_per_rank: int, out: torch.Tensor | None = None, phase: int = PHASE_ALL) -> torch.Tensor:
+        """Weighted expert outputs back to the tokens' owners; returns out[my rows, d] (sum over contributing ranks).
+        ``phase`` PHASE_TILES = scatter only, PHASE_TAIL = owner-side reduction only (single-device tests)."""
+        lay, bo = self.layout, self.base_off
+        d, k = y.shape[1], wts_all.shape[1]
+        R = self.rows_per_rank(M)
+        if out is None:
+            out = torch.empty((R, d), dtype=torch.bfloat16, device=self.device)
+        if phase & PHASE_TILES:
+            rc = _lib.lib().b200_ep_combine_scatter(
+                y.data_ptr(), y.stride(0), work.inv.data_ptr(), wts_all.data_ptr(), M, k, d, R, self._c_data, self.world,
+                self.rank, bo + lay.recv_off[0], bo + lay.recv_off[1], bo + lay.ctr_off, lay.r_cap,
+                self.rs_words.data_ptr(), self.ep_blk_ctr.data_ptr(), lay.blk_cap, self.status.data_ptr(), self.limit_ms,
+                _lib.stream())
+            _lib.check(rc, "ep_combine_scatter")
+        if phase & PHASE_TAIL:
+            rc = _lib.lib().b200_ep_combine_reduce(
+                ids_local.data_ptr(), M, k, d, experts_per_rank, R, self._c_data, self.world, self.rank,
+                bo + lay.recv_off[0], bo + lay.recv_off[1], bo + lay.ctr_off, lay.r_cap, self.rs_words.data_ptr(),
+                out.data_ptr(), out.stride(0), self.status.data_ptr(), self.limit_ms, _lib.num_sms(self.device.index),
+                _lib.stream())
+            _lib.check(rc, "ep_combine_reduce")
+        return out
 
 
 def virtual_links(world: int, m_cap: int, k_cap: int, n_cap: int, device=None) -> list[SPLink]:

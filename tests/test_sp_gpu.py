@@ -85,3 +85,59 @@ def test_rs_linear_virtual_ranks(world, M, K, N, with_residual):
             ref = exact[a:b] + (res[r][: b - a].float() if with_residual else 0)
             assert torch.allclose(got.float(), ref, rtol=2e-2, atol=tol)
             assert int(ln.rs_words[0].item()) == epoch + 1
+
+
+@pytest.mark.parametrize("world,M,d,E,k", [(4, 520, 256, 16, 4), (8, 1024, 512, 128, 8), (2, 200, 128, 8, 2)])
+def test_ep_dispatch_and_combine_virtual_ranks(world, M, d, E, k):
+    """Expert all-to-all over virtual ranks: rows reach exactly the ranks that own one of their experts, the routing
+    reaches everyone, and the weighted expert outputs come back summed at the owners."""
+    from mojo_linuxperiments_b200.ops import moe as MO
+    from mojo_linuxperiments_b200.parallel import sp as SP
+    links = SP.virtual_links(world, m_cap=1024, k_cap=512, n_cap=512)
+    epr = E // world
+    g = torch.Generator(device="cpu").manual_seed(11)
+    for epoch in range(3):
+        xq = torch.randint(-127, 128, (M, d), generator=g, dtype=torch.int8).cuda()
+        sx = (torch.rand((M,), generator=g) + 0.1).cuda()
+        ids = torch.rand((M, E), generator=g).topk(k, dim=1).indices.to(torch.int32).cuda()
+        wts = torch.rand((M, k), generator=g).cuda()
+        rows = [ln.my_rows(M) for ln in links]
+        for r, ln in enumerate(links):
+            a, b = rows[r]
+            ln.ep_dispatch(xq[a:b].contiguous(), sx[a:b].contiguous(), ids[a:b].contiguous(), wts[a:b].contiguous(), M, epr)
+        works, ys = [], []
+        for r, ln in enumerate(links):
+            ids_all, wts_all = ln.ep_wait(M, k)
+            assert torch.equal(ids_all, ids) and torch.equal(wts_all, wts), f"routing on rank {r}"
+            work = MO.moe_align(ids_all, r * epr, epr)
+            xp, sp_scale = ln.ep_gather(work, d)
+            ln.ag_sync(M, wait=False, finish=True)
+            torch.cuda.synchronize()
+            n = int(work.meta[0].item())
+            tok = work.slot_token[:n].long()
+            assert torch.equal(xp[:n], xq[tok]) and torch.equal(sp_scale[:n], sx[tok]), f"gathered rows on rank {r}"
+            y = torch.randn((work.max_slots, d), generator=torch.Generator(device="cpu").manual_seed(100 * epoch + r)).to(torch.bfloat16).cuda()
+            works.append((work, wts_all))
+            ys.append(y)
+        R = links[0].rows_per_rank(M)
+        outs = [torch.full((R, d), float("nan"), dtype=torch.bfloat16, device="cuda") for _ in range(world)]
+        for r, ln in enumerate(links):
+            a, b = rows[r]
+            ln.ep_combine(ys[r], works[r][0], works[r][1], ids[a:b].contiguous(), M, epr, out=outs[r], phase=SP.PHASE_TILES)
+        for r, ln in enumerate(links):
+            a, b = rows[r]
+            ln.ep_combine(ys[r], works[r][0], works[r][1], ids[a:b].contiguous(), M, epr, out=outs[r], phase=SP.PHASE_TAIL)
+        torch.cuda.synchronize()
+        # reference: per rank the plain combine kernel (bf16 partial per token), summed in rank order over the ranks
+        # that own one of the token's experts
+        partial = [MO.moe_combine(ys[r], works[r][0], works[r][1]).float() for r in range(world)]
+        owner_of = (ids // epr).long()
+        total = torch.zeros((M, d), device="cuda")
+        for r in range(world):
+            has = (owner_of == r).any(dim=1, keepdim=True)
+            total += torch.where(has, partial[r], torch.zeros((), device="cuda"))
+        for r, ln in enumerate(links):
+            ln.check_status()
+            a, b = rows[r]
+            assert torch.equal(outs[r][: b - a], total[a:b].to(torch.bfloat16)), f"combine on rank {r} epoch {epoch}"
+            assert int(ln.rs_words[0].item()) == epoch + 1 and int(ln.ag_words[0].item()) == epoch + 1
