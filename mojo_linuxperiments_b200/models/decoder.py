@@ -126,7 +126,7 @@ class Decoder:
         """
         cfg = self.cfg
         if (mode == "prefill" and self.tp_ctx is not None and last_idx is not None
-                and self.tp_ctx.sp_ok(token_ids.shape[0])):
+                and self.tp_ctx.sp_ok(token_ids.shape[0], moe=self.moe is not None)):
             return self._forward_prefill_sharded(token_ids, positions, kv, cu_seqlens, max_len, seq_ids, last_idx)
         h = A.embed_gather(token_ids, self.w["embed"])
         delta = None

@@ -58,9 +58,17 @@ class TPContext:
         self.sp = SPLink.on_heap(self.heap, max_tokens, d_model, d_model, use_nvls=self.use_nvls,
                                  limit_ms=wait_limit_ms) if want_sp else None
 
-    def sp_ok(self, M: int) -> bool:
-        """Whether an M-token call should use the token-sharded path."""
-        return self.sp is not None and SP_MIN_TOKENS_PER_RANK * self.world <= M <= self.sp.layout.m_cap and M > FUSED_MAX_M
+    def sp_ok(self, M: int, moe: bool = False) -> bool:
+        """Whether an M-token prefill call should use the token-sharded path.  Mixture-of-experts models take it from
+        four ranks up (B200RT_SP_MOE=0/1 overrides): on two ranks the dispatch / combine kernels cost more than the
+        all-reduce they replace."""
+        if self.sp is None or not (SP_MIN_TOKENS_PER_RANK * self.world <= M <= self.sp.layout.m_cap and M > FUSED_MAX_M):
+            return False
+        if moe:
+            import os
+            want = os.environ.get("B200RT_SP_MOE")
+            return want != "0" if want is not None else self.world >= 4
+        return True
 
     def row_parallel(self, xq: torch.Tensor, sx: torch.Tensor, lw, residual: torch.Tensor | None = None) -> torch.Tensor:
         """Sum over ranks of this rank's K-shard product; returns the full [M, N] bf16 result on every rank."""

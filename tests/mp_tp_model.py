@@ -22,6 +22,7 @@ def main():
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     rank, world = dist.get_rank(), dist.get_world_size()
     if kind == "moe":
+        os.environ.setdefault("B200RT_SP_MOE", "1")      # exercise the expert dispatch / combine kernels at any rank count
         # 4 KV heads on up to 8 ranks (heads replicated on rank pairs), 16 experts sharded over the ranks
         cfg = C.tiny_moe(n_layers=2, d_model=1024, n_heads=8, n_kv_heads=4, n_experts=16, top_k=4, moe_ffn=256, vocab=2048)
     else:
