@@ -2,7 +2,7 @@
 
 Timing: CUDA events around one CUDA graph of `iters` back-to-back launches that rotate through enough distinct weight / activation
 buffers to exceed the 126 MB L2 (so every launch streams its operands from HBM), after warm-up.
-Usage: python benchmarks/bench_gemm.py [--out gpurun_out/gemm.json]
+Usage: python benchmarks/bench_gemm.py [--out gemm.json]
 """
 import argparse
 import json
