@@ -64,8 +64,8 @@ def main():
         q = torch.randn((B, hq, 128), device=dev).to(torch.bfloat16)
         out = torch.empty_like(q)
         byts = B * ctx * hkv * 512
-        for impl in ("tc", "tma"):
-            if impl == "tc":
+        for impl in ("tcp", "tc", "tma"):
+            if impl in ("tc", "tcp"):
                 splits = A.pick_decode_splits_tc(B, hkv, max_pages * ps)
             else:
                 splits = A.pick_decode_splits(B, hkv, ctx + 64)
@@ -76,8 +76,8 @@ def main():
         if os.environ.get("SWEEP_SPLITS"):
             for splits in range(A.tc_min_splits(max_pages * ps), 10):
                 sc = A.DecodeAttnScratch(B, hq, hkv, splits, dev)
-                t = graph_time(lambda i: A.attn_decode(q, caches[i % n_layers], pt, lens, scratch=sc, splits=splits, out=out, impl="tc"))
-                print(json.dumps({"op": "attn_decode", "impl": "tc", "case": tag, "splits": splits, "us": t * 1e6}), flush=True)
+                t = graph_time(lambda i: A.attn_decode(q, caches[i % n_layers], pt, lens, scratch=sc, splits=splits, out=out, impl="tcp"))
+                print(json.dumps({"op": "attn_decode", "impl": "tcp", "case": tag, "splits": splits, "us": t * 1e6}), flush=True)
         del caches
     for (M, K, mode, tag) in [(32, 4096, L.AQ_ADD_NORM, "add_norm bs32"), (1, 4096, L.AQ_ADD_NORM, "add_norm bs1"),
                               (32, 14336, L.AQ_SWIGLU, "swiglu bs32"), (32, 4096, L.AQ_PLAIN, "plain bs32"),

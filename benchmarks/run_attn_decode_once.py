@@ -1,5 +1,5 @@
 """Launch paged decode attention a few times on one shape (for profiler captures).
-python benchmarks/run_attn_decode_once.py [impl=tc|tma|simple] [B=32] [ctx=1024] [hq=32] [hkv=8] [splits=0(auto)]"""
+python benchmarks/run_attn_decode_once.py [impl=tcp|tc|tma|simple] [B=32] [ctx=1024] [hq=32] [hkv=8] [splits=0(auto)]"""
 import sys
 
 import torch
@@ -23,7 +23,7 @@ pt = torch.arange(B * max_pages, dtype=torch.int32, device=dev).view(B, max_page
 lens = torch.full((B,), ctx, dtype=torch.int32, device=dev)
 q = torch.randn((B, hq, 128), device=dev).to(torch.bfloat16)
 if splits <= 0:
-    if impl == "tc":
+    if impl in ("tc", "tcp"):
         splits = A.pick_decode_splits_tc(B, hkv, max_pages * ps)
     else:
         splits = A.pick_decode_splits(B, hkv, ctx + 64)

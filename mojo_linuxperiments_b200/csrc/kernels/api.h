@@ -78,6 +78,11 @@ int b200_attn_decode_tc_min_splits(int max_len);
 int b200_attn_decode_tc(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
                         void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
                         int max_pages, int splits, float scale, int* status, cudaStream_t stream);
+// Persistent form: two CTAs per SM walk the (kv head, sequence, split) items, loads of the next item overlap the
+// softmax / output phase of the current one.
+int b200_attn_decode_tcp(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
+                         void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
+                         int max_pages, int splits, float scale, int* status, int num_sms, cudaStream_t stream);
 int b200_attn_prefill(const void* q, long long ld_q, const void* k, long long ld_k, const void* v, long long ld_v,
                       void* out, const int* cu_seqlens, int B, int total_tokens, int max_len, int hq, int hkv,
                       float scale, int* status, cudaStream_t stream);

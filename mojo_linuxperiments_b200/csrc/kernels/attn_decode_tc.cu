@@ -317,6 +317,385 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   }
 }
 
+// ------------------------------------------------------------------------------------------------------------------
+// Persistent form: the grid is two CTAs per SM and every CTA walks the work items (kv_head, sequence, split) w =
+// blockIdx.x, blockIdx.x + gridDim.x, ...  The three roles loop over the items independently, so the TMA producer runs
+// ahead into the next item's K tiles while the softmax warps are still exchanging maxima or writing the output of the
+// current one: the per-CTA set-up, the first-tile latency and the epilogue of the one-item kernel above are paid once
+// per CTA instead of once per item, and there is no wave quantisation.  Extra hand-shakes: SFREE / OFREE tell the MMA
+// warp that the softmax warps have copied the scores / the output out of TMEM, QFULL[2] double-buffers the Q^T
+// operand (the softmax warps load the next item's queries while they wait for the current scores), page ids and
+// sequence lengths are prefetched one and two items ahead.  Barriers that are not used by every item (an item of a
+// short sequence may have fewer blocks, or none) keep their own use counters, which every role derives from the same
+// sequence length.
+// ------------------------------------------------------------------------------------------------------------------
+struct ItemGeom { int kvh, b, split, len, total_pages, blk0, nb; };
+
+__device__ __forceinline__ ItemGeom item_geom(int w, int len, const DecodeTcParams& p) {
+  ItemGeom g;
+  g.split = w % p.splits;
+  const int rest = w / p.splits;
+  g.kvh = rest % p.hkv;
+  g.b = rest / p.hkv;
+  g.len = len;
+  g.total_pages = (len + 15) >> 4;
+  const int total_blocks = (len + 127) >> 7;
+  const int per = (total_blocks + p.splits - 1) / p.splits;
+  g.blk0 = g.split * per;
+  g.nb = min(max(min(total_blocks, g.blk0 + per) - g.blk0, 0), ADC_NB);
+  return g;
+}
+__device__ __forceinline__ int item_seq(int w, const DecodeTcParams& p) { return w / (p.splits * p.hkv); }
+
+template <int G>
+__global__ void __launch_bounds__(ADC_THREADS, 2)
+attn_decode_tcp_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeTcParams p, const int num_items) {
+  pdl_launch_dependents();
+  pdl_wait();
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // [ring 2 x 32K][P ADC_NB x 4K][Q 2 x 4K][exchange floats][barriers][flags][page ids 2 x 32]
+  uint8_t* pP = smem + 2 * ADC_TILE;
+  uint8_t* pQ = pP + ADC_NB * ADC_P_TILE;
+  float* xch = reinterpret_cast<float*>(pQ + 2 * ADC_Q_TILE);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(xch + 64);
+  enum { B_FULL = 0, B_EMPTY = 2, B_SFULL = 4, B_PFULL = 4 + ADC_NB, B_OFULL = 4 + 2 * ADC_NB, B_XCH = 5 + 2 * ADC_NB,
+         B_SFREE = 6 + 2 * ADC_NB, B_OFREE = 8 + 2 * ADC_NB, B_QFULL = 10 + 2 * ADC_NB, B_COUNT = 12 + 2 * ADC_NB };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* last_flag = abort_flag + 1;
+  int* page_s = const_cast<int*>(last_flag) + 1;   // [2][ADC_NB * 8]
+  const uint32_t sRing = smem_u32(smem);
+  const uint32_t sP = smem_u32(pP), sQ = smem_u32(pQ);
+  const uint32_t bar0 = smem_u32(bars);
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint64_t limit = p.limit_ns;
+  const int stride = gridDim.x;
+  const int w0 = blockIdx.x;
+
+  if (tid == 0) {
+    for (int i = 0; i < B_COUNT; ++i) {
+      const bool four = (i >= B_PFULL && i < B_PFULL + ADC_NB) || i == B_XCH || i >= B_SFREE;
+      mbar_init(bar(i), four ? 4 : 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), ADC_TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer (whole warp: lanes prefetch page ids) ------------------------------
+    prefetch_tmap(&tmap_kv);
+    int len_cur = w0 < num_items ? p.seq_lens[item_seq(w0, p)] : 0;
+    int len_nxt = w0 + stride < num_items ? p.seq_lens[item_seq(w0 + stride, p)] : 0;
+    {
+      const ItemGeom g = item_geom(w0, len_cur, p);
+      if (w0 < num_items && g.total_pages > 0)
+        page_s[lane] = p.page_table[static_cast<size_t>(g.b) * p.max_pages + min(g.blk0 * 8 + lane, g.total_pages - 1)];
+    }
+    __syncwarp();
+    uint32_t t = 0;                                   // tiles issued so far: ring stage t & 1, use (t >> 1)
+    bool ok = true;
+    int it = 0;
+    for (int w = w0; w < num_items && ok; w += stride, ++it) {
+      const ItemGeom g = item_geom(w, len_cur, p);
+      // page ids of the next item and the length of the one after it are requested now and consumed after this
+      // item's tiles have been issued
+      const int w1 = w + stride, w2 = w + 2 * stride;
+      int pid_nxt = 0;
+      ItemGeom g1 = g;
+      if (w1 < num_items) {
+        g1 = item_geom(w1, len_nxt, p);
+        if (g1.total_pages > 0)
+          pid_nxt = p.page_table[static_cast<size_t>(g1.b) * p.max_pages + min(g1.blk0 * 8 + lane, g1.total_pages - 1)];
+      }
+      const int len_nn = w2 < num_items ? p.seq_lens[item_seq(w2, p)] : 0;
+      const int* pg = page_s + (it & 1) * (ADC_NB * 8);
+      if (lane == 0) {
+        for (int i = 0; i < 2 * g.nb && ok; ++i, ++t) {
+          const int st = t & 1;
+          const uint32_t ph = (t >> 1) & 1u;
+          const int blk = i < g.nb ? i : i - g.nb;
+          const int kv = i < g.nb ? 0 : 1;
+          if (!mbar_wait(bar(B_EMPTY + st), ph ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (6 << 8)), limit)) { ok = false; break; }
+          mbar_expect_tx(bar(B_FULL + st), ADC_TILE);
+          const uint32_t dst = sRing + st * ADC_TILE;
+#pragma unroll 1
+          for (int j = 0; j < 8; ++j) {
+            const int row = ((pg[blk * 8 + j] * 2 + kv) * p.hkv + g.kvh) * 16;
+            tma_load_3d(dst + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 0, row);
+            tma_load_3d(dst + ADC_HALF + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 1, row);
+          }
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      t = __shfl_sync(0xffffffffu, t, 0);
+      page_s[((it + 1) & 1) * (ADC_NB * 8) + lane] = pid_nxt;
+      __syncwarp();
+      len_cur = len_nxt;
+      len_nxt = len_nn;
+    }
+    if (!ok && lane == 0) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 2000000ull) { } }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = umma_idesc_bf16(128, ADC_NH, 0, 0);
+      constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, ADC_NH, 1, 0);
+      uint32_t t = 0, o_uses = 0;
+      uint32_t blk_uses[ADC_NB];
+#pragma unroll
+      for (int i = 0; i < ADC_NB; ++i) blk_uses[i] = 0;
+      int len_cur = w0 < num_items ? p.seq_lens[item_seq(w0, p)] : 0;
+      bool ok = true;
+      int it = 0;
+      for (int w = w0; w < num_items && ok; w += stride, ++it) {
+        const ItemGeom g = item_geom(w, len_cur, p);
+        const int len_nxt = w + stride < num_items ? p.seq_lens[item_seq(w + stride, p)] : 0;
+        const uint32_t sQb = sQ + (it & 1) * ADC_Q_TILE;
+        if (!mbar_wait(bar(B_QFULL + (it & 1)), (it >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (6 << 8)), limit)) { ok = false; break; }
+        // SFREE / OFREE alternate between two barriers: an item without blocks lets the softmax warps run one item
+        // ahead, which must not complete the phase this warp is about to wait for
+        if (it > 0 && !mbar_wait(bar(B_SFREE + ((it - 1) & 1)), ((it - 1) >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_TMEM_EMPTY | (6 << 8)), limit)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll 1
+        for (int i = 0; i < g.nb && ok; ++i, ++t) {
+          const int st = t & 1;
+          if (!mbar_wait(bar(B_FULL + st), (t >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (6 << 8)), limit)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d = tmem_base + i * ADC_NH;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t a = umma_desc_k_sw128(sRing + st * ADC_TILE + (kk >> 2) * ADC_HALF) + 2ull * (kk & 3);
+            const uint64_t bd = umma_desc_k_sw128(sQb + (kk >> 2) * 2048) + 2ull * (kk & 3);
+            umma_f16_ss(d, a, bd, IDESC_S, kk > 0 ? 1u : 0u);
+          }
+          umma_commit(bar(B_EMPTY + st));
+          umma_commit(bar(B_SFULL + i));
+        }
+        if (!ok) break;
+        if (it > 0 && !mbar_wait(bar(B_OFREE + ((it - 1) & 1)), ((it - 1) >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_TMEM_EMPTY | (6 << 8)), limit)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll 1
+        for (int blk = 0; blk < g.nb && ok; ++blk, ++t) {
+          const int st = t & 1;
+          if (!mbar_wait(bar(B_PFULL + blk), blk_uses[blk] & 1u, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (6 << 8)), limit)) { ok = false; break; }
+          if (!mbar_wait(bar(B_FULL + st), (t >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (6 << 8)), limit)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d = tmem_base + ADC_O_COL;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t a = umma_desc_mn_sw128(sRing + st * ADC_TILE + kk * 2048, ADC_HALF, 1024);
+            const uint64_t bd = umma_desc_k_sw128(sP + blk * ADC_P_TILE + (kk >> 2) * 2048) + 2ull * (kk & 3);
+            umma_f16_ss(d, a, bd, IDESC_PV, (blk > 0 || kk > 0) ? 1u : 0u);
+          }
+          umma_commit(bar(B_EMPTY + st));
+          if (blk == g.nb - 1) umma_commit(bar(B_OFULL));
+          ++blk_uses[blk];
+        }
+        if (ok && g.nb == 0) umma_commit(bar(B_OFULL));     // every item completes one OFULL phase: it paces the softmax warps
+        ++o_uses;
+        len_cur = len_nxt;
+      }
+      (void)o_uses;
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------ softmax / output warps ------------------------------
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;
+    const int wi = warp - 2;
+    const int st4 = tid - 64;                        // 0..127
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
+    uint32_t o_uses = 0, x_uses = 0;
+    uint32_t blk_uses[ADC_NB];
+#pragma unroll
+    for (int i = 0; i < ADC_NB; ++i) blk_uses[i] = 0;
+    int len_cur = w0 < num_items ? p.seq_lens[item_seq(w0, p)] : 0;
+    auto load_q = [&](int w, int buf) {
+      const int rest = w / p.splits;
+      const int kvh = rest % p.hkv, b = rest / p.hkv;
+      if (st4 < G * 16) {
+        const int g = st4 >> 4, c = st4 & 15;
+        const uint4 v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(b) * p.hq + kvh * G + g) * ADC_D + c * 8);
+        *reinterpret_cast<uint4*>(pQ + buf * ADC_Q_TILE + (c >> 3) * 2048 + (g >> 3) * 1024 + (g & 7) * 128 + (((c & 7) ^ (g & 7)) << 4)) = v;
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_QFULL + buf));
+    };
+    if (w0 < num_items) load_q(w0, 0);
+    bool ok = true;
+    int it = 0;
+    for (int w = w0; w < num_items && ok; w += stride, ++it) {
+      const ItemGeom gm = item_geom(w, len_cur, p);
+      const int len_nxt = w + stride < num_items ? p.seq_lens[item_seq(w + stride, p)] : 0;
+      if (w + stride < num_items) load_q(w + stride, (it + 1) & 1);
+      const int nb = gm.nb;
+      float s[ADC_NB][G];
+      float mx[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) mx[g] = -INFINITY;
+#pragma unroll
+      for (int blk = 0; blk < ADC_NB; ++blk) {
+        if (blk < nb && ok) {
+          if (!mbar_wait(bar(B_SFULL + blk), blk_uses[blk] & 1u, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (6 << 8)), limit)) { ok = false; }
+          else {
+            tc_fence_after();
+            uint32_t v[16];
+            tmem_ld_x16(t_lane + blk * ADC_NH, v);
+            tmem_ld_wait();
+            const bool valid = (gm.blk0 + blk) * 128 + r < gm.len;
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              s[blk][g] = valid ? __uint_as_float(v[g]) * p.scale_log2 : -INFINITY;
+              mx[g] = fmaxf(mx[g], s[blk][g]);
+            }
+          }
+        } else {
+#pragma unroll
+          for (int g = 0; g < G; ++g) s[blk][g] = -INFINITY;
+        }
+      }
+      // the scores are in registers: the MMA warp may overwrite the S columns with the next item's
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_SFREE + (it & 1)));
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx[g] = fmaxf(mx[g], __shfl_xor_sync(0xffffffffu, mx[g], o));
+      }
+      if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) xch[wi * 8 + g] = mx[g];
+        mbar_arrive(bar(B_XCH));
+      }
+      if (ok && !mbar_wait(bar(B_XCH), x_uses & 1u, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (6 << 8)), limit)) ok = false;
+      ++x_uses;
+      float m[G], sum[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        m[g] = fmaxf(fmaxf(xch[g], xch[8 + g]), fmaxf(xch[16 + g], xch[24 + g]));
+        sum[g] = 0.f;
+      }
+#pragma unroll
+      for (int blk = 0; blk < ADC_NB; ++blk) {
+        if (blk < nb && ok) {
+          uint8_t* pt_blk = pP + blk * ADC_P_TILE + (r >> 6) * 2048;
+          const int c = (r & 63) >> 3, e = (r & 7) * 2;
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const float pr = (m[g] == -INFINITY) ? 0.f : exp2f(s[blk][g] - m[g]);
+            const __nv_bfloat16 pb = __float2bfloat16(pr);
+            sum[g] += __bfloat162float(pb);
+            *reinterpret_cast<__nv_bfloat16*>(pt_blk + (g >> 3) * 1024 + (g & 7) * 128 + ((c ^ (g & 7)) << 4) + e) = pb;
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar(B_PFULL + blk));
+        }
+        if (blk < nb) ++blk_uses[blk];
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum[g] += __shfl_xor_sync(0xffffffffu, sum[g], o);
+      }
+      if (lane == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) xch[32 + wi * 8 + g] = sum[g];
+        mbar_arrive(bar(B_XCH));
+      }
+      if (ok && !mbar_wait(bar(B_XCH), x_uses & 1u, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (6 << 8)), limit)) ok = false;
+      ++x_uses;
+      float l[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) l[g] = xch[32 + g] + xch[40 + g] + xch[48 + g] + xch[56 + g];
+      float o[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) o[g] = 0.f;
+      if (ok) {
+        if (!mbar_wait(bar(B_OFULL), o_uses & 1u, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (6 << 8)), limit)) ok = false;
+        else if (nb > 0) {
+          tc_fence_after();
+          uint32_t v[16];
+          tmem_ld_x16(t_lane + ADC_O_COL, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int g = 0; g < G; ++g) o[g] = __uint_as_float(v[g]);
+        }
+      }
+      ++o_uses;
+      // the output is in registers: the MMA warp may start the next item's P.V
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(B_OFREE + (it & 1)));
+      if (nb == 0) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; }
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const size_t hrow = static_cast<size_t>(gm.b) * p.hq + gm.kvh * G + g;
+        if (p.splits == 1) {
+          p.out[hrow * ADC_D + r] = __float2bfloat16(l[g] > 0.f ? o[g] / l[g] : 0.f);
+        } else {
+          p.part_acc[(hrow * p.splits + gm.split) * ADC_D + r] = o[g];
+          if (r == 0) { p.part_ml[(hrow * p.splits + gm.split) * 2] = m[g]; p.part_ml[(hrow * p.splits + gm.split) * 2 + 1] = l[g]; }
+        }
+      }
+      if (p.splits > 1) {
+        // ---- the last CTA to finish a (sequence, kv head) merges its splits; the four warps agree through XCH ----
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_XCH));
+        if (ok && !mbar_wait(bar(B_XCH), x_uses & 1u, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (6 << 8)), limit)) ok = false;
+        ++x_uses;
+        if (st4 == 0) {
+          unsigned* ctr = p.counters + static_cast<size_t>(gm.b) * p.hkv + gm.kvh;
+          const unsigned old = atomicAdd(ctr, 1u);
+          const int last = (old == static_cast<unsigned>(p.splits - 1)) ? 1 : 0;
+          if (last) *ctr = 0;
+          *last_flag = last;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(B_XCH));
+        if (ok && !mbar_wait(bar(B_XCH), x_uses & 1u, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (6 << 8)), limit)) ok = false;
+        ++x_uses;
+        if (ok && *last_flag) {
+          __threadfence();
+          for (int i = st4; i < G * ADC_D; i += 128) {
+            const int g = i / ADC_D, d = i % ADC_D;
+            const size_t base = (static_cast<size_t>(gm.b) * p.hq + gm.kvh * G + g) * p.splits;
+            float mm = -INFINITY;
+            for (int sI = 0; sI < p.splits; ++sI) mm = fmaxf(mm, __ldcg(p.part_ml + (base + sI) * 2));
+            float ll = 0.f, oo = 0.f;
+            for (int sI = 0; sI < p.splits; ++sI) {
+              const float ms = __ldcg(p.part_ml + (base + sI) * 2);
+              const float wgt = (ms == -INFINITY) ? 0.f : exp2f(ms - mm);
+              ll += wgt * __ldcg(p.part_ml + (base + sI) * 2 + 1);
+              oo += wgt * __ldcg(p.part_acc + (base + sI) * ADC_D + d);
+            }
+            p.out[(static_cast<size_t>(gm.b) * p.hq + gm.kvh * G + g) * ADC_D + d] = __float2bfloat16(ll > 0.f ? oo / ll : 0.f);
+          }
+        }
+      }
+      len_cur = len_nxt;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, ADC_TMEM_COLS); }
+}
+
 typedef CUresult (*EncodeTiledFn3)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -335,6 +714,21 @@ static int launch_adc(const CUtensorMap& tm, const DecodeTcParams& p, dim3 grid,
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
 
+template <int G>
+static int launch_adcp(const CUtensorMap& tm, const DecodeTcParams& p, int num_items, int num_sms, cudaStream_t stream) {
+  constexpr int SMEM = 2 * ADC_TILE + ADC_NB * ADC_P_TILE + 2 * ADC_Q_TILE + 64 * 4 + (12 + 2 * ADC_NB) * 8 + 64 + 2 * ADC_NB * 8 * 4 + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tcp_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return -1000 - static_cast<int>(e);
+    configured = true;
+  }
+  const int grid = num_items < 2 * num_sms ? num_items : 2 * num_sms;
+  launch_ex(attn_decode_tcp_kernel<G>, dim3(grid), dim3(ADC_THREADS), SMEM, stream, 0, tm, p, num_items);
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
+}
+
 }  // namespace b200
 
 using namespace b200;
@@ -345,10 +739,10 @@ extern "C" int b200_attn_decode_tc_min_splits(int max_len) {
   return (blocks + ADC_NB - 1) / ADC_NB > 0 ? (blocks + ADC_NB - 1) / ADC_NB : 1;
 }
 
-// Same contract as b200_attn_decode_tma.  splits must be at least b200_attn_decode_tc_min_splits(longest sequence).
-extern "C" int b200_attn_decode_tc(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
-                                   void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
-                                   int max_pages, int splits, float scale, int* status, cudaStream_t stream) {
+static int attn_decode_tc_common(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
+                                 void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
+                                 int max_pages, int splits, float scale, int* status, int persistent, int num_sms,
+                                 cudaStream_t stream) {
   if (B <= 0) return 0;
   if (page_size != 16 || (hq % hkv)) return -3;
   const int G = hq / hkv;
@@ -378,6 +772,15 @@ extern "C" int b200_attn_decode_tc(const void* q, const void* cache, int num_pag
   p.part_ml = scratch ? scratch + static_cast<size_t>(B) * hq * splits * ADC_D : nullptr;
   p.counters = counters; p.hq = hq; p.hkv = hkv; p.max_pages = max_pages; p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.limit_ns = 2000000000ull;
+  if (persistent) {
+    const int items = B * hkv * splits;
+    switch (G) {
+      case 1: return launch_adcp<1>(tm, p, items, num_sms, stream);
+      case 2: return launch_adcp<2>(tm, p, items, num_sms, stream);
+      case 4: return launch_adcp<4>(tm, p, items, num_sms, stream);
+      default: return launch_adcp<8>(tm, p, items, num_sms, stream);
+    }
+  }
   dim3 grid(hkv, B, splits);
   switch (G) {
     case 1: return launch_adc<1>(tm, p, grid, stream);
@@ -385,4 +788,20 @@ extern "C" int b200_attn_decode_tc(const void* q, const void* cache, int num_pag
     case 4: return launch_adc<4>(tm, p, grid, stream);
     default: return launch_adc<8>(tm, p, grid, stream);
   }
+}
+
+// Same contract as b200_attn_decode_tma.  splits must be at least b200_attn_decode_tc_min_splits(longest sequence).
+extern "C" int b200_attn_decode_tc(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
+                                   void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
+                                   int max_pages, int splits, float scale, int* status, cudaStream_t stream) {
+  return attn_decode_tc_common(q, cache, num_pages, page_table, seq_lens, out, scratch, counters, B, hq, hkv, page_size,
+                               max_pages, splits, scale, status, 0, 0, stream);
+}
+
+// Persistent form of the same kernel: two CTAs per SM walk the (kv head, sequence, split) items.
+extern "C" int b200_attn_decode_tcp(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
+                                    void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
+                                    int max_pages, int splits, float scale, int* status, int num_sms, cudaStream_t stream) {
+  return attn_decode_tc_common(q, cache, num_pages, page_table, seq_lens, out, scratch, counters, B, hq, hkv, page_size,
+                               max_pages, splits, scale, status, 1, num_sms > 0 ? num_sms : 148, stream);
 }

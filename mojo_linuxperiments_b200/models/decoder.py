@@ -95,7 +95,7 @@ class Decoder:
                             page_table=kv.page_table, seq_ids=None, q_norm_w=W.get("q_norm"),
                             k_norm_w=W.get("k_norm"), eps=self.cfg.eps)
         impl = A.decode_impl(cache.page_size, self.hq // self.hkv)
-        if impl == "tc":
+        if impl in ("tc", "tcp"):
             splits = A.pick_decode_splits_tc(M, self.hkv, kv.page_table.shape[1] * cache.page_size)
         else:
             splits = A.pick_decode_splits(M, self.hkv, max_len)

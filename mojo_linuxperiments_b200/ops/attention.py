@@ -89,7 +89,7 @@ def decode_impl(page_size: int, group: int) -> str:
     import os
     want = os.environ.get("B200RT_ATTN", "tc")
     if page_size == 16 and group in (1, 2, 4, 8):
-        return want if want in ("tc", "tma", "simple") else "tc"
+        return want if want in ("tc", "tcp", "tma", "simple") else "tc"
     return "simple"
 
 
@@ -129,7 +129,8 @@ def attn_decode(q: torch.Tensor, cache: PagedKVCache, page_table: torch.Tensor, 
     """q [B, hq, 128] against the first seq_lens[b] cached tokens of sequence b.
 
     impl "tc" (page size 16, group size 1/2/4/8): tcgen05 MMAs for Q.K^T and P.V, scores in TMEM, pages by TMA
-    (raises ``splits`` to what the longest representable sequence needs); "tma": TMA-fed ring with CUDA-core dot
+    (raises ``splits`` to what the longest representable sequence needs); "tcp": the same as a persistent grid whose
+    producer runs ahead into the next work item; "tma": TMA-fed ring with CUDA-core dot
     products; "simple": the general kernel; "auto" picks the first that applies."""
     B, hq, d = q.shape
     assert d == HEAD_DIM and q.is_contiguous() and page_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
@@ -138,19 +139,21 @@ def attn_decode(q: torch.Tensor, cache: PagedKVCache, page_table: torch.Tensor, 
     G = hq // cache.kv_heads
     if impl == "auto":
         impl = decode_impl(cache.page_size, G)
-    if impl == "tc":
+    if impl in ("tc", "tcp"):
         splits = max(splits, tc_min_splits(page_table.shape[1] * cache.page_size))
     if splits > 1 and (scratch is None or scratch.splits != splits):
         scratch = DecodeAttnScratch(B, hq, cache.kv_heads, splits, q.device)
-    if impl in ("tc", "tma"):
-        fn = _lib.lib().b200_attn_decode_tc if impl == "tc" else _lib.lib().b200_attn_decode_tma
+    if impl in ("tc", "tcp", "tma"):
+        fn = {"tc": _lib.lib().b200_attn_decode_tc, "tcp": _lib.lib().b200_attn_decode_tcp,
+              "tma": _lib.lib().b200_attn_decode_tma}[impl]
+        extra = (_lib.num_sms(q.device.index),) if impl == "tcp" else ()
         rc = fn(
             q.data_ptr(), cache.data.data_ptr(), cache.num_pages, page_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),
             scratch.buf.data_ptr() if scratch is not None else None,
             scratch.counters.data_ptr() if scratch is not None else None,
             B, hq, cache.kv_heads, cache.page_size, page_table.shape[1], splits,
             float(scale if scale is not None else 1.0 / math.sqrt(d)), default_workspace(q.device).status.data_ptr(),
-            _lib.stream())
+            *extra, _lib.stream())
         _lib.check(rc, "attn_decode_" + impl)
         return out
     rc = _lib.lib().b200_attn_decode(

@@ -85,10 +85,10 @@ def test_attn_prefill_reads_strided_qkv():
 
 @pytest.mark.parametrize("hq,hkv", [(32, 8), (4, 1), (8, 1), (16, 1), (2, 2)])
 @pytest.mark.parametrize("splits", [1, 4])
-@pytest.mark.parametrize("impl", ["simple", "tma", "tc"])
+@pytest.mark.parametrize("impl", ["simple", "tma", "tc", "tcp"])
 def test_attn_decode_paged(hq, hkv, splits, impl):
     from mojo_linuxperiments_b200.ops import attention as A
-    if impl in ("tma", "tc") and hq // hkv == 16:
+    if impl in ("tma", "tc", "tcp") and hq // hkv == 16:
         pytest.skip("the TMA-fed forms cover group sizes up to 8")
     ps = 16
     lens = [1, 17, 300, 1280, 64]
