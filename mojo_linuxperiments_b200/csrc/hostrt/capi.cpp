@@ -5,6 +5,7 @@
 
 #include "arena.hpp"
 #include "collectives.hpp"
+#include "w8a8_host.hpp"
 #include "numa.hpp"
 #include "pool.hpp"
 #include "scenarios.hpp"
@@ -178,6 +179,16 @@ long hostrt_fill_reduce(void* numa, unsigned long long n, unsigned long long see
   return r.status;
 }
 double hostrt_fill_reduce_serial(unsigned long long n, unsigned long long seed) { return fill_reduce_serial(n, seed); }
+// info5: {quant_ns, gemm_ns, workers, used_vnni, -}
+long hostrt_w8a8_linear(void* numa, const void* x_bf16, int M, int K, const void* wq, const float* sw, int N, void* y_bf16,
+                        int max_workers_per_node, int force_scalar, void* q_out, float* sx_out, int* acc_out, long* info5) {
+  const W8A8HostResult r = w8a8_linear_host(*static_cast<NumaInfo*>(numa), static_cast<const uint16_t*>(x_bf16), M, K,
+                                            static_cast<const int8_t*>(wq), sw, N, static_cast<uint16_t*>(y_bf16),
+                                            max_workers_per_node, force_scalar, static_cast<int8_t*>(q_out), sx_out,
+                                            reinterpret_cast<int32_t*>(acc_out));
+  if (info5) { info5[0] = r.quant_ns; info5[1] = r.gemm_ns; info5[2] = r.workers; info5[3] = r.used_vnni; info5[4] = 0; }
+  return r.status;
+}
 float hostrt_philox_uniform(unsigned long long i, unsigned long long seed) { return b200::philox_uniform_pm1(i, seed); }
 void hostrt_philox_block(unsigned long long counter, unsigned long long seed, unsigned* out4) {
   const b200::Philox4 r = b200::philox4x32_10(counter, seed);

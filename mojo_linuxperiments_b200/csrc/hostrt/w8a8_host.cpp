@@ -1,0 +1,202 @@
+#include "w8a8_host.hpp"
+
+#include <immintrin.h>
+
+#include <cstring>
+#include <vector>
+
+#include "heap_move_array.hpp"
+#include "pool.hpp"
+#include "sys.hpp"
+
+namespace hostrt {
+
+namespace {
+
+inline float bf16_to_f32(uint16_t b) {
+  uint32_t u = static_cast<uint32_t>(b) << 16;
+  float f;
+  std::memcpy(&f, &u, 4);
+  return f;
+}
+inline uint16_t f32_to_bf16_rne(float f) {
+  uint32_t u;
+  std::memcpy(&u, &f, 4);
+  if ((u & 0x7f800000u) == 0x7f800000u) return static_cast<uint16_t>((u >> 16) | ((u & 0xffffu) ? 0x40u : 0u));   // inf / nan
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return static_cast<uint16_t>(u >> 16);
+}
+
+// in-place fast Walsh-Hadamard transform of 128 floats in Sylvester order, scaled by 1/sqrt(128)
+inline void fwht128(float* v) {
+  for (int h = 1; h < 128; h <<= 1)
+    for (int i = 0; i < 128; i += 2 * h)
+      for (int j = i; j < i + h; ++j) {
+        const float a = v[j], b = v[j + h];
+        v[j] = a + b;
+        v[j + h] = a - b;
+      }
+  const float s = 0.08838834764831845f;
+  for (int i = 0; i < 128; ++i) v[i] *= s;
+}
+
+struct QuantJob {
+  const uint16_t* x; int K; int m0, m1;
+  int8_t* q; uint8_t* qu; float* sx;
+};
+
+// rows [m0, m1): rotate, quantise, and also store the +128-biased copy the VNNI path multiplies
+void quant_worker(uint64_t a0, uint64_t, uint64_t, uint64_t, uint64_t, uint64_t) {
+  QuantJob& j = *reinterpret_cast<QuantJob*>(a0);
+  float blk[128];
+  for (int m = j.m0; m < j.m1; ++m) {
+    const uint16_t* xr = j.x + static_cast<size_t>(m) * j.K;
+    float amax = 0.f;
+    // pass 1: the row maximum of the rotated values
+    for (int b = 0; b < j.K; b += 128) {
+      for (int i = 0; i < 128; ++i) blk[i] = bf16_to_f32(xr[b + i]);
+      fwht128(blk);
+      for (int i = 0; i < 128; ++i) {           // no libm calls on pool threads
+        const float a = blk[i] < 0.f ? -blk[i] : blk[i];
+        amax = a > amax ? a : amax;
+      }
+    }
+    const float s = amax > 0.f ? amax / 127.f : 1.f;
+    j.sx[m] = s;
+    // pass 2: quantise (the rotation is recomputed: it is cheap next to keeping K floats per row around)
+    int8_t* qr = j.q + static_cast<size_t>(m) * j.K;
+    uint8_t* qur = j.qu + static_cast<size_t>(m) * j.K;
+    for (int b = 0; b < j.K; b += 128) {
+      for (int i = 0; i < 128; ++i) blk[i] = bf16_to_f32(xr[b + i]);
+      fwht128(blk);
+      for (int i = 0; i < 128; ++i) {
+        int qi = _mm_cvtss_si32(_mm_set_ss(blk[i] / s));      // round to nearest even (default MXCSR mode)
+        qi = qi > 127 ? 127 : (qi < -127 ? -127 : qi);
+        qr[b + i] = static_cast<int8_t>(qi);
+        qur[b + i] = static_cast<uint8_t>(qi + 128);
+      }
+    }
+  }
+}
+
+struct GemmJob {
+  const int8_t* q; const uint8_t* qu; const float* sx;
+  const int8_t* wq; const float* sw;
+  uint16_t* y; int32_t* acc_out;
+  int M, K, N, n0, n1, vnni;
+};
+
+inline void finish(const GemmJob& j, int m, int n, int32_t acc) {
+  if (j.acc_out) j.acc_out[static_cast<size_t>(m) * j.N + n] = acc;
+  j.y[static_cast<size_t>(m) * j.N + n] = f32_to_bf16_rne(static_cast<float>(acc) * (j.sw[n] * j.sx[m]));
+}
+
+void gemm_scalar(const GemmJob& j) {
+  for (int n = j.n0; n < j.n1; ++n) {
+    const int8_t* w = j.wq + static_cast<size_t>(n) * j.K;
+    for (int m = 0; m < j.M; ++m) {
+      const int8_t* q = j.q + static_cast<size_t>(m) * j.K;
+      int32_t acc = 0;
+      for (int k = 0; k < j.K; ++k) acc += static_cast<int32_t>(q[k]) * static_cast<int32_t>(w[k]);
+      finish(j, m, n, acc);
+    }
+  }
+}
+
+constexpr int MB = 16;   // token rows per register block
+
+__attribute__((target("avx512f,avx512bw,avx512vnni")))
+void gemm_vnni(const GemmJob& j) {
+  const __m512i ones = _mm512_set1_epi8(1);
+  for (int n = j.n0; n < j.n1; ++n) {
+    const int8_t* w = j.wq + static_cast<size_t>(n) * j.K;
+    // 128 * sum_k w[k]: what the +128 bias of the activations adds to every dot product with this channel
+    __m512i ws = _mm512_setzero_si512();
+    for (int k = 0; k < j.K; k += 64) ws = _mm512_dpbusd_epi32(ws, ones, _mm512_loadu_si512(w + k));
+    const int32_t corr = 128 * _mm512_reduce_add_epi32(ws);
+    for (int m0 = 0; m0 < j.M; m0 += MB) {
+      const int mb = j.M - m0 < MB ? j.M - m0 : MB;
+      __m512i acc[MB];
+      for (int i = 0; i < MB; ++i) acc[i] = _mm512_setzero_si512();
+      for (int k = 0; k < j.K; k += 64) {
+        const __m512i wv = _mm512_loadu_si512(w + k);
+        for (int i = 0; i < mb; ++i)
+          acc[i] = _mm512_dpbusd_epi32(acc[i], _mm512_loadu_si512(j.qu + static_cast<size_t>(m0 + i) * j.K + k), wv);
+      }
+      for (int i = 0; i < mb; ++i) finish(j, m0 + i, n, _mm512_reduce_add_epi32(acc[i]) - corr);
+    }
+  }
+}
+
+void gemm_worker(uint64_t a0, uint64_t, uint64_t, uint64_t, uint64_t, uint64_t) {
+  const GemmJob& j = *reinterpret_cast<GemmJob*>(a0);
+  if (j.vnni && (j.K % 64) == 0) gemm_vnni(j); else gemm_scalar(j);
+}
+
+}  // namespace
+
+W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, int K, const int8_t* wq, const float* sw,
+                                int N, uint16_t* y, int max_workers_per_node, int force_scalar, int8_t* q_out,
+                                float* sx_out, int32_t* acc_out) {
+  W8A8HostResult res{};
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 128) != 0 || !x || !wq || !sw || !y) { res.status = -err::kINVAL; return res; }
+  const int nn = info.num_nodes();
+  if (nn == 0) { res.status = -err::kNOENT; return res; }
+  std::vector<int> per_node(nn);
+  int total = 0;
+  for (int k = 0; k < nn; ++k) {
+    int c = static_cast<int>(info.nodes()[k].cpu_ids.size());
+    if (max_workers_per_node > 0 && c > max_workers_per_node) c = max_workers_per_node;
+    per_node[k] = c;
+    total += c;
+  }
+  if (total == 0) { res.status = -err::kNOENT; return res; }
+  res.workers = total;
+  res.used_vnni = (!force_scalar && __builtin_cpu_supports("avx512vnni") && __builtin_cpu_supports("avx512bw")) ? 1 : 0;
+
+  std::vector<int8_t> q_own;
+  std::vector<float> sx_own;
+  int8_t* q = q_out;
+  float* sx = sx_out;
+  if (!q) { q_own.resize(static_cast<size_t>(M) * K); q = q_own.data(); }
+  if (!sx) { sx_own.resize(M); sx = sx_own.data(); }
+  std::vector<uint8_t> qu(static_cast<size_t>(M) * K);
+
+  HeapMoveArray<ThreadPool> pools(nn);
+  for (int k = 0; k < nn; ++k) {
+    const int node = info.nodes()[k].id;
+    auto m = info.get_node_mask<128>(node);
+    pools.emplace(per_node[k], m.ptr(), size_t(128), node, stack_size::DEFAULT);
+    if (!pools[k]) { res.status = -err::kNOMEM; return res; }
+  }
+  auto run = [&](WorkerFn fn, auto& jobs) -> long {
+    int w = 0;
+    long st = 0;
+    for (int k = 0; k < nn; ++k)
+      for (int i = 0; i < per_node[k]; ++i, ++w)
+        if (pools[k].launch(fn, reinterpret_cast<uint64_t>(&jobs[w])) < 0) st = -err::kAGAIN;
+    for (int k = 0; k < nn; ++k) if (pools[k].wait_all(120'000'000'000l) != 0) st = -err::kTIMEDOUT;
+    return st;
+  };
+
+  // phase 1: rows split over the workers
+  std::vector<QuantJob> qjobs(total);
+  for (int w = 0; w < total; ++w)
+    qjobs[w] = QuantJob{x, K, static_cast<int>(static_cast<long>(M) * w / total), static_cast<int>(static_cast<long>(M) * (w + 1) / total), q, qu.data(), sx};
+  long t0 = sys_clock_monotonic_ns();
+  res.status = run(&quant_worker, qjobs);
+  res.quant_ns = sys_clock_monotonic_ns() - t0;
+  if (res.status != 0) return res;
+
+  // phase 2: output channels split over the workers
+  std::vector<GemmJob> gjobs(total);
+  for (int w = 0; w < total; ++w)
+    gjobs[w] = GemmJob{q, qu.data(), sx, wq, sw, y, acc_out, M, K, N, static_cast<int>(static_cast<long>(N) * w / total),
+                       static_cast<int>(static_cast<long>(N) * (w + 1) / total), res.used_vnni};
+  t0 = sys_clock_monotonic_ns();
+  res.status = run(&gemm_worker, gjobs);
+  res.gemm_ns = sys_clock_monotonic_ns() - t0;
+  return res;
+}
+
+}  // namespace hostrt

@@ -1,0 +1,33 @@
+// W8A8 Hadamard linear on the host CPUs, parallelised over the pinned worker pools: the CPU point of the
+// tensor-parallel linear benchmark and a bit-exact cross-check of the GPU kernels' integer arithmetic.
+//
+//   y[m,n] = bf16( (sum_k q[m,k] * wq[n,k])_int32 * sx[m] * sw[n] ),  (q, sx) = quantise(rotate(x[m,:]))
+//
+// rotate = block-128 Sylvester-Hadamard / sqrt(128) (seven butterfly stages, fp32), quantise = per-row symmetric int8
+// (scale = max|.| / 127, 1 for an all-zero row; round to nearest even; clamp to [-127, 127]).  The integer dot products
+// use AVX-512 VNNI (vpdpbusd on activations biased by +128, corrected with 128 * sum_k wq[n,k]) when the CPU has it and
+// plain scalar code otherwise; both give the exact int32 result.  Work is split by output channel over one pinned
+// worker per core of every NUMA node (the pool, arena and topology code of this directory; the reference's pool is
+// threading/linux_threading.mojo:43-158).
+#pragma once
+#include <cstdint>
+
+#include "numa.hpp"
+
+namespace hostrt {
+
+struct W8A8HostResult {
+  long status;          // 0 or -errno
+  long quant_ns;        // rotate + quantise (all rows)
+  long gemm_ns;         // integer GEMM + scale epilogue
+  int workers;
+  int used_vnni;
+};
+
+// x: bf16 bits [M][K] (K % 128 == 0), wq: int8 [N][K], sw: fp32 [N], y: bf16 bits [M][N].
+// q_out (int8 [M][K]), sx_out (fp32 [M]) and acc_out (int32 [M][N]) are optional.
+W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, int K, const int8_t* wq, const float* sw,
+                                int N, uint16_t* y, int max_workers_per_node, int force_scalar, int8_t* q_out,
+                                float* sx_out, int32_t* acc_out);
+
+}  // namespace hostrt

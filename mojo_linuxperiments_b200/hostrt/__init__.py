@@ -72,6 +72,8 @@ def lib() -> ctypes.CDLL:
         "hostrt_fill_reduce": (c_long, [c_void_p, c_ulonglong, c_ulonglong, c_int, POINTER(c_double), POINTER(c_long),
                                         POINTER(c_int), POINTER(c_int)]),
         "hostrt_fill_reduce_serial": (c_double, [c_ulonglong, c_ulonglong]),
+        "hostrt_w8a8_linear": (c_long, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                        c_void_p, c_void_p, c_void_p, POINTER(c_long)]),
         "hostrt_philox_uniform": (c_float, [c_ulonglong, c_ulonglong]),
         "hostrt_philox_block": (None, [c_ulonglong, c_ulonglong, POINTER(c_uint)]),
         "hostrt_scenario_count": (c_int, []), "hostrt_scenario_name": (c_char_p, [c_int]),
@@ -293,6 +295,28 @@ def fill_reduce(info: NumaInfo, n_elems: int = 16 * 1024 * 1024, seed: int = 0, 
     s, ns, w, mis = c_double(), c_long(), c_int(), c_int()
     st = lib().hostrt_fill_reduce(info._h, n_elems, seed, max_workers_per_node, byref(s), byref(ns), byref(w), byref(mis))
     return {"status": st, "sum": s.value, "elapsed_ns": ns.value, "workers": w.value, "misplaced": mis.value}
+
+
+def w8a8_linear(info: NumaInfo, x, wq, sw, max_workers_per_node: int = 0, force_scalar: bool = False):
+    """W8A8 Hadamard linear on the host CPUs over the pinned worker pools (``csrc/hostrt/w8a8_host.cpp``).
+
+    x: torch bf16 [M, K] (CPU), wq: int8 [N, K], sw: fp32 [N].  Returns a dict with ``y`` (bf16 [M, N]), the quantised
+    activations ``q`` / ``sx``, the exact int32 accumulators ``acc`` and timing / dispatch info."""
+    import torch
+    assert x.dtype == torch.bfloat16 and wq.dtype == torch.int8 and sw.dtype == torch.float32
+    assert not x.is_cuda and x.is_contiguous() and wq.is_contiguous() and sw.is_contiguous()
+    M, K = x.shape
+    N = wq.shape[0]
+    y = torch.empty((M, N), dtype=torch.bfloat16)
+    q = torch.empty((M, K), dtype=torch.int8)
+    sx = torch.empty((M,), dtype=torch.float32)
+    acc = torch.empty((M, N), dtype=torch.int32)
+    info5 = (c_long * 5)()
+    st = lib().hostrt_w8a8_linear(info._h, x.data_ptr(), M, K, wq.data_ptr(), sw.data_ptr(), N, y.data_ptr(),
+                                  max_workers_per_node, 1 if force_scalar else 0, q.data_ptr(), sx.data_ptr(),
+                                  acc.data_ptr(), info5)
+    return {"status": st, "y": y, "q": q, "sx": sx, "acc": acc, "quant_ns": info5[0], "gemm_ns": info5[1],
+            "workers": info5[2], "used_vnni": bool(info5[3])}
 
 
 def philox_uniform(i: int, seed: int) -> float:

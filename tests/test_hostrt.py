@@ -269,3 +269,33 @@ def test_selftest_executable_exit_code():
     p = subprocess.run([str(exe)], capture_output=True, text=True, timeout=120)
     assert p.returncode == 0, p.stdout
     assert p.stdout.count("[PASS]") + p.stdout.count("[SKIP]") == 12 and "[FAIL]" not in p.stdout
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 128, 64), (5, 512, 130), (32, 1024, 257), (37, 256, 96)])
+@pytest.mark.parametrize("force_scalar", [False, True])
+def test_w8a8_linear_on_the_worker_pools_matches_the_oracle(M, K, N, force_scalar):
+    """Host W8A8 Hadamard linear (rotate + quantise + int8 GEMM over the pinned pools): the integer accumulators are
+    exact, the quantisation matches the PyTorch reference up to rounding ties, VNNI and scalar paths agree."""
+    import torch
+    from mojo_linuxperiments_b200.oracle import quant as Q
+    g = torch.Generator().manual_seed(M * 1000 + K + N)
+    x = torch.randn((M, K), generator=g)
+    x = torch.where(torch.rand((M, K), generator=g) < 1e-2, x * 50, x).to(torch.bfloat16)
+    if M > 2:
+        x[2].zero_()                                  # an all-zero row quantises with scale 1
+    wq = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8)
+    sw = torch.rand((N,), generator=g) * 9e-3 + 1e-3
+    info = H.NumaInfo()
+    r = H.w8a8_linear(info, x, wq, sw, force_scalar=force_scalar)
+    assert r["status"] == 0 and r["workers"] >= 1
+    q_ref, s_ref = Q.rotate_quantize(x)
+    assert torch.allclose(r["sx"], s_ref, rtol=1e-5, atol=0)
+    d = (r["q"].int() - q_ref.int()).abs()
+    assert d.max().item() <= 1 and (d > 0).float().mean().item() < 5e-3
+    # exact integer product of what the host itself quantised
+    assert torch.equal(r["acc"].double(), Q.int_gemm(r["q"], wq))
+    want = Q.w8a8_linear(r["q"], r["sx"], wq, sw)
+    assert torch.allclose(r["y"].float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()))
+    if not force_scalar:
+        r2 = H.w8a8_linear(info, x, wq, sw, force_scalar=True)
+        assert torch.equal(r["acc"], r2["acc"]) and torch.equal(r["y"], r2["y"]) and torch.equal(r["q"], r2["q"])
