@@ -137,11 +137,8 @@ class Decoder:
             attn = self._attention(l, qkv, positions, kv, mode, cu_seqlens, max_len, seq_ids)
             aq, sa = L.act_quant(attn.view(attn.shape[0], -1))
             delta = self._row_parallel(aq, sa, W["o"])
-            if self.moe is not None:
-                xq, sx, xn = self._norm_quant(h, delta, W["mlp_norm"], want_normed=True)
-            else:
-                (xq, sx), xn = self._norm_quant(h, delta, W["mlp_norm"]), None
-            delta = self._mlp(l, xq, sx, xn)
+            xq, sx = self._norm_quant(h, delta, W["mlp_norm"])      # the router, too, consumes the quantised rows
+            delta = self._mlp(l, xq, sx, None)
         if last_idx is not None:
             h = h.index_select(0, last_idx)
             delta = delta.index_select(0, last_idx)
