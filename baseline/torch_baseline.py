@@ -1,6 +1,9 @@
-"""GPU baseline: the same W8A8 Hadamard decoder written with stock PyTorch ops only - cuBLASLt int8 GEMMs
-(torch._int_mm), a matmul with H128 for the rotation, scaled_dot_product_attention, NCCL all-reduce between ops -
-with the same engine interface as the product so bench.py can time both.  None of this package's kernels run here."""
+"""GPU baseline: the same W8A8 Hadamard decoder (dense and mixture-of-experts) written with stock PyTorch ops only -
+cuBLASLt int8 GEMMs (torch._int_mm), a matmul with H128 for the rotation, scaled_dot_product_attention, NCCL all-reduce
+between ops - with the same engine interface as the product so bench.py can time both.  None of this package's kernels
+run here.  Experts use replicated tokens like the product: prefill gathers each local expert's rows (data-dependent
+shapes, eager only); decode evaluates every local expert on all rows and masks, which is what makes the step
+capturable in a CUDA graph.  The engine also runs on the CPU (eager), which is how the tests check it against the oracle."""
 from __future__ import annotations
 
 import math
@@ -17,14 +20,19 @@ from mojo_linuxperiments_b200.parallel.comm import Comm
 class BaselineEngine:
     def __init__(self, cfg: ModelConfig, rt: RuntimeConfig, weights: dict | None = None, seed: int = 0, comm: Comm | None = None,
                  device=None):
-        assert not cfg.is_moe, "the PyTorch baseline covers the dense model"
         self.cfg, self.rt = cfg, rt
         self.comm = comm or Comm.single()
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.w = weights or Wt.random_shard(cfg, rt.tp, self.comm.rank, self.device, seed)
         for L in self.w["layers"]:
-            for k in ("qkv", "o", "gate_up", "down"):
-                L[k + "_t"] = L[k].qweight.t()          # _int_mm wants [K, N] (column-major view is fine)
+            for k in ("qkv", "o", "gate_up", "down", "router"):
+                if k in L:
+                    L[k + "_t"] = L[k].qweight.t()      # _int_mm wants [K, N] (column-major view is fine)
+            if cfg.is_moe:
+                L["experts_gate_up_t"] = L["experts_gate_up"].qweight.transpose(1, 2)     # [E_local, d, 2F]
+                L["experts_down_t"] = L["experts_down"].qweight.transpose(1, 2)           # [E_local, F, d]
+        self.n_local = cfg.n_experts // max(rt.ep, 1) if cfg.is_moe else 0
+        self.e0 = self.comm.rank * self.n_local if rt.ep > 1 else 0
         self.w["lm_head_t"] = self.w["lm_head"].qweight.t()
         self.H = hadamard_matrix(128, torch.bfloat16, self.device)
         self.hq = cfg.n_heads // rt.tp
@@ -33,7 +41,7 @@ class BaselineEngine:
         ang = torch.arange(rt.max_seq_len, dtype=torch.float64)[:, None] * inv[None, :]
         self.cos, self.sin = ang.cos().float().to(self.device), ang.sin().float().to(self.device)
         self._graphs = {}
-        self._stream = torch.cuda.Stream(device=self.device)
+        self._stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.kernels_per_step = 0
 
     # ---- ops -------------------------------------------------------------------------------------------------
@@ -44,13 +52,50 @@ class BaselineEngine:
         q = torch.clamp(torch.round(xr / s[:, None]), -127, 127).to(torch.int8)
         return q, s
 
-    def _linear(self, x, wt, sw):
-        q, s = self._quant(x)
+    def _int_linear(self, q, s, wt, sw, out_dtype=torch.bfloat16):
         M = q.shape[0]
         if M <= 16:
-            q = F.pad(q, (0, 0, 0, 32 - M))
+            q = F.pad(q, (0, 0, 0, 32 - M))             # cuBLASLt's int8 path wants more than 16 rows
         acc = torch._int_mm(q, wt)[:M]
-        return (acc.float() * s[:, None] * sw[None, :]).to(torch.bfloat16)
+        return (acc.float() * s[:, None] * sw[None, :]).to(out_dtype)
+
+    def _linear(self, x, wt, sw):
+        q, s = self._quant(x)
+        return self._int_linear(q, s, wt, sw)
+
+    def _head_norm(self, x, g):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + self.cfg.eps) * g.float()).to(torch.bfloat16)
+
+    def _moe(self, x, L, decode: bool):
+        """x bf16 [T, d] (normalised) -> this rank's partial MoE output bf16 [T, d] (summed over ranks by the caller)."""
+        cfg = self.cfg
+        q, s = self._quant(x)
+        logits = self._int_linear(q, s, L["router_t"], L["router"].scale, out_dtype=torch.float32)
+        topv, topi = logits.softmax(-1).topk(cfg.top_k, dim=-1)
+        if cfg.norm_topk_prob:
+            topv = topv / topv.sum(-1, keepdim=True)
+        out = torch.zeros((x.shape[0], cfg.d_model), dtype=torch.float32, device=x.device)
+        gu_s, dn_s = L["experts_gate_up"].scale, L["experts_down"].scale
+        for j in range(self.n_local):
+            sel = topi == (self.e0 + j)
+            wgt = (topv * sel).sum(-1, keepdim=True)                  # 0 for rows that did not pick this expert
+            if decode:
+                qe, se, rows = q, s, None                             # all rows, masked by the zero weight
+            else:
+                rows = sel.any(-1).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                qe, se, wgt = q[rows], s[rows], wgt[rows]
+            gu = self._int_linear(qe, se, L["experts_gate_up_t"][j], gu_s[j])
+            f = gu.shape[1] // 2
+            act = (F.silu(gu[:, :f].float()) * gu[:, f:].float()).to(torch.bfloat16)
+            y = self._linear(act, L["experts_down_t"][j], dn_s[j]).float()
+            if rows is None:
+                out += wgt * y
+            else:
+                out.index_add_(0, rows, wgt * y)
+        return out.to(torch.bfloat16)
 
     def _norm(self, x, g):
         xf = x.float()
@@ -71,6 +116,8 @@ class BaselineEngine:
             x = self._norm(h, L["attn_norm"])
             qkv = self._linear(x, L["qkv_t"], L["qkv"].scale).view(-1, self.hq + 2 * self.hkv, hd)
             q, k, v = qkv[:, : self.hq], qkv[:, self.hq: self.hq + self.hkv], qkv[:, self.hq + self.hkv:]
+            if cfg.qk_norm:
+                q, k = self._head_norm(q, L["q_norm"]), self._head_norm(k, L["k_norm"])
             q, k = self._rope(q, pos), self._rope(k, pos)
             if decode:
                 self.k_cache[l].scatter_(2, self.pos_idx[:, None, None, None].expand(B, self.hkv, 1, hd), k.view(B, self.hkv, 1, hd))
@@ -89,10 +136,13 @@ class BaselineEngine:
             o = self._linear(attn, L["o_t"], L["o"].scale)
             h = h + self.comm.all_reduce(o)
             x = self._norm(h, L["mlp_norm"])
-            gu = self._linear(x, L["gate_up_t"], L["gate_up"].scale)
-            f = gu.shape[1] // 2
-            act = (F.silu(gu[:, :f].float()) * gu[:, f:].float()).to(torch.bfloat16)
-            d = self._linear(act, L["down_t"], L["down"].scale)
+            if cfg.is_moe:
+                d = self._moe(x, L, decode)
+            else:
+                gu = self._linear(x, L["gate_up_t"], L["gate_up"].scale)
+                f = gu.shape[1] // 2
+                act = (F.silu(gu[:, :f].float()) * gu[:, f:].float()).to(torch.bfloat16)
+                d = self._linear(act, L["down_t"], L["down"].scale)
             h = h + self.comm.all_reduce(d)
         if not decode:
             h = h.view(B, S, -1)[:, -1]
@@ -137,7 +187,7 @@ class BaselineEngine:
         self.mask.scatter_(3, self.pos_idx[:, None, None, None], True)
 
     def decode_step(self, use_graph: bool = True) -> torch.Tensor:
-        if not use_graph:
+        if not use_graph or self.device.type != "cuda":
             self._decode_body()
             return self.tokens
         g = self._graphs.get(self.batch)
@@ -161,5 +211,15 @@ class BaselineEngine:
         self.tokens.copy_(ids_in, non_blocking=True)
         nxt = self.decode_step()
         ids_out.copy_(nxt, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
         return ids_out
+
+    def generate(self, prompts: torch.Tensor, max_new_tokens: int, use_graph: bool = True) -> torch.Tensor:
+        """Greedy generation. prompts int64 [B, S] -> int64 [B, max_new_tokens] on the host."""
+        B, S = prompts.shape
+        self.start_batch(B, S + max_new_tokens)
+        out = [self.prefill(prompts).cpu()]
+        for _ in range(1, max_new_tokens):
+            out.append(self.decode_step(use_graph).cpu().clone())
+        return torch.stack(out, 1)
