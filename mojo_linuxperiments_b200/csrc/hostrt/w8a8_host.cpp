@@ -83,7 +83,8 @@ struct GemmJob {
   const int8_t* q; const uint8_t* qu; const float* sx;
   const int8_t* wq; const float* sw;
   uint16_t* y; int32_t* acc_out;
-  int M, K, N, n0, n1, vnni;
+  int M, K, N, n0, n1, vnni;     // vnni: 0 scalar, 1 AVX-512 VNNI, 2 AMX int8 tiles
+  const int8_t* q_pack;          // AMX: activations as [M/16 blocks][K/4][16 tokens][4] (zero padded)
 };
 
 inline void finish(const GemmJob& j, int m, int n, int32_t acc) {
@@ -128,9 +129,63 @@ void gemm_vnni(const GemmJob& j) {
   }
 }
 
+// AMX: C[16 channels][16 tokens] += W[16 channels][64 k] . A[16 k-groups][16 tokens x 4 k], signed x signed.  The
+// weights are tile-loaded straight from their row-major layout (row stride K); four token blocks share one weight tile.
+struct alignas(64) TileCfg {
+  uint8_t palette, start_row, reserved[14];
+  uint16_t colsb[16];
+  uint8_t rows[16];
+};
+
+__attribute__((target("amx-tile,amx-int8,avx512f")))
+void gemm_amx(const GemmJob& j) {
+  TileCfg cfg{};
+  cfg.palette = 1;
+  for (int t = 0; t < 6; ++t) { cfg.colsb[t] = 64; cfg.rows[t] = 16; }
+  _tile_loadconfig(&cfg);
+  alignas(64) int32_t cbuf[4][16][16];
+  alignas(64) int8_t wtail[16][64];
+  const int mblocks = (j.M + 15) / 16;
+  const size_t blk_stride = static_cast<size_t>(j.K / 4) * 64;      // bytes of one packed token block
+  for (int n0 = j.n0; n0 < j.n1; n0 += 16) {
+    const int nrows = j.n1 - n0 < 16 ? j.n1 - n0 : 16;
+    for (int mb0 = 0; mb0 < mblocks; mb0 += 4) {
+      const int nmb = mblocks - mb0 < 4 ? mblocks - mb0 : 4;
+      _tile_zero(0); _tile_zero(1); _tile_zero(2); _tile_zero(3);
+      for (int k = 0; k < j.K; k += 64) {
+        if (nrows == 16) {
+          _tile_loadd(4, j.wq + static_cast<size_t>(n0) * j.K + k, j.K);
+        } else {                                                    // last, partial channel block: stage with zero rows
+          for (int r = 0; r < 16; ++r)
+            for (int c = 0; c < 64; ++c) wtail[r][c] = r < nrows ? j.wq[static_cast<size_t>(n0 + r) * j.K + k + c] : 0;
+          _tile_loadd(4, wtail, 64);
+        }
+        const int8_t* a = j.q_pack + static_cast<size_t>(mb0) * blk_stride + static_cast<size_t>(k / 4) * 64;
+        _tile_loadd(5, a, 64); _tile_dpbssd(0, 4, 5);
+        if (nmb > 1) { _tile_loadd(5, a + blk_stride, 64); _tile_dpbssd(1, 4, 5); }
+        if (nmb > 2) { _tile_loadd(5, a + 2 * blk_stride, 64); _tile_dpbssd(2, 4, 5); }
+        if (nmb > 3) { _tile_loadd(5, a + 3 * blk_stride, 64); _tile_dpbssd(3, 4, 5); }
+      }
+      _tile_stored(0, cbuf[0], 64);
+      if (nmb > 1) _tile_stored(1, cbuf[1], 64);
+      if (nmb > 2) _tile_stored(2, cbuf[2], 64);
+      if (nmb > 3) _tile_stored(3, cbuf[3], 64);
+      for (int b = 0; b < nmb; ++b)
+        for (int r = 0; r < nrows; ++r)
+          for (int c = 0; c < 16; ++c) {
+            const int m = (mb0 + b) * 16 + c;
+            if (m < j.M) finish(j, m, n0 + r, cbuf[b][r][c]);
+          }
+    }
+  }
+  _tile_release();
+}
+
 void gemm_worker(uint64_t a0, uint64_t, uint64_t, uint64_t, uint64_t, uint64_t) {
   const GemmJob& j = *reinterpret_cast<GemmJob*>(a0);
-  if (j.vnni && (j.K % 64) == 0) gemm_vnni(j); else gemm_scalar(j);
+  if (j.vnni == 2 && (j.K % 64) == 0) gemm_amx(j);
+  else if (j.vnni == 1 && (j.K % 64) == 0) gemm_vnni(j);
+  else gemm_scalar(j);
 }
 
 }  // namespace
@@ -152,7 +207,13 @@ W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, 
   }
   if (total == 0) { res.status = -err::kNOENT; return res; }
   res.workers = total;
-  res.used_vnni = (!force_scalar && __builtin_cpu_supports("avx512vnni") && __builtin_cpu_supports("avx512bw")) ? 1 : 0;
+  // force_scalar: 0 best available, 1 scalar, 2 at most AVX-512 VNNI
+  res.used_vnni = (force_scalar != 1 && __builtin_cpu_supports("avx512vnni") && __builtin_cpu_supports("avx512bw")) ? 1 : 0;
+  if (res.used_vnni && force_scalar == 0 && __builtin_cpu_supports("amx-int8") && __builtin_cpu_supports("amx-tile")) {
+    // the tile registers are an opt-in extended state: ask the kernel once for the whole process (ARCH_REQ_XCOMP_PERM,
+    // feature 18 = XTILEDATA); without the permission the first tile instruction would fault
+    if (raw_syscall(158 /* arch_prctl */, 0x1023, 18) == 0) res.used_vnni = 2;
+  }
 
   std::vector<int8_t> q_own;
   std::vector<float> sx_own;
@@ -188,11 +249,21 @@ W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, 
   res.quant_ns = sys_clock_monotonic_ns() - t0;
   if (res.status != 0) return res;
 
+  // AMX wants the activations in groups of four k per token: [token block of 16][k / 4][token][4]
+  std::vector<int8_t> q_pack;
+  if (res.used_vnni == 2) {
+    const int mblocks = (M + 15) / 16;
+    q_pack.assign(static_cast<size_t>(mblocks) * (K / 4) * 64 + 64, 0);
+    for (int m = 0; m < M; ++m)
+      for (int k = 0; k < K; ++k)
+        q_pack[(static_cast<size_t>(m / 16) * (K / 4) + k / 4) * 64 + (m % 16) * 4 + (k % 4)] = q[static_cast<size_t>(m) * K + k];
+  }
+
   // phase 2: output channels split over the workers
   std::vector<GemmJob> gjobs(total);
   for (int w = 0; w < total; ++w)
     gjobs[w] = GemmJob{q, qu.data(), sx, wq, sw, y, acc_out, M, K, N, static_cast<int>(static_cast<long>(N) * w / total),
-                       static_cast<int>(static_cast<long>(N) * (w + 1) / total), res.used_vnni};
+                       static_cast<int>(static_cast<long>(N) * (w + 1) / total), res.used_vnni, q_pack.data()};
   t0 = sys_clock_monotonic_ns();
   res.status = run(&gemm_worker, gjobs);
   res.gemm_ns = sys_clock_monotonic_ns() - t0;

@@ -5,8 +5,9 @@
 //
 // rotate = block-128 Sylvester-Hadamard / sqrt(128) (seven butterfly stages, fp32), quantise = per-row symmetric int8
 // (scale = max|.| / 127, 1 for an all-zero row; round to nearest even; clamp to [-127, 127]).  The integer dot products
-// use AVX-512 VNNI (vpdpbusd on activations biased by +128, corrected with 128 * sum_k wq[n,k]) when the CPU has it and
-// plain scalar code otherwise; both give the exact int32 result.  Work is split by output channel over one pinned
+// use AMX int8 tiles (tdpbssd, weights tile-loaded from their row-major layout) when the CPU and the kernel grant them,
+// else AVX-512 VNNI (vpdpbusd on activations biased by +128, corrected with 128 * sum_k wq[n,k]), else plain scalar
+// code; all three give the exact int32 result.  Work is split by output channel over one pinned
 // worker per core of every NUMA node (the pool, arena and topology code of this directory; the reference's pool is
 // threading/linux_threading.mojo:43-158).
 #pragma once
@@ -21,7 +22,7 @@ struct W8A8HostResult {
   long quant_ns;        // rotate + quantise (all rows)
   long gemm_ns;         // integer GEMM + scale epilogue
   int workers;
-  int used_vnni;
+  int used_vnni;        // 0 scalar, 1 AVX-512 VNNI, 2 AMX int8
 };
 
 // x: bf16 bits [M][K] (K % 128 == 0), wq: int8 [N][K], sw: fp32 [N], y: bf16 bits [M][N].

@@ -297,11 +297,12 @@ def fill_reduce(info: NumaInfo, n_elems: int = 16 * 1024 * 1024, seed: int = 0, 
     return {"status": st, "sum": s.value, "elapsed_ns": ns.value, "workers": w.value, "misplaced": mis.value}
 
 
-def w8a8_linear(info: NumaInfo, x, wq, sw, max_workers_per_node: int = 0, force_scalar: bool = False):
+def w8a8_linear(info: NumaInfo, x, wq, sw, max_workers_per_node: int = 0, force_scalar: bool = False, isa: str = "best"):
     """W8A8 Hadamard linear on the host CPUs over the pinned worker pools (``csrc/hostrt/w8a8_host.cpp``).
 
     x: torch bf16 [M, K] (CPU), wq: int8 [N, K], sw: fp32 [N].  Returns a dict with ``y`` (bf16 [M, N]), the quantised
-    activations ``q`` / ``sx``, the exact int32 accumulators ``acc`` and timing / dispatch info."""
+    activations ``q`` / ``sx``, the exact int32 accumulators ``acc`` and timing / dispatch info.  ``isa``: "best"
+    (AMX int8, else AVX-512 VNNI, else scalar), "vnni" (no AMX), "scalar"."""
     import torch
     assert x.dtype == torch.bfloat16 and wq.dtype == torch.int8 and sw.dtype == torch.float32
     assert not x.is_cuda and x.is_contiguous() and wq.is_contiguous() and sw.is_contiguous()
@@ -313,10 +314,10 @@ def w8a8_linear(info: NumaInfo, x, wq, sw, max_workers_per_node: int = 0, force_
     acc = torch.empty((M, N), dtype=torch.int32)
     info5 = (c_long * 5)()
     st = lib().hostrt_w8a8_linear(info._h, x.data_ptr(), M, K, wq.data_ptr(), sw.data_ptr(), N, y.data_ptr(),
-                                  max_workers_per_node, 1 if force_scalar else 0, q.data_ptr(), sx.data_ptr(),
-                                  acc.data_ptr(), info5)
+                                  max_workers_per_node, 1 if (force_scalar or isa == "scalar") else (2 if isa == "vnni" else 0),
+                                  q.data_ptr(), sx.data_ptr(), acc.data_ptr(), info5)
     return {"status": st, "y": y, "q": q, "sx": sx, "acc": acc, "quant_ns": info5[0], "gemm_ns": info5[1],
-            "workers": info5[2], "used_vnni": bool(info5[3])}
+            "workers": info5[2], "used_vnni": bool(info5[3]), "isa": ("scalar", "avx512-vnni", "amx-int8")[info5[3]]}
 
 
 def philox_uniform(i: int, seed: int) -> float:

@@ -297,5 +297,6 @@ def test_w8a8_linear_on_the_worker_pools_matches_the_oracle(M, K, N, force_scala
     want = Q.w8a8_linear(r["q"], r["sx"], wq, sw)
     assert torch.allclose(r["y"].float(), want, rtol=1e-2, atol=1e-2 * float(want.abs().max()))
     if not force_scalar:
-        r2 = H.w8a8_linear(info, x, wq, sw, force_scalar=True)
-        assert torch.equal(r["acc"], r2["acc"]) and torch.equal(r["y"], r2["y"]) and torch.equal(r["q"], r2["q"])
+        for isa in ("scalar", "vnni"):            # every instruction-set path gives the same bits
+            r2 = H.w8a8_linear(info, x, wq, sw, isa=isa)
+            assert torch.equal(r["acc"], r2["acc"]) and torch.equal(r["y"], r2["y"]) and torch.equal(r["q"], r2["q"]), (r["isa"], r2["isa"])
