@@ -300,3 +300,33 @@ def test_w8a8_linear_on_the_worker_pools_matches_the_oracle(M, K, N, force_scala
         for isa in ("scalar", "vnni"):            # every instruction-set path gives the same bits
             r2 = H.w8a8_linear(info, x, wq, sw, isa=isa)
             assert torch.equal(r["acc"], r2["acc"]) and torch.equal(r["y"], r2["y"]) and torch.equal(r["q"], r2["q"]), (r["isa"], r2["isa"])
+
+
+@pytest.mark.parametrize("kind", ["dense", "moe"])
+def test_host_decoder_on_the_worker_pools_follows_the_oracle(kind):
+    """A whole miniature decoder with every linear on the pinned pools (prefill + cached decode) against the oracle's
+    re-computation: token for token unless the oracle's own top-2 margin is within rounding noise."""
+    import torch
+    from mojo_linuxperiments_b200.hostrt.host_model import HostDecoder
+    from mojo_linuxperiments_b200.models import config as C
+    from mojo_linuxperiments_b200.models import weights as Wt
+    from mojo_linuxperiments_b200.oracle import model as OM
+    if kind == "moe":
+        cfg = C.tiny_moe(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, n_experts=8, top_k=2, moe_ffn=128, vocab=512)
+    else:
+        cfg = C.tiny_dense(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, ffn=512, vocab=512)
+    ck = Wt.quantize_master(Wt.init_master(cfg, 0))
+    dec = HostDecoder(cfg, ck)
+    prompt = torch.randint(0, cfg.vocab, (11,), generator=torch.Generator().manual_seed(7))
+    NEW = 5
+    toks, _ = dec.generate(prompt, NEW)
+    ref, logs = OM.greedy_generate(cfg, ck, prompt, NEW)
+    agree = 0
+    for t in range(NEW):
+        if toks[t] == ref[t]:
+            agree += 1
+            continue
+        top2 = logs[t].topk(2).values
+        assert (top2[0] - top2[1]).item() < 0.05 * logs[t].abs().max().item(), f"step {t} diverged with a clear margin"
+        break
+    assert agree >= NEW // 2 and dec.linear_ns > 0
