@@ -172,6 +172,11 @@ long hostrt_butterfly_allreduce(void* numa, int world, long long* out, long time
 long hostrt_fabric_allreduce(void* numa, int world, const double* in, double* out, int rounds, long timeout_ns, int drop_rank) {
   return fabric_allreduce(*static_cast<NumaInfo*>(numa), world, in, out, rounds, timeout_ns, drop_rank);
 }
+long hostrt_fabric_token_exchange(void* numa, int world, int rows_per_rank, int blocks, int iters, long timeout_ns,
+                                  unsigned skew_seed, int mode, int fault, int* mismatches) {
+  return fabric_token_exchange(*static_cast<NumaInfo*>(numa), world, rows_per_rank, blocks, iters, timeout_ns, skew_seed, mode, fault,
+                               mismatches);
+}
 long hostrt_fill_reduce(void* numa, unsigned long long n, unsigned long long seed, int max_workers_per_node, double* sum,
                         long* elapsed_ns, int* workers, int* misplaced) {
   const FillReduceResult r = fill_reduce(*static_cast<NumaInfo*>(numa), n, seed, max_workers_per_node);

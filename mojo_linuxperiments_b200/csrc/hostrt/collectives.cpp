@@ -98,6 +98,101 @@ void fabric_worker(uint64_t rank, uint64_t shared_p, uint64_t, uint64_t, uint64_
   sh->out[r] = acc;
 }
 
+// ---- token-sharded exchange protocol (threads as ranks) -------------------------------------------------
+// The CPU statement of the protocol the GPU kernels of csrc/kernels/tp_link.cuh use: per-rank "heaps" with two
+// gather buffers and two receive areas selected by the parity of a per-rank epoch, per-(source, block) epoch flags,
+// per-consumer "done" words that gate the reuse of a gather buffer two calls later, and arrival counters that the
+// owner resets.  Ranks are skewed against each other on purpose; any hole in the protocol shows up as a payload that
+// does not match its closed-form expectation.
+struct ExchangeShared {
+  int world, rows, blocks, iters;
+  int mode;                            // 1 all-gather only, 2 reduce-scatter only, 3 both in turn
+  int fault;                           // deliberate holes: 1 skip the wait for the done acknowledgements, 2 one buffer instead of two
+  long timeout_ns;
+  uint32_t skew_seed;
+  uint64_t* gather;                    // [world heaps][2][world * rows] rows as one 64-bit word each
+  uint64_t* recv;                      // [world heaps][2][world sources][rows]
+  std::atomic<uint32_t>* flags;        // [world heaps][world sources][blocks]
+  std::atomic<uint32_t>* done;         // [world heaps][world consumers]
+  std::atomic<uint32_t>* ctr;          // [world heaps][2]
+  std::atomic<int> errors;
+  std::atomic<int> timeouts;
+};
+
+inline uint64_t exch_row_value(int src, int row, uint32_t epoch) { return (static_cast<uint64_t>(epoch) << 32) | (static_cast<uint64_t>(src) << 20) | row; }
+inline uint64_t exch_part_value(int src, int owner, int row, uint32_t epoch) { return static_cast<uint64_t>(epoch) * 1000003ull + src * 7919ull + owner * 104729ull + row; }
+
+void exchange_worker(uint64_t rank, uint64_t shared_p, uint64_t, uint64_t, uint64_t, uint64_t) {
+  auto* sh = reinterpret_cast<ExchangeShared*>(shared_p);
+  const int r = static_cast<int>(rank), w = sh->world, R = sh->rows, B = sh->blocks;
+  const size_t M = static_cast<size_t>(w) * R;
+  uint32_t rng = sh->skew_seed * 2654435761u + r * 40503u + 1u;
+  auto skew = [&]() {                                  // a pseudo-random pause of up to ~20 us
+    rng = rng * 1664525u + 1013904223u;
+    const long until = sys_clock_monotonic_ns() + static_cast<long>((rng >> 8) % 20000u);
+    while (sys_clock_monotonic_ns() < until) asm volatile("pause");
+  };
+  auto wait_ge = [&](std::atomic<uint32_t>& word, uint32_t target) -> bool {
+    const long deadline = sys_clock_monotonic_ns() + sh->timeout_ns;
+    while (!b200::epoch_reached(word.load(std::memory_order_acquire), target)) {
+      if (sys_clock_monotonic_ns() > deadline) { sh->timeouts.fetch_add(1); return false; }
+      asm volatile("pause");
+    }
+    return true;
+  };
+  auto gather_of = [&](int heap, int par) { return sh->gather + (static_cast<size_t>(heap) * 2 + par) * M; };
+  auto recv_of = [&](int heap, int par, int src) { return sh->recv + ((static_cast<size_t>(heap) * 2 + par) * w + src) * R; };
+  for (int it = 0; it < sh->iters; ++it) {
+    const uint32_t e = static_cast<uint32_t>(it + 1);
+    const int par = (sh->fault & 2) ? 0 : static_cast<int>(e & 1u);
+    skew();
+    if (sh->mode & 1) {
+    // ---- all-gather: wait for the acknowledgements of the call before last, push my rows block by block ----
+    if (!(sh->fault & 1))
+      for (int p = 0; p < w; ++p) if (!wait_ge(sh->done[static_cast<size_t>(r) * w + p], e - 2u)) return;
+    for (int blk = 0; blk < B; ++blk) {
+      const int r0 = blk * (R / B), r1 = blk + 1 == B ? R : (blk + 1) * (R / B);
+      for (int s = 0; s < w; ++s) {
+        const int dst = b200::staggered_peer(r, s, w);
+        uint64_t* g = gather_of(dst, par);
+        for (int row = r0; row < r1; ++row) g[static_cast<size_t>(r) * R + row] = exch_row_value(r, row, e);
+      }
+      for (int dst = 0; dst < w; ++dst) sh->flags[(static_cast<size_t>(dst) * w + r) * B + blk].store(e, std::memory_order_release);
+      if (blk & 1) skew();
+    }
+    if (r == 0 && sh->fault) { skew(); skew(); skew(); skew(); skew(); }   // a slow consumer makes a hole visible
+    // ---- consume: every source, every block, starting with my own rows ----
+    for (int s = 0; s < w; ++s) {
+      const int src = b200::staggered_peer(r, s, w);
+      for (int blk = 0; blk < B; ++blk) {
+        if (!wait_ge(sh->flags[(static_cast<size_t>(r) * w + src) * B + blk], e)) return;
+        const int r0 = blk * (R / B), r1 = blk + 1 == B ? R : (blk + 1) * (R / B);
+        const uint64_t* g = gather_of(r, par);
+        for (int row = r0; row < r1; ++row)
+          if (g[static_cast<size_t>(src) * R + row] != exch_row_value(src, row, e)) sh->errors.fetch_add(1);
+      }
+    }
+    for (int p = 0; p < w; ++p) sh->done[static_cast<size_t>(p) * w + r].store(e, std::memory_order_release);
+    }
+    skew();
+    if (!(sh->mode & 2)) continue;
+    // ---- reduce-scatter: my partial of every owner's rows into its receive area, own rows last ----
+    for (int s = 1; s <= w; ++s) {
+      const int owner = b200::staggered_peer(r, s, w);
+      uint64_t* dst = recv_of(owner, par, r);
+      for (int row = 0; row < R; ++row) dst[row] = exch_part_value(r, owner, row, e);
+      sh->ctr[static_cast<size_t>(owner) * 2 + par].fetch_add(static_cast<uint32_t>(R), std::memory_order_release);
+    }
+    if (!wait_ge(sh->ctr[static_cast<size_t>(r) * 2 + par], static_cast<uint32_t>(w) * R)) return;
+    for (int row = 0; row < R; ++row) {
+      uint64_t got = 0, want = 0;
+      for (int src = 0; src < w; ++src) { got += recv_of(r, par, src)[row]; want += exch_part_value(src, r, row, e); }
+      if (got != want) sh->errors.fetch_add(1);
+    }
+    sh->ctr[static_cast<size_t>(r) * 2 + par].store(0, std::memory_order_release);     // the owner resets its own counter
+  }
+}
+
 // ---- fill + reduce ---------------------------------------------------------------------------------
 struct FillJob {
   float* buf;
@@ -198,6 +293,35 @@ long fabric_allreduce(const NumaInfo& info, int world, const double* in, double*
   long st = 0;
   for (int r = 0; r < world; ++r) if (pools[r].wait_all(timeout_ns * 4 + 1'000'000'000l) != 0) st = -err::kTIMEDOUT;
   if (st == 0 && sh.errors.load() != 0) st = -err::kTIMEDOUT;
+  return st;
+}
+
+long fabric_token_exchange(const NumaInfo& info, int world, int rows_per_rank, int blocks, int iters, long timeout_ns,
+                           uint32_t skew_seed, int mode, int fault, int* mismatches) {
+  if (world < 1 || rows_per_rank < 1 || blocks < 1 || blocks > rows_per_rank || iters < 1 || mode < 1 || mode > 3) return -err::kINVAL;
+  const size_t M = static_cast<size_t>(world) * rows_per_rank;
+  const size_t words = static_cast<size_t>(world) * 2 * M * 2;
+  const size_t bytes = words * 8 + static_cast<size_t>(world) * world * (blocks + 1) * 4 + static_cast<size_t>(world) * 8 + 65536;
+  NumaArena arena(node_for_rank(info, 0), bytes, 64, page_size::STANDARD);
+  if (!arena) return -err::kNOMEM;
+  ExchangeShared sh{};
+  sh.world = world; sh.rows = rows_per_rank; sh.blocks = blocks; sh.iters = iters; sh.timeout_ns = timeout_ns; sh.skew_seed = skew_seed;
+  sh.mode = mode; sh.fault = fault;
+  sh.gather = arena.alloc<uint64_t>(static_cast<size_t>(world) * 2 * M);
+  sh.recv = arena.alloc<uint64_t>(static_cast<size_t>(world) * 2 * M);
+  sh.flags = arena.alloc<std::atomic<uint32_t>>(static_cast<size_t>(world) * world * blocks);
+  sh.done = arena.alloc<std::atomic<uint32_t>>(static_cast<size_t>(world) * world);
+  sh.ctr = arena.alloc<std::atomic<uint32_t>>(static_cast<size_t>(world) * 2);
+  sh.errors.store(0); sh.timeouts.store(0);
+  if (!sh.gather || !sh.recv || !sh.flags || !sh.done || !sh.ctr) return -err::kNOMEM;
+  HeapMoveArray<ThreadPool> pools(world);
+  if (!make_rank_pools(info, world, pools)) return -err::kNOMEM;
+  for (int r = 0; r < world; ++r)
+    if (pools[r].launch(&exchange_worker, r, reinterpret_cast<uint64_t>(&sh)) < 0) return -err::kAGAIN;
+  long st = 0;
+  for (int r = 0; r < world; ++r) if (pools[r].wait_all(timeout_ns * 4 + 10'000'000'000l) != 0) st = -err::kTIMEDOUT;
+  if (mismatches) *mismatches = sh.errors.load();
+  if (st == 0 && sh.timeouts.load() != 0) st = -err::kTIMEDOUT;
   return st;
 }
 

@@ -37,6 +37,15 @@ struct FillReduceResult {
   int misplaced;          // workers that observed themselves or their buffer on the wrong node
 };
 // n_elems floats of uniform[-1,1) (Philox, keyed by global index) spread over all CPUs of all nodes
+// The token-sharded all-gather / reduce-scatter protocol of the GPU kernels (epoch parity, per-block flags, done
+// acknowledgements, owner-reset arrival counters) with threads as ranks and deliberate skew; *mismatches counts payload
+// words that differ from their closed-form expectation.  0, or -ETIMEDOUT when a wait ran out.  mode: 1 all-gather only,
+// 2 reduce-scatter only, 3 both in turn.  fault: 1 removes the wait for the done acknowledgements (harmless while every
+// rank consumes every source each call, which is itself a barrier: the acknowledgements protect consumers that do not),
+// 2 uses one buffer instead of two, which the harness must catch as mismatches.
+long fabric_token_exchange(const NumaInfo& info, int world, int rows_per_rank, int blocks, int iters, long timeout_ns,
+                           uint32_t skew_seed, int mode, int fault, int* mismatches);
+
 FillReduceResult fill_reduce(const NumaInfo& info, uint64_t n_elems, uint64_t seed, int max_workers_per_node);
 // single-threaded reference of the same sum (Kahan-free double accumulation in index order per chunk)
 double fill_reduce_serial(uint64_t n_elems, uint64_t seed);

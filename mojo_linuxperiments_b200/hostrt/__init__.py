@@ -69,6 +69,7 @@ def lib() -> ctypes.CDLL:
         "hostrt_chain_reduce": (c_long, [c_void_p, c_int, c_long, POINTER(c_longlong)]),
         "hostrt_butterfly_allreduce": (c_long, [c_void_p, c_int, POINTER(c_longlong), c_long]),
         "hostrt_fabric_allreduce": (c_long, [c_void_p, c_int, POINTER(c_double), POINTER(c_double), c_int, c_long, c_int]),
+        "hostrt_fabric_token_exchange": (c_long, [c_void_p, c_int, c_int, c_int, c_int, c_long, c_uint, c_int, c_int, POINTER(c_int)]),
         "hostrt_fill_reduce": (c_long, [c_void_p, c_ulonglong, c_ulonglong, c_int, POINTER(c_double), POINTER(c_long),
                                         POINTER(c_int), POINTER(c_int)]),
         "hostrt_fill_reduce_serial": (c_double, [c_ulonglong, c_ulonglong]),
@@ -289,6 +290,17 @@ def fabric_allreduce(info: NumaInfo, values, rounds: int = 1, timeout_ns: int = 
     out = (c_double * w)()
     st = lib().hostrt_fabric_allreduce(info._h, w, inp, out, rounds, timeout_ns, drop_rank)
     return st, list(out)
+
+
+def fabric_token_exchange(info: NumaInfo, world: int, rows_per_rank: int = 64, blocks: int = 4, iters: int = 50,
+                          timeout_ns: int = 2_000_000_000, skew_seed: int = 1, mode: int = 3, fault: int = 0):
+    """Threads-as-ranks run of the token-sharded all-gather / reduce-scatter protocol; returns (status, mismatches).
+    mode 1 all-gather only, 2 reduce-scatter only, 3 both; fault 1 drops the wait for the done acknowledgements, fault 2
+    uses a single buffer instead of two (a hole the run must report as mismatches)."""
+    mis = c_int()
+    st = lib().hostrt_fabric_token_exchange(info._h, world, rows_per_rank, blocks, iters, timeout_ns, skew_seed, mode, fault,
+                                            byref(mis))
+    return st, mis.value
 
 
 def fill_reduce(info: NumaInfo, n_elems: int = 16 * 1024 * 1024, seed: int = 0, max_workers_per_node: int = 0):

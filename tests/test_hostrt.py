@@ -330,3 +330,19 @@ def test_host_decoder_on_the_worker_pools_follows_the_oracle(kind):
         assert (top2[0] - top2[1]).item() < 0.05 * logs[t].abs().max().item(), f"step {t} diverged with a clear margin"
         break
     assert agree >= NEW // 2 and dec.linear_ns > 0
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+def test_token_exchange_protocol_on_the_thread_fabric(world):
+    """The all-gather / reduce-scatter protocol of the GPU kernels (epoch parity, per-block flags, done acknowledgements,
+    owner-reset arrival counters) run by skewed threads-as-ranks: no payload word may ever differ from its expectation,
+    and the harness must notice when one of the two buffers is taken away."""
+    info = H.NumaInfo()
+    for mode in (1, 2, 3):
+        st, mis = H.fabric_token_exchange(info, world, rows_per_rank=48, blocks=3, iters=200, skew_seed=world + mode, mode=mode)
+        assert (st, mis) == (0, 0), (mode, st, mis)
+    st, mis = H.fabric_token_exchange(info, world, iters=200, mode=1, fault=1)      # acknowledgements are belt and braces here
+    assert (st, mis) == (0, 0)
+    if world > 1:
+        st, mis = H.fabric_token_exchange(info, world, iters=300, mode=1, fault=2)  # single buffer: must be caught
+        assert st == 0 and mis > 0
