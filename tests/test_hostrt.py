@@ -89,6 +89,21 @@ def test_numa_info_on_fixture_trees(tmp_path):
     assert "node 1" in info.debug_string()
 
 
+def test_numa_info_eight_nodes_many_cpus(tmp_path):
+    """An 8-socket tree with 256 CPUs: wide masks, symmetric distances, per-node memory."""
+    nodes = {}
+    for n in range(8):
+        dist = [10 if m == n else (21 if m // 4 == n // 4 else 32) for m in range(8)]
+        nodes[n] = (f"{32 * n}-{32 * n + 31}", dist, 1000 * (n + 1), 100 * (n + 1))
+    info = H.NumaInfo(_fake_sysfs(tmp_path, nodes))
+    assert info.ok and info.num_nodes == 8 and info.node_ids == list(range(8))
+    assert info.total_cpus() == 256 and info.cpus_per_node() == 32
+    assert info.get_node_cpus(7) == list(range(224, 256)) and info.get_node_mask(7).cpus() == list(range(224, 256))
+    assert info.distance(0, 3) == 21 and info.distance(0, 4) == 32 and info.distance(5, 5) == 10
+    assert [info.mem_total_kb(n) for n in range(8)] == [1000 * (n + 1) for n in range(8)]
+    assert info.mem_free_kb(7) == 800
+
+
 def test_numa_info_sparse_ids_and_missing_tree(tmp_path):
     (tmp_path / "a").mkdir()
     sparse = _fake_sysfs(tmp_path / "a", {0: ("0-1", [10, 40], 10, 5), 2: ("8-9,12", [40, 10], 20, 6)})
