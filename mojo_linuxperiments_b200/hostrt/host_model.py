@@ -6,8 +6,6 @@ oracle and as the CPU point of the decode benchmark.  The reference itself has n
 (test_linux_threading.mojo only exercises pools, arenas and two reductions)."""
 from __future__ import annotations
 
-import math
-
 import torch
 
 from . import NumaInfo, w8a8_linear
@@ -103,15 +101,13 @@ class HostDecoder:
 
     def _attend(self, q, k_all, v_all):
         """q [T, hq, D] (the last T positions), k_all / v_all [S, hkv, D] -> [T, hq, D] fp32, causal."""
-        T, hq, d = q.shape
-        S, hkv = k_all.shape[0], k_all.shape[1]
-        g = hq // hkv
-        kf = k_all.float().repeat_interleave(g, dim=1)
-        vf = v_all.float().repeat_interleave(g, dim=1)
-        s = torch.einsum("thd,shd->hts", q.float(), kf) / math.sqrt(d)
+        T, S = q.shape[0], k_all.shape[0]
         qpos = torch.arange(S - T, S)[:, None]
-        s = s.masked_fill(torch.arange(S)[None, :] > qpos, float("-inf"))
-        return torch.einsum("hts,shd->thd", s.softmax(-1), vf)
+        mask = torch.arange(S)[None, :] <= qpos                       # [T, S]: key s visible to query t
+        out = torch.nn.functional.scaled_dot_product_attention(
+            q.float().transpose(0, 1)[None], k_all.float().transpose(0, 1)[None], v_all.float().transpose(0, 1)[None],
+            attn_mask=mask, enable_gqa=True)
+        return out[0].transpose(0, 1)
 
     def generate(self, prompt: torch.Tensor, n_new: int):
         """Greedy tokens after ``prompt`` (int64 [S]); returns (tokens, per-step logits)."""
