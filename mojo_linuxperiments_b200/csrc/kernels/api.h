@@ -87,6 +87,13 @@ int b200_attn_prefill(const void* q, long long ld_q, const void* k, long long ld
                       void* out, const int* cu_seqlens, int B, int total_tokens, int max_len, int hq, int hkv,
                       float scale, int* status, cudaStream_t stream);
 
+// Split-KV form of b200_attn_prefill: every `chunk` KV tiles (of 128 tokens) of a query tile are one CTA; partial rows go
+// through `scratch` (b200_attn_prefill_split_scratch_floats floats) and a merge kernel.  Opt-in, not yet run on hardware.
+size_t b200_attn_prefill_split_scratch_floats(int B, int hq, int max_len, int chunk);
+int b200_attn_prefill_split(const void* q, long long ld_q, const void* k, long long ld_k, const void* v, long long ld_v,
+                            void* out, const int* cu_seqlens, int B, int total_tokens, int max_len, int hq, int hkv,
+                            float scale, int chunk, float* scratch, int* status, cudaStream_t stream);
+
 // ---- config-1 workload: counter-RNG fill + sum ------------------------------------------------------------
 int b200_fill_uniform_reduce(float* out, unsigned long long begin, unsigned long long end, unsigned long long seed,
                              double* partials, int max_ctas, unsigned* counter, double* result, cudaStream_t stream);

@@ -1,0 +1,351 @@
+// Causal prefill attention with the KV range of a query tile split over several CTAs (see attn_prefill.cu for the
+// tile pipeline; this file repeats it with a [j_lo, j_lo + n_tiles) KV range per CTA).
+//
+// Why: the un-split kernel runs one CTA per (query tile, head, sequence), and the CTA of the last query tile walks
+// every KV tile alone.  With few heads per GPU (tensor parallel 8: four) and one sequence that is 32 CTAs whose longest
+// takes eight tiles: 66 us per layer for 6 us of tensor work.  Here a query tile's KV tiles are cut into chunks of
+// `chunk` tiles, each chunk is a CTA, chunks of one tile row write unnormalised partial rows (o, max, sum) and a small
+// merge kernel combines them; query tiles that fit one chunk write their result directly.
+// Opt-in (B200RT_PREFILL_SPLIT=chunk): it has not been measured yet.
+#include "ptx.cuh"
+#include "api.h"
+#include "launch.cuh"
+#include <cuda.h>
+
+namespace b200 {
+
+constexpr int AP_THREADS = 192;
+constexpr int AP_BM = 128, AP_BN = 128, AP_D = 128;
+constexpr int AP_CHUNK_BYTES = 128 * 128;            // 128 rows x 64 bf16
+constexpr int AP_TILE_BYTES = 2 * AP_CHUNK_BYTES;    // 128 x 128 bf16
+
+struct PrefillSplitParams {
+  const int* cu_seqlens;      // [B+1]
+  __nv_bfloat16* out;         // [tokens][hq][128]
+  float* part_o;              // [B][hq][n_q][max_chunks][128 rows][128] unnormalised partial outputs
+  float* part_ml;             // [B][hq][n_q][max_chunks][128 rows][2]  running max (log2 units) and sum
+  int hq, hkv;
+  int n_q, chunk, max_chunks;
+  float scale_log2;
+  int* status;
+  unsigned long long limit_ns;
+};
+
+int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows, uint64_t pitch_bytes);
+
+__global__ void __launch_bounds__(AP_THREADS, 1)
+attn_prefill_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, const PrefillSplitParams p) {
+  pdl_launch_dependents();   // the next kernel may start its prologue now
+  pdl_wait();                // everything before this kernel in the stream has completed
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // [Q 32K][K0 32K][K1 32K][V0 32K][V1 32K][P 32K][barriers]
+  const uint32_t sQ = smem_u32(smem);
+  const uint32_t sK = sQ + AP_TILE_BYTES;
+  const uint32_t sV = sK + 2 * AP_TILE_BYTES;
+  const uint32_t sP = sV + 2 * AP_TILE_BYTES;
+  uint8_t* pP = smem + 5 * AP_TILE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * AP_TILE_BYTES);
+  const uint32_t bar0 = smem_u32(bars);
+  enum { B_QFULL = 0, B_KFULL = 1, B_VFULL = 3, B_KEMPTY = 5, B_VEMPTY = 7, B_SFULL = 9, B_PFULL = 11, B_OFULL = 12, B_COUNT = 14 };
+  auto bar = [&](int i) { return bar0 + 8u * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // blockIdx.x enumerates (query tile, chunk of KV tiles), late (heavy) query tiles first
+  int qt = p.n_q - 1, rem = static_cast<int>(blockIdx.x);
+  while (qt > 0 && rem >= (qt + p.chunk) / p.chunk) { rem -= (qt + p.chunk) / p.chunk; --qt; }
+  const int chunk_idx = rem;
+  const int head = blockIdx.y, b = blockIdx.z;
+  const int seq0 = p.cu_seqlens[b];
+  const int len = p.cu_seqlens[b + 1] - seq0;
+  const int q0 = qt * AP_BM;
+  if (q0 >= len) return;                            // uniform across the CTA, before any barrier / TMEM use
+  const int nchunks = (qt + p.chunk) / p.chunk;     // causal: kv tiles 0..qt in chunks of p.chunk
+  const int j_lo = chunk_idx * p.chunk;
+  const int n_tiles = min(qt + 1, j_lo + p.chunk) - j_lo;      // tiles of this CTA: j_lo .. j_lo + n_tiles - 1
+  const int kvh = head / (p.hq / p.hkv);
+  const uint64_t limit = p.limit_ns;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i == B_PFULL) ? 128 : 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), 512); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tmap(&tmap_q); prefetch_tmap(&tmap_k); prefetch_tmap(&tmap_v);
+      mbar_expect_tx(bar(B_QFULL), AP_TILE_BYTES);
+      tma_load_2d(sQ, &tmap_q, bar(B_QFULL), head * AP_D, seq0 + q0);
+      tma_load_2d(sQ + AP_CHUNK_BYTES, &tmap_q, bar(B_QFULL), head * AP_D + 64, seq0 + q0);
+      bool ok = true;
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        const int row = seq0 + (j_lo + j) * AP_BN;
+        if (!mbar_wait(bar(B_KEMPTY + st), ph ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (3 << 8)), limit)) { ok = false; break; }
+        mbar_expect_tx(bar(B_KFULL + st), AP_TILE_BYTES);
+        tma_load_2d(sK + st * AP_TILE_BYTES, &tmap_k, bar(B_KFULL + st), kvh * AP_D, row);
+        tma_load_2d(sK + st * AP_TILE_BYTES + AP_CHUNK_BYTES, &tmap_k, bar(B_KFULL + st), kvh * AP_D + 64, row);
+        if (!mbar_wait(bar(B_VEMPTY + st), ph ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (3 << 8)), limit)) { ok = false; break; }
+        mbar_expect_tx(bar(B_VFULL + st), AP_TILE_BYTES);
+        tma_load_2d(sV + st * AP_TILE_BYTES, &tmap_v, bar(B_VFULL + st), kvh * AP_D, row);
+        tma_load_2d(sV + st * AP_TILE_BYTES + AP_CHUNK_BYTES, &tmap_v, bar(B_VFULL + st), kvh * AP_D + 64, row);
+      }
+      if (!ok) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 2000000ull) { } }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t IDESC_S = umma_idesc_bf16(128, 128, 0, 0);
+      constexpr uint32_t IDESC_PV = umma_idesc_bf16(128, 128, 0, 1);     // B (= V) is MN-major
+      auto issue_s = [&](int j) {
+        const int st = j & 1;
+        const uint32_t d = tmem_base + (j & 1) * 128;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint32_t off = (kk >> 2) * AP_CHUNK_BYTES;
+          const uint64_t a = umma_desc_k_sw128(sQ + off) + 2ull * (kk & 3);
+          const uint64_t bd = umma_desc_k_sw128(sK + st * AP_TILE_BYTES + off) + 2ull * (kk & 3);
+          umma_f16_ss(d, a, bd, IDESC_S, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(bar(B_KEMPTY + st));
+        umma_commit(bar(B_SFULL + (j & 1)));
+      };
+      bool ok = mbar_wait(bar(B_QFULL), 0, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (3 << 8)), limit) &&
+                mbar_wait(bar(B_KFULL + 0), 0, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (3 << 8)), limit);
+      if (ok) { tc_fence_after(); issue_s(0); }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1u;
+        if (j + 1 < n_tiles) {
+          if (!mbar_wait(bar(B_KFULL + ((j + 1) & 1)), ((j + 1) >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (3 << 8)), limit)) { ok = false; break; }
+          tc_fence_after();
+          issue_s(j + 1);
+        }
+        if (!mbar_wait(bar(B_PFULL), j & 1u, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (3 << 8)), limit)) { ok = false; break; }
+        if (!mbar_wait(bar(B_VFULL + st), ph, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (3 << 8)), limit)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d = tmem_base + 256 + (j & 1) * 128;
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t a = umma_desc_k_sw128(sP + (kk >> 2) * AP_CHUNK_BYTES) + 2ull * (kk & 3);
+          const uint64_t bd = umma_desc_mn_sw128(sV + st * AP_TILE_BYTES + kk * 2048, AP_CHUNK_BYTES, 1024);
+          umma_f16_ss(d, a, bd, IDESC_PV, kk > 0 ? 1u : 0u);
+        }
+        umma_commit(bar(B_VEMPTY + st));
+        umma_commit(bar(B_OFULL + (j & 1)));
+      }
+    }
+    __syncwarp();
+  } else {
+    const int qd = warp & 3;
+    const int r = qd * 32 + lane;                    // row inside the tile == TMEM lane
+    const int q_idx = q0 + r;
+    const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
+    float o[AP_D];
+#pragma unroll
+    for (int i = 0; i < AP_D; ++i) o[i] = 0.f;
+    float m_run = -INFINITY, l_run = 0.f, alpha_prev = 1.f;
+    bool ok = true;
+    uint8_t* p_row = pP + (r >> 3) * 1024 + (r & 7) * 128;
+    const int sw = r & 7;
+
+    auto o_update = [&](int j, float alpha) -> bool {
+      if (!mbar_wait(bar(B_OFULL + (j & 1)), (j >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (3 << 8)), limit)) return false;
+      tc_fence_after();
+      const uint32_t t_pv = t_lane + 256 + (j & 1) * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(t_pv + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[c * 32 + i] = o[c * 32 + i] * alpha + __uint_as_float(v[i]);
+      }
+      tc_fence_before();
+      return true;
+    };
+
+    for (int j = 0; j < n_tiles; ++j) {
+      if (!mbar_wait(bar(B_SFULL + (j & 1)), (j >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (3 << 8)), limit)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_s = t_lane + (j & 1) * 128;
+      const int kv0 = (j_lo + j) * AP_BN;
+      const bool need_mask = (kv0 + AP_BN > q0) || (kv0 + AP_BN > len);
+      // pass 1: row max
+      float mx = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(t_s + c * 32, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float s = __uint_as_float(v[i]);
+          if (need_mask) { const int kv = kv0 + c * 32 + i; if (kv > q_idx || kv >= len) s = -INFINITY; }
+          mx = fmaxf(mx, s);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx * p.scale_log2);
+      const float alpha = (m_run == -INFINITY) ? 0.f : exp2f(m_run - m_new);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      // the P buffer is free once the PV MMA of the previous tile has completed
+      if (j > 0) {
+        if (!mbar_wait(bar(B_OFULL + ((j - 1) & 1)), ((j - 1) >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (3 << 8)), limit)) { ok = false; break; }
+      }
+      // pass 2: probabilities -> bf16 -> swizzled shared memory
+      float sum = 0.f;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_x32(t_s + c * 32, v);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
+          if (need_mask) {
+            const int kv = kv0 + c * 32 + i;
+            if (kv > q_idx || kv >= len) s0 = -INFINITY;
+            if (kv + 1 > q_idx || kv + 1 >= len) s1 = -INFINITY;
+          }
+          const float e0 = exp2f(s0 * p.scale_log2 - m_use), e1 = exp2f(s1 * p.scale_log2 - m_use);
+          const __nv_bfloat162 pb = __floats2bfloat162_rn(e0, e1);
+          // sum what the MMA will actually see
+          sum += __low2float(pb) + __high2float(pb);
+          pk[i >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+        }
+        // 32 columns = 4 sixteen-byte units; unit u of 128-byte row chunk lands at (u ^ (row & 7))
+        uint8_t* chunk = p_row + (c >> 1) * AP_CHUNK_BYTES;
+#pragma unroll
+        for (int u4 = 0; u4 < 4; ++u4) {
+          const int u = (c & 1) * 4 + u4;
+          *reinterpret_cast<uint4*>(chunk + ((u ^ sw) << 4)) = make_uint4(pk[4 * u4], pk[4 * u4 + 1], pk[4 * u4 + 2], pk[4 * u4 + 3]);
+        }
+      }
+      l_run = l_run * alpha + sum;
+      m_run = m_new;
+      tc_fence_before();
+      fence_proxy_async_smem();
+      mbar_arrive(bar(B_PFULL));
+      // while the tensor core works on PV of this tile, fold in PV of the previous one
+      if (j > 0) { if (!o_update(j - 1, alpha_prev)) { ok = false; break; } }
+      alpha_prev = alpha;
+    }
+    if (ok) ok = o_update(n_tiles - 1, alpha_prev);
+    if (ok && q_idx < len && nchunks == 1) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      uint4* dst = reinterpret_cast<uint4*>(p.out + (static_cast<size_t>(seq0 + q_idx) * p.hq + head) * AP_D);
+#pragma unroll
+      for (int u = 0; u < 16; ++u) {
+        uint32_t w[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const __nv_bfloat162 pb = __floats2bfloat162_rn(o[u * 8 + 2 * k] * inv, o[u * 8 + 2 * k + 1] * inv);
+          w[k] = *reinterpret_cast<const uint32_t*>(&pb);
+        }
+        dst[u] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    } else if (ok && q_idx < len) {
+      // several chunks share this query tile: park the unnormalised row and its (max, sum) for the merge kernel
+      const size_t slot = ((static_cast<size_t>(b) * p.hq + head) * p.n_q + qt) * p.max_chunks + chunk_idx;
+      float4* dst = reinterpret_cast<float4*>(p.part_o + (slot * AP_BM + r) * AP_D);
+#pragma unroll
+      for (int u = 0; u < 32; ++u) dst[u] = make_float4(o[4 * u], o[4 * u + 1], o[4 * u + 2], o[4 * u + 3]);
+      p.part_ml[(slot * AP_BM + r) * 2] = m_run;
+      p.part_ml[(slot * AP_BM + r) * 2 + 1] = l_run;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, 512); }
+}
+
+
+// one CTA per (query tile, head, sequence) that was split; thread <-> output dim, rows walked in order
+__global__ void __launch_bounds__(128) attn_prefill_merge_kernel(const PrefillSplitParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int qt = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+  const int nchunks = (qt + p.chunk) / p.chunk;
+  if (nchunks <= 1) return;
+  const int seq0 = p.cu_seqlens[b];
+  const int len = p.cu_seqlens[b + 1] - seq0;
+  const int d = threadIdx.x;
+  const size_t slot0 = ((static_cast<size_t>(b) * p.hq + head) * p.n_q + qt) * p.max_chunks;
+  for (int r = 0; r < AP_BM; ++r) {
+    const int q_idx = qt * AP_BM + r;
+    if (q_idx >= len) break;
+    float m = -INFINITY;
+    for (int c = 0; c < nchunks; ++c) m = fmaxf(m, p.part_ml[((slot0 + c) * AP_BM + r) * 2]);
+    float l = 0.f, o = 0.f;
+    for (int c = 0; c < nchunks; ++c) {
+      const float mc = p.part_ml[((slot0 + c) * AP_BM + r) * 2];
+      const float w = (mc == -INFINITY) ? 0.f : exp2f(mc - m);
+      l += w * p.part_ml[((slot0 + c) * AP_BM + r) * 2 + 1];
+      o += w * p.part_o[((slot0 + c) * AP_BM + r) * AP_D + d];
+    }
+    p.out[(static_cast<size_t>(seq0 + q_idx) * p.hq + head) * AP_D + d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
+  }
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" size_t b200_attn_prefill_split_scratch_floats(int B, int hq, int max_len, int chunk) {
+  if (chunk < 1) chunk = 1;
+  const size_t n_q = (max_len + AP_BM - 1) / AP_BM;
+  const size_t max_chunks = (n_q + chunk - 1) / chunk;
+  return static_cast<size_t>(B) * hq * n_q * max_chunks * AP_BM * (AP_D + 2);
+}
+
+// Same contract as b200_attn_prefill plus `chunk` (KV tiles of 128 tokens per CTA) and a scratch buffer of
+// b200_attn_prefill_split_scratch_floats(B, hq, max_len, chunk) floats.
+extern "C" int b200_attn_prefill_split(const void* q, long long ld_q, const void* k, long long ld_k, const void* v, long long ld_v,
+                                       void* out, const int* cu_seqlens, int B, int total_tokens, int max_len, int hq, int hkv,
+                                       float scale, int chunk, float* scratch, int* status, cudaStream_t stream) {
+  if (B <= 0 || total_tokens <= 0 || max_len <= 0) return 0;
+  if (hq % hkv || chunk < 1 || !scratch) return -1;
+  if ((ld_q % 8) || (ld_k % 8) || (ld_v % 8)) return -2;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(scratch) & 15)) return -2;
+  CUtensorMap tq, tk, tv;
+  if (make_tmap_2d_bf16(&tq, q, static_cast<uint64_t>(hq) * AP_D, total_tokens, static_cast<uint64_t>(ld_q) * 2)) return -11;
+  if (make_tmap_2d_bf16(&tk, k, static_cast<uint64_t>(hkv) * AP_D, total_tokens, static_cast<uint64_t>(ld_k) * 2)) return -12;
+  if (make_tmap_2d_bf16(&tv, v, static_cast<uint64_t>(hkv) * AP_D, total_tokens, static_cast<uint64_t>(ld_v) * 2)) return -13;
+  PrefillSplitParams p;
+  p.cu_seqlens = cu_seqlens; p.out = static_cast<__nv_bfloat16*>(out); p.hq = hq; p.hkv = hkv;
+  p.n_q = (max_len + AP_BM - 1) / AP_BM; p.chunk = chunk; p.max_chunks = (p.n_q + chunk - 1) / chunk;
+  p.part_o = scratch;
+  p.part_ml = scratch + static_cast<size_t>(B) * hq * p.n_q * p.max_chunks * AP_BM * AP_D;
+  p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.limit_ns = 2000000000ull;
+  constexpr int SMEM = 6 * AP_TILE_BYTES + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_split_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (e != cudaSuccess) return -1000 - static_cast<int>(e);
+    configured = true;
+  }
+  int total_chunks = 0;
+  for (int qt = 0; qt < p.n_q; ++qt) total_chunks += (qt + chunk) / chunk;
+  launch_ex(attn_prefill_split_kernel, dim3(total_chunks, hq, B), dim3(AP_THREADS), SMEM, stream, 0, tq, tk, tv, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return -2000 - static_cast<int>(e);
+  if (p.max_chunks > 1) {
+    launch_ex(attn_prefill_merge_kernel, dim3(p.n_q, hq, B), dim3(128), 0, stream, 0, p);
+    e = cudaGetLastError();
+  }
+  return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
+}

@@ -79,6 +79,8 @@ class _Sig:
     b200_attn_decode_tc_min_splits = (I, [I])
     b200_attn_decode_tcp = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, I, P])
     b200_attn_prefill = (I, [P, LL, P, LL, P, LL, P, P, I, I, I, I, I, F, P, P])
+    b200_attn_prefill_split = (I, [P, LL, P, LL, P, LL, P, P, I, I, I, I, I, F, I, P, P, P])
+    b200_attn_prefill_split_scratch_floats = (c_size_t, [I, I, I, I])
 
 
 def ptr(t: torch.Tensor | None) -> int | None:

@@ -48,9 +48,16 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor,
     return q_out
 
 
+_PREFILL_SPLIT_SCRATCH: dict = {}
+
+
 def attn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: torch.Tensor, max_len: int,
-                 scale: float | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
-    """Causal GQA attention over concatenated sequences. q [T, hq, 128], k/v [T, hkv, 128] (token stride free)."""
+                 scale: float | None = None, out: torch.Tensor | None = None, kv_chunk: int | None = None) -> torch.Tensor:
+    """Causal GQA attention over concatenated sequences. q [T, hq, 128], k/v [T, hkv, 128] (token stride free).
+
+    ``kv_chunk`` > 0 (default: B200RT_PREFILL_SPLIT, else 0) selects the split-KV form: every ``kv_chunk`` KV tiles of
+    128 tokens of a query tile are a CTA of their own and a merge kernel combines them - more parallelism when there are
+    few (sequence, head) pairs.  That form is opt-in: it compiles but has not been run on hardware yet."""
     T, hq, d = q.shape
     hkv = k.shape[1]
     assert d == HEAD_DIM and q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == d
@@ -59,6 +66,23 @@ def attn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: 
     if out is None:
         out = torch.empty((T, hq, d), dtype=torch.bfloat16, device=q.device)
     ws = default_workspace(q.device)
+    if kv_chunk is None:
+        import os
+        kv_chunk = int(os.environ.get("B200RT_PREFILL_SPLIT", "0") or 0)
+    if kv_chunk > 0:
+        B = cu_seqlens.numel() - 1
+        n = _lib.lib().b200_attn_prefill_split_scratch_floats(B, hq, int(max_len), kv_chunk)
+        key = (q.device.index, n)
+        scratch = _PREFILL_SPLIT_SCRATCH.get(key)
+        if scratch is None:
+            scratch = _PREFILL_SPLIT_SCRATCH[key] = torch.empty(max(n, 4), dtype=torch.float32, device=q.device)
+        rc = _lib.lib().b200_attn_prefill_split(
+            q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(),
+            cu_seqlens.data_ptr(), B, T, int(max_len), hq, hkv,
+            float(scale if scale is not None else 1.0 / math.sqrt(d)), kv_chunk, scratch.data_ptr(), ws.status.data_ptr(),
+            _lib.stream())
+        _lib.check(rc, "attn_prefill_split")
+        return out
     rc = _lib.lib().b200_attn_prefill(
         q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), out.data_ptr(),
         cu_seqlens.data_ptr(), cu_seqlens.numel() - 1, T, int(max_len), hq, hkv,

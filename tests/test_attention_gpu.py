@@ -1,6 +1,8 @@
 """Attention-side kernels on the GPU against plain PyTorch fp32 references."""
 import math
 
+import os
+
 import pytest
 import torch
 
@@ -66,6 +68,29 @@ def test_attn_prefill_matches_reference(lens, hq, hkv):
         ref = OA.causal_gqa(q[o:o + L], k[o:o + L], v[o:o + L])
         got = out[o:o + L].float()
         assert torch.allclose(got, ref, rtol=3e-2, atol=3e-2), (got - ref).abs().max().item()
+        o += L
+
+
+@pytest.mark.skipif(os.environ.get("B200RT_TEST_PREFILL_SPLIT") != "1",
+                    reason="split-KV prefill attention is opt-in until it has been run on hardware once: set B200RT_TEST_PREFILL_SPLIT=1")
+@pytest.mark.parametrize("lens,hq,hkv", [([128], 4, 1), ([1024], 4, 1), ([100, 333, 128], 4, 1), ([1, 129], 8, 1), ([640], 8, 2)])
+@pytest.mark.parametrize("chunk", [1, 2, 3])
+def test_attn_prefill_split_kv_matches_reference(lens, hq, hkv, chunk):
+    from mojo_linuxperiments_b200.ops import attention as A
+    from mojo_linuxperiments_b200.ops.workspace import default_workspace
+    T = sum(lens)
+    q, k, v = _rand((T, hq, D), 1), _rand((T, hkv, D), 2), _rand((T, hkv, D), 3)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32).cuda()
+    out = A.attn_prefill(q, k, v, cu, max(lens), kv_chunk=chunk)
+    base = A.attn_prefill(q, k, v, cu, max(lens), kv_chunk=0)
+    torch.cuda.synchronize()
+    default_workspace(q.device).check_status()
+    o = 0
+    for L in lens:
+        ref = OA.causal_gqa(q[o:o + L], k[o:o + L], v[o:o + L])
+        got = out[o:o + L].float()
+        assert torch.allclose(got, ref, rtol=3e-2, atol=3e-2), (got - ref).abs().max().item()
+        assert torch.allclose(got, base[o:o + L].float(), rtol=2e-2, atol=2e-2)
         o += L
 
 
