@@ -50,6 +50,14 @@ class KVState:
         self.free_pages.extend(reversed(self.owned.pop(seq, [])))
 
 
+def own_last_rows(last_idx: torch.Tensor, a: int, b: int):
+    """For a rank that owns token rows [a, b): which of the sequences' last rows (global indices ``last_idx``) it holds
+    (bool [n, 1]) and where they sit in its local tensors (clamped so that the gather is always in range)."""
+    mine = ((last_idx >= a) & (last_idx < b)).unsqueeze(1)
+    loc = (last_idx - a).clamp(0, max(b - a - 1, 0))
+    return mine, loc
+
+
 class Decoder:
     def __init__(self, cfg: ModelConfig, rt: RuntimeConfig, weights: dict, comm: Comm | None = None, device=None,
                  tp_ctx=None):
@@ -170,8 +178,7 @@ class Decoder:
             hq, sh = L.act_quant(gu, mode=L.AQ_SWIGLU)
             delta = sp.rs_linear(hq, sh, W["down"].qweight, W["down"].scale)[: b - a]
         # each sequence's last row lives on exactly one rank: the others contribute zeros to a small all-reduce
-        mine = ((last_idx >= a) & (last_idx < b)).unsqueeze(1)
-        loc = (last_idx - a).clamp(0, max(b - a - 1, 0))
+        mine, loc = own_last_rows(last_idx, a, b)
         d = cfg.d_model
         nb = last_idx.shape[0]
 

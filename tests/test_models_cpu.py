@@ -120,3 +120,25 @@ def test_oracle_model_is_causal_and_tp_consistent():
     assert torch.allclose(a[:7], b, atol=1e-3)                          # a prefix sees the same logits
     c = OM.forward_sequence(cfg, ck, ids, tp=2)
     assert (a - c).abs().max() < 0.1 * a.abs().max()                    # K-sharded quantisation only perturbs
+
+
+def test_last_token_rows_of_a_token_sharded_prefill_sum_to_the_replicated_rows():
+    """Each sequence's last row lives on exactly one rank: summing every rank's masked gather reproduces the rows."""
+    import torch
+    from mojo_linuxperiments_b200.models.decoder import own_last_rows
+    g = torch.Generator().manual_seed(0)
+    for world, lens in ((2, [70, 70, 70]), (8, [70, 70, 70]), (4, [1024]), (8, [5, 300, 33, 129]), (3, [16, 16])):
+        M = sum(lens)
+        last = torch.tensor([sum(lens[: i + 1]) - 1 for i in range(len(lens))])
+        h = torch.randn((M, 8), generator=g)
+        R = (M + world - 1) // world
+        total = torch.zeros((len(lens), 8))
+        owners = torch.zeros(len(lens))
+        for r in range(world):
+            a = min(M, r * R)
+            b = min(M, a + R)
+            mine, loc = own_last_rows(last, a, b)
+            owners += mine.squeeze(1).float()
+            if b > a:
+                total += torch.where(mine, h[a:b].index_select(0, loc), torch.zeros(()))
+        assert torch.equal(owners, torch.ones(len(lens))) and torch.equal(total, h[last])
