@@ -43,11 +43,76 @@ inline void fwht128(float* v) {
 struct QuantJob {
   const uint16_t* x; int K; int m0, m1;
   int8_t* q; uint8_t* qu; float* sx;
+  int simd;                      // 1: AVX-512 rotation / quantisation (same butterflies, same bits as the scalar code)
 };
+
+// The same transform on eight 16-float registers: stages 1..8 inside a register (partner = lane ^ h through a
+// permute, the lower element of a pair takes the sum, the upper one lower - upper), stages 16..64 between registers.
+__attribute__((target("avx512f,avx512bw")))
+inline void fwht128_avx512(__m512 (&z)[8]) {
+  const __m512i lane = _mm512_set_epi32(15, 14, 13, 12, 11, 10, 9, 8, 7, 6, 5, 4, 3, 2, 1, 0);
+  const __mmask16 upper[4] = {0xAAAA, 0xCCCC, 0xF0F0, 0xFF00};
+  for (int st = 0; st < 4; ++st) {
+    const __m512i idx = _mm512_xor_si512(lane, _mm512_set1_epi32(1 << st));
+    for (int i = 0; i < 8; ++i) {
+      const __m512 t = _mm512_permutexvar_ps(idx, z[i]);
+      z[i] = _mm512_mask_blend_ps(upper[st], _mm512_add_ps(z[i], t), _mm512_sub_ps(t, z[i]));
+    }
+  }
+  for (int h = 1; h < 8; h <<= 1)
+    for (int i = 0; i < 8; i += 2 * h)
+      for (int j = i; j < i + h; ++j) {
+        const __m512 a = z[j], b = z[j + h];
+        z[j] = _mm512_add_ps(a, b);
+        z[j + h] = _mm512_sub_ps(a, b);
+      }
+  const __m512 s = _mm512_set1_ps(0.08838834764831845f);
+  for (int i = 0; i < 8; ++i) z[i] = _mm512_mul_ps(z[i], s);
+}
+
+__attribute__((target("avx512f,avx512bw")))
+inline void load_block_avx512(const uint16_t* xr, __m512 (&z)[8]) {
+  for (int i = 0; i < 8; ++i) {
+    const __m256i h = _mm256_loadu_si256(reinterpret_cast<const __m256i*>(xr + 16 * i));
+    z[i] = _mm512_castsi512_ps(_mm512_slli_epi32(_mm512_cvtepu16_epi32(h), 16));      // bf16 -> fp32
+  }
+}
+
+__attribute__((target("avx512f,avx512bw")))
+void quant_rows_avx512(const QuantJob& j) {
+  for (int m = j.m0; m < j.m1; ++m) {
+    const uint16_t* xr = j.x + static_cast<size_t>(m) * j.K;
+    __m512 vmax = _mm512_setzero_ps();
+    __m512 z[8];
+    for (int b = 0; b < j.K; b += 128) {
+      load_block_avx512(xr + b, z);
+      fwht128_avx512(z);
+      for (int i = 0; i < 8; ++i) vmax = _mm512_max_ps(vmax, _mm512_abs_ps(z[i]));
+    }
+    const float amax = _mm512_reduce_max_ps(vmax);
+    const float s = amax > 0.f ? amax / 127.f : 1.f;
+    j.sx[m] = s;
+    const __m512 vs = _mm512_set1_ps(s);
+    const __m512i lo = _mm512_set1_epi32(-127), hi = _mm512_set1_epi32(127), bias = _mm512_set1_epi32(128);
+    int8_t* qr = j.q + static_cast<size_t>(m) * j.K;
+    uint8_t* qur = j.qu + static_cast<size_t>(m) * j.K;
+    for (int b = 0; b < j.K; b += 128) {
+      load_block_avx512(xr + b, z);
+      fwht128_avx512(z);
+      for (int i = 0; i < 8; ++i) {
+        __m512i qi = _mm512_cvtps_epi32(_mm512_div_ps(z[i], vs));            // round to nearest even
+        qi = _mm512_min_epi32(_mm512_max_epi32(qi, lo), hi);
+        _mm_storeu_si128(reinterpret_cast<__m128i*>(qr + b + 16 * i), _mm512_cvtepi32_epi8(qi));
+        _mm_storeu_si128(reinterpret_cast<__m128i*>(qur + b + 16 * i), _mm512_cvtepi32_epi8(_mm512_add_epi32(qi, bias)));
+      }
+    }
+  }
+}
 
 // rows [m0, m1): rotate, quantise, and also store the +128-biased copy the VNNI path multiplies
 void quant_worker(uint64_t a0, uint64_t, uint64_t, uint64_t, uint64_t, uint64_t) {
   QuantJob& j = *reinterpret_cast<QuantJob*>(a0);
+  if (j.simd) { quant_rows_avx512(j); return; }
   float blk[128];
   for (int m = j.m0; m < j.m1; ++m) {
     const uint16_t* xr = j.x + static_cast<size_t>(m) * j.K;
@@ -243,7 +308,8 @@ W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, 
   // phase 1: rows split over the workers
   std::vector<QuantJob> qjobs(total);
   for (int w = 0; w < total; ++w)
-    qjobs[w] = QuantJob{x, K, static_cast<int>(static_cast<long>(M) * w / total), static_cast<int>(static_cast<long>(M) * (w + 1) / total), q, qu.data(), sx};
+    qjobs[w] = QuantJob{x, K, static_cast<int>(static_cast<long>(M) * w / total), static_cast<int>(static_cast<long>(M) * (w + 1) / total), q, qu.data(), sx,
+                        res.used_vnni ? 1 : 0};
   long t0 = sys_clock_monotonic_ns();
   res.status = run(&quant_worker, qjobs);
   res.quant_ns = sys_clock_monotonic_ns() - t0;

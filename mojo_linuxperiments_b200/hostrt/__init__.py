@@ -136,7 +136,10 @@ class NumaInfo:
 
     def __del__(self):
         if getattr(self, "_h", None):
-            lib().hostrt_numa_destroy(self._h)
+            try:
+                lib().hostrt_numa_destroy(self._h)
+            except TypeError:          # interpreter shutdown: module globals are already gone
+                pass
             self._h = None
 
     @property
