@@ -15,6 +15,7 @@
 //               the final maximum and the PV accumulation needs no rescaling; then thread <-> output dim for O^T.
 // Pages beyond the end of the sequence are replaced by the sequence's last valid page (an L2 hit) and masked.
 // With several splits each CTA writes (o, m, l) partials and the last one to finish merges them.  All waits bounded.
+// No counterpart in the reference (it has no attention or any other model kernel).
 #include "ptx.cuh"
 #include "api.h"
 #include "launch.cuh"

@@ -6,7 +6,7 @@
 // takes eight tiles: 66 us per layer for 6 us of tensor work.  Here a query tile's KV tiles are cut into chunks of
 // `chunk` tiles, each chunk is a CTA, chunks of one tile row write unnormalised partial rows (o, max, sum) and a small
 // merge kernel combines them; query tiles that fit one chunk write their result directly.
-// Opt-in (B200RT_PREFILL_SPLIT=chunk): it has not been measured yet.
+// Opt-in (B200RT_PREFILL_SPLIT=chunk): it has not been measured yet.  No counterpart in the reference.
 #include "ptx.cuh"
 #include "api.h"
 #include "launch.cuh"

@@ -15,6 +15,8 @@
 //   reduce     the owner waits until all world ranks reported all of its rows and sums, per row, the slots of exactly
 //              those ranks its own routing list says contributed.
 // No barrier and no library collective; every wait is bounded and reports through the status word.
+// No counterpart in the reference (it has no model code); the transport is the same store-then-gate pattern as its
+// ring reduce (test_linux_threading.mojo:400-414).
 #include "ptx.cuh"
 #include "api.h"
 #include "launch.cuh"

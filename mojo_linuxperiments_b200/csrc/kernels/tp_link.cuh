@@ -21,6 +21,10 @@
 // overwrites data a slower rank is still reading; the gather additionally waits for every consumer's "done" word of
 // the call before last.  Epoch words live in device memory and are advanced by the kernels themselves, so captured
 // launches replay without host involvement.
+//
+// Reference counterpart: none for the exchanges themselves.  The building blocks are the GPU forms of the reference's
+// shared arena that every worker can address (test_linux_threading.mojo:426-435) and of its MutexGate latch
+// (threading/linux_threading.mojo:174-198): stores into a peer's mapped memory, then an epoch flag the peer polls.
 #pragma once
 #include "peer.cuh"
 

@@ -16,6 +16,9 @@
 // (1 tiles, 2 scatter tail, 4 gather push) exists so that a test can run several virtual ranks on one GPU as
 // consecutive launches (all pushes, then all consumers): kernels that wait on each other must never be separate
 // launches on one device.  Production launches use phase 7.
+// The reference has no GEMM and no collective beyond the chain / butterfly sums of test_linux_threading.mojo:400-553;
+// what is kept from it is the discipline of its ring reduce: a producer writes into memory the consumer can address,
+// then opens a gate (threading/linux_threading.mojo:187-194).
 #include "ptx.cuh"
 #include "api.h"
 #include "launch.cuh"
