@@ -172,6 +172,22 @@ long hostrt_butterfly_allreduce(void* numa, int world, long long* out, long time
 long hostrt_fabric_allreduce(void* numa, int world, const double* in, double* out, int rounds, long timeout_ns, int drop_rank) {
   return fabric_allreduce(*static_cast<NumaInfo*>(numa), world, in, out, rounds, timeout_ns, drop_rank);
 }
+void* hostrt_team_create(void* numa, int max_workers_per_node) {
+  auto* t = new WorkerTeam(*static_cast<NumaInfo*>(numa), max_workers_per_node);
+  if (!*t) { delete t; return nullptr; }
+  return t;
+}
+void hostrt_team_destroy(void* team) { delete static_cast<WorkerTeam*>(team); }
+int hostrt_team_size(void* team) { return static_cast<WorkerTeam*>(team)->size(); }
+unsigned long long hostrt_team_jobs_run(void* team) { return static_cast<WorkerTeam*>(team)->jobs_run(); }
+long hostrt_w8a8_linear_team(void* team, const void* x_bf16, int M, int K, const void* wq, const float* sw, int N, void* y_bf16,
+                             int force_scalar, void* q_out, float* sx_out, int* acc_out, long* info5) {
+  const W8A8HostResult r = w8a8_linear_team(*static_cast<WorkerTeam*>(team), static_cast<const uint16_t*>(x_bf16), M, K,
+                                            static_cast<const int8_t*>(wq), sw, N, static_cast<uint16_t*>(y_bf16), force_scalar,
+                                            static_cast<int8_t*>(q_out), sx_out, reinterpret_cast<int32_t*>(acc_out));
+  if (info5) { info5[0] = r.quant_ns; info5[1] = r.gemm_ns; info5[2] = r.workers; info5[3] = r.used_vnni; info5[4] = 0; }
+  return r.status;
+}
 long hostrt_fabric_token_exchange(void* numa, int world, int rows_per_rank, int blocks, int iters, long timeout_ns,
                                   unsigned skew_seed, int mode, int fault, int* mismatches) {
   return fabric_token_exchange(*static_cast<NumaInfo*>(numa), world, rows_per_rank, blocks, iters, timeout_ns, skew_seed, mode, fault,

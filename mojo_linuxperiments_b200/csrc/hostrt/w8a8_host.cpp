@@ -8,6 +8,7 @@
 #include "heap_move_array.hpp"
 #include "pool.hpp"
 #include "sys.hpp"
+#include "team.hpp"
 
 namespace hostrt {
 
@@ -255,22 +256,15 @@ void gemm_worker(uint64_t a0, uint64_t, uint64_t, uint64_t, uint64_t, uint64_t) 
 
 }  // namespace
 
-W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, int K, const int8_t* wq, const float* sw,
-                                int N, uint16_t* y, int max_workers_per_node, int force_scalar, int8_t* q_out,
-                                float* sx_out, int32_t* acc_out) {
+namespace {
+
+// `run(fn, args)` executes fn(args[i]) on worker i for i < total and returns 0 or -errno
+template <typename Run>
+W8A8HostResult linear_core(int total, Run&& run, const uint16_t* x, int M, int K, const int8_t* wq, const float* sw, int N,
+                           uint16_t* y, int force_scalar, int8_t* q_out, float* sx_out, int32_t* acc_out) {
   W8A8HostResult res{};
   if (M <= 0 || N <= 0 || K <= 0 || (K % 128) != 0 || !x || !wq || !sw || !y) { res.status = -err::kINVAL; return res; }
-  const int nn = info.num_nodes();
-  if (nn == 0) { res.status = -err::kNOENT; return res; }
-  std::vector<int> per_node(nn);
-  int total = 0;
-  for (int k = 0; k < nn; ++k) {
-    int c = static_cast<int>(info.nodes()[k].cpu_ids.size());
-    if (max_workers_per_node > 0 && c > max_workers_per_node) c = max_workers_per_node;
-    per_node[k] = c;
-    total += c;
-  }
-  if (total == 0) { res.status = -err::kNOENT; return res; }
+  if (total <= 0) { res.status = -err::kNOENT; return res; }
   res.workers = total;
   // force_scalar: 0 best available, 1 scalar, 2 at most AVX-512 VNNI
   res.used_vnni = (force_scalar != 1 && __builtin_cpu_supports("avx512vnni") && __builtin_cpu_supports("avx512bw")) ? 1 : 0;
@@ -287,31 +281,17 @@ W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, 
   if (!q) { q_own.resize(static_cast<size_t>(M) * K); q = q_own.data(); }
   if (!sx) { sx_own.resize(M); sx = sx_own.data(); }
   std::vector<uint8_t> qu(static_cast<size_t>(M) * K);
-
-  HeapMoveArray<ThreadPool> pools(nn);
-  for (int k = 0; k < nn; ++k) {
-    const int node = info.nodes()[k].id;
-    auto m = info.get_node_mask<128>(node);
-    pools.emplace(per_node[k], m.ptr(), size_t(128), node, stack_size::DEFAULT);
-    if (!pools[k]) { res.status = -err::kNOMEM; return res; }
-  }
-  auto run = [&](WorkerFn fn, auto& jobs) -> long {
-    int w = 0;
-    long st = 0;
-    for (int k = 0; k < nn; ++k)
-      for (int i = 0; i < per_node[k]; ++i, ++w)
-        if (pools[k].launch(fn, reinterpret_cast<uint64_t>(&jobs[w])) < 0) st = -err::kAGAIN;
-    for (int k = 0; k < nn; ++k) if (pools[k].wait_all(120'000'000'000l) != 0) st = -err::kTIMEDOUT;
-    return st;
-  };
+  std::vector<uint64_t> args(total);
 
   // phase 1: rows split over the workers
   std::vector<QuantJob> qjobs(total);
-  for (int w = 0; w < total; ++w)
+  for (int w = 0; w < total; ++w) {
     qjobs[w] = QuantJob{x, K, static_cast<int>(static_cast<long>(M) * w / total), static_cast<int>(static_cast<long>(M) * (w + 1) / total), q, qu.data(), sx,
                         res.used_vnni ? 1 : 0};
+    args[w] = reinterpret_cast<uint64_t>(&qjobs[w]);
+  }
   long t0 = sys_clock_monotonic_ns();
-  res.status = run(&quant_worker, qjobs);
+  res.status = run(&quant_worker, args.data());
   res.quant_ns = sys_clock_monotonic_ns() - t0;
   if (res.status != 0) return res;
 
@@ -327,13 +307,56 @@ W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, 
 
   // phase 2: output channels split over the workers
   std::vector<GemmJob> gjobs(total);
-  for (int w = 0; w < total; ++w)
+  for (int w = 0; w < total; ++w) {
     gjobs[w] = GemmJob{q, qu.data(), sx, wq, sw, y, acc_out, M, K, N, static_cast<int>(static_cast<long>(N) * w / total),
                        static_cast<int>(static_cast<long>(N) * (w + 1) / total), res.used_vnni, q_pack.data()};
+    args[w] = reinterpret_cast<uint64_t>(&gjobs[w]);
+  }
   t0 = sys_clock_monotonic_ns();
-  res.status = run(&gemm_worker, gjobs);
+  res.status = run(&gemm_worker, args.data());
   res.gemm_ns = sys_clock_monotonic_ns() - t0;
   return res;
+}
+
+}  // namespace
+
+W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, int K, const int8_t* wq, const float* sw,
+                                int N, uint16_t* y, int max_workers_per_node, int force_scalar, int8_t* q_out,
+                                float* sx_out, int32_t* acc_out) {
+  const int nn = info.num_nodes();
+  std::vector<int> per_node(nn > 0 ? nn : 0);
+  int total = 0;
+  for (int k = 0; k < nn; ++k) {
+    int c = static_cast<int>(info.nodes()[k].cpu_ids.size());
+    if (max_workers_per_node > 0 && c > max_workers_per_node) c = max_workers_per_node;
+    per_node[k] = c;
+    total += c;
+  }
+  HeapMoveArray<ThreadPool> pools(nn > 0 ? nn : 1);
+  bool pools_ok = nn > 0;
+  for (int k = 0; k < nn && pools_ok; ++k) {
+    const int node = info.nodes()[k].id;
+    auto m = info.get_node_mask<128>(node);
+    pools.emplace(per_node[k], m.ptr(), size_t(128), node, stack_size::DEFAULT);
+    if (!pools[k]) pools_ok = false;
+  }
+  if (!pools_ok) { W8A8HostResult r{}; r.status = nn > 0 ? -err::kNOMEM : -err::kNOENT; return r; }
+  auto run = [&](WorkerFn fn, const uint64_t* args) -> long {        // one fresh thread per job, as the pool does it
+    int w = 0;
+    long st = 0;
+    for (int k = 0; k < nn; ++k)
+      for (int i = 0; i < per_node[k]; ++i, ++w)
+        if (pools[k].launch(fn, args[w]) < 0) st = -err::kAGAIN;
+    for (int k = 0; k < nn; ++k) if (pools[k].wait_all(120'000'000'000l) != 0) st = -err::kTIMEDOUT;
+    return st;
+  };
+  return linear_core(total, run, x, M, K, wq, sw, N, y, force_scalar, q_out, sx_out, acc_out);
+}
+
+W8A8HostResult w8a8_linear_team(WorkerTeam& team, const uint16_t* x, int M, int K, const int8_t* wq, const float* sw, int N,
+                                uint16_t* y, int force_scalar, int8_t* q_out, float* sx_out, int32_t* acc_out) {
+  auto run = [&](WorkerFn fn, const uint64_t* args) -> long { return team.run(fn, args); };
+  return linear_core(team ? team.size() : 0, run, x, M, K, wq, sw, N, y, force_scalar, q_out, sx_out, acc_out);
 }
 
 }  // namespace hostrt

@@ -14,6 +14,7 @@
 #include <cstdint>
 
 #include "numa.hpp"
+#include "team.hpp"
 
 namespace hostrt {
 
@@ -30,5 +31,9 @@ struct W8A8HostResult {
 W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, int K, const int8_t* wq, const float* sw,
                                 int N, uint16_t* y, int max_workers_per_node, int force_scalar, int8_t* q_out,
                                 float* sx_out, int32_t* acc_out);
+
+// The same over a team of parked workers (team.hpp): no thread is created or destroyed per call.
+W8A8HostResult w8a8_linear_team(WorkerTeam& team, const uint16_t* x, int M, int K, const int8_t* wq, const float* sw, int N,
+                                uint16_t* y, int force_scalar, int8_t* q_out, float* sx_out, int32_t* acc_out);
 
 }  // namespace hostrt

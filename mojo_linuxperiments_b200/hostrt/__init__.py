@@ -69,6 +69,10 @@ def lib() -> ctypes.CDLL:
         "hostrt_chain_reduce": (c_long, [c_void_p, c_int, c_long, POINTER(c_longlong)]),
         "hostrt_butterfly_allreduce": (c_long, [c_void_p, c_int, POINTER(c_longlong), c_long]),
         "hostrt_fabric_allreduce": (c_long, [c_void_p, c_int, POINTER(c_double), POINTER(c_double), c_int, c_long, c_int]),
+        "hostrt_team_create": (c_void_p, [c_void_p, c_int]), "hostrt_team_destroy": (None, [c_void_p]),
+        "hostrt_team_size": (c_int, [c_void_p]), "hostrt_team_jobs_run": (c_ulonglong, [c_void_p]),
+        "hostrt_w8a8_linear_team": (c_long, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                             c_void_p, c_void_p, c_void_p, POINTER(c_long)]),
         "hostrt_fabric_token_exchange": (c_long, [c_void_p, c_int, c_int, c_int, c_int, c_long, c_uint, c_int, c_int, POINTER(c_int)]),
         "hostrt_fill_reduce": (c_long, [c_void_p, c_ulonglong, c_ulonglong, c_int, POINTER(c_double), POINTER(c_long),
                                         POINTER(c_int), POINTER(c_int)]),
@@ -312,7 +316,33 @@ def fill_reduce(info: NumaInfo, n_elems: int = 16 * 1024 * 1024, seed: int = 0, 
     return {"status": st, "sum": s.value, "elapsed_ns": ns.value, "workers": w.value, "misplaced": mis.value}
 
 
-def w8a8_linear(info: NumaInfo, x, wq, sw, max_workers_per_node: int = 0, force_scalar: bool = False, isa: str = "best"):
+class WorkerTeam:
+    """Parked, pinned workers (one per core of every NUMA node) that are woken for each job instead of being created
+    for it (``csrc/hostrt/team.hpp``).  Pass it to ``w8a8_linear(..., team=...)``."""
+
+    def __init__(self, info: NumaInfo, max_workers_per_node: int = 0):
+        self._h = lib().hostrt_team_create(info._h, max_workers_per_node)
+        if not self._h:
+            raise RuntimeError("could not create the worker team")
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            try:
+                lib().hostrt_team_destroy(self._h)
+            except TypeError:          # interpreter shutdown
+                pass
+            self._h = None
+
+    close = __del__
+
+    @property
+    def size(self) -> int: return lib().hostrt_team_size(self._h)
+    @property
+    def jobs_run(self) -> int: return lib().hostrt_team_jobs_run(self._h)
+
+
+def w8a8_linear(info: NumaInfo, x, wq, sw, max_workers_per_node: int = 0, force_scalar: bool = False, isa: str = "best",
+                team: "WorkerTeam | None" = None):
     """W8A8 Hadamard linear on the host CPUs over the pinned worker pools (``csrc/hostrt/w8a8_host.cpp``).
 
     x: torch bf16 [M, K] (CPU), wq: int8 [N, K], sw: fp32 [N].  Returns a dict with ``y`` (bf16 [M, N]), the quantised
@@ -328,9 +358,13 @@ def w8a8_linear(info: NumaInfo, x, wq, sw, max_workers_per_node: int = 0, force_
     sx = torch.empty((M,), dtype=torch.float32)
     acc = torch.empty((M, N), dtype=torch.int32)
     info5 = (c_long * 5)()
-    st = lib().hostrt_w8a8_linear(info._h, x.data_ptr(), M, K, wq.data_ptr(), sw.data_ptr(), N, y.data_ptr(),
-                                  max_workers_per_node, 1 if (force_scalar or isa == "scalar") else (2 if isa == "vnni" else 0),
-                                  q.data_ptr(), sx.data_ptr(), acc.data_ptr(), info5)
+    mode = 1 if (force_scalar or isa == "scalar") else (2 if isa == "vnni" else 0)
+    if team is not None:
+        st = lib().hostrt_w8a8_linear_team(team._h, x.data_ptr(), M, K, wq.data_ptr(), sw.data_ptr(), N, y.data_ptr(), mode,
+                                           q.data_ptr(), sx.data_ptr(), acc.data_ptr(), info5)
+    else:
+        st = lib().hostrt_w8a8_linear(info._h, x.data_ptr(), M, K, wq.data_ptr(), sw.data_ptr(), N, y.data_ptr(),
+                                      max_workers_per_node, mode, q.data_ptr(), sx.data_ptr(), acc.data_ptr(), info5)
     return {"status": st, "y": y, "q": q, "sx": sx, "acc": acc, "quant_ns": info5[0], "gemm_ns": info5[1],
             "workers": info5[2], "used_vnni": bool(info5[3]), "isa": ("scalar", "avx512-vnni", "amx-int8")[info5[3]]}
 

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from . import NumaInfo, w8a8_linear
+from . import NumaInfo, WorkerTeam, w8a8_linear
 from ..oracle import attention as OA
 from ..oracle import quant as Q
 
@@ -19,6 +19,7 @@ class HostDecoder:
     def __init__(self, cfg, ck: dict, info: NumaInfo | None = None, isa: str = "best"):
         self.cfg, self.ck = cfg, ck
         self.info = info or NumaInfo()
+        self.team = WorkerTeam(self.info)          # parked workers: a decode step is ~7 linears per layer
         self.isa = isa
         self.linear_ns = 0
         self._fused = {}
@@ -40,7 +41,7 @@ class HostDecoder:
 
     # ---- linears on the worker pools ----------------------------------------------------------------------------
     def _lin(self, x: torch.Tensor, qweight: torch.Tensor, scale: torch.Tensor, fp32_out: bool = False) -> torch.Tensor:
-        r = w8a8_linear(self.info, x.to(BF).contiguous(), qweight, scale, isa=self.isa)
+        r = w8a8_linear(self.info, x.to(BF).contiguous(), qweight, scale, isa=self.isa, team=self.team)
         if r["status"] != 0:
             raise RuntimeError(f"host linear failed with status {r['status']}")
         self.linear_ns += r["quant_ns"] + r["gemm_ns"]

@@ -361,3 +361,23 @@ def test_token_exchange_protocol_on_the_thread_fabric(world):
     if world > 1:
         st, mis = H.fabric_token_exchange(info, world, iters=300, mode=1, fault=2)  # single buffer: must be caught
         assert st == 0 and mis > 0
+
+
+def test_worker_team_runs_many_jobs_on_the_same_parked_threads():
+    """The parked-worker team gives the same bits as thread-per-job pools, job after job, and shuts down cleanly."""
+    import torch
+    info = H.NumaInfo()
+    team = H.WorkerTeam(info)
+    assert team.size >= 1
+    g = torch.Generator().manual_seed(5)
+    wq = torch.randint(-127, 128, (96, 256), generator=g, dtype=torch.int8)
+    sw = torch.rand((96,), generator=g) * 9e-3 + 1e-3
+    before = team.jobs_run
+    for i in range(20):
+        x = torch.randn((1 + i % 7, 256), generator=g).to(torch.bfloat16)
+        a = H.w8a8_linear(info, x, wq, sw, team=team)
+        b = H.w8a8_linear(info, x, wq, sw)
+        assert a["status"] == 0 and a["workers"] == team.size
+        assert torch.equal(a["y"], b["y"]) and torch.equal(a["acc"], b["acc"]) and torch.equal(a["q"], b["q"])
+    assert team.jobs_run == before + 40            # two phases per linear
+    team.close()
