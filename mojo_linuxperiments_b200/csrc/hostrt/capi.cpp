@@ -188,6 +188,22 @@ long hostrt_w8a8_linear_team(void* team, const void* x_bf16, int M, int K, const
   if (info5) { info5[0] = r.quant_ns; info5[1] = r.gemm_ns; info5[2] = r.workers; info5[3] = r.used_vnni; info5[4] = 0; }
   return r.status;
 }
+void* hostrt_weights_create(void* team, const void* wq, int N, int K) {
+  auto* w = new NodeShardedWeights(*static_cast<WorkerTeam*>(team), static_cast<const int8_t*>(wq), N, K);
+  if (!*w) { delete w; return nullptr; }
+  return w;
+}
+void hostrt_weights_destroy(void* w) { delete static_cast<NodeShardedWeights*>(w); }
+int hostrt_weights_misplaced(void* w) { return static_cast<NodeShardedWeights*>(w)->misplaced(); }
+long hostrt_w8a8_linear_sharded(void* team, void* weights, const void* x_bf16, int M, const float* sw, void* y_bf16,
+                                int force_scalar, void* q_out, float* sx_out, int* acc_out, long* info5) {
+  const W8A8HostResult r = w8a8_linear_team_sharded(*static_cast<WorkerTeam*>(team), *static_cast<NodeShardedWeights*>(weights),
+                                                    static_cast<const uint16_t*>(x_bf16), M, sw, static_cast<uint16_t*>(y_bf16),
+                                                    force_scalar, static_cast<int8_t*>(q_out), sx_out,
+                                                    reinterpret_cast<int32_t*>(acc_out));
+  if (info5) { info5[0] = r.quant_ns; info5[1] = r.gemm_ns; info5[2] = r.workers; info5[3] = r.used_vnni; info5[4] = 0; }
+  return r.status;
+}
 long hostrt_fabric_token_exchange(void* numa, int world, int rows_per_rank, int blocks, int iters, long timeout_ns,
                                   unsigned skew_seed, int mode, int fault, int* mismatches) {
   return fabric_token_exchange(*static_cast<NumaInfo*>(numa), world, rows_per_rank, blocks, iters, timeout_ns, skew_seed, mode, fault,

@@ -12,6 +12,12 @@ constexpr uint32_t kFutex = futex2::SIZE_U32 | futex2::PRIVATE;
 
 void team_loop(uint64_t slot_p, uint64_t, uint64_t, uint64_t, uint64_t, uint64_t) {
   auto* s = reinterpret_cast<TeamSlot*>(slot_p);
+  if (s->cpu >= 0 && s->cpu < 1024) {
+    // one worker per core: a parked thread that wakes on a CPU another worker occupies would halve both
+    uint64_t mask[16] = {};
+    mask[s->cpu >> 6] = 1ull << (s->cpu & 63);
+    sys_sched_setaffinity(0, sizeof(mask), mask);
+  }
   uint32_t seen = 0;
   for (;;) {
     // a short spin keeps back-to-back jobs off the futex path, then sleep until the epoch moves
@@ -49,6 +55,7 @@ WorkerTeam::WorkerTeam(const NumaInfo& info, int max_workers_per_node) : pools_(
     for (int i = 0; i < per_node[k]; ++i, ++w) {
       TeamSlot& s = slots_[w];
       s.go.store(0); s.done.store(0); s.fn = nullptr; s.arg = 0; s.quit = 0; s.node = node;
+      s.cpu = i < static_cast<int>(info.nodes()[k].cpu_ids.size()) ? info.nodes()[k].cpu_ids[i] : -1;
       if (pools_[k].launch(&team_loop, reinterpret_cast<uint64_t>(&s)) < 0) return;
     }
   }

@@ -21,6 +21,7 @@ struct alignas(64) TeamSlot {
   uint64_t arg;
   uint32_t quit;
   int node;
+  int cpu;                       // the one CPU this worker pins itself to (-1: the node's mask)
 };
 
 class WorkerTeam {

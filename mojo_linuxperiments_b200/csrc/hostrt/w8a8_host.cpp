@@ -261,9 +261,11 @@ namespace {
 // `run(fn, args)` executes fn(args[i]) on worker i for i < total and returns 0 or -errno
 template <typename Run>
 W8A8HostResult linear_core(int total, Run&& run, const uint16_t* x, int M, int K, const int8_t* wq, const float* sw, int N,
-                           uint16_t* y, int force_scalar, int8_t* q_out, float* sx_out, int32_t* acc_out) {
+                           uint16_t* y, int force_scalar, int8_t* q_out, float* sx_out, int32_t* acc_out,
+                           const NodeShardedWeights* shards = nullptr) {
   W8A8HostResult res{};
-  if (M <= 0 || N <= 0 || K <= 0 || (K % 128) != 0 || !x || !wq || !sw || !y) { res.status = -err::kINVAL; return res; }
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 128) != 0 || !x || (!wq && !shards) || !sw || !y) { res.status = -err::kINVAL; return res; }
+  if (shards && (shards->workers() != total || shards->N() != N || shards->K() != K)) { res.status = -err::kINVAL; return res; }
   if (total <= 0) { res.status = -err::kNOENT; return res; }
   res.workers = total;
   // force_scalar: 0 best available, 1 scalar, 2 at most AVX-512 VNNI
@@ -308,7 +310,7 @@ W8A8HostResult linear_core(int total, Run&& run, const uint16_t* x, int M, int K
   // phase 2: output channels split over the workers
   std::vector<GemmJob> gjobs(total);
   for (int w = 0; w < total; ++w) {
-    gjobs[w] = GemmJob{q, qu.data(), sx, wq, sw, y, acc_out, M, K, N, static_cast<int>(static_cast<long>(N) * w / total),
+    gjobs[w] = GemmJob{q, qu.data(), sx, shards ? shards->base_for(w) : wq, sw, y, acc_out, M, K, N, static_cast<int>(static_cast<long>(N) * w / total),
                        static_cast<int>(static_cast<long>(N) * (w + 1) / total), res.used_vnni, q_pack.data()};
     args[w] = reinterpret_cast<uint64_t>(&gjobs[w]);
   }
@@ -351,6 +353,57 @@ W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, 
     return st;
   };
   return linear_core(total, run, x, M, K, wq, sw, N, y, force_scalar, q_out, sx_out, acc_out);
+}
+
+NodeShardedWeights::NodeShardedWeights(const WorkerTeam& team, const int8_t* wq, int N, int K)
+    : arenas_(team.size() > 0 ? team.size() : 1), N_(N), K_(K) {
+  const int total = team.size();
+  if (total <= 0 || N <= 0 || K <= 0 || !wq) return;
+  bases_.assign(total, nullptr);
+  firsts_.assign(total, nullptr);
+  nodes_.assign(total, -1);
+  // one arena per run of consecutive workers on the same node (workers are ordered node by node)
+  int w = 0;
+  while (w < total) {
+    int w_end = w;
+    const int node = team.node_of(w);
+    while (w_end < total && team.node_of(w_end) == node) ++w_end;
+    const long n_lo = static_cast<long>(N) * w / total, n_hi = static_cast<long>(N) * w_end / total;
+    const size_t bytes = static_cast<size_t>(n_hi - n_lo) * K;
+    arenas_.emplace(node, bytes + 4096, size_t(64), page_size::THP_2MB);
+    NumaArena& a = arenas_[arenas_.size() - 1];
+    if (!a) return;
+    int8_t* dst = bytes ? a.alloc<int8_t>(bytes) : nullptr;
+    if (bytes && !dst) return;
+    if (bytes) __builtin_memcpy(dst, wq + static_cast<size_t>(n_lo) * K, bytes);      // first touch happens here, on the bound node
+    for (int i = w; i < w_end; ++i) {
+      const long n0 = static_cast<long>(N) * i / total;
+      bases_[i] = dst ? dst - static_cast<size_t>(n_lo) * K : nullptr;   // so that base + n*K addresses global row n
+      firsts_[i] = dst ? dst + static_cast<size_t>(n0 - n_lo) * K : nullptr;
+      nodes_[i] = node;
+    }
+    w = w_end;
+  }
+  valid_ = true;
+}
+
+int NodeShardedWeights::misplaced() const {
+  int bad = 0;
+  for (size_t i = 0; i < firsts_.size(); ++i) {
+    const long n0 = static_cast<long>(N_) * static_cast<long>(i) / static_cast<long>(firsts_.size());
+    const long n1 = static_cast<long>(N_) * static_cast<long>(i + 1) / static_cast<long>(firsts_.size());
+    if (!firsts_[i] || n1 <= n0) continue;
+    const long where = sys_move_pages_query(const_cast<int8_t*>(firsts_[i]));
+    if (where < 0) return -1;
+    if (where != nodes_[i]) ++bad;
+  }
+  return bad;
+}
+
+W8A8HostResult w8a8_linear_team_sharded(WorkerTeam& team, const NodeShardedWeights& w, const uint16_t* x, int M, const float* sw,
+                                        uint16_t* y, int force_scalar, int8_t* q_out, float* sx_out, int32_t* acc_out) {
+  auto run = [&](WorkerFn fn, const uint64_t* args) -> long { return team.run(fn, args); };
+  return linear_core(team ? team.size() : 0, run, x, M, w.K(), nullptr, sw, w.N(), y, force_scalar, q_out, sx_out, acc_out, &w);
 }
 
 W8A8HostResult w8a8_linear_team(WorkerTeam& team, const uint16_t* x, int M, int K, const int8_t* wq, const float* sw, int N,

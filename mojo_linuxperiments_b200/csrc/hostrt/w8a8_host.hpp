@@ -13,6 +13,10 @@
 #pragma once
 #include <cstdint>
 
+#include <vector>
+
+#include "arena.hpp"
+#include "heap_move_array.hpp"
 #include "numa.hpp"
 #include "team.hpp"
 
@@ -32,8 +36,35 @@ W8A8HostResult w8a8_linear_host(const NumaInfo& info, const uint16_t* x, int M, 
                                 int N, uint16_t* y, int max_workers_per_node, int force_scalar, int8_t* q_out,
                                 float* sx_out, int32_t* acc_out);
 
+// int8 weights [N][K] placed where they are used: worker w of a team handles output channels
+// [N*w/size, N*(w+1)/size), and those rows are copied into a NumaArena bound to that worker's node (one arena per
+// node, threading/numa_arena.mojo:6-140 in the reference), so every worker streams node-local memory.
+class NodeShardedWeights {
+ public:
+  NodeShardedWeights(const WorkerTeam& team, const int8_t* wq, int N, int K);
+  explicit operator bool() const { return valid_; }
+  int N() const { return N_; }
+  int K() const { return K_; }
+  // pointer p such that p + n*K is row n for every n of worker w's range
+  const int8_t* base_for(int worker) const { return bases_[worker]; }
+  int workers() const { return static_cast<int>(bases_.size()); }
+  // shards whose first page is not on the node of the worker that reads them (-1: the kernel would not say)
+  int misplaced() const;
+
+ private:
+  HeapMoveArray<NumaArena> arenas_;
+  std::vector<const int8_t*> bases_;
+  std::vector<const int8_t*> firsts_;
+  std::vector<int> nodes_;
+  int N_ = 0, K_ = 0;
+  bool valid_ = false;
+};
+
 // The same over a team of parked workers (team.hpp): no thread is created or destroyed per call.
 W8A8HostResult w8a8_linear_team(WorkerTeam& team, const uint16_t* x, int M, int K, const int8_t* wq, const float* sw, int N,
                                 uint16_t* y, int force_scalar, int8_t* q_out, float* sx_out, int32_t* acc_out);
+// ... with the weights taken from their node-local shards (wq of the other entry points is then unused)
+W8A8HostResult w8a8_linear_team_sharded(WorkerTeam& team, const NodeShardedWeights& w, const uint16_t* x, int M, const float* sw,
+                                        uint16_t* y, int force_scalar, int8_t* q_out, float* sx_out, int32_t* acc_out);
 
 }  // namespace hostrt

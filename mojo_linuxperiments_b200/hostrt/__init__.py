@@ -73,6 +73,10 @@ def lib() -> ctypes.CDLL:
         "hostrt_team_size": (c_int, [c_void_p]), "hostrt_team_jobs_run": (c_ulonglong, [c_void_p]),
         "hostrt_w8a8_linear_team": (c_long, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                              c_void_p, c_void_p, c_void_p, POINTER(c_long)]),
+        "hostrt_weights_create": (c_void_p, [c_void_p, c_void_p, c_int, c_int]), "hostrt_weights_destroy": (None, [c_void_p]),
+        "hostrt_weights_misplaced": (c_int, [c_void_p]),
+        "hostrt_w8a8_linear_sharded": (c_long, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p,
+                                                c_void_p, c_void_p, POINTER(c_long)]),
         "hostrt_fabric_token_exchange": (c_long, [c_void_p, c_int, c_int, c_int, c_int, c_long, c_uint, c_int, c_int, POINTER(c_int)]),
         "hostrt_fill_reduce": (c_long, [c_void_p, c_ulonglong, c_ulonglong, c_int, POINTER(c_double), POINTER(c_long),
                                         POINTER(c_int), POINTER(c_int)]),
@@ -341,25 +345,60 @@ class WorkerTeam:
     def jobs_run(self) -> int: return lib().hostrt_team_jobs_run(self._h)
 
 
+class HostWeights:
+    """int8 weights [N, K] copied into NUMA arenas so that each team worker's output-channel range is local to the node
+    the worker is pinned to (``NodeShardedWeights`` in ``csrc/hostrt/w8a8_host.hpp``)."""
+
+    def __init__(self, team: WorkerTeam, wq, sw):
+        import torch
+        assert wq.dtype == torch.int8 and wq.is_contiguous() and not wq.is_cuda and sw.dtype == torch.float32
+        self.team, self.N, self.K = team, wq.shape[0], wq.shape[1]
+        self.sw = sw.contiguous()
+        self._h = lib().hostrt_weights_create(team._h, wq.data_ptr(), self.N, self.K)
+        if not self._h:
+            raise MemoryError("could not place the weights in the node arenas")
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            try:
+                lib().hostrt_weights_destroy(self._h)
+            except TypeError:
+                pass
+            self._h = None
+
+    @property
+    def misplaced(self) -> int:
+        """Shards whose first page is not on its reader's node (-1 when the kernel does not tell)."""
+        return lib().hostrt_weights_misplaced(self._h)
+
+
 def w8a8_linear(info: NumaInfo, x, wq, sw, max_workers_per_node: int = 0, force_scalar: bool = False, isa: str = "best",
-                team: "WorkerTeam | None" = None):
+                team: "WorkerTeam | None" = None, weights: "HostWeights | None" = None):
     """W8A8 Hadamard linear on the host CPUs over the pinned worker pools (``csrc/hostrt/w8a8_host.cpp``).
 
     x: torch bf16 [M, K] (CPU), wq: int8 [N, K], sw: fp32 [N].  Returns a dict with ``y`` (bf16 [M, N]), the quantised
     activations ``q`` / ``sx``, the exact int32 accumulators ``acc`` and timing / dispatch info.  ``isa``: "best"
     (AMX int8, else AVX-512 VNNI, else scalar), "vnni" (no AMX), "scalar"."""
     import torch
-    assert x.dtype == torch.bfloat16 and wq.dtype == torch.int8 and sw.dtype == torch.float32
-    assert not x.is_cuda and x.is_contiguous() and wq.is_contiguous() and sw.is_contiguous()
+    if weights is not None:
+        team, sw = weights.team, weights.sw
+        N = weights.N
+        assert x.shape[1] == weights.K
+    else:
+        assert wq.dtype == torch.int8 and sw.dtype == torch.float32 and wq.is_contiguous() and sw.is_contiguous()
+        N = wq.shape[0]
+    assert x.dtype == torch.bfloat16 and not x.is_cuda and x.is_contiguous()
     M, K = x.shape
-    N = wq.shape[0]
     y = torch.empty((M, N), dtype=torch.bfloat16)
     q = torch.empty((M, K), dtype=torch.int8)
     sx = torch.empty((M,), dtype=torch.float32)
     acc = torch.empty((M, N), dtype=torch.int32)
     info5 = (c_long * 5)()
     mode = 1 if (force_scalar or isa == "scalar") else (2 if isa == "vnni" else 0)
-    if team is not None:
+    if weights is not None:
+        st = lib().hostrt_w8a8_linear_sharded(team._h, weights._h, x.data_ptr(), M, sw.data_ptr(), y.data_ptr(), mode,
+                                              q.data_ptr(), sx.data_ptr(), acc.data_ptr(), info5)
+    elif team is not None:
         st = lib().hostrt_w8a8_linear_team(team._h, x.data_ptr(), M, K, wq.data_ptr(), sw.data_ptr(), N, y.data_ptr(), mode,
                                            q.data_ptr(), sx.data_ptr(), acc.data_ptr(), info5)
     else:

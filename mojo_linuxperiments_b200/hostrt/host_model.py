@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import torch
 
-from . import NumaInfo, WorkerTeam, w8a8_linear
+from . import HostWeights, NumaInfo, WorkerTeam, w8a8_linear
 from ..oracle import attention as OA
 from ..oracle import quant as Q
 
@@ -22,17 +22,23 @@ class HostDecoder:
         self.team = WorkerTeam(self.info)          # parked workers: a decode step is ~7 linears per layer
         self.isa = isa
         self.linear_ns = 0
-        self._fused = {}
+        # every dense linear's weights go into the NUMA arena of the node whose workers stream them (fused where the
+        # GPU engine fuses them); expert weights stay in the checkpoint tensors
+        self._w = {}
         for l in range(cfg.n_layers):
             p = f"layers.{l}."
-            self._fused[p + "qkv"] = self._cat(p, ("wq", "wk", "wv"))
+            self._w[p + "qkv"] = self._place(p, ("wq", "wk", "wv"))
+            self._w[p + "wo"] = self._place(p, ("wo",))
             if not cfg.is_moe:
-                self._fused[p + "gate_up"] = self._cat(p, ("gate", "up"))
+                self._w[p + "gate_up"] = self._place(p, ("gate", "up"))
+                self._w[p + "down"] = self._place(p, ("down",))
+        self._w["lm_head"] = HostWeights(self.team, ck["lm_head.qweight"].contiguous(), ck["lm_head.scale"])
         self.reset()
 
-    def _cat(self, p, names):
-        return (torch.cat([self.ck[p + n + ".qweight"] for n in names], 0).contiguous(),
-                torch.cat([self.ck[p + n + ".scale"] for n in names], 0).contiguous())
+    def _place(self, p, names) -> HostWeights:
+        q = torch.cat([self.ck[p + n + ".qweight"] for n in names], 0).contiguous()
+        s = torch.cat([self.ck[p + n + ".scale"] for n in names], 0).contiguous()
+        return HostWeights(self.team, q, s)          # the concatenated copy is dropped once it sits in the arenas
 
     def reset(self):
         self.k_cache = [None] * self.cfg.n_layers
@@ -40,8 +46,13 @@ class HostDecoder:
         self.pos = 0
 
     # ---- linears on the worker pools ----------------------------------------------------------------------------
-    def _lin(self, x: torch.Tensor, qweight: torch.Tensor, scale: torch.Tensor, fp32_out: bool = False) -> torch.Tensor:
-        r = w8a8_linear(self.info, x.to(BF).contiguous(), qweight, scale, isa=self.isa, team=self.team)
+    def _lin(self, x: torch.Tensor, qweight, scale=None, fp32_out: bool = False) -> torch.Tensor:
+        """``qweight``: a ``HostWeights`` (node-local shards) or an int8 tensor with its ``scale``."""
+        if isinstance(qweight, HostWeights):
+            r = w8a8_linear(self.info, x.to(BF).contiguous(), None, None, isa=self.isa, weights=qweight)
+            scale = qweight.sw
+        else:
+            r = w8a8_linear(self.info, x.to(BF).contiguous(), qweight, scale, isa=self.isa, team=self.team)
         if r["status"] != 0:
             raise RuntimeError(f"host linear failed with status {r['status']}")
         self.linear_ns += r["quant_ns"] + r["gemm_ns"]
@@ -78,7 +89,7 @@ class HostDecoder:
         for l in range(cfg.n_layers):
             p = f"layers.{l}."
             xn = Q.rmsnorm(h, ck[p + "attn_norm"], cfg.eps)
-            qkv = self._lin(xn, *self._fused[p + "qkv"]).view(T, cfg.n_heads + 2 * cfg.n_kv_heads, hd)
+            qkv = self._lin(xn, self._w[p + "qkv"]).view(T, cfg.n_heads + 2 * cfg.n_kv_heads, hd)
             q, k, v = qkv[:, : cfg.n_heads], qkv[:, cfg.n_heads: cfg.n_heads + cfg.n_kv_heads], qkv[:, cfg.n_heads + cfg.n_kv_heads:]
             if cfg.qk_norm:
                 q = OA.head_rmsnorm(q, ck[p + "q_norm"], cfg.eps)
@@ -88,17 +99,17 @@ class HostDecoder:
             self.k_cache[l] = k if self.k_cache[l] is None else torch.cat([self.k_cache[l], k], 0)
             self.v_cache[l] = v.to(BF) if self.v_cache[l] is None else torch.cat([self.v_cache[l], v.to(BF)], 0)
             attn = self._attend(q, self.k_cache[l], self.v_cache[l]).to(BF).reshape(T, -1)
-            h = (h.float() + self._lin(attn, ck[p + "wo.qweight"], ck[p + "wo.scale"]).float()).to(BF)
+            h = (h.float() + self._lin(attn, self._w[p + "wo"]).float()).to(BF)
             xn = Q.rmsnorm(h, ck[p + "mlp_norm"], cfg.eps)
             if cfg.is_moe:
                 delta = self._moe(p, xn)
             else:
-                gu = self._lin(xn, *self._fused[p + "gate_up"])
-                delta = self._lin(Q.swiglu(gu), ck[p + "down.qweight"], ck[p + "down.scale"])
+                gu = self._lin(xn, self._w[p + "gate_up"])
+                delta = self._lin(Q.swiglu(gu), self._w[p + "down"])
             h = (h.float() + delta.float()).to(BF)
         self.pos += T
         xn = Q.rmsnorm(h[-1:], ck["final_norm"], cfg.eps)
-        return self._lin(xn, ck["lm_head.qweight"], ck["lm_head.scale"]).float()[0]
+        return self._lin(xn, self._w["lm_head"]).float()[0]
 
     def _attend(self, q, k_all, v_all):
         """q [T, hq, D] (the last T positions), k_all / v_all [S, hkv, D] -> [T, hq, D] fp32, causal."""

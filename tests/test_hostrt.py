@@ -381,3 +381,23 @@ def test_worker_team_runs_many_jobs_on_the_same_parked_threads():
         assert torch.equal(a["y"], b["y"]) and torch.equal(a["acc"], b["acc"]) and torch.equal(a["q"], b["q"])
     assert team.jobs_run == before + 40            # two phases per linear
     team.close()
+
+
+def test_node_sharded_weights_live_where_their_readers_run():
+    """Weights copied into per-node arenas: every shard's pages are on the node of the worker that streams them, and the
+    linear over them gives the same bits as the linear over the original tensor."""
+    import torch
+    info = H.NumaInfo()
+    team = H.WorkerTeam(info)
+    g = torch.Generator().manual_seed(9)
+    wq = torch.randint(-127, 128, (203, 384), generator=g, dtype=torch.int8)
+    sw = torch.rand((203,), generator=g) * 9e-3 + 1e-3
+    hw = H.HostWeights(team, wq, sw)
+    assert hw.misplaced in (0, -1)                 # -1: move_pages is not permitted in this sandbox
+    for m in (1, 9, 40):
+        x = torch.randn((m, 384), generator=g).to(torch.bfloat16)
+        a = H.w8a8_linear(info, x, None, None, weights=hw)
+        b = H.w8a8_linear(info, x, wq, sw)
+        assert a["status"] == 0 and torch.equal(a["y"], b["y"]) and torch.equal(a["acc"], b["acc"])
+    del hw
+    team.close()
