@@ -43,3 +43,61 @@ def test_decode_attention_split_policy_and_sp_layout():
             assert a % 1024 == 0 and a + n <= b
         assert areas[-1][0] + areas[-1][1] <= lay.nbytes
         assert lay.r_cap * world >= m_cap and lay.blk_cap * 128 >= lay.r_cap
+
+
+def test_index_arithmetic_of_the_fused_tp_gemms():
+    """Python restatement of the integer bookkeeping in csrc/kernels/w8a8_gemm_tp.cu, swept over awkward shapes:
+    (a) scatter form: the row counts the epilogue warps report to each owner add up to rows_owner x column tiles;
+    (b) gather form: every (source, block) flag a tile waits for is one the source publishes, and the grouped push
+        covers each of a rank's 16-byte vectors exactly once with `members` arrivals per block."""
+    def ceil_div(a, b): return -(-a // b)
+    for world in (1, 2, 3, 4, 8):
+        for M in (65, 128, 130, 200, 256, 520, 1000, 1024, 4096 + 17):
+            R = ceil_div(M, world)
+            m_tiles = ceil_div(M, 128)
+            for n_tiles in (1, 3):
+                # (a) arrival counts per owner
+                got = [0] * world
+                for m_tile in range(m_tiles):
+                    for _ in range(n_tiles):
+                        for q in range(4):
+                            m0, m1 = m_tile * 128 + q * 32, min(m_tile * 128 + q * 32 + 32, M)
+                            if m0 >= m1:
+                                continue
+                            for o in range(m0 // R, (m1 - 1) // R + 1):
+                                got[o] += min(m1, (o + 1) * R) - max(m0, o * R)
+                want = [max(0, min(R, M - o * R)) * n_tiles for o in range(world)]
+                assert got == want, (world, M, n_tiles)
+            # (b) flags a consumer tile needs vs flags a source publishes
+            for m_tile in range(m_tiles):
+                r_lo, r_hi = m_tile * 128, min(m_tile * 128 + 128, M) - 1
+                for s in range(r_lo // R, r_hi // R + 1):
+                    assert s < world
+                    rows_s = max(0, min(R, M - s * R))
+                    a, b = max(r_lo, s * R) - s * R, min(r_hi, (s + 1) * R - 1) - s * R
+                    for blk in range(a >> 7, (b >> 7) + 1):
+                        assert blk * 128 < rows_s, (world, M, m_tile, s, blk)       # published by the push
+            # grouped push of one rank's rows: CTA groups, members per block, vector coverage
+            G, K = 148, 256
+            for rank in range(world):
+                my_rows = max(0, min(R, M - rank * R))
+                nblk = ceil_div(my_rows, 128)
+                members = G // nblk if 0 < nblk <= G else 1
+                arrivals = [0] * nblk
+                covered = [0] * (my_rows * (K // 16))
+                for cta in range(G):
+                    first = cta // members if nblk <= G else cta
+                    step = nblk if nblk <= G else G
+                    mtid0 = (cta % members if nblk <= G else 0) * 64
+                    blk = first
+                    while blk < nblk:
+                        rows_b = min(128, my_rows - blk * 128)
+                        for ct in range(64):
+                            v = mtid0 + ct
+                            while v < rows_b * (K // 16):
+                                covered[blk * 128 * (K // 16) + v] += 1
+                                v += members * 64
+                        arrivals[blk] += 1
+                        blk += step
+                assert all(c == 1 for c in covered), (world, M, rank)
+                assert all(a == members for a in arrivals), (world, M, rank, arrivals, members)
