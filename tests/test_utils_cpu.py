@@ -101,3 +101,31 @@ def test_index_arithmetic_of_the_fused_tp_gemms():
                         blk += step
                 assert all(c == 1 for c in covered), (world, M, rank)
                 assert all(a == members for a in arrivals), (world, M, rank, arrivals, members)
+
+
+def test_split_prefill_attention_work_decomposition():
+    """Python restatement of the (query tile, KV chunk) enumeration of csrc/kernels/attn_prefill_split.cu: every pair is
+    visited exactly once, heavy query tiles first, and the chunks of a tile cover KV tiles 0..qt without overlap."""
+    for n_q in (1, 2, 3, 8, 13):
+        for chunk in (1, 2, 3, 5):
+            total = sum((qt + chunk) // chunk for qt in range(n_q))
+            seen = {}
+            order = []
+            for bx in range(total):
+                qt, rem = n_q - 1, bx
+                while qt > 0 and rem >= (qt + chunk) // chunk:
+                    rem -= (qt + chunk) // chunk
+                    qt -= 1
+                nchunks = (qt + chunk) // chunk
+                assert 0 <= rem < nchunks
+                j_lo = rem * chunk
+                n_tiles = min(qt + 1, j_lo + chunk) - j_lo
+                assert n_tiles >= 1
+                seen.setdefault(qt, []).extend(range(j_lo, j_lo + n_tiles))
+                order.append(qt)
+            assert order == sorted(order, reverse=True)
+            assert sorted(seen) == list(range(n_q))
+            for qt, tiles in seen.items():
+                assert sorted(tiles) == list(range(qt + 1)), (n_q, chunk, qt)
+            max_chunks = (n_q + chunk - 1) // chunk
+            assert all((qt + chunk) // chunk <= max_chunks for qt in range(n_q))
