@@ -129,3 +129,27 @@ def test_split_prefill_attention_work_decomposition():
                 assert sorted(tiles) == list(range(qt + 1)), (n_q, chunk, qt)
             max_chunks = (n_q + chunk - 1) // chunk
             assert all((qt + chunk) // chunk <= max_chunks for qt in range(n_q))
+
+
+def test_decode_attention_split_geometry_covers_every_block_once():
+    """Python restatement of the per-CTA geometry of csrc/kernels/attn_decode_tc.cu: with at least ``tc_min_splits`` splits
+    no CTA gets more than four 128-token blocks, and the splits cover blocks 0..ceil(len/128)-1 exactly once."""
+    from mojo_linuxperiments_b200.ops import attention as A
+    for max_len in (64, 128, 512, 513, 1088, 2048, 5000):
+        smin = A.tc_min_splits(max_len)
+        for splits in (smin, smin + 1, 2 * smin + 3):
+            for length in sorted({1, 17, 127, 128, 129, 640, max_len // 2, max_len - 1, max_len}):
+                if length < 1:
+                    continue
+                total_blocks = (length + 127) // 128
+                per = -(-total_blocks // splits)
+                covered = []
+                for split in range(splits):
+                    blk0 = split * per
+                    nb = max(0, min(total_blocks, blk0 + per) - blk0)
+                    assert nb <= A.TC_BLOCKS_PER_CTA, (max_len, splits, length, nb)
+                    covered += list(range(blk0, blk0 + nb))
+                    total_pages = (length + 15) // 16
+                    for lane in range(32):                       # page-id prefetch stays inside the sequence's pages
+                        assert 0 <= min(blk0 * 8 + lane, total_pages - 1) < total_pages
+                assert covered == list(range(total_blocks)), (max_len, splits, length)
