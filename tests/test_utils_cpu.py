@@ -139,7 +139,7 @@ def test_decode_attention_split_geometry_covers_every_block_once():
         smin = A.tc_min_splits(max_len)
         for splits in (smin, smin + 1, 2 * smin + 3):
             for length in sorted({1, 17, 127, 128, 129, 640, max_len // 2, max_len - 1, max_len}):
-                if length < 1:
+                if length < 1 or length > max_len:
                     continue
                 total_blocks = (length + 127) // 128
                 per = -(-total_blocks // splits)
