@@ -94,6 +94,9 @@ int b200_attn_prefill_split(const void* q, long long ld_q, const void* k, long l
                             void* out, const int* cu_seqlens, int B, int total_tokens, int max_len, int hq, int hkv,
                             float scale, int chunk, float* scratch, int* status, cudaStream_t stream);
 
+// ---- locality query: every CTA writes {sm id, number of sm ids, rank_tag, cta index} (int32 [ctas][4]) -------------
+int b200_where_am_i(int* out, int ctas, int rank_tag, cudaStream_t stream);
+
 // ---- config-1 workload: counter-RNG fill + sum ------------------------------------------------------------
 int b200_fill_uniform_reduce(float* out, unsigned long long begin, unsigned long long end, unsigned long long seed,
                              double* partials, int max_ctas, unsigned* counter, double* result, cudaStream_t stream);

@@ -59,6 +59,7 @@ class _Sig:
     b200_ep_combine_reduce = (I, [P, I, I, I, I, I, P, I, I, c_size_t, c_size_t, c_size_t, I, P, P, LL, P, I, I, P])
     b200_ag_sync = (I, [P, I, I, c_size_t, c_size_t, I, I, I, P, I, I, P, I, P])
     b200_w8a8_gemm_decode_ar = (I, [P, P, P, P, P, P, I, I, I, I, P, I, P, P, P, I, I, c_size_t, c_size_t, P, I, I, c_size_t, c_size_t, c_size_t, P])
+    b200_where_am_i = (I, [P, I, I, P])
     b200_fill_uniform_reduce = (I, [P, c_uint64, c_uint64, c_uint64, P, I, P, P, P])
     b200_w8a8_gemm_decode_grouped = (I, [P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, P])
     b200_w8a8_gemm_grouped = (I, [P, P, P, P, P, I, I, I, I, I, P, P, I, P, I, P])

@@ -26,3 +26,15 @@ class FillReduce:
                                                  self.max_ctas, self.counter.data_ptr(), self.result.data_ptr(), _lib.stream())
         _lib.check(rc, "fill_uniform_reduce")
         return self.result
+
+
+def where_am_i(ctas: int = 296, rank_tag: int = 0, device=None):
+    """Locality tags written by ``ctas`` CTAs: int32 [ctas, 4] = (SM id, number of SM ids, rank tag, CTA index) - the
+    in-kernel counterpart of the host runtime's ``get_current_cpu_and_node`` (reference: numa/numa.mojo:6-24)."""
+    import torch
+    from . import _lib
+    dev = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+    out = torch.full((ctas, 4), -1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().b200_where_am_i(out.data_ptr(), ctas, rank_tag, _lib.stream()), "where_am_i")
+    return out
