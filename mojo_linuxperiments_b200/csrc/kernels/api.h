@@ -57,19 +57,24 @@ int b200_act_quant(const void* x, long long ldx, void* residual, long long ldr, 
                    cudaStream_t stream);
 
 // ---- attention and token-wise glue ---------------------------------------------------------------------
+// max_pos: rows of cos_tab / sin_tab; num_pages: pages of the cache.  A token whose position is outside the tables,
+// outside the max_pages pages of its sequence, or whose page id is not a page of the cache is skipped and
+// ST_BAD_ARGUMENT is recorded in *status (optional) - never a stray write.
 int b200_rope_kv_write(const void* qkv, long long ld_qkv, const int* positions, const int* seq_ids,
                        const float* cos_tab, const float* sin_tab, const void* q_norm_w, const void* k_norm_w,
                        float eps, void* q_out, void* k_out, void* v_out, void* cache, const int* page_table,
-                       int max_pages, int page_size, int hq, int hkv, int M, cudaStream_t stream);
+                       int max_pages, int page_size, int hq, int hkv, int M, int max_pos, int num_pages, int* status,
+                       cudaStream_t stream);
 int b200_embed_gather(const long long* ids, const void* table, void* out, int M, int d, int vocab, cudaStream_t stream);
 int b200_argmax_rows(const void* logits, long long ld, int rows, int n, int index_offset, int chunks, float* out_val,
                      long long* out_idx, cudaStream_t stream);
 int b200_argmax_merge(const float* cand_val, const long long* cand_idx, int world, int rows, long long* out_idx,
                       cudaStream_t stream);
 size_t b200_attn_decode_scratch_floats(int B, int hq, int splits);
+// seq_lens[b] > max_pages * page_size is clamped to that and ST_BAD_ARGUMENT is recorded in *status (optional).
 int b200_attn_decode(const void* q, const void* cache, const int* page_table, const int* seq_lens, void* out,
                      float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size, int max_pages,
-                     int splits, float scale, cudaStream_t stream);
+                     int splits, float scale, int* status, cudaStream_t stream);
 int b200_attn_decode_tma(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
                          void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
                          int max_pages, int splits, float scale, int* status, cudaStream_t stream);

@@ -30,6 +30,7 @@ struct DecodeParams {
   unsigned* counters;                 // [B][hkv], zero between launches
   int hq, hkv, page_size, max_pages, splits;
   float scale_log2;                   // softmax scale * log2(e)
+  int* status;                        // optional: ST_BAD_ARGUMENT when a length exceeds the page table row
 };
 
 __device__ __forceinline__ void bf16x8_to_float(const uint4& raw, float (&f)[8]) {
@@ -54,7 +55,14 @@ __global__ void __launch_bounds__(AD_THREADS) attn_decode_kernel(const DecodePar
 
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int len = p.seq_lens[b];
+  // A length beyond the sequence's page-table row would index the next row (or past the table): attend to what the
+  // row can describe and say so in the status word.
+  int len = p.seq_lens[b];
+  if (len > p.max_pages * p.page_size) {
+    if (tid == 0 && p.status) atomicCAS(p.status, 0, static_cast<int>(ST_BAD_ARGUMENT) | (8 << 8));
+    len = p.max_pages * p.page_size;
+  }
+  if (len < 0) len = 0;
   const int per = ((len + p.splits - 1) / p.splits + 31) & ~31;
   const int t0 = split * per;
   const int t1 = min(len, t0 + per);
@@ -237,9 +245,9 @@ extern "C" size_t b200_attn_decode_scratch_floats(int B, int hq, int splits) {
 
 extern "C" int b200_attn_decode(const void* q, const void* cache, const int* page_table, const int* seq_lens, void* out,
                                 float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size, int max_pages,
-                                int splits, float scale, cudaStream_t stream) {
+                                int splits, float scale, int* status, cudaStream_t stream) {
   if (B <= 0) return 0;
-  if (hq % hkv) return -1;
+  if (hq % hkv || page_size <= 0 || max_pages <= 0) return -1;
   const int G = hq / hkv;
   if (splits < 1) splits = 1;
   if (splits > 1 && (!scratch || !counters)) return -1;
@@ -251,6 +259,7 @@ extern "C" int b200_attn_decode(const void* q, const void* cache, const int* pag
   p.counters = counters;
   p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.max_pages = max_pages; p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
   dim3 grid(hkv, B, splits);
   switch (G) {
     case 1: launch_ex(attn_decode_kernel<1>, dim3(grid), dim3(AD_THREADS), 0, stream, 0, p); break;
@@ -268,6 +277,7 @@ extern "C" int b200_attn_decode(const void* q, const void* cache, const int* pag
 // Allocation-free entry point (declared and documented in attn_decode_noalloc.h).
 // ---------------------------------------------------------------------------------------------------------------
 #include "attn_decode_noalloc.h"
+#include <atomic>
 #include <cstdio>
 
 namespace b200 {
@@ -284,20 +294,22 @@ static __device__ __align__(256) unsigned char g_attn_decode_scratch[ADN_BYTES];
 
 // device address of the array on the current device, looked up once per device
 static int adn_scratch_address(unsigned char** out) {
-  static unsigned char* cached[ADN_MAX_DEVICES] = {nullptr};
+  // Threads that make their first call on a device at the same time each look the address up and store the same
+  // value; the atomic only makes that well defined.
+  static std::atomic<unsigned char*> cached[ADN_MAX_DEVICES];
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess || dev < 0 || dev >= ADN_MAX_DEVICES) return -3000 - static_cast<int>(e);
-  if (!cached[dev]) {
+  if (!cached[dev].load(std::memory_order_acquire)) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_attn_decode_scratch);        // resolves against the device that is current now
     if (e != cudaSuccess || !p) {
       std::fprintf(stderr, "b200_attn_decode_noalloc: cudaGetSymbolAddress failed on device %d: %s\n", dev, cudaGetErrorString(e));
       return -3000 - static_cast<int>(e);
     }
-    cached[dev] = static_cast<unsigned char*>(p);
+    cached[dev].store(static_cast<unsigned char*>(p), std::memory_order_release);
   }
-  *out = cached[dev];
+  *out = cached[dev].load(std::memory_order_acquire);
   return 0;
 }
 
@@ -309,6 +321,11 @@ extern "C" int b200_attn_decode_noalloc(const void* q, const void* cache, const 
   if (B <= 0) return 0;
   if (hq <= 0 || hkv <= 0 || (hq % hkv)) return -1;
   if (splits < 1) splits = 1;
+  // One split per sequence: the kernel touches neither the partials nor the counters, so no limit applies and
+  // nothing has to be cleared.
+  if (splits == 1)
+    return b200_attn_decode(q, cache, page_table, seq_lens, out, nullptr, nullptr, B, hq, hkv, page_size, max_pages, 1, scale,
+                            nullptr, stream);
   const size_t need_floats = b200_attn_decode_scratch_floats(B, hq, splits);
   const size_t need_counters = static_cast<size_t>(B) * hkv;
   if (need_floats > ADN_MAX_FLOATS || need_counters > ADN_MAX_COUNTERS) {
@@ -327,5 +344,5 @@ extern "C" int b200_attn_decode_noalloc(const void* q, const void* cache, const 
   cudaError_t e = cudaMemsetAsync(counters, 0, need_counters * sizeof(unsigned), stream);
   if (e != cudaSuccess) return -2000 - static_cast<int>(e);
   return b200_attn_decode(q, cache, page_table, seq_lens, out, partials, counters, B, hq, hkv, page_size, max_pages, splits,
-                          scale, stream);
+                          scale, nullptr, stream);
 }

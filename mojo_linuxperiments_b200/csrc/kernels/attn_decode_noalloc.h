@@ -9,10 +9,17 @@
 //
 // Contract
 //   * Same arguments and result as b200_attn_decode (attn_decode.cu), minus the scratch and counter pointers.
-//   * Limits: B * hq * splits * 130 floats must fit 1 Mi floats (4 MiB) and B * hkv must not exceed 4096.  A call
-//     beyond either limit is rejected with B200_NOALLOC_TOO_LARGE and a message on stderr; nothing is launched.
-//   * The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that device
-//     current) and caches it; make that first call outside any stream capture.
+//   * Limits (splits > 1 only): B * hq * splits * 130 floats must fit 1 Mi floats (4 MiB) and B * hkv must not
+//     exceed 4096.  A call beyond either limit is rejected with B200_NOALLOC_TOO_LARGE and a message on stderr;
+//     nothing is launched.  With splits == 1 the kernel uses no scratch at all, so any batch is accepted and nothing
+//     is cleared.
+//   * The first call with splits > 1 on each device looks up the array's device address (cudaGetSymbolAddress, with
+//     that device current) and caches it for the life of the process; make that first call outside any stream
+//     capture.  First calls may come from several host threads at once.  The address belongs to the device that is
+//     current at the call: `stream` must be a stream of that device.  A cudaDeviceReset invalidates the cached
+//     address; do not call this function again in a process that reset the device.
+//   * A sequence length beyond max_pages * page_size is treated as max_pages * page_size (the page-table row cannot
+//     describe more); b200_attn_decode reports the same case through its status word.
 //   * Every call on a device uses the same array.  The counters are cleared on the stream at the start of each call;
 //     the partials are fully rewritten before they are read.  Two calls whose kernels can overlap on the GPU (different
 //     streams without an ordering between them) race on the array: serialise them.

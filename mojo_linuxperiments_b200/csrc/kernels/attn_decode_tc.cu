@@ -74,7 +74,12 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
 
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int len = p.seq_lens[b];
+  int len = p.seq_lens[b];
+  if (len > p.max_pages * 16) {            // the page-table row cannot describe more tokens than this
+    if (tid == 0 && p.status) atomicCAS(p.status, 0, (int)ST_BAD_ARGUMENT | (5 << 8));
+    len = p.max_pages * 16;
+  }
+  if (len < 0) len = 0;
   const int total_pages = (len + 15) >> 4;
   const int total_blocks = (len + 127) >> 7;
   const int per = (total_blocks + p.splits - 1) / p.splits;
@@ -334,6 +339,7 @@ struct ItemGeom { int kvh, b, split, len, total_pages, blk0, nb; };
 
 __device__ __forceinline__ ItemGeom item_geom(int w, int len, const DecodeTcParams& p) {
   ItemGeom g;
+  len = max(0, min(len, p.max_pages * 16));      // never index past the sequence's page-table row
   g.split = w % p.splits;
   const int rest = w / p.splits;
   g.kvh = rest % p.hkv;

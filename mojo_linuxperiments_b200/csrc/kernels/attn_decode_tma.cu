@@ -69,7 +69,12 @@ __global__ void __launch_bounds__(ADT_THREADS) attn_decode_tma_kernel(const __gr
 
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int len = p.seq_lens[b];
+  int len = p.seq_lens[b];
+  if (len > p.max_pages * ADT_PS) {         // the page-table row cannot describe more tokens than this
+    if (tid == 0 && p.status) atomicCAS(p.status, 0, (int)ST_BAD_ARGUMENT | (4 << 8));
+    len = p.max_pages * ADT_PS;
+  }
+  if (len < 0) len = 0;
   const int total_pages = (len + ADT_PS - 1) / ADT_PS;
   const int per = (total_pages + p.splits - 1) / p.splits;
   const int pg0 = split * per, pg1 = min(total_pages, pg0 + per);

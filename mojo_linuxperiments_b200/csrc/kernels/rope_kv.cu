@@ -38,6 +38,9 @@ struct RopeParams {
   const int* page_table;         // [num_seqs][max_pages]
   int max_pages, page_size;
   int hq, hkv, M;
+  int max_pos;                   // rows of cos_tab / sin_tab
+  int num_pages;                 // pages of the cache
+  int* status;                   // optional status word: ST_BAD_ARGUMENT when a token is skipped
 };
 
 // grid (tokens, ceil(heads / 4)), 4 warps; a warp handles one head, lane l holds elements l, l+32, l+64, l+96
@@ -49,14 +52,23 @@ __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int pos = p.positions[tok];
   const int seq = p.seq_ids ? p.seq_ids[tok] : tok;
+  // A position beyond the tables or beyond the pages admitted for the sequence must not become a stray write: the
+  // token is skipped (q_out keeps what it held) and the status word says so.
+  bool bad = pos < 0 || pos >= p.max_pos || (p.cache && pos / p.page_size >= p.max_pages);
+  int page = 0;
+  if (!bad && p.cache) {
+    page = p.page_table[static_cast<size_t>(seq) * p.max_pages + pos / p.page_size];
+    bad = page < 0 || page >= p.num_pages;
+  }
+  if (bad) {
+    if (threadIdx.x == 0 && blockIdx.y == 0 && p.status) atomicCAS(p.status, 0, static_cast<int>(ST_BAD_ARGUMENT) | (7 << 8));
+    return;
+  }
   const __nv_bfloat16* row = p.qkv + static_cast<size_t>(tok) * p.ld_qkv;
   const float c0 = p.cos_tab[static_cast<size_t>(pos) * 64 + lane], s0 = p.sin_tab[static_cast<size_t>(pos) * 64 + lane];
   const float c1 = p.cos_tab[static_cast<size_t>(pos) * 64 + lane + 32], s1 = p.sin_tab[static_cast<size_t>(pos) * 64 + lane + 32];
   size_t cache_row = 0;
-  if (p.cache) {
-    const int page = p.page_table[static_cast<size_t>(seq) * p.max_pages + pos / p.page_size];
-    cache_row = static_cast<size_t>(page) * 2 * p.hkv * p.page_size + (pos % p.page_size);
-  }
+  if (p.cache) cache_row = static_cast<size_t>(page) * 2 * p.hkv * p.page_size + (pos % p.page_size);
   const int nheads = p.hq + 2 * p.hkv;
   const int h = blockIdx.y * 4 + warp;
   if (h < nheads) {
@@ -181,10 +193,11 @@ using namespace b200;
 extern "C" int b200_rope_kv_write(const void* qkv, long long ld_qkv, const int* positions, const int* seq_ids,
                                   const float* cos_tab, const float* sin_tab, const void* q_norm_w, const void* k_norm_w,
                                   float eps, void* q_out, void* k_out, void* v_out, void* cache, const int* page_table,
-                                  int max_pages, int page_size, int hq, int hkv, int M, cudaStream_t stream) {
+                                  int max_pages, int page_size, int hq, int hkv, int M, int max_pos, int num_pages,
+                                  int* status, cudaStream_t stream) {
   if (M <= 0) return 0;
-  if (!qkv || !positions || !cos_tab || !sin_tab || !q_out || hq <= 0 || hkv <= 0) return -1;
-  if (cache && (!page_table || page_size <= 0 || max_pages <= 0)) return -1;
+  if (!qkv || !positions || !cos_tab || !sin_tab || !q_out || hq <= 0 || hkv <= 0 || max_pos <= 0) return -1;
+  if (cache && (!page_table || page_size <= 0 || max_pages <= 0 || num_pages <= 0)) return -1;
   RopeParams p;
   p.qkv = static_cast<const __nv_bfloat16*>(qkv); p.ld_qkv = ld_qkv; p.positions = positions; p.seq_ids = seq_ids;
   p.cos_tab = cos_tab; p.sin_tab = sin_tab;
@@ -192,7 +205,7 @@ extern "C" int b200_rope_kv_write(const void* qkv, long long ld_qkv, const int* 
   p.eps = eps; p.q_out = static_cast<__nv_bfloat16*>(q_out); p.k_out = static_cast<__nv_bfloat16*>(k_out);
   p.v_out = static_cast<__nv_bfloat16*>(v_out);
   p.cache = static_cast<__nv_bfloat16*>(cache); p.page_table = page_table; p.max_pages = max_pages; p.page_size = page_size;
-  p.hq = hq; p.hkv = hkv; p.M = M;
+  p.hq = hq; p.hkv = hkv; p.M = M; p.max_pos = max_pos; p.num_pages = num_pages; p.status = status;
   launch_ex(rope_kv_kernel, dim3(dim3(M, (hq + 2 * hkv + 3) / 4)), dim3(128), 0, stream, 0, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);

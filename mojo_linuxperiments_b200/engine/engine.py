@@ -41,6 +41,8 @@ class Engine:
         self.positions = None
         self.kernels_per_step = 0
         self._stream = torch.cuda.Stream(device=self.device)
+        self._admitted = 0          # tokens per sequence the KV pages of the running batch can hold
+        self._host_len = 0          # tokens per sequence already in the cache (host-side mirror of ``positions``)
 
     # ------------------------------------------------------------------------------------------------------
     def start_batch(self, batch: int, max_total_len: int) -> None:
@@ -62,6 +64,8 @@ class Engine:
         for s in range(batch):
             self.kv.admit(s, max_total_len)
         self.batch = batch
+        self._admitted = max_total_len
+        self._host_len = 0
 
     def prefill(self, prompts: torch.Tensor, use_graph: bool = True) -> torch.Tensor:
         """prompts int64 [B, S] (host or device; equal lengths).  Returns the first generated token per sequence
@@ -100,6 +104,7 @@ class Engine:
             entry[0].replay()
         self.positions.fill_(S)
         self.kv.seq_lens.fill_(S + 1)      # the next decode step attends to the prompt plus its own token
+        self._host_len = S
         return self.tokens.clone()
 
     def _prefill_consts(self, b0: int, b1: int, S: int):
@@ -123,7 +128,14 @@ class Engine:
         self.kv.seq_lens.add_(1)
 
     def decode_step(self, use_graph: bool = True) -> torch.Tensor:
-        """One greedy token for every sequence of the batch; returns the device tensor of new ids [B]."""
+        """One greedy token for every sequence of the batch; returns the device tensor of new ids [B].
+
+        Raises before anything is launched when the step would write past the KV pages admitted in ``start_batch``:
+        the kernels would refuse the write as well (status word), but the host knows first."""
+        if self._host_len + 1 > self._admitted:
+            raise RuntimeError(f"decode step at position {self._host_len} exceeds the {self._admitted} tokens per "
+                               f"sequence admitted by start_batch")
+        self._host_len += 1
         if not use_graph:
             self._decode_body()
             return self.tokens

@@ -68,12 +68,12 @@ class _Sig:
     b200_moe_gather = (I, [P, P, I, P, P, I, P, P, P])
     b200_moe_combine = (I, [P, LL, P, P, I, I, I, P, LL, P])
     b200_act_quant = (I, [P, LL, P, LL, P, F, P, LL, P, P, LL, I, I, I, P])
-    b200_rope_kv_write = (I, [P, LL, P, P, P, P, P, P, F, P, P, P, P, P, I, I, I, I, I, P])
+    b200_rope_kv_write = (I, [P, LL, P, P, P, P, P, P, F, P, P, P, P, P, I, I, I, I, I, I, I, P, P])
     b200_embed_gather = (I, [P, P, P, I, I, I, P])
     b200_argmax_rows = (I, [P, LL, I, I, I, I, P, P, P])
     b200_argmax_merge = (I, [P, P, I, I, P, P])
     b200_attn_decode_scratch_floats = (c_size_t, [I, I, I])
-    b200_attn_decode = (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P])
+    b200_attn_decode = (I, [P, P, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
     b200_attn_decode_noalloc = (I, [P, P, P, P, P, I, I, I, I, I, I, F, P])
     b200_attn_decode_tma = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
     b200_attn_decode_tc = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, P])

@@ -43,7 +43,8 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor,
         _lib.ptr(q_norm_w), _lib.ptr(k_norm_w), float(eps), q_out.data_ptr(), _lib.ptr(k_out), _lib.ptr(v_out),
         cache.data.data_ptr() if cache is not None else None, _lib.ptr(page_table),
         page_table.shape[1] if page_table is not None else 0, cache.page_size if cache is not None else 0,
-        hq, hkv, M, _lib.stream())
+        hq, hkv, M, cos.shape[0], cache.num_pages if cache is not None else 0,
+        default_workspace(qkv.device).status.data_ptr(), _lib.stream())
     _lib.check(rc, "rope_kv_write")
     return q_out
 
@@ -185,7 +186,8 @@ def attn_decode(q: torch.Tensor, cache: PagedKVCache, page_table: torch.Tensor, 
         scratch.buf.data_ptr() if scratch is not None else None,
         scratch.counters.data_ptr() if scratch is not None else None,
         B, hq, cache.kv_heads, cache.page_size, page_table.shape[1], splits,
-        float(scale if scale is not None else 1.0 / math.sqrt(d)), _lib.stream())
+        float(scale if scale is not None else 1.0 / math.sqrt(d)), default_workspace(q.device).status.data_ptr(),
+        _lib.stream())
     _lib.check(rc, "attn_decode")
     return out
 

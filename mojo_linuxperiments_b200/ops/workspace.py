@@ -30,7 +30,8 @@ class Workspace:
         code = int(self.status[0].item())
         if code != 0:
             self.status.zero_()
-            kernel = {0: "?", 1: "w8a8_gemm", 2: "w8a8_gemm_decode", 3: "attn_prefill", 4: "attn_decode_tma"}.get(code >> 8, "?")
+            kernel = {0: "?", 1: "w8a8_gemm", 2: "w8a8_gemm_decode", 3: "attn_prefill", 4: "attn_decode_tma", 5: "attn_decode_tc",
+                      6: "attn_decode_tcp", 7: "rope_kv_write", 8: "attn_decode"}.get(code >> 8, "?")
             raise RuntimeError(f"kernel status {code & 255} in {kernel}: {_STATUS_NAMES.get(code & 255, 'unknown')}")
 
 

@@ -156,3 +156,50 @@ def test_embed_and_argmax():
     cv3 = torch.stack([val, val + 1.0, val - 1.0])
     ci3 = torch.stack([idx, idx + 5, idx + 9])
     assert torch.equal(A.argmax_merge(cv3, ci3), idx + 5)
+
+
+def test_rope_kv_write_skips_positions_outside_the_admitted_pages():
+    """One token past the pages of its sequence (and one past the rotary tables) must be refused with a status code,
+    not written to whatever page id lies behind the row of the page table."""
+    from mojo_linuxperiments_b200.ops import attention as A
+    from mojo_linuxperiments_b200.ops.workspace import default_workspace
+    hq, hkv, ps, B = 4, 1, 16, 3
+    max_pages = 2                                          # 32 tokens per sequence
+    page_table = torch.arange(B * max_pages, dtype=torch.int32).view(B, max_pages).cuda()
+    cache = A.PagedKVCache(B * max_pages, hkv, ps, "cuda")
+    cos, sin = A.rope_tables(64, 10000.0, "cuda")
+    qkv = _rand((B, (hq + 2 * hkv) * D), 7)
+    ws = default_workspace(qkv.device)
+    ws.status.zero_()
+    # sequence 0 in range, sequence 1 one token past its pages, sequence 2 past the tables
+    pos = torch.tensor([31, 32, 64], dtype=torch.int32).cuda()
+    q_out = torch.full((B, hq, D), 7.0, dtype=torch.bfloat16, device="cuda")
+    A.rope_kv_write(qkv, pos, cos, sin, hq, hkv, q_out=q_out, cache=cache, page_table=page_table)
+    torch.cuda.synchronize()
+    code = int(ws.status[0].item())
+    assert code & 255 == 6 and code >> 8 == 7, code          # bad argument, reported by rope_kv_write
+    ws.status.zero_()
+    assert cache.data[1, :, :, 15].abs().sum().item() > 0    # sequence 0 wrote token 31 (page 1, slot 15)
+    assert cache.data[2:].abs().sum().item() == 0             # nothing else was touched
+    assert torch.all(q_out[1:] == 7.0) and not torch.all(q_out[0] == 7.0)
+
+
+@pytest.mark.parametrize("impl", ["simple", "tma", "tc"])
+def test_attn_decode_clamps_lengths_beyond_the_page_table_row(impl):
+    from mojo_linuxperiments_b200.ops import attention as A
+    from mojo_linuxperiments_b200.ops.workspace import default_workspace
+    hq, hkv, ps, B = 4, 1, 16, 2
+    max_pages = 8                                          # 128 tokens per sequence
+    page_table = torch.arange(B * max_pages, dtype=torch.int32).view(B, max_pages).cuda()
+    cache = A.PagedKVCache(B * max_pages, hkv, ps, "cuda")
+    cache.data.copy_(_rand(tuple(cache.data.shape), 8))
+    q = _rand((B, hq, D), 9)
+    ws = default_workspace(q.device)
+    ws.status.zero_()
+    ok = A.attn_decode(q, cache, page_table, torch.tensor([128, 128], dtype=torch.int32).cuda(), impl=impl)
+    over = A.attn_decode(q, cache, page_table, torch.tensor([128, 129], dtype=torch.int32).cuda(), impl=impl)
+    torch.cuda.synchronize()
+    code = int(ws.status[0].item())
+    ws.status.zero_()
+    assert code & 255 == 6, code
+    assert torch.equal(ok, over)                             # the over-long sequence was read as its 128 admitted tokens

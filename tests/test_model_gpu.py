@@ -62,3 +62,20 @@ def test_graph_and_eager_decode_agree():
     a = eng.generate(prompts, 10, use_graph=True)
     b = eng.generate(prompts, 10, use_graph=False)
     assert torch.equal(a, b)
+
+
+def test_decode_past_the_admitted_length_is_refused_on_the_host():
+    from mojo_linuxperiments_b200.engine.engine import Engine
+    cfg = C.tiny_dense()
+    rt = C.RuntimeConfig(max_seq_len=128)
+    ck, _ = _setup(cfg, 4)
+    eng = Engine(cfg, rt, weights=Wt.shard_from_checkpoint(cfg, ck, 1, 0, "cuda"))
+    prompts = torch.randint(0, cfg.vocab, (2, 20), generator=torch.Generator().manual_seed(5))
+    eng.start_batch(2, 22)
+    eng.prefill(prompts)
+    eng.decode_step()
+    eng.decode_step()                # positions 20 and 21 fit the 22 admitted tokens
+    with pytest.raises(RuntimeError, match="admitted"):
+        eng.decode_step()
+    torch.cuda.synchronize()
+    eng.check_status()               # and nothing on the device went out of range either

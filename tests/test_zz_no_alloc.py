@@ -54,6 +54,21 @@ def test_noalloc_entry_point_matches_regular_one_twice_in_a_row():
         assert torch.allclose(out.float(), ref.float(), rtol=2e-2, atol=2e-2), (out.float() - ref.float()).abs().max().item()
 
 
+def test_noalloc_entry_point_takes_any_batch_when_nothing_is_split():
+    """With one split the kernel needs neither partials nor counters, so the built-in array's limits do not apply:
+    B * hkv = 5,000 (sequence, head) pairs is beyond the 4,096 counters and must still be served."""
+    from mojo_linuxperiments_b200.ops import _lib
+    from mojo_linuxperiments_b200.ops import attention as A
+    lib = _lib.lib()
+    B, hq, hkv = 2500, 4, 2
+    lens = [1 + (i * 7) % 48 for i in range(B)]
+    cache, page_table, seq_lens, q = _setup(B, hq, hkv, lens, 4)
+    ref = A.attn_decode(q, cache, page_table, seq_lens, splits=1, impl="simple")
+    rc, out = _noalloc(lib, q, cache, page_table, seq_lens, 1)
+    assert rc == 0
+    assert torch.allclose(out.float(), ref.float(), rtol=2e-2, atol=2e-2)
+
+
 def test_noalloc_entry_point_rejects_requests_beyond_its_scratch(capfd):
     from mojo_linuxperiments_b200.ops import _lib
     lib = _lib.lib()
