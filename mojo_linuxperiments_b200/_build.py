@@ -29,8 +29,18 @@ NO_FAST_MATH = {"act_quant.cu"}
 GXX_FLAGS = ["-O2", "-std=c++20", "-fPIC", "-Wall", "-Wextra", "-fno-stack-protector", "-pthread"]
 
 KERNEL_LIB = "libb200_kernels.so"
+# Variants of the kernel library: same sources, one extra define each.  "trace": in-kernel %globaltimer stamps
+# (csrc/kernels/trace.cuh); "debug": range checks on peer / scratch accesses that record the bad offset in the status
+# word and skip the access (csrc/kernels/debug_check.h).  The production library has neither.
+KERNEL_VARIANTS = {"": [], "trace": ["-DB200RT_TRACE"], "debug": ["-DB200RT_DEBUG"]}
+
+
 HOSTRT_LIB = "libb200_hostrt.so"
 DEVRT_LIB = "libb200_devrt.so"
+
+
+def kernel_lib_name(variant: str = "") -> str:
+    return KERNEL_LIB if not variant else KERNEL_LIB.replace(".so", f"_{variant}.so")
 
 
 def _nvcc() -> str:
@@ -67,24 +77,26 @@ def _stale(stamp: Path, digest: str, product: Path) -> bool:
         return True
 
 
-def build_kernels(verbose: bool = False) -> Path:
-    """Compile every .cu under csrc/kernels for sm_100a and link libb200_kernels.so."""
+def build_kernels(verbose: bool = False, variant: str = "") -> Path:
+    """Compile every .cu under csrc/kernels for sm_100a and link libb200_kernels[_variant].so."""
     srcdir = CSRC / "kernels"
     sources = sorted(srcdir.glob("*.cu"))
     headers = sorted(list(srcdir.glob("*.cuh")) + list(srcdir.glob("*.h")) + list((CSRC / "fabric").glob("*.h")))
     LIBDIR.mkdir(parents=True, exist_ok=True)
-    OBJDIR.mkdir(parents=True, exist_ok=True)
+    objdir = OBJDIR / variant if variant else OBJDIR
+    objdir.mkdir(parents=True, exist_ok=True)
     nvcc = _nvcc()
-    hdigest = _digest(headers, " ".join(NVCC_FLAGS))
+    vflags = NVCC_FLAGS + KERNEL_VARIANTS[variant]
+    hdigest = _digest(headers, " ".join(vflags))
 
     def compile_one(src: Path) -> Path:
-        obj = OBJDIR / (src.stem + ".o")
-        stamp = OBJDIR / (src.stem + ".stamp")
+        obj = objdir / (src.stem + ".o")
+        stamp = objdir / (src.stem + ".stamp")
         digest = _digest([src], hdigest)
         if _stale(stamp, digest, obj):
-            flags = [f for f in NVCC_FLAGS if not (f == "--use_fast_math" and src.name in NO_FAST_MATH)]
+            flags = [f for f in vflags if not (f == "--use_fast_math" and src.name in NO_FAST_MATH)]
             out = _run([nvcc, *flags, "-I", str(srcdir), "-I", str(CSRC), "-c", str(src), "-o", str(obj)],
-                       OBJDIR / (src.stem + ".log"))
+                       objdir / (src.stem + ".log"))
             if verbose:
                 print(out, file=sys.stderr)
             stamp.write_text(json.dumps({"digest": digest}))
@@ -92,9 +104,9 @@ def build_kernels(verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, max(1, len(sources)))) as ex:
         objs = list(ex.map(compile_one, sources))
-    lib = LIBDIR / KERNEL_LIB
+    lib = LIBDIR / kernel_lib_name(variant)
     link_digest = _digest(objs, "link")
-    stamp = OBJDIR / "kernels.link.stamp"
+    stamp = objdir / "kernels.link.stamp"
     if _stale(stamp, link_digest, lib):
         _run([nvcc, "-shared", "-o", str(lib), *map(str, objs), "-cudart", "static"])
         stamp.write_text(json.dumps({"digest": link_digest}))
@@ -146,17 +158,20 @@ def build_devrt() -> Path:
     return _build_cpp(DEVRT_LIB, "devrt", extra_flags=("-I", str(cuda_inc)), libs=("-ldl",))
 
 
-def build_all(verbose: bool = False) -> dict:
+def build_all(verbose: bool = False, variants=("",)) -> dict:
+    """Host runtime, device runtime and the kernel library; ``variants`` adds "trace" / "debug" kernel libraries."""
     out = {}
     if any((CSRC / "hostrt").glob("*.cpp")):
         out["hostrt"] = build_hostrt()
         out["hostrt_selftest"] = build_hostrt_selftest()
     if any((CSRC / "devrt").glob("*.cpp")):
         out["devrt"] = build_devrt()
-    out["kernels"] = build_kernels(verbose)
+    for v in variants:
+        out["kernels" + ("_" + v if v else "")] = build_kernels(verbose, v)
     return out
 
 
 if __name__ == "__main__":
-    for k, v in build_all(verbose="-v" in sys.argv).items():
+    want = [""] + [v for v in ("trace", "debug") if ("--" + v) in sys.argv or "--all" in sys.argv]
+    for k, v in build_all(verbose="-v" in sys.argv, variants=want).items():
         print(f"{k}: {v}")

@@ -2,7 +2,8 @@
 
 namespace hostrt {
 
-void* mmap_numa(size_t size, int node, long page_size_mode, long pr) {
+void* mmap_numa(size_t size, int node, long page_size_mode, long pr, size_t* mapped_len) {
+  if (mapped_len) *mapped_len = 0;
   if (size == 0) return nullptr;
   long flags = map_flag::PRIVATE | map_flag::ANONYMOUS | map_flag::NORESERVE;
   size_t len = size;
@@ -19,20 +20,23 @@ void* mmap_numa(size_t size, int node, long page_size_mode, long pr) {
     mask[node >> 6] = 1ull << (node & 63);
     if (sys_mbind(p, len, mempolicy::BIND, mask, 1025) < 0) { sys_munmap(p, len); return nullptr; }
   }
+  if (mapped_len) *mapped_len = len;
   return p;
 }
 
 NumaArena::NumaArena(int node, size_t size, size_t alignment, long page_size_mode)
     : alignment_(alignment ? alignment : 1), node_(node) {
-  base_ = mmap_numa(size, node, page_size_mode);
+  base_ = mmap_numa(size, node, page_size_mode, prot::RW, &mapped_);
   size_ = base_ ? size : 0;
 }
 NumaArena::NumaArena(NumaArena&& o) noexcept
-    : base_(o.base_), size_(o.size_), offset_(o.offset_), alignment_(o.alignment_), node_(o.node_) {
-  o.base_ = nullptr; o.size_ = 0; o.offset_ = 0;
+    : base_(o.base_), size_(o.size_), offset_(o.offset_), alignment_(o.alignment_), mapped_(o.mapped_), node_(o.node_) {
+  o.base_ = nullptr; o.size_ = 0; o.offset_ = 0; o.mapped_ = 0;
 }
 NumaArena::~NumaArena() {
-  if (base_) sys_munmap(base_, align_up(size_, static_cast<size_t>(page_size::STANDARD)));
+  // exactly the length that was mapped: a hugetlb mapping was rounded up to its page size and munmap of any other
+  // length fails with EINVAL, which would leak the reserved huge pages
+  if (base_) sys_munmap(base_, mapped_);
 }
 void* NumaArena::alloc_bytes(size_t bytes) {
   if (!base_) return nullptr;

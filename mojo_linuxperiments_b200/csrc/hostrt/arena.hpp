@@ -11,7 +11,10 @@
 namespace hostrt {
 
 // mmap + (madvise | MAP_HUGETLB) + mbind.  node < 0 skips the binding.  Returns nullptr on any failure.
-void* mmap_numa(size_t size, int node, long page_size_mode = page_size::THP_2MB, long pr = prot::RW);
+// mapped_len (optional) receives the length actually mapped (size rounded up to the page size of the mode): the
+// length munmap wants back.
+void* mmap_numa(size_t size, int node, long page_size_mode = page_size::THP_2MB, long pr = prot::RW,
+                size_t* mapped_len = nullptr);
 
 class NumaArena {
  public:
@@ -32,6 +35,8 @@ class NumaArena {
   size_t remaining() const { return size_ - offset_; }
   size_t used() const { return offset_; }
   size_t size() const { return size_; }
+  size_t mapped_bytes() const { return mapped_; }
+  void forget() { base_ = nullptr; size_ = 0; offset_ = 0; mapped_ = 0; }      // the caller unmapped the range itself
   int node() const { return node_; }
   void* base() const { return base_; }
   // True when nothing was allocated yet, or when the first page (if faulted in) lives on node().
@@ -40,6 +45,7 @@ class NumaArena {
  private:
   void* base_ = nullptr;
   size_t size_ = 0, offset_ = 0, alignment_ = 8;
+  size_t mapped_ = 0;            // bytes the kernel mapped for this arena (>= size_)
   int node_ = -1;
 };
 

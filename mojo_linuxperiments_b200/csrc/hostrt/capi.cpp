@@ -107,6 +107,15 @@ void* hostrt_arena_create(int node, unsigned long size, unsigned long alignment,
 }
 void hostrt_arena_destroy(void* a) { delete static_cast<NumaArena*>(a); }
 int hostrt_arena_valid(void* a) { return *static_cast<NumaArena*>(a) ? 1 : 0; }
+unsigned long hostrt_arena_mapped_bytes(void* a) { return static_cast<NumaArena*>(a)->mapped_bytes(); }
+// destroys the arena and reports what its munmap returned (0, or -errno): only tests need the value
+long hostrt_arena_unmap_status(void* a) {
+  auto* ar = static_cast<NumaArena*>(a);
+  const long r = ar->base() ? sys_munmap(ar->base(), ar->mapped_bytes()) : 0;
+  ar->forget();
+  delete ar;
+  return r;
+}
 void* hostrt_arena_alloc(void* a, unsigned long bytes) { return static_cast<NumaArena*>(a)->alloc_bytes(bytes); }
 unsigned long hostrt_arena_mark(void* a) { return static_cast<NumaArena*>(a)->mark(); }
 void hostrt_arena_reset_to(void* a, unsigned long w) { static_cast<NumaArena*>(a)->reset_to(w); }
@@ -178,6 +187,23 @@ void* hostrt_team_create(void* numa, int max_workers_per_node) {
   return t;
 }
 void hostrt_team_destroy(void* team) { delete static_cast<WorkerTeam*>(team); }
+int hostrt_team_valid(void* team) { return static_cast<bool>(*static_cast<WorkerTeam*>(team)) ? 1 : 0; }
+int hostrt_team_stragglers(void* team) { return static_cast<WorkerTeam*>(team)->stragglers() ? 1 : 0; }
+int hostrt_team_node_of(void* team, int worker) { return static_cast<WorkerTeam*>(team)->node_of(worker); }
+// Test hook for the timeout path: every worker sleeps sleep_ms inside the job, the caller waits timeout_ms at most.
+// The job's argument block lives on the heap and is intentionally kept alive until the team is destroyed.
+long hostrt_team_run_sleep(void* team, long sleep_ms, long timeout_ms) {
+  auto* t = static_cast<WorkerTeam*>(team);
+  static std::vector<uint64_t>* keep = new std::vector<uint64_t>();
+  keep->assign(static_cast<size_t>(t->size()), static_cast<uint64_t>(sleep_ms));
+  return t->run(
+      +[](uint64_t ms, uint64_t, uint64_t, uint64_t, uint64_t, uint64_t) {
+        const long end = sys_clock_monotonic_ns() + static_cast<long>(ms) * 1'000'000l;
+        uint32_t word = 0;
+        while (sys_clock_monotonic_ns() < end) sys_futex_wait(&word, 0, futex2::SIZE_U32 | futex2::PRIVATE, 1'000'000l);
+      },
+      keep->data(), timeout_ms * 1'000'000l);
+}
 int hostrt_team_size(void* team) { return static_cast<WorkerTeam*>(team)->size(); }
 unsigned long long hostrt_team_jobs_run(void* team) { return static_cast<WorkerTeam*>(team)->jobs_run(); }
 long hostrt_w8a8_linear_team(void* team, const void* x_bf16, int M, int K, const void* wq, const float* sw, int N, void* y_bf16,

@@ -106,7 +106,12 @@ int NumaInfo::distance(int from_id, int to_id) const {
   if (!f || ti < 0 || ti >= static_cast<int>(f->distances.size())) return -1;
   return f->distances[ti];
 }
-int NumaInfo::cpus_per_node() const { return nodes_.empty() ? 0 : static_cast<int>(nodes_[0].cpu_ids.size()); }
+int NumaInfo::cpus_per_node() const {
+  // the first node that has CPUs: a memory-only node (no cpulist) in front must not report 0 for the machine
+  for (const auto& n : nodes_)
+    if (!n.cpu_ids.empty()) return static_cast<int>(n.cpu_ids.size());
+  return 0;
+}
 int NumaInfo::cpus_on_node(int id) const { return static_cast<int>(get_node_cpus(id).size()); }
 int NumaInfo::total_cpus() const {
   int t = 0;

@@ -48,15 +48,19 @@ WorkerTeam::WorkerTeam(const NumaInfo& info, int max_workers_per_node) : pools_(
   slots_ = std::vector<TeamSlot>(total);
   int w = 0;
   for (int k = 0; k < nn; ++k) {
+    // A node that is online but has no CPUs (memory-only: CXL or device memory) gets no pool and no workers; the
+    // pools of the other nodes are indexed by their own running count, not by the node's position.
+    if (per_node[k] == 0) continue;
     const int node = info.nodes()[k].id;
     auto m = info.get_node_mask<128>(node);
+    const size_t pi = pools_.size();
     pools_.emplace(per_node[k], m.ptr(), size_t(128), node, stack_size::DEFAULT);
-    if (!pools_[k]) return;
+    if (!pools_[pi]) return;
     for (int i = 0; i < per_node[k]; ++i, ++w) {
       TeamSlot& s = slots_[w];
       s.go.store(0); s.done.store(0); s.fn = nullptr; s.arg = 0; s.quit = 0; s.node = node;
       s.cpu = i < static_cast<int>(info.nodes()[k].cpu_ids.size()) ? info.nodes()[k].cpu_ids[i] : -1;
-      if (pools_[k].launch(&team_loop, reinterpret_cast<uint64_t>(&s)) < 0) return;
+      if (pools_[pi].launch(&team_loop, reinterpret_cast<uint64_t>(&s)) < 0) return;
     }
   }
   valid_ = true;
@@ -88,7 +92,22 @@ long WorkerTeam::run(WorkerFn fn, const uint64_t* args, long timeout_ns) {
     for (int i = 0; i < 2000 && s.done.load(std::memory_order_acquire) != epoch_; ++i) asm volatile("pause");
     while (s.done.load(std::memory_order_acquire) != epoch_) {
       const long left = deadline - sys_clock_monotonic_ns();
-      if (left <= 0) return -err::kTIMEDOUT;
+      if (left <= 0) {
+        // Stragglers may still be running the job and reading its arguments, which usually live on the caller's
+        // stack.  Give them a second bounded grace period; whatever happens the team is dead afterwards (later run()
+        // calls fail fast) so that fn / arg are never rewritten under a worker that is still reading them.
+        valid_ = false;
+        const long grace_end = sys_clock_monotonic_ns() + kTimeoutGraceNs;
+        bool all_done = false;
+        while (!all_done && sys_clock_monotonic_ns() < grace_end) {
+          all_done = true;
+          for (auto& t : slots_)
+            if (t.done.load(std::memory_order_acquire) != epoch_) { all_done = false; break; }
+          if (!all_done) sys_futex_wait(&s.done, s.done.load(std::memory_order_acquire), kFutex, 10'000'000l);
+        }
+        stragglers_ = !all_done;
+        return -err::kTIMEDOUT;
+      }
       sys_futex_wait(&s.done, s.done.load(std::memory_order_acquire), kFutex, left < 100'000'000l ? left : 100'000'000l);
     }
   }

@@ -33,8 +33,14 @@ class WorkerTeam {
   explicit operator bool() const { return valid_; }
   int size() const { return static_cast<int>(slots_.size()); }
   int node_of(int worker) const { return slots_[worker].node; }
-  // fn(args[i]) on worker i for every i < size(); 0, or -ETIMEDOUT if a worker did not finish in time
+  // fn(args[i]) on worker i for every i < size(); 0, or -ETIMEDOUT if a worker did not finish in time.
+  // After a timeout the team is invalid (every later run() returns -EINVAL).  run() then waits up to
+  // kTimeoutGraceNs more for the stragglers before it returns; if `stragglers()` is still true afterwards, workers
+  // may still be using `args` and what it points to: that storage has to outlive the team (or the process has to
+  // end, as ThreadPool::~ThreadPool does for live threads).
+  static constexpr long kTimeoutGraceNs = 2'000'000'000l;
   long run(WorkerFn fn, const uint64_t* args, long timeout_ns = 120'000'000'000l);
+  bool stragglers() const { return stragglers_; }
   uint64_t jobs_run() const { return epoch_; }
 
  private:
@@ -42,6 +48,7 @@ class WorkerTeam {
   HeapMoveArray<ThreadPool> pools_;
   uint32_t epoch_ = 0;
   bool valid_ = false;
+  bool stragglers_ = false;
 };
 
 }  // namespace hostrt

@@ -69,7 +69,9 @@ act_quant_kernel(const __nv_bfloat16* x, long long ldx, __nv_bfloat16* residual,
                  long long ldq, float* scale, __nv_bfloat16* xn_out, long long ldn,
                  int K) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
+  if (threadIdx.x == 0) B200_TRACE(TK_ACT_QUANT, TP_START);
   pdl_wait();                // everything before this kernel in the stream has completed
+  if (threadIdx.x == 0) B200_TRACE(TK_ACT_QUANT, TP_DEPS);
 
   __shared__ float red[AQ_WARPS];
   __shared__ float bcast;
@@ -179,6 +181,7 @@ act_quant_kernel(const __nv_bfloat16* x, long long ldx, __nv_bfloat16* residual,
       for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
     }
   }
+  if (threadIdx.x == 0) B200_TRACE(TK_ACT_QUANT, 2);
   amax = warp_max(amax);
   if (lane == 0) red[warp] = amax;
   __syncthreads();
@@ -208,6 +211,7 @@ act_quant_kernel(const __nv_bfloat16* x, long long ldx, __nv_bfloat16* residual,
       *reinterpret_cast<uint32_t*>(qr + b * 128 + lane * 4) = packed;
     }
   }
+  if (threadIdx.x == 0) B200_TRACE(TK_ACT_QUANT, TP_EXIT);
 }
 
 template <int MAXB>

@@ -99,6 +99,10 @@ int b200_attn_prefill_split(const void* q, long long ld_q, const void* k, long l
                             void* out, const int* cu_seqlens, int B, int total_tokens, int max_len, int hq, int hkv,
                             float scale, int chunk, float* scratch, int* status, cudaStream_t stream);
 
+// ---- in-kernel time stamps (trace.cuh; only in the library variant built with -DB200RT_TRACE) -----------------------
+int b200_trace_compiled(void);
+int b200_trace_set(void* ring, unsigned capacity);
+
 // ---- locality query: every CTA writes {sm id, number of sm ids, rank_tag, cta index} (int32 [ctas][4]) -------------
 int b200_where_am_i(int* out, int ctas, int rank_tag, cudaStream_t stream);
 

@@ -52,7 +52,9 @@ template <int G>
 __global__ void __launch_bounds__(ADC_THREADS, 2)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeTcParams p) {
   pdl_launch_dependents();
+  if (threadIdx.x == 0) B200_TRACE(TK_ATTN_DECODE, TP_START);
   pdl_wait();
+  if (threadIdx.x == 0) B200_TRACE(TK_ATTN_DECODE, TP_DEPS);
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -208,6 +210,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
         for (int g = 0; g < G; ++g) s[blk][g] = -INFINITY;
       }
     }
+    if (tid == 64) B200_TRACE(TK_ATTN_DECODE, 2);           // all scores of this CTA are in registers
     // ---- maximum per head over the CTA's tokens: warp shuffle, then the four warps through shared memory ----
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -220,6 +223,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
       mbar_arrive(bar(B_XCH));
     }
     if (ok && !mbar_wait(bar(B_XCH), 0, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (5 << 8)), limit)) ok = false;
+    if (tid == 64) B200_TRACE(TK_ATTN_DECODE, 3);
     float m[G], sum[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -274,6 +278,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
         for (int g = 0; g < G; ++g) o[g] = __uint_as_float(v[g]);
       }
     }
+    if (tid == 64) B200_TRACE(TK_ATTN_DECODE, 5);           // P.V accumulator read back
     if (nb == 0) {
 #pragma unroll
       for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; }
@@ -293,6 +298,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   tc_fence_before();
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, ADC_TMEM_COLS); }
+  if (tid == 0) B200_TRACE(TK_ATTN_DECODE, 6);
   if (p.splits == 1) return;
 
   // ---- the last CTA of this (sequence, kv head) merges the splits ----
@@ -306,6 +312,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   }
   __syncthreads();
   if (!*last_flag) return;
+  if (tid == 0) B200_TRACE(TK_ATTN_DECODE, 7);
   __threadfence();
   for (int i = tid; i < G * ADC_D; i += ADC_THREADS) {
     const int g = i / ADC_D, d = i % ADC_D;
@@ -321,6 +328,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
     }
     p.out[(static_cast<size_t>(b) * p.hq + kvh * G + g) * ADC_D + d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
   }
+  if (tid == 0) B200_TRACE(TK_ATTN_DECODE, TP_EXIT);
 }
 
 // ------------------------------------------------------------------------------------------------------------------

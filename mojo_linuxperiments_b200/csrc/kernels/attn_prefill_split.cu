@@ -273,31 +273,38 @@ attn_prefill_split_kernel(const __grid_constant__ CUtensorMap tmap_q, const __gr
 }
 
 
-// one CTA per (query tile, head, sequence) that was split; thread <-> output dim, rows walked in order
-__global__ void __launch_bounds__(128) attn_prefill_merge_kernel(const PrefillSplitParams p) {
+// Merge of the chunks of a split query tile: grid (16 * query tiles, heads, sequences), 8 warps; a warp owns one query
+// row (lane <-> four output dims), so the 128 rows of a tile are merged by 16 CTAs of 8 independent warps.
+__global__ void __launch_bounds__(256) attn_prefill_merge_kernel(const PrefillSplitParams p) {
   pdl_launch_dependents();
   pdl_wait();
-  const int qt = blockIdx.x, head = blockIdx.y, b = blockIdx.z;
+  const int qt = blockIdx.x >> 4, head = blockIdx.y, b = blockIdx.z;
   const int nchunks = (qt + p.chunk) / p.chunk;
   if (nchunks <= 1) return;
   const int seq0 = p.cu_seqlens[b];
   const int len = p.cu_seqlens[b + 1] - seq0;
-  const int d = threadIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = (blockIdx.x & 15) * 8 + warp;
+  const int q_idx = qt * AP_BM + r;
+  if (q_idx >= len) return;
   const size_t slot0 = ((static_cast<size_t>(b) * p.hq + head) * p.n_q + qt) * p.max_chunks;
-  for (int r = 0; r < AP_BM; ++r) {
-    const int q_idx = qt * AP_BM + r;
-    if (q_idx >= len) break;
-    float m = -INFINITY;
-    for (int c = 0; c < nchunks; ++c) m = fmaxf(m, p.part_ml[((slot0 + c) * AP_BM + r) * 2]);
-    float l = 0.f, o = 0.f;
-    for (int c = 0; c < nchunks; ++c) {
-      const float mc = p.part_ml[((slot0 + c) * AP_BM + r) * 2];
-      const float w = (mc == -INFINITY) ? 0.f : exp2f(mc - m);
-      l += w * p.part_ml[((slot0 + c) * AP_BM + r) * 2 + 1];
-      o += w * p.part_o[((slot0 + c) * AP_BM + r) * AP_D + d];
-    }
-    p.out[(static_cast<size_t>(seq0 + q_idx) * p.hq + head) * AP_D + d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
+  float m = -INFINITY;
+  for (int c = 0; c < nchunks; ++c) m = fmaxf(m, p.part_ml[((slot0 + c) * AP_BM + r) * 2]);
+  float l = 0.f;
+  float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int c = 0; c < nchunks; ++c) {
+    const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + ((slot0 + c) * AP_BM + r) * 2);
+    const float w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - m);
+    const float4 v = *reinterpret_cast<const float4*>(p.part_o + ((slot0 + c) * AP_BM + r) * AP_D + 4 * lane);
+    l += w * ml.y;
+    o.x += w * v.x; o.y += w * v.y; o.z += w * v.z; o.w += w * v.w;
   }
+  const float inv = l > 0.f ? 1.f / l : 0.f;
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x * inv, o.y * inv), hi = __floats2bfloat162_rn(o.z * inv, o.w * inv);
+  uint2 packed;
+  packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+  packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p.out + (static_cast<size_t>(seq0 + q_idx) * p.hq + head) * AP_D + 4 * lane) = packed;
 }
 
 }  // namespace b200
@@ -344,7 +351,7 @@ extern "C" int b200_attn_prefill_split(const void* q, long long ld_q, const void
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return -2000 - static_cast<int>(e);
   if (p.max_chunks > 1) {
-    launch_ex(attn_prefill_merge_kernel, dim3(p.n_q, hq, B), dim3(128), 0, stream, 0, p);
+    launch_ex(attn_prefill_merge_kernel, dim3(p.n_q * 16, hq, B), dim3(256), 0, stream, 0, p);
     e = cudaGetLastError();
   }
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);

@@ -24,6 +24,7 @@
 #include "gemm_common.cuh"
 #include "peer.cuh"
 #include "launch.cuh"
+#include <cstdlib>
 
 namespace b200 {
 
@@ -67,6 +68,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   static_assert(STAGES * STAGE_BYTES >= 2 * BN * TILE_N * 4, "exchange and staging buffers alias the pipeline stages");
 
   pdl_launch_dependents();     // the next kernel may be scheduled: it only reads our output after its own pdl_wait
+  if (threadIdx.x == 0) B200_TRACE(TK_GEMM_DECODE, TP_START);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);      // full[S], empty[S], tfull
@@ -141,6 +143,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         tma_load_2d_hint(smem_base + i * STAGE_BYTES, &tmap_w, full_bar(i), (kb0 + i) * BLOCK_K, w_base + n_tile * TILE_N, pol_w);
       }
       if (!grouped) pdl_wait();
+      B200_TRACE(TK_GEMM_DECODE, TP_DEPS);
       for (int i = 0; i < pre; ++i)
         tma_load_2d(smem_base + i * STAGE_BYTES + A_BYTES, &tmap_x, full_bar(i), (kb0 + i) * BLOCK_K, m0);
       if (pre == STAGES) phase = 1u; else stage = pre;
@@ -162,6 +165,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       for (int kb = kb0; kb < kb1; ++kb) {
         if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (2 << 8)), limit)) { ok = false; break; }
         tc_fence_after();
+        if (kb == kb0) B200_TRACE(TK_GEMM_DECODE, 2);
         const uint32_t a_src = smem_base + stage * STAGE_BYTES;
         const uint64_t a_desc = umma_desc_k_sw128(a_src);
         const uint64_t b_desc = umma_desc_k_sw128(a_src + A_BYTES);
@@ -172,6 +176,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
       if (ok) umma_commit(tfull_bar);
+      B200_TRACE(TK_GEMM_DECODE, 3);
     }
     __syncwarp();
   }
@@ -195,6 +200,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   if (epi) {
     acc_ok = (kb1 > kb0) && mbar_wait(tfull_bar, 0, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (2 << 8)), limit);
     tc_fence_after();
+    if (et == 0) B200_TRACE(TK_GEMM_DECODE, 4);
   }
 
   if (S == 1) {
@@ -219,6 +225,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   } else {
     // every pipeline of the cluster has drained: stage memory can now hold the exchange buffer
     cluster_sync_all();
+    if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 5);
     const int rows_per = TILE_N / S;                        // channels each CTA of the cluster finishes
     if (epi) {
       // exchange buffer in the owner CTA: [sender][token j][channel in slice] int32
@@ -244,6 +251,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     }
     tc_fence_before();
     cluster_sync_all();
+    if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 6);
     if (epi) {
       const int32_t* ex = reinterpret_cast<const int32_t*>(smem);
       const int total = rows_per * jmax;
@@ -259,6 +267,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 7);
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 
   if (ll) {
@@ -279,6 +288,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if (p.ar.use_nvls) multimem_st_ll(t.mc + off, payload, ar_epoch);
         else for (int r = 0; r < t.world; ++r) st_ll_peer(t.data[r] + off, payload, ar_epoch);
       }
+      if (et == 0) B200_TRACE(TK_GEMM_DECODE, 8);
       const uint8_t* mine = t.data[t.rank] + slot;
       const uint64_t t_start = globaltimer_ns();
       bool good = true;
@@ -319,6 +329,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     }
     __syncthreads();
     if (threadIdx.x == 0) {
+      B200_TRACE(TK_GEMM_DECODE, 9);
       const unsigned total_ctas = gridDim.x * gridDim.y * gridDim.z;
       const unsigned old = atomicAdd(p.ar.words + 2, 1u);
       if (old == total_ctas - 1) { p.ar.words[2] = 0; __threadfence(); p.ar.words[0] = ar_epoch; }
@@ -416,8 +427,11 @@ static int resident_clusters(int bn, int s) {
 
 // splits along K: aim for about two CTAs per SM, powers of two up to 8, at least one k-block per CTA
 int decode_pick_splits(int tiles, int kblocks, int num_sms) {
+  static int limit_env = -1;
+  if (limit_env < 0) { const char* e = std::getenv("B200RT_GEMM_MAX_CTAS"); limit_env = e ? std::atoi(e) : 0; }
+  const int limit = limit_env > 0 ? limit_env : 2 * num_sms + num_sms / 2;
   int s = 1;
-  while (s < 8 && tiles * s * 2 <= 2 * num_sms + num_sms / 2 && kblocks >= s * 2) s *= 2;
+  while (s < 8 && tiles * s * 2 <= limit && kblocks >= s * 2) s *= 2;
   return s;
 }
 

@@ -57,6 +57,7 @@ def lib() -> ctypes.CDLL:
         "hostrt_arena_valid": (c_int, [c_void_p]), "hostrt_arena_alloc": (c_void_p, [c_void_p, c_ulong]),
         "hostrt_arena_mark": (c_ulong, [c_void_p]), "hostrt_arena_reset_to": (None, [c_void_p, c_ulong]),
         "hostrt_arena_reset": (None, [c_void_p]), "hostrt_arena_remaining": (c_ulong, [c_void_p]),
+        "hostrt_arena_mapped_bytes": (c_ulong, [c_void_p]), "hostrt_arena_unmap_status": (c_long, [c_void_p]),
         "hostrt_arena_used": (c_ulong, [c_void_p]), "hostrt_arena_base": (c_void_p, [c_void_p]),
         "hostrt_arena_verify_placement": (c_int, [c_void_p]),
         "hostrt_pool_create": (c_void_p, [c_int, c_void_p, c_ulong, c_int, c_ulong]), "hostrt_pool_destroy": (None, [c_void_p]),
@@ -71,6 +72,8 @@ def lib() -> ctypes.CDLL:
         "hostrt_fabric_allreduce": (c_long, [c_void_p, c_int, POINTER(c_double), POINTER(c_double), c_int, c_long, c_int]),
         "hostrt_team_create": (c_void_p, [c_void_p, c_int]), "hostrt_team_destroy": (None, [c_void_p]),
         "hostrt_team_size": (c_int, [c_void_p]), "hostrt_team_jobs_run": (c_ulonglong, [c_void_p]),
+        "hostrt_team_valid": (c_int, [c_void_p]), "hostrt_team_stragglers": (c_int, [c_void_p]),
+        "hostrt_team_node_of": (c_int, [c_void_p, c_int]), "hostrt_team_run_sleep": (c_long, [c_void_p, c_long, c_long]),
         "hostrt_w8a8_linear_team": (c_long, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                              c_void_p, c_void_p, c_void_p, POINTER(c_long)]),
         "hostrt_weights_create": (c_void_p, [c_void_p, c_void_p, c_int, c_int]), "hostrt_weights_destroy": (None, [c_void_p]),
@@ -222,6 +225,13 @@ class NumaArena:
     def reset(self): lib().hostrt_arena_reset(self._h)
     def remaining(self) -> int: return lib().hostrt_arena_remaining(self._h)
     def used(self) -> int: return lib().hostrt_arena_used(self._h)
+    def mapped_bytes(self) -> int: return lib().hostrt_arena_mapped_bytes(self._h)
+
+    def unmap(self) -> int:
+        """Destroy the arena now and return what munmap answered (0 or -errno)."""
+        h, self._h = self._h, None
+        return lib().hostrt_arena_unmap_status(h) if h else 0
+
     def base(self): return lib().hostrt_arena_base(self._h)
     def verify_placement(self) -> bool: return bool(lib().hostrt_arena_verify_placement(self._h))
 
@@ -343,6 +353,17 @@ class WorkerTeam:
     def size(self) -> int: return lib().hostrt_team_size(self._h)
     @property
     def jobs_run(self) -> int: return lib().hostrt_team_jobs_run(self._h)
+    @property
+    def valid(self) -> bool: return bool(lib().hostrt_team_valid(self._h))
+    @property
+    def stragglers(self) -> bool: return bool(lib().hostrt_team_stragglers(self._h))
+
+    def node_of(self, worker: int) -> int: return lib().hostrt_team_node_of(self._h, worker)
+
+    def run_sleep(self, sleep_ms: int, timeout_ms: int) -> int:
+        """Every worker sleeps ``sleep_ms`` inside one job while the caller waits ``timeout_ms`` at most; returns the
+        status of ``WorkerTeam::run`` (0, or -ETIMEDOUT = -110).  A timed-out team is invalid from then on."""
+        return lib().hostrt_team_run_sleep(self._h, sleep_ms, timeout_ms)
 
 
 class HostWeights:

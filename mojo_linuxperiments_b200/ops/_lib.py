@@ -13,7 +13,20 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libb200_kernels.so"
+import os
+
+
+def _variant() -> str:
+    """Which build of the kernel library this process loads: B200RT_KERNELS=trace (in-kernel time stamps) or debug
+    (range-checked peer / scratch accesses); B200RT_DEBUG=1 also selects the debug build.  Default: production."""
+    v = os.environ.get("B200RT_KERNELS", "").strip().lower()
+    if v in ("trace", "debug"):
+        return v
+    return "debug" if os.environ.get("B200RT_DEBUG", "0") not in ("", "0") else ""
+
+
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / (
+    "libb200_kernels.so" if not _variant() else f"libb200_kernels_{_variant()}.so")
 
 
 class KernelError(RuntimeError):
@@ -24,7 +37,7 @@ class KernelError(RuntimeError):
 def lib() -> ctypes.CDLL:
     if not _LIB_PATH.exists():
         raise KernelError(
-            f"{_LIB_PATH} is missing: run `python -m mojo_linuxperiments_b200._build` (needs nvcc, no GPU)")
+            f"{_LIB_PATH} is missing: run `python -m mojo_linuxperiments_b200._build --all` (needs nvcc, no GPU)")
     L = ctypes.CDLL(str(_LIB_PATH))
     for name in dir(_Sig):
         if name.startswith("b200_"):
@@ -60,6 +73,8 @@ class _Sig:
     b200_ag_sync = (I, [P, I, I, c_size_t, c_size_t, I, I, I, P, I, I, P, I, P])
     b200_w8a8_gemm_decode_ar = (I, [P, P, P, P, P, P, I, I, I, I, P, I, P, P, P, I, I, c_size_t, c_size_t, P, I, I, c_size_t, c_size_t, c_size_t, P])
     b200_where_am_i = (I, [P, I, I, P])
+    b200_trace_compiled = (I, [])
+    b200_trace_set = (I, [P, ctypes.c_uint])
     b200_fill_uniform_reduce = (I, [P, c_uint64, c_uint64, c_uint64, P, I, P, P, P])
     b200_w8a8_gemm_decode_grouped = (I, [P, P, P, P, P, I, I, I, I, I, I, P, P, P, I, P])
     b200_w8a8_gemm_grouped = (I, [P, P, P, P, P, I, I, I, I, I, P, P, I, P, I, P])

@@ -127,3 +127,87 @@ def summarize_timeline(per_iter: list[list[tuple[str, float, float]]]) -> str:
     for name, d in sorted(by_name.items(), key=lambda kv: -sum(kv[1])):
         lines.append(f"{len(d):>6} {sum(d):>10.1f} {sum(d) / len(d):>8.2f}  {name}")
     return "\n".join(lines) + "\n"
+
+
+TRACE_KERNELS = {1: "act_quant", 2: "gemm_decode", 3: "gemm_prefill", 4: "rope_kv", 5: "attn_decode", 6: "attn_prefill",
+                 7: "peer_allreduce", 8: "gemm_tp", 9: "moe", 10: "argmax"}
+
+
+class DeviceTrace:
+    """Ring of in-kernel ``%globaltimer`` stamps (csrc/kernels/trace.cuh).
+
+    Needs the kernel library built with ``-DB200RT_TRACE`` (``B200RT_KERNELS=trace`` selects it).  ``start()`` hands
+    a zeroed device ring to the library, ``records()`` reads it back as dicts ``{t_ns, kernel, phase, sm, cta, grid}``
+    sorted by time, ``launches()`` groups them per kernel launch.  Call ``start()`` before the warm-up run that
+    precedes a CUDA-graph capture."""
+
+    def __init__(self, capacity: int = 1 << 18, device=None):
+        import torch
+        from ..ops import _lib
+        self._lib = _lib.lib()
+        if not self._lib.b200_trace_compiled():
+            raise RuntimeError("this kernel library has no time stamps: set B200RT_KERNELS=trace before importing the ops")
+        self.capacity = capacity
+        self.ring = torch.zeros(2 + 2 * capacity, dtype=torch.int64, device=device or "cuda")
+
+    def start(self) -> None:
+        self.ring.zero_()
+        import torch
+        torch.cuda.synchronize()
+        if self._lib.b200_trace_set(self.ring.data_ptr(), self.capacity) != 0:
+            raise RuntimeError("b200_trace_set failed")
+
+    def clear(self) -> None:
+        self.ring[:2].zero_()
+
+    def stop(self) -> None:
+        self._lib.b200_trace_set(None, 0)
+
+    def records(self) -> list[dict]:
+        import torch
+        torch.cuda.synchronize()
+        host = self.ring.cpu()
+        n = min(int(host[0].item()) & 0xffffffff, self.capacity)
+        out = []
+        for i in range(n):
+            t, w = int(host[2 + 2 * i].item()), int(host[3 + 2 * i].item()) & 0xffffffffffffffff
+            out.append({"t_ns": t & 0xffffffffffffffff, "kernel": (w >> 58) & 63, "phase": (w >> 52) & 63,
+                        "sm": (w >> 42) & 1023, "cta": (w >> 21) & 0x1fffff, "grid": w & 0x1fffff})
+        out.sort(key=lambda r: r["t_ns"])
+        return out
+
+    @staticmethod
+    def launches(records: list[dict]) -> list[dict]:
+        """Group stamps into launches.  Stamps of one (kernel, grid size, CTA, phase) appear once per launch and in
+        launch order, so the n-th such stamp belongs to the n-th launch of that (kernel, grid size)."""
+        seen: dict[tuple, int] = {}
+        groups: dict[tuple, dict] = {}
+        for r in records:
+            key = (r["kernel"], r["grid"], r["cta"], r["phase"])
+            n = seen.get(key, 0)
+            seen[key] = n + 1
+            g = groups.setdefault((r["kernel"], r["grid"], n), {"kernel": r["kernel"], "grid": r["grid"], "n": n, "phases": {}})
+            g["phases"].setdefault(r["phase"], []).append(r["t_ns"])
+        out = list(groups.values())
+        for g in out:
+            g["t0"] = min(min(v) for v in g["phases"].values())
+        out.sort(key=lambda g: g["t0"])
+        return out
+
+    @staticmethod
+    def summarize(records: list[dict], max_launches: int = 64) -> str:
+        """Per launch: for every phase the first / median / last stamp in microseconds relative to the launch's first
+        stamp, and the launch's start relative to the first launch."""
+        ls = DeviceTrace.launches(records)
+        if not ls:
+            return "(no stamps)\n"
+        base = ls[0]["t0"]
+        lines = []
+        for g in ls[:max_launches]:
+            name = TRACE_KERNELS.get(g["kernel"], str(g["kernel"]))
+            lines.append(f"{name} grid {g['grid']} launch #{g['n']} at {(g['t0'] - base) / 1e3:.2f} us")
+            for ph in sorted(g["phases"]):
+                ts = sorted(g["phases"][ph])
+                rel = [(t - g["t0"]) / 1e3 for t in ts]
+                lines.append(f"    phase {ph:2d}: n {len(ts):4d}  first {rel[0]:7.2f}  median {rel[len(rel) // 2]:7.2f}  last {rel[-1]:7.2f}")
+        return "\n".join(lines) + "\n"

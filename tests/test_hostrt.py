@@ -3,6 +3,7 @@ import ctypes
 import os
 import re
 import subprocess
+import time
 from pathlib import Path
 
 import numpy as np
@@ -400,4 +401,51 @@ def test_node_sharded_weights_live_where_their_readers_run():
         b = H.w8a8_linear(info, x, wq, sw)
         assert a["status"] == 0 and torch.equal(a["y"], b["y"]) and torch.equal(a["acc"], b["acc"])
     del hw
+    team.close()
+
+
+def test_arena_unmaps_exactly_what_it_mapped():
+    """The mapped length is the size rounded up to the page size of the mode, and that is what munmap gets back."""
+    info = H.NumaInfo()
+    a = H.NumaArena(info.node_ids[0], 5000, page_size=H.PAGE_STANDARD)
+    assert a and a.mapped_bytes() == 8192 and a.unmap() == 0
+    huge = H.NumaArena(info.node_ids[0], (2 << 20) + 4096, page_size=H.PAGE_EXPLICIT_2MB)
+    if not huge:
+        pytest.skip("no hugetlb pool on this machine: the explicit 2 MiB mapping cannot be made")
+    assert huge.mapped_bytes() == 4 << 20
+    assert huge.unmap() == 0              # a 4 KiB-rounded length would be refused with EINVAL and leak the huge pages
+
+
+def test_worker_team_skips_nodes_without_cpus(tmp_path):
+    """A memory-only node (online, empty cpulist) gets no pool and no workers; the team on the other node works."""
+    live = H.NumaInfo()
+    node0 = live.node_ids[0]
+    cpus = live.get_node_cpus(node0)[:2]
+    nodes = {node0: (",".join(map(str, cpus)), [10, 80], 1000, 500), node0 + 1: ("", [80, 10], 4000, 4000)}
+    info = H.NumaInfo(_fake_sysfs(tmp_path, nodes))
+    assert info.num_nodes == 2 and info.get_node_cpus(node0 + 1) == []
+    assert info.cpus_per_node() == len(cpus) and info.total_cpus() == len(cpus)
+    team = H.WorkerTeam(info)
+    assert team.valid and team.size == len(cpus)
+    assert {team.node_of(i) for i in range(team.size)} == {node0}
+    assert team.run_sleep(1, 5000) == 0
+    team.close()
+    # the memory-only node in front of the CPU node
+    (tmp_path / "b").mkdir()
+    info2 = H.NumaInfo(_fake_sysfs(tmp_path / "b", {node0: ("", [10, 80], 10, 10), node0 + 1: (",".join(map(str, cpus)), [80, 10], 10, 10)}))
+    assert info2.cpus_per_node() == len(cpus)
+
+
+def test_worker_team_timeout_kills_the_team_instead_of_racing_on_the_job():
+    """A job that overruns its timeout: run() reports -ETIMEDOUT, waits (bounded) for the stragglers so that the job's
+    storage is not freed under them, and the team refuses every later job."""
+    info = H.NumaInfo()
+    team = H.WorkerTeam(info, max_workers_per_node=2)
+    assert team.run_sleep(1, 5000) == 0 and team.valid
+    t0 = time.monotonic()
+    assert team.run_sleep(300, 30) == -110            # -ETIMEDOUT
+    waited = time.monotonic() - t0
+    assert 0.25 < waited < 2.5                         # it stayed until the sleepers were done, not just 30 ms
+    assert not team.valid and not team.stragglers
+    assert team.run_sleep(1, 5000) == -22             # -EINVAL: fail fast from now on
     team.close()
