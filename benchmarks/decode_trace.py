@@ -46,9 +46,10 @@ eng.check_status()
 text = (f"decode step phase stamps: model {a.model}, {a.layers} layers, batch {a.batch}, context {a.prompt_len}, "
         f"shard 1/{a.shard_of}; {len(recs)} stamps\n"
         "gemm_decode phases: 0 start, 1 producer past dependency wait, 2 first stage landed, 3 last MMA issued, "
-        "4 accumulator complete, 5/6 cluster barriers, 7 outputs stored, 8 pushed to peers, 9 peers summed\n"
+        "4 accumulator complete, 5 cluster is running, 10 partials sent, 6 cluster barrier passed, 11 slice reduced and stored, "
+        "7 CTA past its last barrier, 8 pushed to peers, 9 peers summed\n"
         "attn_decode phases: 0 start, 1 dependency wait passed, 2 scores in registers, 3 maxima exchanged, 5 P.V read, "
-        "6 partial written, 7 merge begins (last CTA of a head), 63 merge done\n"
+        "6 partial written, 7 merge begins (last CTA of a head), 63 merge done, 62 output quantised\n"
         "act_quant phases: 0 start, 1 dependency wait passed, 2 row rotated, 63 row stored\n" + DeviceTrace.summarize(recs, 400))
 print(text)
 if a.out:

@@ -48,7 +48,7 @@ else:
         rc = _lib.lib().b200_w8a8_gemm_decode_ar(
             x.data_ptr(), sx.data_ptr(), w.data_ptr(), sw.data_ptr(), out.data_ptr(), None, M, N, K, N,
             status.data_ptr(), _lib.num_sms(0), data, fl, None, 1, 0, 0, small, words.data_ptr(), 200, 1,
-            2 * small, 2 * small + recv, recv, _lib.stream())
+            2 * small, 2 * small + recv, recv, 0, 0, 0, 0, _lib.stream())
         _lib.check(rc, "w8a8_gemm_decode_ar")
     torch.cuda.synchronize()
     assert int(status[0].item()) == 0, int(status[0].item())

@@ -8,6 +8,7 @@
 #include "ptx.cuh"
 #include "api.h"
 #include "launch.cuh"
+#include "hadamard.cuh"
 
 namespace b200 {
 
@@ -15,37 +16,6 @@ constexpr int AQ_THREADS = 256;
 constexpr int AQ_WARPS = AQ_THREADS / 32;
 
 enum ActQuantMode : int { AQ_PLAIN = 0, AQ_NORM = 1, AQ_ADD_NORM = 2, AQ_SWIGLU = 3 };
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-
-__device__ __forceinline__ void fwht128_lane4(float (&v)[4], int lane) {
-  // stages on index bits 0 and 1 (inside the lane)
-  float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
-  v[0] = a0 + a2; v[1] = a1 + a3; v[2] = a0 - a2; v[3] = a1 - a3;
-  // stages on index bits 2..6 (lane bits 0..4)
-#pragma unroll
-  for (int b = 0; b < 5; ++b) {
-    const int mask = 1 << b;
-    const bool upper = (lane & mask) != 0;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float o = __shfl_xor_sync(0xffffffffu, v[i], mask);
-      v[i] = upper ? (o - v[i]) : (v[i] + o);
-    }
-  }
-  const float s = 0.08838834764831845f;  // 1/sqrt(128)
-#pragma unroll
-  for (int i = 0; i < 4; ++i) v[i] *= s;
-}
 
 __device__ __forceinline__ void load4_bf16(const __nv_bfloat16* p, float (&v)[4]) {
   const uint2 raw = *reinterpret_cast<const uint2*>(p);
@@ -69,6 +39,7 @@ act_quant_kernel(const __nv_bfloat16* x, long long ldx, __nv_bfloat16* residual,
                  long long ldq, float* scale, __nv_bfloat16* xn_out, long long ldn,
                  int K) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
+  B200_TRACE_INIT();
   if (threadIdx.x == 0) B200_TRACE(TK_ACT_QUANT, TP_START);
   pdl_wait();                // everything before this kernel in the stream has completed
   if (threadIdx.x == 0) B200_TRACE(TK_ACT_QUANT, TP_DEPS);
@@ -189,29 +160,23 @@ act_quant_kernel(const __nv_bfloat16* x, long long ldx, __nv_bfloat16* residual,
     float t = 0.f;
 #pragma unroll
     for (int w = 0; w < AQ_WARPS; ++w) t = fmaxf(t, red[w]);
-    const float s = (t > 0.f) ? (t / 127.f) : 1.f;
+    const float s = quant_scale_from_amax(t);
     bcast = s;
     scale[row] = s;
   }
   __syncthreads();
   const float s = bcast;
-  const float inv_s = 1.0f / s;
+  const float inv_s = quant_inv_scale(s);
   int8_t* qr = q + static_cast<size_t>(row) * ldq;
 #pragma unroll
   for (int i = 0; i < MAXB; ++i) {
     const int b = warp + i * AQ_WARPS;
     if (b < nblocks) {
-      uint32_t packed = 0;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        int qi = __float2int_rn(v[i][j] * inv_s);
-        qi = max(-127, min(127, qi));
-        packed |= (static_cast<uint32_t>(qi) & 0xffu) << (8 * j);
-      }
-      *reinterpret_cast<uint32_t*>(qr + b * 128 + lane * 4) = packed;
+      *reinterpret_cast<uint32_t*>(qr + b * 128 + lane * 4) = quant_pack4(v[i], inv_s);
     }
   }
   if (threadIdx.x == 0) B200_TRACE(TK_ACT_QUANT, TP_EXIT);
+  B200_TRACE_FLUSH(TK_ACT_QUANT);
 }
 
 template <int MAXB>

@@ -26,13 +26,18 @@ int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void* wq, const
                           const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
                           int num_sms, int force_splits, cudaStream_t stream);
 
+int b200_w8a8_gemm_decode_resident_clusters(int m, int splits);
+
 // Same, fused with the tensor-parallel all-reduce over peer memory (one launch).  -20: grid not co-resident, use
-// b200_w8a8_gemm_decode followed by b200_peer_allreduce instead.
+// b200_w8a8_gemm_decode followed by b200_peer_allreduce instead.  ll: low-latency {payload, epoch} words; two_hop
+// (with ll): partials go only to the rank owning the column slice, which sums and broadcasts them through a second
+// receive area of M * N/2 words per slot (recv2_off0/1) - less NVLink traffic at more than a few tokens.
 int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
                              const void* residual, int M, int N, int K, int ldy, int* status, int num_sms,
                              void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
                              size_t part_off0, size_t part_off1, void* words, int limit_ms, int ll,
-                             size_t recv_off0, size_t recv_off1, size_t recv_bytes, cudaStream_t stream);
+                             size_t recv_off0, size_t recv_off1, size_t recv_bytes, int two_hop, size_t recv2_off0,
+                             size_t recv2_off1, size_t recv2_bytes, cudaStream_t stream);
 
 // Mixture-of-experts grouped forms (device-side offsets / tile tables, no host sync).
 int b200_w8a8_gemm_decode_grouped(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
@@ -83,6 +88,15 @@ int b200_attn_decode_tc_min_splits(int max_len);
 int b200_attn_decode_tc(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
                         void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
                         int max_pages, int splits, float scale, int* status, cudaStream_t stream);
+// The same kernel with its neighbours folded in: raw q | k | v of the new token in, (optional per-head RMSNorm,) rotary
+// embedding, KV append, attention over the cache plus the new token, and (xq given) Hadamard rotation + per-token int8
+// of the output out.  seq_lens[b] counts the new token; positions[b] is where it goes.  See attn_decode_tc.cu.
+int b200_attn_decode_fused(const void* qkv, long long ld_qkv, const int* positions, const float* cos_tab,
+                           const float* sin_tab, int max_pos, const void* q_norm_w, const void* k_norm_w, float eps,
+                           void* cache, int num_pages, const int* page_table, const int* seq_lens, void* out, void* xq,
+                           long long ldq, float* sx, float* scratch, unsigned* counters, float* rot_scratch,
+                           float* blk_amax, unsigned* seq_counters, int B, int hq, int hkv, int page_size, int max_pages,
+                           int splits, float scale, int* status, cudaStream_t stream);
 // Persistent form: two CTAs per SM walk the (kv head, sequence, split) items, loads of the next item overlap the
 // softmax / output phase of the current one.
 int b200_attn_decode_tcp(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
@@ -93,7 +107,7 @@ int b200_attn_prefill(const void* q, long long ld_q, const void* k, long long ld
                       float scale, int* status, cudaStream_t stream);
 
 // Split-KV form of b200_attn_prefill: every `chunk` KV tiles (of 128 tokens) of a query tile are one CTA; partial rows go
-// through `scratch` (b200_attn_prefill_split_scratch_floats floats) and a merge kernel.  Opt-in, not yet run on hardware.
+// through `scratch` (b200_attn_prefill_split_scratch_floats floats) and a merge kernel.
 size_t b200_attn_prefill_split_scratch_floats(int B, int hq, int max_len, int chunk);
 int b200_attn_prefill_split(const void* q, long long ld_q, const void* k, long long ld_k, const void* v, long long ld_v,
                             void* out, const int* cu_seqlens, int B, int total_tokens, int max_len, int hq, int hkv,

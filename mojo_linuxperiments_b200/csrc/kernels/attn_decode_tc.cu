@@ -19,6 +19,7 @@
 #include "ptx.cuh"
 #include "api.h"
 #include "launch.cuh"
+#include "hadamard.cuh"
 #include <cuda.h>
 
 namespace b200 {
@@ -34,6 +35,30 @@ constexpr int ADC_Q_TILE = ADC_NH * ADC_D * 2;  // 4 KiB
 constexpr int ADC_TMEM_COLS = 128;              // S: ADC_NB x 16 columns, O: 16 columns at 64
 constexpr int ADC_O_COL = 64;
 
+// Fused form (attn_decode_tc_kernel<G, true>): the kernel takes the raw q | k | v projections of the new token instead of
+// a rotated q, applies the optional per-head RMSNorm and the rotary embedding itself, appends k and v to the paged
+// cache, attends to the new token from registers (the cached tokens still arrive by TMA), and can finish with the
+// block-128 Hadamard rotation + per-token int8 quantisation of the attention output, i.e. the operand of o_proj.
+struct DecodeFuse {
+  const __nv_bfloat16* qkv;        // [B][(hq + 2 hkv) * 128] (row pitch ld_qkv elements)
+  long long ld_qkv;
+  const int* positions;            // [B] position of the new token (seq_lens[b] counts it: cached tokens = seq_lens[b] - 1)
+  const float* cos_tab;            // [max_pos][64]
+  const float* sin_tab;
+  int max_pos;
+  const __nv_bfloat16* q_norm_w;   // [128] or nullptr
+  const __nv_bfloat16* k_norm_w;
+  float eps;
+  __nv_bfloat16* cache;            // same storage the tensor map reads
+  int num_pages;
+  int8_t* xq;                      // [B][hq * 128] int8 rows (pitch ldq) or nullptr: no quantising epilogue
+  long long ldq;
+  float* sx;                       // [B] per-token scales
+  float* rot_scratch;              // [B][hq][128] rotated rows, used when a token's heads span several CTAs (hkv > 1)
+  float* blk_amax;                 // [B][hkv]
+  unsigned* seq_counters;          // [B], zero between launches
+};
+
 struct DecodeTcParams {
   const __nv_bfloat16* q;
   const int* page_table;
@@ -46,12 +71,57 @@ struct DecodeTcParams {
   float scale_log2;
   int* status;
   unsigned long long limit_ns;
+  DecodeFuse f;
 };
 
-template <int G>
+__device__ __forceinline__ void unpack8_bf16(const uint4& raw, float (&o)[8]) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { o[2 * i] = __uint_as_float(w[i] << 16); o[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+__device__ __forceinline__ uint4 pack8_bf16(const float (&v)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    w[i] = *reinterpret_cast<const uint32_t*>(&b);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+__device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16(v)); }
+
+// One head (128 values) handled by 8 consecutive lanes: lane c holds elements 8c..8c+7 (lo) and 64+8c..64+8c+7 (hi).
+// Optional RMSNorm over the head, then the rotate-half rotary embedding with the pairs (i, i + 64).  All 32 lanes of the
+// warp must call this together (the reduction shuffles inside groups of 8 lanes).
+__device__ __forceinline__ void head_norm_rope(float (&lo)[8], float (&hi)[8], const __nv_bfloat16* nw, float eps, int c,
+                                               const float (&cs)[8], const float (&sn)[8]) {
+  if (nw) {
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += lo[j] * lo[j] + hi[j] * hi[j];
+    ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+    ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+    const float r = rsqrtf(ss * (1.f / 128.f) + eps);
+    float wl[8], wh[8];
+    unpack8_bf16(*reinterpret_cast<const uint4*>(nw + 8 * c), wl);
+    unpack8_bf16(*reinterpret_cast<const uint4*>(nw + 64 + 8 * c), wh);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { lo[j] *= r * wl[j]; hi[j] *= r * wh[j]; }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const float a = lo[j], b = hi[j];
+    lo[j] = a * cs[j] - b * sn[j];
+    hi[j] = b * cs[j] + a * sn[j];
+  }
+}
+
+template <int G, bool FUSED>
 __global__ void __launch_bounds__(ADC_THREADS, 2)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeTcParams p) {
   pdl_launch_dependents();
+  B200_TRACE_INIT();
   if (threadIdx.x == 0) B200_TRACE(TK_ATTN_DECODE, TP_START);
   pdl_wait();
   if (threadIdx.x == 0) B200_TRACE(TK_ATTN_DECODE, TP_DEPS);
@@ -69,6 +139,11 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
   int* page_s = last_flag + 1;                     // [ADC_NB * 8] page ids of this CTA's blocks
+  // fused form only: the finished (bf16-rounded) output rows of this CTA's heads, v and the scores of the new token
+  float* row_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(page_s + ADC_NB * 8) + 15) & ~uintptr_t(15));   // [G][128]
+  float* vnew_s = row_s + G * ADC_D;               // [128]
+  float* snew_s = vnew_s + ADC_D;                  // [8]
+  float* amax_s = snew_s + 8;                      // [8]
   const uint32_t sRing = smem_u32(smem);
   const uint32_t sP = smem_u32(pP), sQ = smem_u32(pQ);
   const uint32_t bar0 = smem_u32(bars);
@@ -76,7 +151,10 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
 
   const int kvh = blockIdx.x, b = blockIdx.y, split = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int len = p.seq_lens[b];
+  const int len_total = p.seq_lens[b];
+  // fused: the new token is not read from the cache, so the TMA path covers one token less
+  int len = FUSED ? len_total - 1 : len_total;
+  const bool has_new = FUSED && split == p.splits - 1 && len_total >= 1;
   if (len > p.max_pages * 16) {            // the page-table row cannot describe more tokens than this
     if (tid == 0 && p.status) atomicCAS(p.status, 0, (int)ST_BAD_ARGUMENT | (5 << 8));
     len = p.max_pages * 16;
@@ -107,10 +185,85 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   // Page ids are fetched once, in parallel, so the producer never waits on a global load between two TMA issues;
   // pages past the end of the sequence are replaced by its last page (already in L2) and masked in the softmax.
   if (tid < ADC_NB * 8 && total_pages > 0) page_s[tid] = pt[min(blk0 * 8 + tid, total_pages - 1)];
-  for (int i = tid; i < G * 16; i += ADC_THREADS) {
-    const int g = i >> 4, c = i & 15;
-    const uint4 v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(b) * p.hq + kvh * G + g) * ADC_D + c * 8);
-    *reinterpret_cast<uint4*>(pQ + (c >> 3) * 2048 + (g >> 3) * 1024 + (g & 7) * 128 + (((c & 7) ^ (g & 7)) << 4)) = v;
+  if constexpr (!FUSED) {
+    for (int i = tid; i < G * 16; i += ADC_THREADS) {
+      const int g = i >> 4, c = i & 15;
+      const uint4 v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(b) * p.hq + kvh * G + g) * ADC_D + c * 8);
+      *reinterpret_cast<uint4*>(pQ + (c >> 3) * 2048 + (g >> 3) * 1024 + (g & 7) * 128 + (((c & 7) ^ (g & 7)) << 4)) = v;
+    }
+  } else {
+    // ---- rotate q (every CTA), and in the CTA that owns the new token: rotate k, append k and v to the cache, score ----
+    const int pos = p.f.positions[b];
+    const bool pos_ok = pos >= 0 && pos < p.f.max_pos;
+    const __nv_bfloat16* row = p.f.qkv + static_cast<size_t>(b) * p.f.ld_qkv;
+    // where the new token goes: refuse (status word) a position outside the tables or the pages of the sequence
+    size_t cache_row = 0;
+    bool store_ok = has_new && pos_ok && (pos >> 4) < p.max_pages;
+    if (store_ok) {
+      const int page = pt[pos >> 4];
+      store_ok = page >= 0 && page < p.f.num_pages;
+      cache_row = (static_cast<size_t>(page) * 2 * p.hkv + kvh) * 16 + (pos & 15);      // K row; the V row is hkv * 16 rows further
+    }
+    if (has_new && !store_ok && tid == 0 && p.status) atomicCAS(p.status, 0, (int)ST_BAD_ARGUMENT | (5 << 8));
+    if (warp < (G * 8 + 31) / 32) {
+      const bool act = tid < G * 8;
+      const int g = act ? (tid >> 3) : 0, c = tid & 7;
+      float cs[8], sn[8];
+      if (pos_ok) {
+        const float4 c0 = *reinterpret_cast<const float4*>(p.f.cos_tab + static_cast<size_t>(pos) * 64 + 8 * c);
+        const float4 c1 = *reinterpret_cast<const float4*>(p.f.cos_tab + static_cast<size_t>(pos) * 64 + 8 * c + 4);
+        const float4 s0 = *reinterpret_cast<const float4*>(p.f.sin_tab + static_cast<size_t>(pos) * 64 + 8 * c);
+        const float4 s1 = *reinterpret_cast<const float4*>(p.f.sin_tab + static_cast<size_t>(pos) * 64 + 8 * c + 4);
+        cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+        sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { cs[j] = 1.f; sn[j] = 0.f; }
+      }
+      const __nv_bfloat16* qh = row + static_cast<size_t>(kvh * G + g) * ADC_D;
+      float qlo[8], qhi[8];
+      unpack8_bf16(*reinterpret_cast<const uint4*>(qh + 8 * c), qlo);
+      unpack8_bf16(*reinterpret_cast<const uint4*>(qh + 64 + 8 * c), qhi);
+      head_norm_rope(qlo, qhi, p.f.q_norm_w, p.f.eps, c, cs, sn);
+      const uint4 qa = pack8_bf16(qlo), qb = pack8_bf16(qhi);
+      if (act) {
+        *reinterpret_cast<uint4*>(pQ + (g >> 3) * 1024 + (g & 7) * 128 + ((c ^ (g & 7)) << 4)) = qa;            // chunk c
+        *reinterpret_cast<uint4*>(pQ + 2048 + (g >> 3) * 1024 + (g & 7) * 128 + ((c ^ (g & 7)) << 4)) = qb;     // chunk c + 8
+      }
+      if (has_new) {
+        // every group of 8 lanes rotates the same k head; group 0 stores it
+        const __nv_bfloat16* kh = row + static_cast<size_t>(p.hq + kvh) * ADC_D;
+        float klo[8], khi[8];
+        unpack8_bf16(*reinterpret_cast<const uint4*>(kh + 8 * c), klo);
+        unpack8_bf16(*reinterpret_cast<const uint4*>(kh + 64 + 8 * c), khi);
+        head_norm_rope(klo, khi, p.f.k_norm_w, p.f.eps, c, cs, sn);
+        const uint4 ka = pack8_bf16(klo), kb = pack8_bf16(khi);
+        if (act && g == 0 && store_ok) {
+          __nv_bfloat16* dst = p.f.cache + cache_row * ADC_D;
+          *reinterpret_cast<uint4*>(dst + 8 * c) = ka;
+          *reinterpret_cast<uint4*>(dst + 64 + 8 * c) = kb;
+        }
+        // the score the tensor core would have produced: bf16 operands, fp32 sum
+        float qr0[8], qr1[8], kr0[8], kr1[8];
+        unpack8_bf16(qa, qr0); unpack8_bf16(qb, qr1); unpack8_bf16(ka, kr0); unpack8_bf16(kb, kr1);
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) dot += qr0[j] * kr0[j] + qr1[j] * kr1[j];
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+        if (act && c == 0) snew_s[g] = dot * p.scale_log2;
+      }
+    }
+    if (has_new && tid >= 64 && tid < 80) {
+      const int vc = tid - 64;
+      const uint4 vv = *reinterpret_cast<const uint4*>(row + static_cast<size_t>(p.hq + p.hkv + kvh) * ADC_D + 8 * vc);
+      float vf[8];
+      unpack8_bf16(vv, vf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) vnew_s[8 * vc + j] = vf[j];
+      if (store_ok) *reinterpret_cast<uint4*>(p.f.cache + (cache_row + static_cast<size_t>(p.hkv) * 16) * ADC_D + 8 * vc) = vv;
+    }
   }
   fence_proxy_async_smem();
   tc_fence_before();
@@ -211,6 +364,12 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
       }
     }
     if (tid == 64) B200_TRACE(TK_ATTN_DECODE, 2);           // all scores of this CTA are in registers
+    if constexpr (FUSED) {
+      if (has_new) {
+#pragma unroll
+        for (int g = 0; g < G; ++g) mx[g] = fmaxf(mx[g], snew_s[g]);
+      }
+    }
     // ---- maximum per head over the CTA's tokens: warp shuffle, then the four warps through shared memory ----
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -283,11 +442,28 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
 #pragma unroll
       for (int g = 0; g < G; ++g) { m[g] = -INFINITY; l[g] = 0.f; }
     }
+    if constexpr (FUSED) {
+      if (has_new) {
+        // the new token joins from registers: its probability with the final maximum, its value row from shared memory
+        const float vr = vnew_s[r];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          if (nb == 0 || !ok) { m[g] = snew_s[g]; l[g] = 1.f; o[g] = vr; }
+          else {
+            const float pn = round_bf16(exp2f(snew_s[g] - m[g]));
+            l[g] += pn;
+            o[g] += pn * vr;
+          }
+        }
+      }
+    }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       const size_t hrow = static_cast<size_t>(b) * p.hq + kvh * G + g;
       if (p.splits == 1) {
-        p.out[hrow * ADC_D + r] = __float2bfloat16(l[g] > 0.f ? o[g] / l[g] : 0.f);
+        const __nv_bfloat16 ob = __float2bfloat16(l[g] > 0.f ? o[g] / l[g] : 0.f);
+        if (p.out) p.out[hrow * ADC_D + r] = ob;
+        if constexpr (FUSED) row_s[g * ADC_D + r] = __bfloat162float(ob);
       } else {
         p.part_acc[(hrow * p.splits + split) * ADC_D + r] = o[g];
         if (r == 0) { p.part_ml[(hrow * p.splits + split) * 2] = m[g]; p.part_ml[(hrow * p.splits + split) * 2 + 1] = l[g]; }
@@ -299,36 +475,132 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   __syncthreads();
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, ADC_TMEM_COLS); }
   if (tid == 0) B200_TRACE(TK_ATTN_DECODE, 6);
-  if (p.splits == 1) return;
+  if (p.splits == 1 && !(FUSED && p.f.xq)) { B200_TRACE_FLUSH(TK_ATTN_DECODE); return; }
 
-  // ---- the last CTA of this (sequence, kv head) merges the splits ----
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    unsigned* ctr = p.counters + static_cast<size_t>(b) * p.hkv + kvh;
-    const unsigned old = atomicAdd(ctr, 1u);
-    *last_flag = (old == static_cast<unsigned>(p.splits - 1)) ? 1 : 0;
-    if (*last_flag) *ctr = 0;
-  }
-  __syncthreads();
-  if (!*last_flag) return;
-  if (tid == 0) B200_TRACE(TK_ATTN_DECODE, 7);
-  __threadfence();
-  for (int i = tid; i < G * ADC_D; i += ADC_THREADS) {
-    const int g = i / ADC_D, d = i % ADC_D;
-    const size_t base = (static_cast<size_t>(b) * p.hq + kvh * G + g) * p.splits;
-    float m = -INFINITY;
-    for (int sI = 0; sI < p.splits; ++sI) m = fmaxf(m, __ldcg(p.part_ml + (base + sI) * 2));
-    float l = 0.f, o = 0.f;
-    for (int sI = 0; sI < p.splits; ++sI) {
-      const float ms = __ldcg(p.part_ml + (base + sI) * 2);
-      const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
-      l += w * __ldcg(p.part_ml + (base + sI) * 2 + 1);
-      o += w * __ldcg(p.part_acc + (base + sI) * ADC_D + d);
+  if (p.splits > 1) {
+    // ---- the last CTA of this (sequence, kv head) merges the splits ----
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      unsigned* ctr = p.counters + static_cast<size_t>(b) * p.hkv + kvh;
+      const unsigned old = atomicAdd(ctr, 1u);
+      *last_flag = (old == static_cast<unsigned>(p.splits - 1)) ? 1 : 0;
+      if (*last_flag) *ctr = 0;
     }
-    p.out[(static_cast<size_t>(b) * p.hq + kvh * G + g) * ADC_D + d] = __float2bfloat16(l > 0.f ? o / l : 0.f);
+    __syncthreads();
+    if (!*last_flag) { B200_TRACE_FLUSH(TK_ATTN_DECODE); return; }
+    if (tid == 0) B200_TRACE(TK_ATTN_DECODE, 7);
+    __threadfence();
+    for (int i = tid; i < G * ADC_D; i += ADC_THREADS) {
+      const int g = i / ADC_D, d = i % ADC_D;
+      const size_t base = (static_cast<size_t>(b) * p.hq + kvh * G + g) * p.splits;
+      float m = -INFINITY, l = 0.f, o = 0.f;
+      if (p.splits <= 16) {
+        // all partials are requested at once: the merge is a chain of L2 round trips otherwise
+        float ms[16], ls[16], os[16];
+#pragma unroll
+        for (int sI = 0; sI < 16; ++sI) {
+          ms[sI] = -INFINITY; ls[sI] = 0.f; os[sI] = 0.f;
+          if (sI < p.splits) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + (base + sI) * 2));
+            ms[sI] = ml.x; ls[sI] = ml.y;
+            os[sI] = __ldcg(p.part_acc + (base + sI) * ADC_D + d);
+          }
+        }
+#pragma unroll
+        for (int sI = 0; sI < 16; ++sI) m = fmaxf(m, ms[sI]);
+#pragma unroll
+        for (int sI = 0; sI < 16; ++sI) {
+          const float w = (ms[sI] == -INFINITY) ? 0.f : exp2f(ms[sI] - m);
+          l += w * ls[sI];
+          o += w * os[sI];
+        }
+      } else {
+        for (int sI = 0; sI < p.splits; ++sI) m = fmaxf(m, __ldcg(p.part_ml + (base + sI) * 2));
+        for (int sI = 0; sI < p.splits; ++sI) {
+          const float ms = __ldcg(p.part_ml + (base + sI) * 2);
+          const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+          l += w * __ldcg(p.part_ml + (base + sI) * 2 + 1);
+          o += w * __ldcg(p.part_acc + (base + sI) * ADC_D + d);
+        }
+      }
+      const __nv_bfloat16 ob = __float2bfloat16(l > 0.f ? o / l : 0.f);
+      if (p.out) p.out[(static_cast<size_t>(b) * p.hq + kvh * G + g) * ADC_D + d] = ob;
+      if constexpr (FUSED) row_s[i] = __bfloat162float(ob);
+    }
+    if (tid == 0) B200_TRACE(TK_ATTN_DECODE, TP_EXIT);
   }
-  if (tid == 0) B200_TRACE(TK_ATTN_DECODE, TP_EXIT);
+
+  if constexpr (!FUSED) { B200_TRACE_FLUSH(TK_ATTN_DECODE); }
+  if constexpr (FUSED) {
+    if (!p.f.xq) { B200_TRACE_FLUSH(TK_ATTN_DECODE); return; }
+    // ---- epilogue: block-128 Hadamard rotation (one head = one block) + per-token int8 of the output row ----
+    __syncthreads();                                   // row_s of all heads of this CTA is complete
+    constexpr int NW = ADC_THREADS / 32;
+    float v[2][4];
+    float am = 0.f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int g = warp + i * NW;
+      if (g < G) {
+        const float4 x = *reinterpret_cast<const float4*>(row_s + g * ADC_D + 4 * lane);
+        v[i][0] = x.x; v[i][1] = x.y; v[i][2] = x.z; v[i][3] = x.w;
+        fwht128_lane4(v[i], lane);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) am = fmaxf(am, fabsf(v[i][j]));
+      }
+    }
+    am = warp_max(am);
+    if (lane == 0) amax_s[warp] = am;
+    if (p.hkv == 1) {
+      __syncthreads();
+      float row_amax = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) row_amax = fmaxf(row_amax, amax_s[w]);
+      const float scale = quant_scale_from_amax(row_amax), inv = quant_inv_scale(scale);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int g = warp + i * NW;
+        if (g < G) *reinterpret_cast<uint32_t*>(p.f.xq + static_cast<size_t>(b) * p.f.ldq + g * ADC_D + 4 * lane) = quant_pack4(v[i], inv);
+      }
+      if (tid == 0) p.f.sx[b] = scale;
+    } else {
+      // the token's heads are spread over hkv CTAs: park the rotated rows, the last CTA to arrive quantises the token
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int g = warp + i * NW;
+        if (g < G)
+          *reinterpret_cast<float4*>(p.f.rot_scratch + (static_cast<size_t>(b) * p.hq + kvh * G + g) * ADC_D + 4 * lane) =
+              make_float4(v[i][0], v[i][1], v[i][2], v[i][3]);
+      }
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        float blk = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) blk = fmaxf(blk, amax_s[w]);
+        p.f.blk_amax[static_cast<size_t>(b) * p.hkv + kvh] = blk;
+        __threadfence();
+        const unsigned old = atomicAdd(p.f.seq_counters + b, 1u);
+        *last_flag = (old == static_cast<unsigned>(p.hkv - 1)) ? 1 : 0;
+        if (*last_flag) p.f.seq_counters[b] = 0;
+      }
+      __syncthreads();
+      if (!*last_flag) { B200_TRACE_FLUSH(TK_ATTN_DECODE); return; }
+      __threadfence();
+      float row_amax = 0.f;
+      for (int k = 0; k < p.hkv; ++k) row_amax = fmaxf(row_amax, __ldcg(p.f.blk_amax + static_cast<size_t>(b) * p.hkv + k));
+      const float scale = quant_scale_from_amax(row_amax), inv = quant_inv_scale(scale);
+      for (int h = warp; h < p.hq; h += NW) {
+        const float4 x = __ldcg(reinterpret_cast<const float4*>(p.f.rot_scratch + (static_cast<size_t>(b) * p.hq + h) * ADC_D + 4 * lane));
+        const float xv[4] = {x.x, x.y, x.z, x.w};
+        *reinterpret_cast<uint32_t*>(p.f.xq + static_cast<size_t>(b) * p.f.ldq + h * ADC_D + 4 * lane) = quant_pack4(xv, inv);
+      }
+      if (tid == 0) p.f.sx[b] = scale;
+    }
+    if (tid == 0) B200_TRACE(TK_ATTN_DECODE, 62);
+    B200_TRACE_FLUSH(TK_ATTN_DECODE);
+  }
 }
 
 // ------------------------------------------------------------------------------------------------------------------
@@ -715,16 +987,21 @@ typedef CUresult (*EncodeTiledFn3)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-template <int G>
+template <int G, bool FUSED>
 static int launch_adc(const CUtensorMap& tm, const DecodeTcParams& p, dim3 grid, cudaStream_t stream) {
-  constexpr int SMEM = 2 * ADC_TILE + ADC_NB * ADC_P_TILE + ADC_Q_TILE + (64 + 16) * 4 + (6 + 2 * ADC_NB) * 8 + 64 + ADC_NB * 8 * 4 + 1024;
+  // the fused form adds the output rows of the CTA's heads, the new token's value row and a few scalars
+  constexpr int SMEM = 2 * ADC_TILE + ADC_NB * ADC_P_TILE + ADC_Q_TILE + (64 + 16) * 4 + (6 + 2 * ADC_NB) * 8 + 64 + ADC_NB * 8 * 4 + 1024 +
+                       (FUSED ? (G * ADC_D + ADC_D + 16) * 4 + 16 : 0);
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<G, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    // ask for the largest shared-memory carveout: with the default preference the occupancy calculator (and the
+    // launch) may settle for a split of the L1 / shared array that holds fewer CTAs per SM than the kernel was sized for
+    cudaFuncSetAttribute(attn_decode_tc_kernel<G, FUSED>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }
-  launch_ex(attn_decode_tc_kernel<G>, dim3(grid), dim3(ADC_THREADS), SMEM, stream, 0, tm, p);
+  launch_ex(attn_decode_tc_kernel<G, FUSED>, dim3(grid), dim3(ADC_THREADS), SMEM, stream, 0, tm, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
@@ -735,6 +1012,9 @@ static int launch_adcp(const CUtensorMap& tm, const DecodeTcParams& p, int num_i
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_tcp_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    // ask for the largest shared-memory carveout: with the default preference the occupancy calculator (and the
+    // launch) may settle for a split of the L1 / shared array that holds fewer CTAs per SM than the kernel was sized for
+    cudaFuncSetAttribute(attn_decode_tcp_kernel<G>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }
@@ -757,14 +1037,24 @@ extern "C" int b200_attn_decode_tc_min_splits(int max_len) {
 static int attn_decode_tc_common(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
                                  void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
                                  int max_pages, int splits, float scale, int* status, int persistent, int num_sms,
-                                 cudaStream_t stream) {
+                                 cudaStream_t stream, const DecodeFuse* fuse = nullptr) {
   if (B <= 0) return 0;
   if (page_size != 16 || (hq % hkv)) return -3;
   const int G = hq / hkv;
   if (G != 1 && G != 2 && G != 4 && G != 8) return -3;
   if (splits < 1) splits = 1;
   if (splits > 1 && (!scratch || !counters)) return -1;
-  if ((reinterpret_cast<uintptr_t>(cache) & 127) || (reinterpret_cast<uintptr_t>(q) & 15)) return -2;
+  if (reinterpret_cast<uintptr_t>(cache) & 127) return -2;
+  if (!fuse && (reinterpret_cast<uintptr_t>(q) & 15)) return -2;
+  if (fuse) {
+    if (persistent || !fuse->qkv || !fuse->positions || !fuse->cos_tab || !fuse->sin_tab || fuse->max_pos <= 0 || !fuse->cache) return -1;
+    if ((reinterpret_cast<uintptr_t>(fuse->qkv) & 15) || (fuse->ld_qkv % 8) || (reinterpret_cast<uintptr_t>(fuse->cos_tab) & 15) ||
+        (reinterpret_cast<uintptr_t>(fuse->sin_tab) & 15)) return -2;
+    if (fuse->xq) {
+      if (!fuse->sx || (fuse->ldq % 4) || (reinterpret_cast<uintptr_t>(fuse->xq) & 3)) return -2;
+      if (hkv > 1 && (!fuse->rot_scratch || !fuse->blk_amax || !fuse->seq_counters || (reinterpret_cast<uintptr_t>(fuse->rot_scratch) & 15))) return -1;
+    }
+  }
   static EncodeTiledFn3 fn = nullptr;
   if (!fn) {
     void* ptr = nullptr;
@@ -787,6 +1077,7 @@ static int attn_decode_tc_common(const void* q, const void* cache, int num_pages
   p.part_ml = scratch ? scratch + static_cast<size_t>(B) * hq * splits * ADC_D : nullptr;
   p.counters = counters; p.hq = hq; p.hkv = hkv; p.max_pages = max_pages; p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.limit_ns = 2000000000ull;
+  if (fuse) p.f = *fuse; else p.f = DecodeFuse{};
   if (persistent) {
     const int items = B * hkv * splits;
     switch (G) {
@@ -797,12 +1088,51 @@ static int attn_decode_tc_common(const void* q, const void* cache, int num_pages
     }
   }
   dim3 grid(hkv, B, splits);
-  switch (G) {
-    case 1: return launch_adc<1>(tm, p, grid, stream);
-    case 2: return launch_adc<2>(tm, p, grid, stream);
-    case 4: return launch_adc<4>(tm, p, grid, stream);
-    default: return launch_adc<8>(tm, p, grid, stream);
+  if (fuse) {
+    switch (G) {
+      case 1: return launch_adc<1, true>(tm, p, grid, stream);
+      case 2: return launch_adc<2, true>(tm, p, grid, stream);
+      case 4: return launch_adc<4, true>(tm, p, grid, stream);
+      default: return launch_adc<8, true>(tm, p, grid, stream);
+    }
   }
+  switch (G) {
+    case 1: return launch_adc<1, false>(tm, p, grid, stream);
+    case 2: return launch_adc<2, false>(tm, p, grid, stream);
+    case 4: return launch_adc<4, false>(tm, p, grid, stream);
+    default: return launch_adc<8, false>(tm, p, grid, stream);
+  }
+}
+
+// Decode attention with its neighbours folded in (one launch instead of rope_kv_write + attention + activation
+// prologue of o_proj): qkv holds the new token's raw q | k | v projections, the kernel normalises / rotates q and k,
+// appends k and v at positions[b] of the paged cache, attends to the seq_lens[b] - 1 cached tokens plus the new one, and,
+// when xq is given, leaves the attention output rotated (block-128 Hadamard, one head = one block) and quantised
+// per token in xq / sx; out (bf16 [B][hq][128]) is optional then.  rot_scratch (B * hq * 128 floats), blk_amax
+// (B * hkv floats) and seq_counters (B zeroed uint32) are needed when hkv > 1 and xq is given.
+extern "C" int b200_attn_decode_fused(const void* qkv, long long ld_qkv, const int* positions, const float* cos_tab,
+                                      const float* sin_tab, int max_pos, const void* q_norm_w, const void* k_norm_w, float eps,
+                                      void* cache, int num_pages, const int* page_table, const int* seq_lens, void* out,
+                                      void* xq, long long ldq, float* sx, float* scratch, unsigned* counters,
+                                      float* rot_scratch, float* blk_amax, unsigned* seq_counters, int B, int hq, int hkv,
+                                      int page_size, int max_pages, int splits, float scale, int* status, cudaStream_t stream) {
+  DecodeFuse f;
+  f.qkv = static_cast<const __nv_bfloat16*>(qkv); f.ld_qkv = ld_qkv; f.positions = positions; f.cos_tab = cos_tab; f.sin_tab = sin_tab;
+  f.max_pos = max_pos; f.q_norm_w = static_cast<const __nv_bfloat16*>(q_norm_w); f.k_norm_w = static_cast<const __nv_bfloat16*>(k_norm_w);
+  f.eps = eps; f.cache = static_cast<__nv_bfloat16*>(cache); f.num_pages = num_pages;
+  f.xq = static_cast<int8_t*>(xq); f.ldq = ldq; f.sx = sx; f.rot_scratch = rot_scratch; f.blk_amax = blk_amax; f.seq_counters = seq_counters;
+  return attn_decode_tc_common(nullptr, cache, num_pages, page_table, seq_lens, out, scratch, counters, B, hq, hkv, page_size,
+                               max_pages, splits, scale, status, 0, 0, stream, &f);
+}
+
+// CTAs of the tensor-core decode attention (group size 4, plain form) one SM holds at once.
+extern "C" int b200_attn_decode_tc_ctas_per_sm() {
+  constexpr int SMEM = 2 * ADC_TILE + ADC_NB * ADC_P_TILE + ADC_Q_TILE + (64 + 16) * 4 + (6 + 2 * ADC_NB) * 8 + 64 + ADC_NB * 8 * 4 + 1024;
+  cudaFuncSetAttribute(attn_decode_tc_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  cudaFuncSetAttribute(attn_decode_tc_kernel<4, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  int blocks = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attn_decode_tc_kernel<4, false>, ADC_THREADS, SMEM);
+  return blocks;
 }
 
 // Same contract as b200_attn_decode_tma.  splits must be at least b200_attn_decode_tc_min_splits(longest sequence).

@@ -247,6 +247,9 @@ static int launch_adt(const CUtensorMap& tm, const DecodeTmaParams& p, dim3 grid
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_tma_kernel<G>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    // ask for the largest shared-memory carveout: with the default preference the occupancy calculator (and the
+    // launch) may settle for a split of the L1 / shared array that holds fewer CTAs per SM than the kernel was sized for
+    cudaFuncSetAttribute(attn_decode_tma_kernel<G>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }

@@ -308,6 +308,9 @@ extern "C" int b200_attn_prefill(const void* q, long long ld_q, const void* k, l
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    // ask for the largest shared-memory carveout: with the default preference the occupancy calculator (and the
+    // launch) may settle for a split of the L1 / shared array that holds fewer CTAs per SM than the kernel was sized for
+    cudaFuncSetAttribute(attn_prefill_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }

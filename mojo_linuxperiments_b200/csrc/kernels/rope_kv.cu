@@ -46,9 +46,11 @@ struct RopeParams {
 // grid (tokens, ceil(heads / 4)), 4 warps; a warp handles one head, lane l holds elements l, l+32, l+64, l+96
 __global__ void __launch_bounds__(128) rope_kv_kernel(const RopeParams p) {
   pdl_launch_dependents();   // the next kernel may start its prologue now
+  B200_TRACE_INIT();
   if (threadIdx.x == 0) B200_TRACE(TK_ROPE_KV, TP_START);
   pdl_wait();                // everything before this kernel in the stream has completed
   if (threadIdx.x == 0) B200_TRACE(TK_ROPE_KV, TP_DEPS);
+  B200_TRACE_FLUSH(TK_ROPE_KV);
 
   const int tok = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;

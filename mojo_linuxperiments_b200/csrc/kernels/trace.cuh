@@ -1,8 +1,8 @@
 // In-kernel time stamps for overlap timelines (compiled in only with -DB200RT_TRACE: the production library has none).
 //
-// A stamped kernel calls B200_TRACE(kernel, phase) from one thread of a CTA at the points of interest; each call
-// appends {%globaltimer, kernel, phase, SM id, CTA index, grid size} to a ring in device memory that the host handed
-// over with b200_trace_set().  Read back, the ring shows for every launch when its CTAs started, when their inputs
+// A stamped kernel calls B200_TRACE_INIT() at its top, B200_TRACE(kernel, phase) from one thread of a CTA at the points
+// of interest and B200_TRACE_FLUSH(kernel) where it leaves; each stamp ends up as {%globaltimer, kernel, phase, SM id,
+// CTA index, grid size} in a ring in device memory that the host handed over with b200_trace_set().  Read back, the ring shows for every launch when its CTAs started, when their inputs
 // arrived, when the tensor core finished, when a peer's data landed: which part of a launch overlaps what.  The
 // reference only prints topology (numa/numa.mojo:166-176); it has no timers.
 //
@@ -29,21 +29,53 @@ TraceHostState& trace_host_state();                        // trace.cu
 static __device__ unsigned long long* g_trace_buf = nullptr;    // [0] = records written so far, records from [2]
 static __device__ unsigned g_trace_cap = 0;
 
+// Stamps are collected in shared memory while the CTA runs (a shared-memory atomic and two stores: tens of cycles) and
+// written to the ring when the CTA leaves, so the round trips to global memory do not sit between the phases that are
+// being timed.  Up to TRACE_MAX_LOCAL stamps per CTA; more are dropped.
+constexpr unsigned TRACE_MAX_LOCAL = 24;
+struct TraceLocal {
+  unsigned n;
+  unsigned phase[TRACE_MAX_LOCAL];
+  unsigned long long t[TRACE_MAX_LOCAL];
+};
+__device__ __forceinline__ TraceLocal& trace_local() {
+  __shared__ TraceLocal tl;
+  return tl;
+}
+// one thread, before the first barrier of the kernel
+__device__ __forceinline__ void trace_init() { trace_local().n = 0; }
+
 __device__ __forceinline__ void trace_stamp(unsigned kernel, unsigned phase) {
-  unsigned long long* b = g_trace_buf;
-  if (!b) return;
-  const unsigned i = atomicAdd(reinterpret_cast<unsigned*>(b), 1u);
-  if (i >= g_trace_cap) return;
-  unsigned smid;
-  asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+  (void)kernel;
+  if (!g_trace_buf) return;
+  TraceLocal& tl = trace_local();
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  const unsigned i = atomicAdd(&tl.n, 1u);
+  if (i < TRACE_MAX_LOCAL) { tl.t[i] = t; tl.phase[i] = phase; }
+}
+
+// one thread, after a barrier that follows the CTA's last stamp
+__device__ __forceinline__ void trace_flush(unsigned kernel) {
+  unsigned long long* b = g_trace_buf;
+  if (!b) return;
+  TraceLocal& tl = trace_local();
+  const unsigned n = min(tl.n, TRACE_MAX_LOCAL);
+  if (n == 0) return;
+  const unsigned base = atomicAdd(reinterpret_cast<unsigned*>(b), n);
+  unsigned smid;
+  asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
   const unsigned cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
   const unsigned grid = gridDim.x * gridDim.y * gridDim.z;
-  b[2 + 2 * static_cast<size_t>(i)] = t;
-  b[3 + 2 * static_cast<size_t>(i)] = (static_cast<unsigned long long>(kernel & 63u) << 58) | (static_cast<unsigned long long>(phase & 63u) << 52) |
-                                      (static_cast<unsigned long long>(smid & 1023u) << 42) | (static_cast<unsigned long long>(cta & 0x1fffffu) << 21) |
-                                      static_cast<unsigned long long>(grid & 0x1fffffu);
+  for (unsigned k = 0; k < n; ++k) {
+    const unsigned i = base + k;
+    if (i >= g_trace_cap) break;
+    b[2 + 2 * static_cast<size_t>(i)] = tl.t[k];
+    b[3 + 2 * static_cast<size_t>(i)] = (static_cast<unsigned long long>(kernel & 63u) << 58) | (static_cast<unsigned long long>(tl.phase[k] & 63u) << 52) |
+                                        (static_cast<unsigned long long>(smid & 1023u) << 42) | (static_cast<unsigned long long>(cta & 0x1fffffu) << 21) |
+                                        static_cast<unsigned long long>(grid & 0x1fffffu);
+  }
+  tl.n = 0;
 }
 
 // host: make this translation unit's device variables follow the ring the host set last
@@ -57,9 +89,14 @@ static inline void trace_refresh() {
   }
 }
 #define B200_TRACE(kernel, phase) ::b200::trace_stamp((kernel), (phase))
+#define B200_TRACE_INIT() do { if (threadIdx.x == 0) ::b200::trace_init(); } while (0)
+// every thread of the CTA calls this (it contains a barrier), at a point all of them reach
+#define B200_TRACE_FLUSH(kernel) do { __syncthreads(); if (threadIdx.x == 0) ::b200::trace_flush(kernel); } while (0)
 #else
 static inline void trace_refresh() {}
 #define B200_TRACE(kernel, phase) do { } while (0)
+#define B200_TRACE_INIT() do { } while (0)
+#define B200_TRACE_FLUSH(kernel) do { } while (0)
 #endif
 
 }  // namespace b200

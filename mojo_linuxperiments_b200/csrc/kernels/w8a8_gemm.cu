@@ -454,6 +454,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(w8a8_gemm_kernel<BN, STAGES, SWAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    // ask for the largest shared-memory carveout: with the default preference the occupancy calculator (and the
+    // launch) may settle for a split of the L1 / shared array that holds fewer CTAs per SM than the kernel was sized for
+    cudaFuncSetAttribute(w8a8_gemm_kernel<BN, STAGES, SWAP>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }

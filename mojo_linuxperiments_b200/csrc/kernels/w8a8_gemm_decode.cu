@@ -4,13 +4,22 @@
 //
 // The op is bound by the bytes of Wq, so the grid is shaped for bandwidth, not for the tensor core:
 //   * one CTA = 128 output channels x (K / S) of the reduction; the S CTAs of a cluster share one output tile;
-//   * S is chosen so that the grid has roughly two CTAs per SM (shared memory is sized for two co-resident CTAs),
-//     which keeps > 150 KB of TMA loads in flight per SM and lets CTAs of different tiles overlap head and tail;
+//   * shared memory is sized for two co-resident CTAs per SM (up to 32 tokens; the 64-token form takes the SM alone
+//     with a deeper pipeline), which keeps > 150 KB of TMA loads in flight per SM and lets CTAs of different tiles
+//     overlap head and tail.  The occupancy calculator answers "1 CTA per SM" for every kernel that allocates tensor
+//     memory (tcgen05.alloc), whatever its other resources; in-kernel time stamps show two CTAs per SM running, so
+//     the host doubles the calculator's cluster counts for the two-CTA forms;
 //   * each CTA runs the usual TMA -> tcgen05.mma.kind::i8 -> TMEM pipeline (weights are the 128-row A operand, the
 //     token tile of BN in {16,32,64} rows is the B operand);
 //   * the S partial accumulators are combined through distributed shared memory: every CTA sends, for each of
-//     the S row slices of the tile, its int32 partial to the CTA that owns the slice (st.shared::cluster), the
-//     cluster synchronises, and each CTA reduces and writes 128/S channels.  No global scratch, no atomics.
+//     the S row slices of the tile, its int32 partial to the CTA that owns the slice (16-byte st.shared::cluster
+//     into an exchange buffer of its own, so nobody waits for a pipeline to drain), the cluster synchronises once,
+//     and each CTA reduces and writes 128/S channels.  No global scratch, no atomics.  The "every CTA of the cluster
+//     runs" barrier that distributed shared memory needs is arrived at when the kernel starts and waited for just
+//     before the exchange, so its latency hides behind the weight stream.
+//   * the host only uses a split whose clusters are all resident at once (occupancy query, with a margin for the
+//     neighbouring kernels that programmatic dependent launch keeps on the SMs): a grid that needs a second wave of
+//     clusters doubles the latency of an op that is all latency.
 // All mbarrier waits are bounded; a CTA that gives up still reaches both cluster barriers, so peers never hang.
 //
 // Fused all-reduce (row-parallel layers under tensor parallelism): with an `ArTail` the CTAs write their bf16 tile of
@@ -38,6 +47,13 @@ struct ArTail {
   // one NVLink trip, no fence, no grid-wide counter.  recv_off: byte offsets of the two slots in every heap.
   int ll;
   size_t recv_off[2];
+  // Two-hop form of the low-latency tail (more than a few tokens): the CTA that finishes a column slice sends its
+  // partial only to the rank that owns the slice (slice index modulo world); the owner's CTA for that slice sums
+  // the world partials and broadcasts the result as {2 x bf16, epoch} words into a second receive area ([M][N/2]
+  // words, two slots by parity) of every rank.  Each rank then receives 2 x M x N/2 words instead of world x M x N/2,
+  // for one more NVLink trip; every rank ends with the owner's bits.  recv2_off: byte offsets of the two slots.
+  int two_hop;
+  size_t recv2_off[2];
 };
 
 struct DecodeGemmParams {
@@ -56,8 +72,42 @@ struct DecodeGemmParams {
   const int* grp_counts;
 };
 
+// Where a finished output element goes.  A plain struct of scalars (not a capturing lambda: called from the epilogue
+// loops, that cost a chain of local-memory loads per element).
+struct OutSink {
+  int mode;                     // 0: y (+ residual), 1: shared-memory staging of the low-latency all-reduce, 2: bf16 partial in the heap
+  float* vals; int cw, m0, n_base;
+  __nv_bfloat16* part; int N;
+  void* y; const __nv_bfloat16* residual; int ldy, out_fp32;
+};
+__device__ __forceinline__ void emit1(const OutSink& k, int m, int n, float v) {
+  if (k.mode == 1) { k.vals[(m - k.m0) * k.cw + (n - k.n_base)] = v; return; }
+  if (k.mode == 2) { k.part[static_cast<size_t>(m) * k.N + n] = __float2bfloat16(v); return; }
+  const size_t o = static_cast<size_t>(m) * k.ldy + n;
+  if (k.residual) v += __bfloat162float(k.residual[o]);
+  if (k.out_fp32) reinterpret_cast<float*>(k.y)[o] = v;
+  else reinterpret_cast<__nv_bfloat16*>(k.y)[o] = __float2bfloat16(v);
+}
+// two adjacent channels n (even), n + 1 of one token
+__device__ __forceinline__ void emit2(const OutSink& k, int m, int n, float v0, float v1) {
+  if (k.mode == 1) { *reinterpret_cast<float2*>(k.vals + (m - k.m0) * k.cw + (n - k.n_base)) = make_float2(v0, v1); return; }
+  if (k.mode == 2) { *reinterpret_cast<__nv_bfloat162*>(k.part + static_cast<size_t>(m) * k.N + n) = __floats2bfloat162_rn(v0, v1); return; }
+  const size_t o = static_cast<size_t>(m) * k.ldy + n;
+  if (k.out_fp32 || (o & 1)) { emit1(k, m, n, v0); emit1(k, m, n + 1, v1); return; }
+  if (k.residual) {
+    const __nv_bfloat162 rb = *reinterpret_cast<const __nv_bfloat162*>(k.residual + o);
+    v0 += __low2float(rb); v1 += __high2float(rb);
+  }
+  *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(k.y) + o) = __floats2bfloat162_rn(v0, v1);
+}
+
+// dynamic shared memory: pipeline stages, split-K exchange buffer, channel / token scales, barriers, alignment slack
+constexpr int decode_smem_bytes(int bn, int stages) {
+  return stages * (TILE_N * BLOCK_K + bn * BLOCK_K) + (TILE_N + 16) * (bn + 4) * 4 + (TILE_N + 64) * 4 + 1024 + 256;
+}
+
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(GEMM_THREADS)
+__global__ void __launch_bounds__(GEMM_THREADS, (BN == 64 ? 1 : 2))
 w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_x,
                         const DecodeGemmParams p) {
   constexpr int A_BYTES = TILE_N * BLOCK_K;
@@ -65,13 +115,18 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
   constexpr uint32_t IDESC = umma_idesc_i8(TILE_N, BN);
-  static_assert(STAGES * STAGE_BYTES >= 2 * BN * TILE_N * 4, "exchange and staging buffers alias the pipeline stages");
+  constexpr int XS = BN + 4;                      // words per channel row of the exchange buffer (16-byte aligned rows)
+  constexpr int EX_ROWS = TILE_N + 16;            // S senders x (slice of at most 2 * ceil(64 / S) channels) <= 128 + 2 S
+  constexpr int EX_BYTES = EX_ROWS * XS * 4;      // [sender][channel of the slice][token]
+  static_assert(STAGES * STAGE_BYTES >= BN * TILE_N * 4, "the staging buffer of the all-reduce tail aliases the pipeline stages");
 
   pdl_launch_dependents();     // the next kernel may be scheduled: it only reads our output after its own pdl_wait
-  if (threadIdx.x == 0) B200_TRACE(TK_GEMM_DECODE, TP_START);
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);      // full[S], empty[S], tfull
+  int32_t* ex = reinterpret_cast<int32_t*>(smem + STAGES * STAGE_BYTES);          // split-K exchange buffer
+  float* sw_s = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + EX_BYTES);  // [128] channel scales of this tile
+  float* sx_s = sw_s + TILE_N;                                                     // [BN] token scales
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sx_s + 64);                         // full[S], empty[S], tfull
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -103,12 +158,20 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     mbar_init(tfull_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
+    B200_TRACE_INIT();
+    B200_TRACE(TK_GEMM_DECODE, TP_START);
   }
   if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS); tmem_relinquish(); }
+  // channel scales never change: they are staged before the dependency wait
+  if (threadIdx.x >= 64) {
+    const int n = n_tile * TILE_N + (threadIdx.x - 64);
+    sw_s[threadIdx.x - 64] = n < p.N ? __ldg(p.sw + w_base + n) : 0.f;
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (S > 1) cluster_arrive_relaxed();          // "this CTA runs": waited for just before the exchange
 
   // where a finished output element goes: y, or (fused all-reduce) this rank's slot of the symmetric partial buffer
   const bool fuse_ar = p.ar.enabled != 0;
@@ -116,18 +179,12 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   __nv_bfloat16* part = nullptr;
   // low-latency all-reduce: finished values are staged in shared memory (behind the exchange buffer) first
   const bool ll = fuse_ar && p.ar.ll != 0;
-  float* vals = reinterpret_cast<float*>(smem + BN * TILE_N * 4);
-  const int cw = (S == 1) ? TILE_N : TILE_N / S;                       // channels this CTA finishes
-  const int n_base = n_tile * TILE_N + ((S == 1) ? 0 : rank * (TILE_N / S));
-  auto store_out = [&](int m, int n, float v) {
-    if (ll) { vals[(m - m0) * cw + (n - n_base)] = v; return; }
-    if (fuse_ar) { part[static_cast<size_t>(m) * p.N + n] = __float2bfloat16(v); return; }
-    const size_t o = static_cast<size_t>(m) * p.ldy + n;
-    if (p.residual) v += __bfloat162float(p.residual[o]);
-    if (p.out_fp32) reinterpret_cast<float*>(p.y)[o] = v;
-    else reinterpret_cast<__nv_bfloat16*>(p.y)[o] = __float2bfloat16(v);
-  };
-
+  float* vals = reinterpret_cast<float*>(smem);
+  // The cluster's CTA r finishes channels [slice0(r), slice0(r + 1)) of the tile: even-sized slices (the all-reduce tail
+  // packs channel pairs) that differ by at most two channels when S does not divide 128.
+  auto slice0 = [S](int r) { return 2 * ((64 * r + S - 1) / S); };
+  const int cw = slice0(rank + 1) - slice0(rank);                       // channels this CTA finishes
+  const int n_base = n_tile * TILE_N + slice0(rank);
   if (warp == 0) {
     if (lane == 0) {
       prefetch_tmap(&tmap_w);
@@ -198,16 +255,24 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   constexpr int CH = (BN >= 32) ? 32 : 16;
   bool acc_ok = false;
   if (epi) {
+    // token scales: the previous kernel's output, readable now that the dependency wait is behind us
+    if (et < BN) sx_s[et] = et < jmax ? p.sx[m0 + et] : 0.f;
     acc_ok = (kb1 > kb0) && mbar_wait(tfull_bar, 0, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (2 << 8)), limit);
     tc_fence_after();
     if (et == 0) B200_TRACE(TK_GEMM_DECODE, 4);
   }
 
+  OutSink sink;
+  sink.mode = ll ? 1 : (fuse_ar ? 2 : 0);
+  sink.vals = vals; sink.cw = cw; sink.m0 = m0; sink.n_base = n_base; sink.part = part; sink.N = p.N;
+  sink.y = p.y; sink.residual = p.residual; sink.ldy = p.ldy; sink.out_fp32 = p.out_fp32;
+
   if (S == 1) {
+    if (epi) asm volatile("bar.sync 1, 128;" ::: "memory");          // sx_s is complete (epilogue warps only)
     if (epi && acc_ok) {
       const int n = n_tile * TILE_N + row;
       const bool n_ok = n < p.N;
-      const float swn = n_ok ? __ldg(p.sw + w_base + n) : 0.f;
+      const float swn = sw_s[row];
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / CH; ++c) {
@@ -219,18 +284,18 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         if (!n_ok || jm <= 0) continue;
 #pragma unroll
         for (int j = 0; j < CH; ++j)
-          if (j < jm) store_out(mc + j, n, static_cast<float>(static_cast<int32_t>(r[j])) * swn * p.sx[mc + j]);
+          if (j < jm) emit1(sink, mc + j, n, static_cast<float>(static_cast<int32_t>(r[j])) * swn * sx_s[c * CH + j]);
       }
     }
   } else {
-    // every pipeline of the cluster has drained: stage memory can now hold the exchange buffer
-    cluster_sync_all();
+    cluster_wait_acquire();                                 // every CTA of the cluster runs: its shared memory exists
     if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 5);
-    const int rows_per = TILE_N / S;                        // channels each CTA of the cluster finishes
     if (epi) {
-      // exchange buffer in the owner CTA: [sender][token j][channel in slice] int32
-      const int owner = row / rows_per, row_in = row - owner * rows_per;
-      const uint32_t remote = mapa_shared(smem_base, static_cast<uint32_t>(owner));
+      // exchange buffer in the owner CTA: [sender][channel in the owner's slice][token] int32, XS words per channel row
+      const int owner = ((row >> 1) * S) >> 6, row_in = row - slice0(owner);
+      const int cw_owner = slice0(owner + 1) - slice0(owner);
+      const uint32_t remote = mapa_shared(smem_u32(ex), static_cast<uint32_t>(owner)) +
+                              4u * static_cast<uint32_t>((rank * cw_owner + row_in) * XS);
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / CH; ++c) {
@@ -242,26 +307,57 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 #pragma unroll
           for (int j = 0; j < CH; ++j) r[j] = 0u;           // empty K range (or aborted): contributes nothing
         }
+        if (c * CH < jmax) {                                // token rows beyond the batch are never read back
 #pragma unroll
-        for (int j = 0; j < CH; ++j) {
-          const int jj = c * CH + j;
-          if (jj < jmax) st_shared_cluster_u32(remote + 4u * ((rank * BN + jj) * rows_per + row_in), r[j]);
+          for (int j = 0; j < CH; j += 4)
+            st_shared_cluster_v4(remote + 4u * (c * CH + j), r[j], r[j + 1], r[j + 2], r[j + 3]);
         }
       }
     }
+    if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 10);
     tc_fence_before();
     cluster_sync_all();
     if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 6);
-    if (epi) {
-      const int32_t* ex = reinterpret_cast<const int32_t*>(smem);
-      const int total = rows_per * jmax;
-      for (int idx = et; idx < total; idx += 128) {
-        const int j = idx / rows_per, row_in = idx - j * rows_per;
-        int32_t acc = 0;
-        for (int s = 0; s < S; ++s) acc += ex[(s * BN + j) * rows_per + row_in];
-        const int n = n_tile * TILE_N + rank * rows_per + row_in;
-        if (n < p.N) store_out(m0 + j, n, static_cast<float>(acc) * __ldg(p.sw + w_base + n) * p.sx[m0 + j]);
+    {
+      // All six warps finish blocks of 4 tokens x 8 channel pairs: shared-memory reads spread over the banks (2-way
+      // conflicts at worst) and every token row gets 32 contiguous bytes, i.e. whole sectors.  With one warp per
+      // scheduler every instruction's latency is exposed, so the loop avoids integer division and works on two
+      // independent blocks at a time (all loads first, then the arithmetic and the stores).
+      const int pairs = cw >> 1, jt_n = (jmax + 3) >> 2, blocks = jt_n * ((pairs + 7) >> 3);
+      const int sw_off = n_base - n_tile * TILE_N;
+      const uint32_t inv_jt = (65536u + jt_n - 1) / jt_n;            // blk / jt_n == (blk * inv_jt) >> 16 for blk < 4096
+      const int lj = lane & 3, lp = lane >> 2;
+      constexpr int NWARP = GEMM_THREADS / 32;
+      for (int blk0 = warp; blk0 < blocks; blk0 += 2 * NWARP) {
+        int32_t a[2][2] = {{0, 0}, {0, 0}};
+        int jj[2], rr[2];
+        bool on[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int blk = blk0 + u * NWARP;
+          const int pt = static_cast<int>((static_cast<uint32_t>(blk) * inv_jt) >> 16), jt = blk - pt * jt_n;
+          jj[u] = 4 * jt + lj;
+          rr[u] = 2 * (8 * pt + lp);
+          on[u] = blk < blocks && jj[u] < jmax && rr[u] < cw;
+          if (on[u]) {
+            for (int s = 0; s < S; ++s) {
+              a[u][0] += ex[(s * cw + rr[u]) * XS + jj[u]];
+              a[u][1] += ex[(s * cw + rr[u] + 1) * XS + jj[u]];
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (!on[u]) continue;
+          const int n = n_base + rr[u];
+          const float sxj = sx_s[jj[u]];
+          const float v0 = static_cast<float>(a[u][0]) * sw_s[sw_off + rr[u]] * sxj;
+          const float v1 = static_cast<float>(a[u][1]) * sw_s[sw_off + rr[u] + 1] * sxj;
+          if (n + 1 < p.N) emit2(sink, m0 + jj[u], n, v0, v1);
+          else if (n < p.N) emit1(sink, m0 + jj[u], n, v0);
+        }
       }
+      if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 11);
     }
   }
 
@@ -271,11 +367,16 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS); }
 
   if (ll) {
-    // ---- low-latency all-reduce: push {payload, epoch} words to every rank, then sum what arrived here ----
+    // ---- low-latency all-reduce: push {payload, epoch} words, then sum what arrived here ----
     const PeerTable& t = p.ar.t;
     const int half = cw / 2, words = half * jmax;
     const size_t slot = p.ar.recv_off[ar_epoch & 1];
     const size_t src_stride = static_cast<size_t>(p.M) * (p.N / 2) * 8;          // bytes per source rank
+    const bool two_hop = p.ar.two_hop != 0;
+    // two-hop: who reduces this CTA's column slice
+    const int unit = n_tile * S + rank;
+    const int owner = two_hop ? unit % t.world : t.rank;
+    const bool own = owner == t.rank;
     __syncthreads();                                                             // vals complete
     if (epi) {
       for (int w = et; w < words; w += 128) {
@@ -285,11 +386,13 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         const __nv_bfloat162 pb = __floats2bfloat162_rn(vals[j * cw + 2 * c2], vals[j * cw + 2 * c2 + 1]);
         const uint32_t payload = *reinterpret_cast<const uint32_t*>(&pb);
         const size_t off = slot + t.rank * src_stride + (static_cast<size_t>(m0 + j) * (p.N / 2) + n / 2) * 8;
-        if (p.ar.use_nvls) multimem_st_ll(t.mc + off, payload, ar_epoch);
+        if (two_hop) st_ll_peer(t.data[owner] + off, payload, ar_epoch);
+        else if (p.ar.use_nvls) multimem_st_ll(t.mc + off, payload, ar_epoch);
         else for (int r = 0; r < t.world; ++r) st_ll_peer(t.data[r] + off, payload, ar_epoch);
       }
       if (et == 0) B200_TRACE(TK_GEMM_DECODE, 8);
       const uint8_t* mine = t.data[t.rank] + slot;
+      const size_t slot2 = p.ar.recv2_off[ar_epoch & 1];
       const uint64_t t_start = globaltimer_ns();
       bool good = true;
       for (int w = et; w < words && good; w += 128) {
@@ -297,28 +400,51 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         const int n = n_base + 2 * c2;
         if (n >= p.N) continue;
         const size_t eoff = (static_cast<size_t>(m0 + j) * (p.N / 2) + n / 2) * 8;
-        // all sources are requested at once so their latencies overlap; words that have not arrived are re-read
-        uint2 v[MAX_RANKS];
-#pragma unroll
-        for (int r = 0; r < MAX_RANKS; ++r)
-          if (r < t.world) v[r] = ld_ll(mine + r * src_stride + eoff);
-        uint32_t spins = 0;
-        while (good) {
-          bool all = true;
+        float a0 = 0.f, a1 = 0.f;
+        if (own) {
+          // all sources are requested at once so their latencies overlap; words that have not arrived are re-read
+          uint2 v[MAX_RANKS];
 #pragma unroll
           for (int r = 0; r < MAX_RANKS; ++r)
-            if (r < t.world && v[r].y != ar_epoch) { all = false; v[r] = ld_ll(mine + r * src_stride + eoff); }
-          if (all) break;
-          if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > limit) {
-            if (p.status) atomicCAS(p.status, 0, (ST_TIMEOUT_PEER_FLAG | (2 << 8)));
-            good = false;
-          }
-        }
-        if (!good) break;
-        float a0 = 0.f, a1 = 0.f;
+            if (r < t.world) v[r] = ld_ll(mine + r * src_stride + eoff);
+          uint32_t spins = 0;
+          while (good) {
+            bool all = true;
 #pragma unroll
-        for (int r = 0; r < MAX_RANKS; ++r)                                      // fixed order: same bits on every rank
-          if (r < t.world) { a0 += __uint_as_float(v[r].x << 16); a1 += __uint_as_float(v[r].x & 0xffff0000u); }
+            for (int r = 0; r < MAX_RANKS; ++r)
+              if (r < t.world && v[r].y != ar_epoch) { all = false; v[r] = ld_ll(mine + r * src_stride + eoff); }
+            if (all) break;
+            if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > limit) {
+              if (p.status) atomicCAS(p.status, 0, (ST_TIMEOUT_PEER_FLAG | (2 << 8)));
+              good = false;
+            }
+          }
+          if (!good) break;
+#pragma unroll
+          for (int r = 0; r < MAX_RANKS; ++r)                                    // fixed order: same bits on every rank
+            if (r < t.world) { a0 += __uint_as_float(v[r].x << 16); a1 += __uint_as_float(v[r].x & 0xffff0000u); }
+          if (two_hop) {
+            // the owner's rounding is what every rank gets
+            const __nv_bfloat162 fb = __floats2bfloat162_rn(a0, a1);
+            const uint32_t fin = *reinterpret_cast<const uint32_t*>(&fb);
+            if (p.ar.use_nvls) multimem_st_ll(t.mc + slot2 + eoff, fin, ar_epoch);
+            else for (int r = 0; r < t.world; ++r) if (r != t.rank) st_ll_peer(t.data[r] + slot2 + eoff, fin, ar_epoch);
+            a0 = __low2float(fb); a1 = __high2float(fb);
+          }
+        } else {
+          uint2 v = ld_ll(t.data[t.rank] + slot2 + eoff);
+          uint32_t spins = 0;
+          while (v.y != ar_epoch) {
+            if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > limit) {
+              if (p.status) atomicCAS(p.status, 0, (ST_TIMEOUT_PEER_FLAG | (2 << 8)));
+              good = false;
+              break;
+            }
+            v = ld_ll(t.data[t.rank] + slot2 + eoff);
+          }
+          if (!good) break;
+          a0 = __uint_as_float(v.x << 16); a1 = __uint_as_float(v.x & 0xffff0000u);
+        }
         const size_t o = static_cast<size_t>(m0 + j) * p.ldy + n;
         if (p.residual) {
           const __nv_bfloat162 rb = *reinterpret_cast<const __nv_bfloat162*>(p.residual + o);
@@ -380,14 +506,18 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       if (old == total_ctas - 1) { p.ar.words[2] = 0; __threadfence(); p.ar.words[0] = ar_epoch; }
     }
   }
+  B200_TRACE_FLUSH(TK_GEMM_DECODE);
 }
 
 template <int BN, int STAGES>
 static int launch_decode(const CUtensorMap& tw, const CUtensorMap& tx, const DecodeGemmParams& p, dim3 grid, cudaStream_t stream) {
-  constexpr int SMEM = STAGES * (TILE_N * BLOCK_K + BN * BLOCK_K) + 1024 + 256;
+  constexpr int SMEM = decode_smem_bytes(BN, STAGES);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(w8a8_gemm_decode_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    // ask for the largest shared-memory carveout: with the default preference the occupancy calculator (and the
+    // launch) may settle for a split of the L1 / shared array that holds fewer CTAs per SM than the kernel was sized for
+    cudaFuncSetAttribute(w8a8_gemm_decode_kernel<BN, STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }
@@ -396,13 +526,18 @@ static int launch_decode(const CUtensorMap& tw, const CUtensorMap& tx, const Dec
 }
 
 // How many clusters of `s` CTAs of this kernel the GPU can hold at once (cached per instantiation and cluster size).
+static int resident_clusters_reported(int bn, int s);
+
 template <int BN, int STAGES>
 static int max_resident_clusters(int s) {
   static int cache[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
   if (s < 1 || s > 8) return 0;
   if (cache[s] > 0) return cache[s];
-  constexpr int SMEM = STAGES * (TILE_N * BLOCK_K + BN * BLOCK_K) + 1024 + 256;
+  constexpr int SMEM = decode_smem_bytes(BN, STAGES);
   cudaFuncSetAttribute(w8a8_gemm_decode_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  // ask for the largest shared-memory carveout: with the default preference the occupancy calculator (and the
+  // launch) may settle for a split of the L1 / shared array that holds fewer CTAs per SM than the kernel was sized for
+  cudaFuncSetAttribute(w8a8_gemm_decode_kernel<BN, STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(s, 64, 1);
   cfg.blockDim = dim3(GEMM_THREADS);
@@ -417,22 +552,37 @@ static int max_resident_clusters(int s) {
   return cache[s];
 }
 
+// CTAs of the decode GEMM one SM really holds: two when twice the shared memory (plus the per-CTA reservation) fits
+static int ctas_per_sm(int bn) {
+  const int smem = bn <= 16 ? decode_smem_bytes(16, 5) : (bn <= 32 ? decode_smem_bytes(32, 4) : decode_smem_bytes(64, 7));
+  return 2 * (smem + 1024) <= 228 * 1024 ? 2 : 1;
+}
+
 static int resident_clusters(int bn, int s) {
+  return resident_clusters_reported(bn, s) * ctas_per_sm(bn);
+}
+
+static int resident_clusters_reported(int bn, int s) {
   switch (bn) {
-    case 16: return max_resident_clusters<16, 6>(s);
-    case 32: return max_resident_clusters<32, 5>(s);
-    default: return max_resident_clusters<64, 4>(s);
+    case 16: return max_resident_clusters<16, 5>(s);
+    case 32: return max_resident_clusters<32, 4>(s);
+    default: return max_resident_clusters<64, 7>(s);
   }
 }
 
-// splits along K: aim for about two CTAs per SM, powers of two up to 8, at least one k-block per CTA
-int decode_pick_splits(int tiles, int kblocks, int num_sms) {
+// Split along K: the largest cluster size (1..8, any value: slices need not divide the tile evenly) whose grid of
+// tiles x S CTAs (a) fits the SMs (two CTAs each for up to 32 tokens), (b) leaves every CTA at least two k-blocks, and (c) is resident at
+// once according to the occupancy query, with `margin` spare clusters.
+int decode_pick_splits(int tiles, int kblocks, int num_sms, int bn, int margin) {
   static int limit_env = -1;
   if (limit_env < 0) { const char* e = std::getenv("B200RT_GEMM_MAX_CTAS"); limit_env = e ? std::atoi(e) : 0; }
-  const int limit = limit_env > 0 ? limit_env : 2 * num_sms + num_sms / 2;
-  int s = 1;
-  while (s < 8 && tiles * s * 2 <= limit && kblocks >= s * 2) s *= 2;
-  return s;
+  const int limit = limit_env > 0 ? limit_env : num_sms * ctas_per_sm(bn);
+  int best = 1;
+  for (int s = 2; s <= 8; ++s) {
+    if (tiles * s > limit || kblocks < 2 * s) break;
+    if (tiles + margin <= resident_clusters(bn, s)) best = s;
+  }
+  return best;
 }
 
 }  // namespace b200
@@ -453,8 +603,10 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
   p.M = M; p.N = N; p.K = K;
   p.kblocks = (K + BLOCK_K - 1) / BLOCK_K;
   const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = groups > 0 ? groups : (M + bn - 1) / bn;
-  int s = force_splits > 0 ? force_splits : decode_pick_splits(n_tiles * m_tiles, p.kblocks, num_sms);
-  if (s != 1 && s != 2 && s != 4 && s != 8) return -1;
+  // A split whose clusters do not all fit on the GPU at once runs as two waves: twice the latency for an op that is
+  // nothing but latency.  (Grouped launches have one grid row per expert and are multi-wave by nature.)
+  int s = force_splits > 0 ? force_splits : decode_pick_splits(n_tiles * m_tiles, p.kblocks, num_sms, bn, groups > 0 ? -100000 : 1);
+  if (s < 1 || s > 8) return -1;
   p.splits = s;
   p.sx = sx; p.sw = sw; p.y = y; p.residual = static_cast<const __nv_bfloat16*>(residual);
   p.ldy = ldy; p.out_fp32 = out_fp32; p.status = status; p.limit_ns = 2000000000ull;
@@ -468,7 +620,7 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
     // many clusters of this size fit (clusters are placed per GPC, so this is less than SMs x CTAs-per-SM / size)
     // and narrow the split until the grid fits, keeping a margin of one cluster.
     if ((N % 8) || (ldy % 8) || out_fp32) return -2;
-    while (s >= 1 && n_tiles * m_tiles + 1 > resident_clusters(bn, s)) s >>= 1;
+    while (s >= 1 && n_tiles * m_tiles + 1 > resident_clusters(bn, s)) --s;
     if (s < 1) return -20;
     p.splits = s;
     p.limit_ns = static_cast<unsigned long long>(ar->limit_ms > 0 ? ar->limit_ms : 2000) * 1000000ull;
@@ -478,10 +630,41 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
   if (make_tmap_2d_u8(&tx, xq, static_cast<uint64_t>(K), static_cast<uint64_t>(xr), static_cast<uint64_t>(K), bn)) return -12;
   dim3 grid(s, n_tiles, m_tiles);
   switch (bn) {
-    case 16: return launch_decode<16, 6>(tw, tx, p, grid, stream);
-    case 32: return launch_decode<32, 5>(tw, tx, p, grid, stream);
-    default: return launch_decode<64, 4>(tw, tx, p, grid, stream);
+    case 16: return launch_decode<16, 5>(tw, tx, p, grid, stream);
+    case 32: return launch_decode<32, 4>(tw, tx, p, grid, stream);
+    default: return launch_decode<64, 7>(tw, tx, p, grid, stream);
   }
+}
+
+template <int BN, int STAGES>
+static void occupancy_facts(int* out) {
+  constexpr int SMEM = decode_smem_bytes(BN, STAGES);
+  cudaFuncSetAttribute(w8a8_gemm_decode_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  // ask for the largest shared-memory carveout: with the default preference the occupancy calculator (and the
+  // launch) may settle for a split of the L1 / shared array that holds fewer CTAs per SM than the kernel was sized for
+  cudaFuncSetAttribute(w8a8_gemm_decode_kernel<BN, STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  int blocks = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, w8a8_gemm_decode_kernel<BN, STAGES>, GEMM_THREADS, SMEM);
+  cudaFuncAttributes a{};
+  cudaFuncGetAttributes(&a, w8a8_gemm_decode_kernel<BN, STAGES>);
+  out[0] = blocks; out[1] = static_cast<int>(a.sharedSizeBytes); out[2] = a.numRegs; out[3] = SMEM;
+}
+// Occupancy facts of the decode GEMM for `m` tokens: {CTAs per SM without clusters, static shared bytes, registers per
+// thread, dynamic shared bytes}.
+extern "C" void b200_w8a8_gemm_decode_occupancy(int m, int* out4) {
+  if (m <= 16) occupancy_facts<16, 5>(out4); else if (m <= 32) occupancy_facts<32, 4>(out4); else occupancy_facts<64, 7>(out4);
+}
+
+// Occupancy calculator's answer for the 32-token decode GEMM at an arbitrary dynamic shared-memory size (diagnostics).
+extern "C" int b200_w8a8_gemm_decode_blocks_at(int smem_bytes) {
+  int blocks = 0;
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, w8a8_gemm_decode_kernel<32, 4>, GEMM_THREADS, smem_bytes);
+  return blocks;
+}
+
+// How many clusters of `splits` CTAs of the decode GEMM for `m` tokens this GPU holds at once (occupancy query).
+extern "C" int b200_w8a8_gemm_decode_resident_clusters(int m, int splits) {
+  return resident_clusters(m <= 16 ? 16 : (m <= 32 ? 32 : 64), splits);
 }
 
 extern "C" int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
@@ -508,7 +691,8 @@ extern "C" int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const v
                                         const void* residual, int M, int N, int K, int ldy, int* status, int num_sms,
                                         void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
                                         size_t part_off0, size_t part_off1, void* words, int limit_ms, int ll,
-                                        size_t recv_off0, size_t recv_off1, size_t recv_bytes, cudaStream_t stream) {
+                                        size_t recv_off0, size_t recv_off1, size_t recv_bytes, int two_hop,
+                                        size_t recv2_off0, size_t recv2_off1, size_t recv2_bytes, cudaStream_t stream) {
   if (world < 1 || world > MAX_RANKS) return -1;
   ArTail ar;
   for (int r = 0; r < MAX_RANKS; ++r) {
@@ -520,9 +704,16 @@ extern "C" int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const v
   ar.words = static_cast<uint32_t*>(words);
   ar.enabled = 1; ar.use_nvls = mc_base != nullptr; ar.limit_ms = limit_ms;
   ar.ll = ll; ar.recv_off[0] = recv_off0; ar.recv_off[1] = recv_off1;
+  ar.two_hop = (ll && two_hop && world > 1) ? 1 : 0; ar.recv2_off[0] = recv2_off0; ar.recv2_off[1] = recv2_off1;
   if (ll) {
     if ((recv_off0 % 8) || (recv_off1 % 8) || (N % 2)) return -2;
     if (static_cast<size_t>(world) * M * (N / 2) * 8 > recv_bytes) return -21;       // receive slot too small
+  }
+  if (ar.two_hop) {
+    if ((recv2_off0 % 8) || (recv2_off1 % 8)) return -2;
+    if (static_cast<size_t>(M) * (N / 2) * 8 > recv2_bytes) return -21;
+    // every rank has to own a slice, or the slot-reuse argument (a rank cannot run two launches ahead) breaks
+    if ((N + TILE_N - 1) / TILE_N < world) ar.two_hop = 0;
   }
   if ((part_off0 % 16) || (part_off1 % 16)) return -2;
   return decode_gemm_impl(xq, sx, wq, sw, y, residual, M, N, K, ldy, 0, status, num_sms, 0, &ar, stream);

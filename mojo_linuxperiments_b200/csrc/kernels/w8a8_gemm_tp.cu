@@ -549,6 +549,9 @@ static int launch_tp(const CUtensorMap& ta0, const CUtensorMap& ta1, const CUten
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(w8a8_gemm_tp_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    // ask for the largest shared-memory carveout: with the default preference the occupancy calculator (and the
+    // launch) may settle for a split of the L1 / shared array that holds fewer CTAs per SM than the kernel was sized for
+    cudaFuncSetAttribute(w8a8_gemm_tp_kernel<BN, STAGES>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }

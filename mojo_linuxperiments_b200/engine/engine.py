@@ -8,22 +8,30 @@ the GPU needs to run them once the model is sharded over several GPUs.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from ..models.config import ModelConfig, RuntimeConfig
 from ..models.decoder import Decoder, KVState
 from ..models import weights as Wt
-from ..ops.workspace import default_workspace
+from ..ops.workspace import Workspace, default_workspace, has_default_workspace, install_default_workspace
 from ..parallel.comm import Comm
+from .runtime import RankRuntime
 
 
 class Engine:
+    _instances = 0
+
     def __init__(self, cfg: ModelConfig, rt: RuntimeConfig | None = None, weights: dict | None = None, seed: int = 0,
                  device=None, comm: Comm | None = None):
         self.cfg = cfg
         self.rt = rt or RuntimeConfig()
         self.comm = comm or Comm.single()
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        # where this rank runs (host thread pinned beside its GPU) and where its long-lived buffers live (HBM arena)
+        self.runtime = RankRuntime(self.device)
+        self.heartbeat = None
         if weights is None:
             weights = Wt.random_shard(cfg, self.rt.tp, self.comm.rank, self.device, seed)
         self.tp_ctx = None
@@ -41,6 +49,8 @@ class Engine:
         self.positions = None
         self.kernels_per_step = 0
         self._stream = torch.cuda.Stream(device=self.device)
+        if self.comm.world > 1 and os.environ.get("B200RT_HEARTBEAT", "1") not in ("0", "false"):
+            self._start_heartbeat()
         self._admitted = 0          # tokens per sequence the KV pages of the running batch can hold
         self._host_len = 0          # tokens per sequence already in the cache (host-side mirror of ``positions``)
 
@@ -52,7 +62,8 @@ class Engine:
             self.kv = None                  # free the old cache before the new one is allocated
             self._graphs.clear()
             self._prefill_graphs.clear()
-            self.kv = KVState(self.cfg, self.rt, self.device, batch, self.rt.max_seq_len)
+            self._place_buffers(batch)
+            self.kv = KVState(self.cfg, self.rt, self.device, batch, self.rt.max_seq_len, alloc=self.runtime.zeros)
             self.tokens = torch.zeros(batch, dtype=torch.int64, device=self.device)
             self.positions = torch.zeros(batch, dtype=torch.int32, device=self.device)
         else:
@@ -67,11 +78,40 @@ class Engine:
         self._admitted = max_total_len
         self._host_len = 0
 
+    def _place_buffers(self, batch: int) -> None:
+        """One arena per rank (the reference: one arena per node, test_linux_threading.mojo:237-250) for the KV cache of
+        the new batch; the kernels' scratch / counters / status words get a small arena of their own the first time, which
+        lives as long as the rank (the KV arena is replaced whenever the batch geometry changes)."""
+        if not has_default_workspace(self.device) and self.runtime.make_scratch_arena(Workspace.nbytes() + (2 << 20)):
+            install_default_workspace(self.device, Workspace(self.device, alloc=self.runtime.scratch_zeros))
+        self.runtime.make_arena(KVState.nbytes(self.cfg, self.rt, batch, self.rt.max_seq_len) + (2 << 20))
+
+    def _start_heartbeat(self) -> None:
+        """Host-side failure detection between steps: every rank beats into the rendezvous store from a background
+        thread that also watches the peers; ``decode_step`` / ``prefill`` look at its verdict before they launch, so
+        a rank that has gone away turns into ``RankFailure`` on the host instead of a device-side wait that runs out."""
+        try:
+            import torch.distributed as dist
+            from ..utils.health import Heartbeat
+            store = dist.distributed_c10d._get_default_store()
+            Engine._instances += 1          # every rank builds its engines in the same order: the same key prefix
+            self.heartbeat = Heartbeat(store, self.comm.rank, self.comm.world, interval_s=0.2, timeout_s=5.0,
+                                       prefix=f"b200rt_hb_{Engine._instances}").start(monitor=True)
+        except Exception as e:
+            self.runtime.notes.append(f"heartbeat not started: {type(e).__name__}: {e}")
+            self.heartbeat = None
+
+    def memory_report(self) -> dict:
+        """Placement of the rank (GPU, NUMA node, pinned CPUs) and the arena's counters (used / remaining / high water)."""
+        return self.runtime.report()
+
     def prefill(self, prompts: torch.Tensor, use_graph: bool = True) -> torch.Tensor:
         """prompts int64 [B, S] (host or device; equal lengths).  Returns the first generated token per sequence
         (device tensor) and leaves the engine ready for ``decode_step``.  Long batches are processed in groups of
         whole sequences so that one call never carries more than ``rt.max_prefill_tokens`` tokens; each group's
         forward pass is one CUDA graph (captured at first use)."""
+        if self.heartbeat is not None:
+            self.heartbeat.check_fast()
         B, S = prompts.shape
         ids_all = prompts.to(self.device, non_blocking=True)
         group = max(1, min(B, self.rt.max_prefill_tokens // S))
@@ -132,6 +172,8 @@ class Engine:
 
         Raises before anything is launched when the step would write past the KV pages admitted in ``start_batch``:
         the kernels would refuse the write as well (status word), but the host knows first."""
+        if self.heartbeat is not None:
+            self.heartbeat.check_fast()
         if self._host_len + 1 > self._admitted:
             raise RuntimeError(f"decode step at position {self._host_len} exceeds the {self._admitted} tokens per "
                                f"sequence admitted by start_batch")

@@ -20,17 +20,28 @@ from .config import ModelConfig, RuntimeConfig, kv_heads_per_rank
 class KVState:
     """Paged KV cache of all layers of one rank plus the page table / lengths of the running batch."""
 
-    def __init__(self, cfg: ModelConfig, rt: RuntimeConfig, device, num_seqs: int, max_seq_len: int):
+    @staticmethod
+    def nbytes(cfg: ModelConfig, rt: RuntimeConfig, num_seqs: int, max_seq_len: int) -> int:
+        """Device bytes of a cache for ``num_seqs`` sequences of up to ``max_seq_len`` tokens (storage + tables)."""
+        max_pages = (max_seq_len + rt.page_size - 1) // rt.page_size
+        hkv = kv_heads_per_rank(cfg, rt.tp)
+        return (cfg.n_layers * num_seqs * max_pages * 2 * hkv * rt.page_size * cfg.head_dim * 2
+                + num_seqs * max_pages * 4 + num_seqs * 4 + 3 * 1024)
+
+    def __init__(self, cfg: ModelConfig, rt: RuntimeConfig, device, num_seqs: int, max_seq_len: int, alloc=None):
+        """``alloc(shape, dtype) -> zeroed tensor``: where the cache lives (the rank's HBM arena); default torch.zeros."""
+        if alloc is None:
+            def alloc(shape, dtype):
+                return torch.zeros(shape, dtype=dtype, device=device)
         self.page_size = rt.page_size
         self.max_pages = (max_seq_len + rt.page_size - 1) // rt.page_size
         self.num_pages = num_seqs * self.max_pages
         hkv = kv_heads_per_rank(cfg, rt.tp)
-        self.storage = torch.zeros((cfg.n_layers, self.num_pages, 2, hkv, rt.page_size, cfg.head_dim),
-                                   dtype=torch.bfloat16, device=device)
+        self.storage = alloc((cfg.n_layers, self.num_pages, 2, hkv, rt.page_size, cfg.head_dim), torch.bfloat16)
         self.layers = [A.PagedKVCache(self.num_pages, hkv, rt.page_size, device, storage=self.storage[l])
                        for l in range(cfg.n_layers)]
-        self.page_table = torch.zeros((num_seqs, self.max_pages), dtype=torch.int32, device=device)
-        self.seq_lens = torch.zeros((num_seqs,), dtype=torch.int32, device=device)
+        self.page_table = alloc((num_seqs, self.max_pages), torch.int32)
+        self.seq_lens = alloc((num_seqs,), torch.int32)
         self.free_pages = list(range(self.num_pages - 1, -1, -1))
         self.owned: dict[int, list[int]] = {}
 
@@ -74,6 +85,9 @@ class Decoder:
             from .moe import MoEBlock
             self.moe = MoEBlock(cfg, rt, self.comm, self.device, tp_ctx=tp_ctx)
         self._decode_scratch: dict[int, A.DecodeAttnScratch] = {}
+        import os
+        # decode attention with rope / KV append / output quantisation folded in (B200RT_FUSED_ATTN=0: three launches)
+        self.fused_attention = os.environ.get("B200RT_FUSED_ATTN", "1") not in ("0", "false")
 
     # -- building blocks ------------------------------------------------------------------------------------
     def _norm_quant(self, h, delta, gamma, want_normed=False):
@@ -99,20 +113,27 @@ class Decoder:
                                 k_norm_w=W.get("k_norm"), eps=self.cfg.eps)
             v = qkv.view(M, self.hq + 2 * self.hkv, self.cfg.head_dim)[:, self.hq + self.hkv:]
             return A.attn_prefill(q, k_rot, v, cu_seqlens, max_len, scale=self.scale)
-        q = A.rope_kv_write(qkv, positions, self.cos, self.sin, self.hq, self.hkv, cache=cache,
-                            page_table=kv.page_table, seq_ids=None, q_norm_w=W.get("q_norm"),
-                            k_norm_w=W.get("k_norm"), eps=self.cfg.eps)
         impl = A.decode_impl(cache.page_size, self.hq // self.hkv)
         if impl in ("tc", "tcp"):
             splits = A.pick_decode_splits_tc(M, self.hkv, kv.page_table.shape[1] * cache.page_size)
         else:
             splits = A.pick_decode_splits(M, self.hkv, max_len)
+        fused = impl == "tc" and self.fused_attention
         sc = None
-        if splits > 1:
+        if splits > 1 or fused:
             sc = self._decode_scratch.get((M, splits))
             if sc is None:
                 sc = A.DecodeAttnScratch(M, self.hq, self.hkv, splits, qkv.device)
                 self._decode_scratch[(M, splits)] = sc
+        if fused:
+            # one launch: per-head norm + rotary embedding + KV append + attention + rotation / int8 of the output
+            xq, sx, _ = A.attn_decode_fused(qkv, positions, self.cos, self.sin, self.hq, self.hkv, cache, kv.page_table,
+                                            kv.seq_lens, scratch=sc, splits=splits, scale=self.scale,
+                                            q_norm_w=W.get("q_norm"), k_norm_w=W.get("k_norm"), eps=self.cfg.eps)
+            return xq, sx
+        q = A.rope_kv_write(qkv, positions, self.cos, self.sin, self.hq, self.hkv, cache=cache,
+                            page_table=kv.page_table, seq_ids=None, q_norm_w=W.get("q_norm"),
+                            k_norm_w=W.get("k_norm"), eps=self.cfg.eps)
         return A.attn_decode(q, cache, kv.page_table, kv.seq_lens, scratch=sc, splits=splits, scale=self.scale)
 
     def _mlp(self, l, xq, sx, xn):
@@ -143,7 +164,7 @@ class Decoder:
             xq, sx = self._norm_quant(h, delta, W["attn_norm"])
             qkv = L.w8a8_gemm(xq, sx, W["qkv"].qweight, W["qkv"].scale)
             attn = self._attention(l, qkv, positions, kv, mode, cu_seqlens, max_len, seq_ids)
-            aq, sa = L.act_quant(attn.view(attn.shape[0], -1))
+            aq, sa = attn if isinstance(attn, tuple) else L.act_quant(attn.view(attn.shape[0], -1))
             delta = self._row_parallel(aq, sa, W["o"])
             xq, sx = self._norm_quant(h, delta, W["mlp_norm"])      # the router, too, consumes the quantised rows
             delta = self._mlp(l, xq, sx, None)

@@ -61,6 +61,7 @@ class _Sig:
     b200_w8a8_gemm_ws_bytes = (c_size_t, [I, I, I, I])
     b200_w8a8_gemm = (I, [P, P, P, P, P, P, I, I, I, I, I, P, c_size_t, P, I, P, I, I, P])
     b200_w8a8_gemm_decode = (I, [P, P, P, P, P, P, I, I, I, I, I, P, I, I, P])
+    b200_w8a8_gemm_decode_resident_clusters = (I, [I, I])
     b200_peer_allreduce = (I, [P, P, P, I, I, c_size_t, c_size_t, P, P, c_size_t, I, I, P, P, I, I, I, P])
     b200_peer_argmax = (I, [P, P, I, I, c_size_t, P, P, I, I, P, P, P, I, P])
     b200_w8a8_gemm_ag = (I, [P, P, P, P, P, I, I, I, I, I, P, P, I, I, c_size_t, c_size_t, c_size_t, c_size_t, c_size_t, c_size_t, I, I, P, P, I, I, P, I, I, P])
@@ -71,7 +72,7 @@ class _Sig:
     b200_ep_combine_scatter = (I, [P, LL, P, P, I, I, I, I, P, I, I, c_size_t, c_size_t, c_size_t, I, P, P, I, P, I, P])
     b200_ep_combine_reduce = (I, [P, I, I, I, I, I, P, I, I, c_size_t, c_size_t, c_size_t, I, P, P, LL, P, I, I, P])
     b200_ag_sync = (I, [P, I, I, c_size_t, c_size_t, I, I, I, P, I, I, P, I, P])
-    b200_w8a8_gemm_decode_ar = (I, [P, P, P, P, P, P, I, I, I, I, P, I, P, P, P, I, I, c_size_t, c_size_t, P, I, I, c_size_t, c_size_t, c_size_t, P])
+    b200_w8a8_gemm_decode_ar = (I, [P, P, P, P, P, P, I, I, I, I, P, I, P, P, P, I, I, c_size_t, c_size_t, P, I, I, c_size_t, c_size_t, c_size_t, I, c_size_t, c_size_t, c_size_t, P])
     b200_where_am_i = (I, [P, I, I, P])
     b200_trace_compiled = (I, [])
     b200_trace_set = (I, [P, ctypes.c_uint])
@@ -93,6 +94,7 @@ class _Sig:
     b200_attn_decode_tma = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
     b200_attn_decode_tc = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
     b200_attn_decode_tc_min_splits = (I, [I])
+    b200_attn_decode_fused = (I, [P, LL, P, P, P, I, P, P, F, P, I, P, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
     b200_attn_decode_tcp = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, I, P])
     b200_attn_prefill = (I, [P, LL, P, LL, P, LL, P, P, I, I, I, I, I, F, P, P])
     b200_attn_prefill_split = (I, [P, LL, P, LL, P, LL, P, P, I, I, I, I, I, F, I, P, P, P])

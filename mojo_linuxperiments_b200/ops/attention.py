@@ -56,9 +56,9 @@ def attn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: 
                  scale: float | None = None, out: torch.Tensor | None = None, kv_chunk: int | None = None) -> torch.Tensor:
     """Causal GQA attention over concatenated sequences. q [T, hq, 128], k/v [T, hkv, 128] (token stride free).
 
-    ``kv_chunk`` > 0 (default: B200RT_PREFILL_SPLIT, else 0) selects the split-KV form: every ``kv_chunk`` KV tiles of
-    128 tokens of a query tile are a CTA of their own and a merge kernel combines them - more parallelism when there are
-    few (sequence, head) pairs.  That form is opt-in: it compiles but has not been run on hardware yet."""
+    ``kv_chunk`` > 0 selects the split-KV form: every ``kv_chunk`` KV tiles of 128 tokens of a query tile are a CTA of
+    their own and a merge kernel combines them - more parallelism when there are few (sequence, head) pairs.  Default
+    (``None``): B200RT_PREFILL_SPLIT if set, else split exactly when the un-split grid would not fill the GPU."""
     T, hq, d = q.shape
     hkv = k.shape[1]
     assert d == HEAD_DIM and q.dtype == torch.bfloat16 and q.stride(2) == 1 and q.stride(1) == d
@@ -69,7 +69,19 @@ def attn_prefill(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_seqlens: 
     ws = default_workspace(q.device)
     if kv_chunk is None:
         import os
-        kv_chunk = int(os.environ.get("B200RT_PREFILL_SPLIT", "0") or 0)
+        env = os.environ.get("B200RT_PREFILL_SPLIT", "")
+        if env != "":
+            kv_chunk = int(env)
+        else:
+            # Few (sequence, head, query tile) CTAs leave most SMs idle while the last query tiles walk their KV tiles
+            # alone: split the KV range then (measured on B200: 1 x 1,024 tokens x 4 heads 33 -> 16 us, 1 x 4,096 x 4
+            # heads 143 -> 103 us; with >= 148 CTAs the un-split kernel is faster).
+            B_ = cu_seqlens.numel() - 1
+            n_q = (int(max_len) + 127) // 128
+            sms = _lib.num_sms(q.device.index)
+            kv_chunk = 0
+            if B_ * hq * n_q < sms and n_q > 1:
+                kv_chunk = max(1, min(8, B_ * hq * n_q * (n_q + 1) // 2 // sms))
     if kv_chunk > 0:
         B = cu_seqlens.numel() - 1
         n = _lib.lib().b200_attn_prefill_split_scratch_floats(B, hq, int(max_len), kv_chunk)
@@ -98,6 +110,10 @@ class DecodeAttnScratch:
         self.buf = torch.empty(max(n, 1), dtype=torch.float32, device=device)
         self.counters = torch.zeros(B * hkv, dtype=torch.int32, device=device)
         self.splits = splits
+        # the fused kernel's quantising epilogue, when a token's heads span several CTAs (hkv > 1)
+        self.rot = torch.empty(B * hq * HEAD_DIM, dtype=torch.float32, device=device) if hkv > 1 else None
+        self.blk_amax = torch.zeros(B * hkv, dtype=torch.float32, device=device) if hkv > 1 else None
+        self.seq_counters = torch.zeros(B, dtype=torch.int32, device=device) if hkv > 1 else None
 
 
 TC_BLOCKS_PER_CTA = 4          # the tensor-core decode kernel holds at most 4 x 128 cached tokens per CTA
@@ -190,6 +206,37 @@ def attn_decode(q: torch.Tensor, cache: PagedKVCache, page_table: torch.Tensor, 
         _lib.stream())
     _lib.check(rc, "attn_decode")
     return out
+
+
+def attn_decode_fused(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, hq: int, hkv: int,
+                      cache: PagedKVCache, page_table: torch.Tensor, seq_lens: torch.Tensor, *,
+                      scratch: DecodeAttnScratch | None = None, splits: int = 1, scale: float | None = None,
+                      q_norm_w=None, k_norm_w=None, eps: float = 1e-6, quantize: bool = True, want_out: bool = False):
+    """One launch for rope_kv_write + decode attention + the activation prologue of o_proj.
+
+    qkv bf16 [B, (hq + 2 hkv) * 128]: the new token's raw projections; ``positions[b]`` is where it goes in the cache and
+    ``seq_lens[b]`` counts it.  Returns ``(xq int8 [B, hq*128], sx fp32 [B], out bf16 [B, hq, 128] or None)``; with
+    ``quantize=False`` only ``out``.  Needs page size 16 and a group size of 1/2/4/8 (the tcgen05 kernel)."""
+    B = qkv.shape[0]
+    d = HEAD_DIM
+    assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape[1] == (hq + 2 * hkv) * d
+    assert positions.dtype == torch.int32 and page_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
+    assert cache.page_size == 16 and cache.kv_heads == hkv and hq // hkv in (1, 2, 4, 8)
+    splits = max(splits, tc_min_splits(page_table.shape[1] * cache.page_size))
+    if scratch is None or scratch.splits != splits:
+        scratch = DecodeAttnScratch(B, hq, hkv, splits, qkv.device)
+    out = torch.empty((B, hq, d), dtype=torch.bfloat16, device=qkv.device) if (want_out or not quantize) else None
+    xq = torch.empty((B, hq * d), dtype=torch.int8, device=qkv.device) if quantize else None
+    sx = torch.empty((B,), dtype=torch.float32, device=qkv.device) if quantize else None
+    rc = _lib.lib().b200_attn_decode_fused(
+        qkv.data_ptr(), qkv.stride(0), positions.data_ptr(), cos.data_ptr(), sin.data_ptr(), cos.shape[0],
+        _lib.ptr(q_norm_w), _lib.ptr(k_norm_w), float(eps), cache.data.data_ptr(), cache.num_pages, page_table.data_ptr(),
+        seq_lens.data_ptr(), _lib.ptr(out), _lib.ptr(xq), xq.stride(0) if xq is not None else 0, _lib.ptr(sx),
+        scratch.buf.data_ptr(), scratch.counters.data_ptr(), _lib.ptr(scratch.rot), _lib.ptr(scratch.blk_amax),
+        _lib.ptr(scratch.seq_counters), B, hq, hkv, cache.page_size, page_table.shape[1], splits,
+        float(scale if scale is not None else 1.0 / math.sqrt(d)), default_workspace(qkv.device).status.data_ptr(), _lib.stream())
+    _lib.check(rc, "attn_decode_fused")
+    return (xq, sx, out) if quantize else out
 
 
 def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -15,11 +15,22 @@ _STATUS_NAMES = {
 
 
 class Workspace:
-    def __init__(self, device: torch.device, ws_bytes: int = 64 << 20, counters: int = 1 << 16):
+    DEFAULT_WS_BYTES = 64 << 20
+    DEFAULT_COUNTERS = 1 << 16
+
+    @classmethod
+    def nbytes(cls, ws_bytes: int | None = None, counters: int | None = None) -> int:
+        return (ws_bytes or cls.DEFAULT_WS_BYTES) + 4 * (counters or cls.DEFAULT_COUNTERS) + 16 + 3 * 1024
+
+    def __init__(self, device: torch.device, ws_bytes: int = 64 << 20, counters: int = 1 << 16, alloc=None):
+        """``alloc(shape, dtype) -> zeroed tensor`` places the buffers (e.g. in a rank's HBM arena); default torch."""
+        if alloc is None:
+            def alloc(shape, dtype):
+                return torch.zeros(shape, dtype=dtype, device=device)
         self.device = device
-        self.ws = torch.zeros(ws_bytes // 4, dtype=torch.int32, device=device)
-        self.counters = torch.zeros(counters, dtype=torch.int32, device=device)
-        self.status = torch.zeros(4, dtype=torch.int32, device=device)
+        self.ws = alloc((ws_bytes // 4,), torch.int32)
+        self.counters = alloc((counters,), torch.int32)
+        self.status = alloc((4,), torch.int32)
 
     @property
     def ws_bytes(self) -> int:
@@ -36,6 +47,17 @@ class Workspace:
 
 
 _default: dict[int, Workspace] = {}
+
+
+def install_default_workspace(device: torch.device, w: Workspace) -> None:
+    """Make ``w`` the workspace every op on ``device`` uses from now on (the engine installs an arena-backed one)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    _default[idx] = w
+
+
+def has_default_workspace(device: torch.device) -> bool:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    return idx in _default
 
 
 def default_workspace(device: torch.device) -> Workspace:

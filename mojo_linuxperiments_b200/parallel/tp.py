@@ -35,9 +35,10 @@ class TPContext:
         big = max(FUSED_MAX_M, max_tokens) * d_model * 2
         # low-latency all-reduce: per slot, one [M, N/2] array of 8-byte {2 x bf16, epoch} words per source rank
         self.recv_bytes = world * FUSED_MAX_M * (d_model // 2) * 8
+        self.recv2_bytes = FUSED_MAX_M * (d_model // 2) * 8                  # two-hop form: the owners' broadcast lands here
         cand_bytes = 2 * world * 1024 * 16                                   # arg-max exchange: up to 1,024 rows
         self.ll_recv_bytes = 2 * world * (512 << 10) * 2                     # low-latency all-reduce of <= 512 KiB
-        total = 2 * small + big + 2 * self.recv_bytes + cand_bytes + self.ll_recv_bytes
+        total = 2 * small + big + 2 * self.recv_bytes + 2 * self.recv2_bytes + cand_bytes + self.ll_recv_bytes
         from .sp import SPLayout, SPLink
         want_sp = os.environ.get("B200RT_SP", "1") != "0" and max_tokens >= SP_MIN_TOKENS_PER_RANK * world
         if want_sp:
@@ -45,6 +46,10 @@ class TPContext:
         self.heap = SymmetricHeap(total + (1 << 20), group=group, device=device)
         self.world, self.rank = self.heap.world, self.heap.rank
         self.recv_off = [self.heap.alloc(self.recv_bytes), self.heap.alloc(self.recv_bytes)]
+        self.recv2_off = [self.heap.alloc(self.recv2_bytes), self.heap.alloc(self.recv2_bytes)]
+        # above this many tokens the fused all-reduce goes through the slice owners (two NVLink trips, 1/4 of the bytes
+        # at 8 ranks); below, one trip wins.  B200RT_AR_TWO_HOP_MIN overrides (0: never).
+        self.two_hop_min = int(os.environ.get("B200RT_AR_TWO_HOP_MIN", "8"))
         self.low_latency = os.environ.get("B200RT_AR", "ll") != "barrier"
         # Fused launches alternate between two small slots by the parity of the device-side epoch, so a rank that runs
         # ahead never overwrites a partial a slower rank is still summing.  The unfused path owns a third slot and its
@@ -84,7 +89,9 @@ class TPContext:
                 _lib.ptr(residual), M, N, K, out.stride(0), ws.status.data_ptr(), _lib.num_sms(xq.device.index),
                 h._c_data, h._c_flags, (h.mc_data_ptr or None) if self.use_nvls else None, h.world, h.rank,
                 self.part_off[0], self.part_off[1], h.epoch_words.data_ptr(), self.limit_ms,
-                1 if self.low_latency else 0, self.recv_off[0], self.recv_off[1], self.recv_bytes, _lib.stream())
+                1 if self.low_latency else 0, self.recv_off[0], self.recv_off[1], self.recv_bytes,
+                1 if (self.two_hop_min > 0 and M >= self.two_hop_min) else 0, self.recv2_off[0], self.recv2_off[1],
+                self.recv2_bytes, _lib.stream())
             if rc != -20:
                 _lib.check(rc, "w8a8_gemm_decode_ar")
                 return out

@@ -27,11 +27,14 @@ class Heartbeat:
         self._thread: threading.Thread | None = None
         self._last_seen: dict[int, tuple[int, float]] = {}
         self._beats = 0
+        self._dead: list[int] = []          # filled by the monitor thread (``start(monitor=True)``)
 
     def _key(self, r: int) -> str:
         return f"{self.prefix}/{r}"
 
-    def start(self) -> "Heartbeat":
+    def start(self, monitor: bool = False) -> "Heartbeat":
+        """Begin beating.  With ``monitor`` the same thread also watches the peers, so that the serving loop's
+        ``check_fast()`` between steps is a plain memory read instead of a round trip to the store per peer."""
         self.store.set(self._key(self.rank), "0")
 
         def loop():
@@ -41,6 +44,13 @@ class Heartbeat:
                     self.store.set(self._key(self.rank), str(self._beats))
                 except Exception:
                     return        # the store went away: peers will see us as dead, which is the truth
+                if monitor:
+                    try:
+                        dead = self.dead_ranks()
+                    except Exception:
+                        dead = []
+                    if dead:
+                        self._dead = dead
 
         self._thread = threading.Thread(target=loop, name=f"heartbeat-{self.rank}", daemon=True)
         self._thread.start()
@@ -76,6 +86,11 @@ class Heartbeat:
         dead = self.dead_ranks()
         if dead:
             raise RankFailure(dead)
+
+    def check_fast(self) -> None:
+        """Raise if the monitor thread has declared a peer dead; costs no store traffic (call it between steps)."""
+        if self._dead:
+            raise RankFailure(self._dead)
 
     def wait_for_failure(self, max_wait_s: float) -> list[int]:
         """Poll until some rank is declared dead or ``max_wait_s`` passed; returns the dead ranks (possibly empty)."""

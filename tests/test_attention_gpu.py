@@ -71,8 +71,6 @@ def test_attn_prefill_matches_reference(lens, hq, hkv):
         o += L
 
 
-@pytest.mark.skipif(os.environ.get("B200RT_TEST_PREFILL_SPLIT") != "1",
-                    reason="split-KV prefill attention is opt-in until it has been run on hardware once: set B200RT_TEST_PREFILL_SPLIT=1")
 @pytest.mark.parametrize("lens,hq,hkv", [([128], 4, 1), ([1024], 4, 1), ([100, 333, 128], 4, 1), ([1, 129], 8, 1), ([640], 8, 2)])
 @pytest.mark.parametrize("chunk", [1, 2, 3])
 def test_attn_prefill_split_kv_matches_reference(lens, hq, hkv, chunk):
@@ -203,3 +201,78 @@ def test_attn_decode_clamps_lengths_beyond_the_page_table_row(impl):
     ws.status.zero_()
     assert code & 255 == 6, code
     assert torch.equal(ok, over)                             # the over-long sequence was read as its 128 admitted tokens
+
+
+@pytest.mark.parametrize("hq,hkv,qk_norm", [(32, 8, False), (4, 1, False), (8, 1, True), (8, 4, True), (2, 2, False)])
+@pytest.mark.parametrize("splits", [1, 4])
+def test_attn_decode_fused_matches_the_three_kernels_it_replaces(hq, hkv, qk_norm, splits):
+    """rope_kv_write + attn_decode + act_quant in one launch: same cache contents, same attention output (against the
+    fp32 oracle), and exactly the int8 rows / scales the stand-alone prologue makes of that output."""
+    from mojo_linuxperiments_b200.ops import attention as A
+    from mojo_linuxperiments_b200.ops import linear as L
+    from mojo_linuxperiments_b200.ops.workspace import default_workspace
+    ps, theta = 16, 500000.0
+    lens = [1, 17, 300, 1280, 64, 128, 513]                # tokens per sequence including the new one
+    B = len(lens)
+    max_pages = (max(lens) + ps - 1) // ps
+    n_pages = B * max_pages
+    g = torch.Generator().manual_seed(11)
+    page_table = torch.randperm(n_pages, generator=g).to(torch.int32).view(B, max_pages).cuda()
+    cache_a = A.PagedKVCache(n_pages, hkv, ps, "cuda")
+    cache_a.data.copy_(_rand(tuple(cache_a.data.shape), 12))
+    cache_b = A.PagedKVCache(n_pages, hkv, ps, "cuda")
+    cache_b.data.copy_(cache_a.data)
+    qkv = _rand((B, (hq + 2 * hkv) * D), 13)
+    seq_lens = torch.tensor(lens, dtype=torch.int32).cuda()
+    pos = (seq_lens - 1).contiguous()
+    cos, sin = A.rope_tables(2048, theta, "cuda")
+    qw = (torch.rand(D) + 0.5).to(torch.bfloat16).cuda() if qk_norm else None
+    kw = (torch.rand(D) + 0.5).to(torch.bfloat16).cuda() if qk_norm else None
+    ws = default_workspace(qkv.device)
+    ws.status.zero_()
+    # the three separate kernels
+    q = A.rope_kv_write(qkv, pos, cos, sin, hq, hkv, cache=cache_a, page_table=page_table, q_norm_w=qw, k_norm_w=kw, eps=1e-6)
+    ref_out = A.attn_decode(q, cache_a, page_table, seq_lens, splits=splits, impl="tc")
+    # the fused kernel, twice (its counters must reset themselves)
+    xq, sx, out = A.attn_decode_fused(qkv, pos, cos, sin, hq, hkv, cache_b, page_table, seq_lens, splits=splits,
+                                      q_norm_w=qw, k_norm_w=kw, eps=1e-6, want_out=True)
+    xq2, sx2, out2 = A.attn_decode_fused(qkv, pos, cos, sin, hq, hkv, cache_b, page_table, seq_lens, splits=splits,
+                                         q_norm_w=qw, k_norm_w=kw, eps=1e-6, want_out=True)
+    torch.cuda.synchronize()
+    assert int(ws.status[0].item()) == 0
+    # the cache received the same new rows (one bf16 ulp of slack: the two kernels may contract a*b-c*d differently)
+    assert torch.allclose(cache_b.data.float(), cache_a.data.float(), rtol=1e-2, atol=1e-2)
+    assert (cache_b.data != cache_a.data).float().mean().item() < 1e-3
+    # attention output against the fp32 oracle over the cache that now holds the new token
+    for b, Ln in enumerate(lens):
+        pages = page_table[b, : (Ln + ps - 1) // ps].long()
+        kk = cache_a.data[pages, 0].permute(0, 2, 1, 3).reshape(-1, hkv, D)[:Ln]
+        vv = cache_a.data[pages, 1].permute(0, 2, 1, 3).reshape(-1, hkv, D)[:Ln]
+        ref = OA.decode_gqa(q[b], kk, vv)
+        assert torch.allclose(out[b].float(), ref, rtol=2e-2, atol=2e-2), (b, (out[b].float() - ref).abs().max().item())
+        assert torch.allclose(out[b].float(), ref_out[b].float(), rtol=2e-2, atol=2e-2)
+    # the quantised rows are exactly what the stand-alone prologue makes of the kernel's own bf16 output
+    q_ref, s_ref = L.act_quant(out.view(B, hq * D))
+    assert torch.equal(sx, s_ref) and torch.equal(xq, q_ref)
+    assert torch.equal(xq, xq2) and torch.equal(sx, sx2) and torch.equal(out, out2)
+
+
+def test_attn_decode_fused_refuses_a_position_outside_the_pages():
+    from mojo_linuxperiments_b200.ops import attention as A
+    from mojo_linuxperiments_b200.ops.workspace import default_workspace
+    hq, hkv, ps, B = 4, 1, 16, 2
+    max_pages = 2
+    page_table = torch.arange(B * max_pages, dtype=torch.int32).view(B, max_pages).cuda()
+    cache = A.PagedKVCache(B * max_pages, hkv, ps, "cuda")
+    cos, sin = A.rope_tables(64, 10000.0, "cuda")
+    qkv = _rand((B, (hq + 2 * hkv) * D), 7)
+    ws = default_workspace(qkv.device)
+    ws.status.zero_()
+    seq_lens = torch.tensor([32, 33], dtype=torch.int32).cuda()       # sequence 1 is one token past its two pages
+    A.attn_decode_fused(qkv, (seq_lens - 1).contiguous(), cos, sin, hq, hkv, cache, page_table, seq_lens)
+    torch.cuda.synchronize()
+    code = int(ws.status[0].item())
+    ws.status.zero_()
+    assert code & 255 == 6, code
+    assert cache.data[1, :, :, 15].abs().sum().item() > 0             # sequence 0 appended token 31
+    assert cache.data[2:].abs().sum().item() == 0                      # nothing was written for sequence 1

@@ -96,7 +96,7 @@ def test_w8a8_gemm_exact(m, n, k, force_mode):
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 128), (1, 6144, 4096), (16, 768, 4096), (17, 1000, 512), (32, 4096, 1792),
                                    (32, 4096, 512), (33, 3584, 4096), (64, 28672, 4096), (50, 4096, 14336), (3, 16032, 256)])
-@pytest.mark.parametrize("splits", [0, 1, 2, 4, 8])
+@pytest.mark.parametrize("splits", [0, 1, 2, 3, 4, 5, 6, 7, 8])
 def test_w8a8_gemm_cluster_splitk(m, n, k, splits):
     """Decode kernel: split-K across a thread-block cluster, reduced through distributed shared memory."""
     from mojo_linuxperiments_b200.ops import linear as L

@@ -1,4 +1,7 @@
 import json
+import time
+
+import pytest
 
 from mojo_linuxperiments_b200.utils.trace import MetricsLog, nvtx_range
 
@@ -153,3 +156,27 @@ def test_decode_attention_split_geometry_covers_every_block_once():
                     for lane in range(32):                       # page-id prefetch stays inside the sequence's pages
                         assert 0 <= min(blk0 * 8 + lane, total_pages - 1) < total_pages
                 assert covered == list(range(total_blocks)), (max_len, splits, length)
+
+
+def test_heartbeat_monitor_thread_feeds_the_fast_check():
+    """With ``start(monitor=True)`` the beating thread also watches the peers; ``check_fast`` is then a memory read
+    that raises once a peer has been silent for the timeout."""
+    from mojo_linuxperiments_b200.utils.health import Heartbeat, RankFailure
+
+    class DictStore:
+        def __init__(self): self.d = {}
+        def set(self, k, v): self.d[k] = v
+        def get(self, k): return self.d[k].encode() if isinstance(self.d[k], str) else self.d[k]
+        def check(self, keys): return all(k in self.d for k in keys)
+
+    store = DictStore()
+    a = Heartbeat(store, 0, 2, interval_s=0.02, timeout_s=0.15, prefix="t").start(monitor=True)
+    b = Heartbeat(store, 1, 2, interval_s=0.02, timeout_s=0.15, prefix="t").start()
+    time.sleep(0.3)
+    a.check_fast()                      # both alive: nothing raised
+    b.stop()                            # rank 1 leaves between steps
+    time.sleep(0.5)
+    with pytest.raises(RankFailure) as e:
+        a.check_fast()
+    assert e.value.ranks == [1]
+    a.stop()
