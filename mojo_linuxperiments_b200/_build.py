@@ -152,6 +152,23 @@ def build_hostrt_selftest() -> Path:
     return exe
 
 
+def build_hostrt_tsan() -> Path:
+    """Thread-sanitizer build of the fabric protocols (ranks as std::threads): ``_lib/hostrt_tsan_fabric``."""
+    srcdir = CSRC / "hostrt"
+    exe = LIBDIR / "hostrt_tsan_fabric"
+    sources = [s for s in sorted(srcdir.glob("*.cpp")) if s.name != "capi.cpp"] + [srcdir / "selftest" / "tsan_fabric.cc"]
+    headers = sorted(srcdir.glob("*.hpp")) + sorted((CSRC / "fabric").glob("*.h"))
+    flags = [f for f in GXX_FLAGS if f != "-fPIC"] + ["-fsanitize=thread", "-g", "-O1", "-DHOSTRT_STD_THREADS"]
+    digest = _digest(sources + headers, "tsan" + " ".join(flags))
+    stamp = OBJDIR / "hostrt_tsan_fabric.stamp"
+    LIBDIR.mkdir(parents=True, exist_ok=True)
+    OBJDIR.mkdir(parents=True, exist_ok=True)
+    if _stale(stamp, digest, exe):
+        _run(["g++", *flags, "-I", str(srcdir), "-I", str(CSRC), "-o", str(exe), *map(str, sources)])
+        stamp.write_text(json.dumps({"digest": digest}))
+    return exe
+
+
 def build_devrt() -> Path:
     """C++ device runtime: GPU topology, HBM arena (CUDA virtual memory management), device masks."""
     cuda_inc = Path(_nvcc()).resolve().parent.parent / "include"
@@ -173,5 +190,7 @@ def build_all(verbose: bool = False, variants=("",)) -> dict:
 
 if __name__ == "__main__":
     want = [""] + [v for v in ("trace", "debug") if ("--" + v) in sys.argv or "--all" in sys.argv]
+    if "--tsan" in sys.argv or "--all" in sys.argv:
+        print(f"hostrt_tsan_fabric: {build_hostrt_tsan()}")
     for k, v in build_all(verbose="-v" in sys.argv, variants=want).items():
         print(f"{k}: {v}")

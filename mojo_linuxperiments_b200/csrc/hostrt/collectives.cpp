@@ -2,6 +2,9 @@
 
 #include <atomic>
 #include <vector>
+#ifdef HOSTRT_STD_THREADS
+#include <thread>
+#endif
 
 #include "arena.hpp"
 #include "fabric/philox.h"
@@ -32,6 +35,31 @@ bool make_rank_pools(const NumaInfo& info, int world, HeapMoveArray<ThreadPool>&
   }
   return true;
 }
+
+// Run worker(rank, shared) on `world` ranks and join them.  Normally every rank is a one-shot thread of its own
+// single-slot pool, pinned to the rank's node.  With -DHOSTRT_STD_THREADS (the thread-sanitizer build) the ranks are
+// std::threads instead: ThreadSanitizer only knows threads that were created through pthreads, and what it is asked to
+// judge is the protocol (epochs, flags, buffer parity), not the clone3 plumbing.
+#ifdef HOSTRT_STD_THREADS
+long run_ranks(const NumaInfo&, int world, WorkerFn worker, void* shared, long) {
+  std::vector<std::thread> th;
+  th.reserve(world);
+  for (int r = 0; r < world; ++r)
+    th.emplace_back([=] { worker(static_cast<uint64_t>(r), reinterpret_cast<uint64_t>(shared), 0, 0, 0, 0); });
+  for (auto& t : th) t.join();
+  return 0;
+}
+#else
+long run_ranks(const NumaInfo& info, int world, WorkerFn worker, void* shared, long join_timeout_ns) {
+  HeapMoveArray<ThreadPool> pools(world);
+  if (!make_rank_pools(info, world, pools)) return -err::kNOMEM;
+  for (int r = 0; r < world; ++r)
+    if (pools[r].launch(worker, r, reinterpret_cast<uint64_t>(shared)) < 0) return -err::kAGAIN;
+  long st = 0;
+  for (int r = 0; r < world; ++r) if (pools[r].wait_all(join_timeout_ns) != 0) st = -err::kTIMEDOUT;
+  return st;
+}
+#endif
 
 // ---- chain reduce ----------------------------------------------------------------------------------
 struct ChainShared { long timeout_ns; std::atomic<int> errors; };
@@ -286,12 +314,7 @@ long fabric_allreduce(const NumaInfo& info, int world, const double* in, double*
   sh.in = in; sh.out = out;
   sh.errors.store(0);
   if (!sh.slots || !sh.flags) return -err::kNOMEM;
-  HeapMoveArray<ThreadPool> pools(world);
-  if (!make_rank_pools(info, world, pools)) return -err::kNOMEM;
-  for (int r = 0; r < world; ++r)
-    if (pools[r].launch(&fabric_worker, r, reinterpret_cast<uint64_t>(&sh)) < 0) return -err::kAGAIN;
-  long st = 0;
-  for (int r = 0; r < world; ++r) if (pools[r].wait_all(timeout_ns * 4 + 1'000'000'000l) != 0) st = -err::kTIMEDOUT;
+  long st = run_ranks(info, world, &fabric_worker, &sh, timeout_ns * 4 + 1'000'000'000l);
   if (st == 0 && sh.errors.load() != 0) st = -err::kTIMEDOUT;
   return st;
 }
@@ -314,12 +337,7 @@ long fabric_token_exchange(const NumaInfo& info, int world, int rows_per_rank, i
   sh.ctr = arena.alloc<std::atomic<uint32_t>>(static_cast<size_t>(world) * 2);
   sh.errors.store(0); sh.timeouts.store(0);
   if (!sh.gather || !sh.recv || !sh.flags || !sh.done || !sh.ctr) return -err::kNOMEM;
-  HeapMoveArray<ThreadPool> pools(world);
-  if (!make_rank_pools(info, world, pools)) return -err::kNOMEM;
-  for (int r = 0; r < world; ++r)
-    if (pools[r].launch(&exchange_worker, r, reinterpret_cast<uint64_t>(&sh)) < 0) return -err::kAGAIN;
-  long st = 0;
-  for (int r = 0; r < world; ++r) if (pools[r].wait_all(timeout_ns * 4 + 10'000'000'000l) != 0) st = -err::kTIMEDOUT;
+  long st = run_ranks(info, world, &exchange_worker, &sh, timeout_ns * 4 + 10'000'000'000l);
   if (mismatches) *mismatches = sh.errors.load();
   if (st == 0 && sh.timeouts.load() != 0) st = -err::kTIMEDOUT;
   return st;

@@ -64,3 +64,16 @@ def test_sequence_parallel_fused_linears(nproc):
     p = _run("mp_sp_ops.py", nproc)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     assert "FAILURES 0" in p.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("nproc", [2, 4, 8])
+def test_fused_gemm_allreduce_one_trip_and_two_hop(nproc):
+    """Decode GEMM + all-reduce in one launch: both tails give the rank-ordered sum of the bf16 partials, the same bits
+    on every rank, eagerly and from a replayed CUDA graph."""
+    if NGPU < nproc:
+        pytest.skip(f"needs {nproc} GPUs, found {NGPU}")
+    p = _run("mp_fused_ar.py", nproc)
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert "FAILURES 0" in p.stdout
