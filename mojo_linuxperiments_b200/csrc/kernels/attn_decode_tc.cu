@@ -21,6 +21,7 @@
 #include "launch.cuh"
 #include "hadamard.cuh"
 #include <cuda.h>
+#include <cstdlib>
 
 namespace b200 {
 
@@ -71,8 +72,15 @@ struct DecodeTcParams {
   float scale_log2;
   int* status;
   unsigned long long limit_ns;
+  // 1: the splits of a (sequence, kv head) are one thread-block cluster (cluster dims 1 x 1 x splits) and their partials
+  // meet in the shared memory of the cluster's first CTA, which merges them: no global scratch, no counter, no fence
+  int cluster_merge;
   DecodeFuse f;
 };
+
+constexpr int ADC_ZONE_ROW = ADC_D + 2;            // one partial row in the merge zone: 128 values, max, sum
+constexpr int ADC_ZONE_MAX_SPLITS = 8;             // portable cluster size
+constexpr int ADC_ZONE_MAX_G = 4;                  // the zone is sized for groups of up to four query heads
 
 __device__ __forceinline__ void unpack8_bf16(const uint4& raw, float (&o)[8]) {
   const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -144,6 +152,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   float* vnew_s = row_s + G * ADC_D;               // [128]
   float* snew_s = vnew_s + ADC_D;                  // [8]
   float* amax_s = snew_s + 8;                      // [8]
+  float* zone = amax_s + 8;                        // cluster merge: [splits][G][ADC_ZONE_ROW] (G <= 4 only)
   const uint32_t sRing = smem_u32(smem);
   const uint32_t sP = smem_u32(pP), sQ = smem_u32(pQ);
   const uint32_t bar0 = smem_u32(bars);
@@ -270,6 +279,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool cmerge = p.cluster_merge != 0;
+  if (cmerge) cluster_arrive_relaxed();          // "this CTA runs": waited for before the first store into a peer's zone
 
   if (warp == 0) {
     if (lane == 0 && nb > 0) {
@@ -464,9 +475,20 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
         const __nv_bfloat16 ob = __float2bfloat16(l[g] > 0.f ? o[g] / l[g] : 0.f);
         if (p.out) p.out[hrow * ADC_D + r] = ob;
         if constexpr (FUSED) row_s[g * ADC_D + r] = __bfloat162float(ob);
-      } else {
+      } else if (!cmerge) {
         p.part_acc[(hrow * p.splits + split) * ADC_D + r] = o[g];
         if (r == 0) { p.part_ml[(hrow * p.splits + split) * 2] = m[g]; p.part_ml[(hrow * p.splits + split) * 2 + 1] = l[g]; }
+      }
+    }
+    if (cmerge && p.splits > 1) {
+      // partial rows go straight into the shared memory of the cluster's first CTA
+      cluster_wait_acquire();
+      const uint32_t z0 = mapa_shared(smem_u32(zone), 0u);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        const uint32_t zr = z0 + 4u * static_cast<uint32_t>((split * G + g) * ADC_ZONE_ROW);
+        st_shared_cluster_u32(zr + 4u * r, __float_as_uint(o[g]));
+        if (r == 0) { st_shared_cluster_u32(zr + 4u * ADC_D, __float_as_uint(m[g])); st_shared_cluster_u32(zr + 4u * (ADC_D + 1), __float_as_uint(l[g])); }
       }
     }
   }
@@ -477,7 +499,28 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   if (tid == 0) B200_TRACE(TK_ATTN_DECODE, 6);
   if (p.splits == 1 && !(FUSED && p.f.xq)) { B200_TRACE_FLUSH(TK_ATTN_DECODE); return; }
 
-  if (p.splits > 1) {
+  if (p.splits > 1 && cmerge) {
+    // ---- cluster merge: every partial has landed in the first CTA's zone once the cluster barrier completes ----
+    if (warp < 2) cluster_wait_acquire();            // the two service warps still owe the wait of the start-up arrive
+    cluster_sync_all();
+    if (split != 0) { B200_TRACE_FLUSH(TK_ATTN_DECODE); return; }
+    if (tid == 0) B200_TRACE(TK_ATTN_DECODE, 7);
+    for (int i = tid; i < G * ADC_D; i += ADC_THREADS) {
+      const int g = i / ADC_D, d = i % ADC_D;
+      float m = -INFINITY, l = 0.f, o = 0.f;
+      for (int sI = 0; sI < p.splits; ++sI) m = fmaxf(m, zone[(sI * G + g) * ADC_ZONE_ROW + ADC_D]);
+      for (int sI = 0; sI < p.splits; ++sI) {
+        const float* zr = zone + (sI * G + g) * ADC_ZONE_ROW;
+        const float w = (zr[ADC_D] == -INFINITY) ? 0.f : exp2f(zr[ADC_D] - m);
+        l += w * zr[ADC_D + 1];
+        o += w * zr[d];
+      }
+      const __nv_bfloat16 ob = __float2bfloat16(l > 0.f ? o / l : 0.f);
+      if (p.out) p.out[(static_cast<size_t>(b) * p.hq + kvh * G + g) * ADC_D + d] = ob;
+      if constexpr (FUSED) row_s[i] = __bfloat162float(ob);
+    }
+    if (tid == 0) B200_TRACE(TK_ATTN_DECODE, TP_EXIT);
+  } else if (p.splits > 1) {
     // ---- the last CTA of this (sequence, kv head) merges the splits ----
     __threadfence();
     __syncthreads();
@@ -989,9 +1032,10 @@ typedef CUresult (*EncodeTiledFn3)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 
 template <int G, bool FUSED>
 static int launch_adc(const CUtensorMap& tm, const DecodeTcParams& p, dim3 grid, cudaStream_t stream) {
-  // the fused form adds the output rows of the CTA's heads, the new token's value row and a few scalars
+  // rows of the CTA's heads, the new token's value row, a few scalars, and (groups of up to four heads) the merge zone
   constexpr int SMEM = 2 * ADC_TILE + ADC_NB * ADC_P_TILE + ADC_Q_TILE + (64 + 16) * 4 + (6 + 2 * ADC_NB) * 8 + 64 + ADC_NB * 8 * 4 + 1024 +
-                       (FUSED ? (G * ADC_D + ADC_D + 16) * 4 + 16 : 0);
+                       (G * ADC_D + ADC_D + 16) * 4 + 16 +
+                       (G <= ADC_ZONE_MAX_G ? ADC_ZONE_MAX_SPLITS * G * ADC_ZONE_ROW * 4 : 0);
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<G, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
@@ -1001,7 +1045,8 @@ static int launch_adc(const CUtensorMap& tm, const DecodeTcParams& p, dim3 grid,
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }
-  launch_ex(attn_decode_tc_kernel<G, FUSED>, dim3(grid), dim3(ADC_THREADS), SMEM, stream, 0, tm, p);
+  if (p.cluster_merge) launch_ex_cluster(attn_decode_tc_kernel<G, FUSED>, dim3(grid), dim3(ADC_THREADS), SMEM, stream, dim3(1, 1, grid.z), tm, p);
+  else launch_ex(attn_decode_tc_kernel<G, FUSED>, dim3(grid), dim3(ADC_THREADS), SMEM, stream, 0, tm, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
@@ -1043,7 +1088,6 @@ static int attn_decode_tc_common(const void* q, const void* cache, int num_pages
   const int G = hq / hkv;
   if (G != 1 && G != 2 && G != 4 && G != 8) return -3;
   if (splits < 1) splits = 1;
-  if (splits > 1 && (!scratch || !counters)) return -1;
   if (reinterpret_cast<uintptr_t>(cache) & 127) return -2;
   if (!fuse && (reinterpret_cast<uintptr_t>(q) & 15)) return -2;
   if (fuse) {
@@ -1078,6 +1122,17 @@ static int attn_decode_tc_common(const void* q, const void* cache, int num_pages
   p.counters = counters; p.hq = hq; p.hkv = hkv; p.max_pages = max_pages; p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.limit_ns = 2000000000ull;
   if (fuse) p.f = *fuse; else p.f = DecodeFuse{};
+  // splits of one (sequence, kv head) as a thread-block cluster that merges in shared memory (B200RT_ATTN_CLUSTER=0: off)
+  static int cluster_env = -1;
+  if (cluster_env < 0) { const char* e = std::getenv("B200RT_ATTN_CLUSTER"); cluster_env = (e && e[0] == '0') ? 0 : 1; }
+  // Only while the grid is resident in one go (two CTAs per SM): with several waves of CTAs, clusters that have to be
+  // placed whole are slower than independent CTAs that merge through global memory (measured: 768 CTAs, 583 vs 569 us
+  // per four layers), while a one-wave grid saves the fence, the counter and the L2 round trips of that merge.
+  static int sm_count = 0;
+  if (!sm_count) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
+  p.cluster_merge = (!persistent && cluster_env && G <= ADC_ZONE_MAX_G && splits >= 2 && splits <= ADC_ZONE_MAX_SPLITS &&
+                     static_cast<long long>(B) * hkv * splits <= 2ll * sm_count) ? 1 : 0;
+  if (splits > 1 && !p.cluster_merge && (!scratch || !counters)) return -1;
   if (persistent) {
     const int items = B * hkv * splits;
     switch (G) {

@@ -142,7 +142,9 @@ def pick_decode_splits_tc(B: int, hkv: int, max_len: int, num_sms: int = 148) ->
     smin = tc_min_splits(max_len)
     slots = 2 * num_sms
     best, best_cost = smin, None
-    for s in range(smin, max(smin, min(32, blocks)) + 1):
+    # up to eight splits are one thread-block cluster that merges in shared memory: stay there when that is possible
+    cap = 8 if smin <= 8 else 32
+    for s in range(smin, max(smin, min(cap, blocks)) + 1):
         cost = -(-(max(1, B * hkv) * s) // slots) * (-(-blocks // s) + 1.6) + 0.15 * s
         if best_cost is None or cost < best_cost - 1e-9:
             best, best_cost = s, cost
