@@ -47,7 +47,8 @@ text = (f"decode step phase stamps: model {a.model}, {a.layers} layers, batch {a
         f"shard 1/{a.shard_of}; {len(recs)} stamps\n"
         "gemm_decode phases: 0 start, 1 producer past dependency wait, 2 first stage landed, 3 last MMA issued, "
         "4 accumulator complete, 5 cluster is running, 10 partials sent, 6 cluster barrier passed, 11 slice reduced and stored, "
-        "7 CTA past its last barrier, 8 pushed to peers, 9 peers summed\n"
+        "7 CTA past its last barrier, 8 pushed to peers, 9 peers summed; quantiser CTAs of a fused launch: 20 start, "
+        "21 dependency wait passed, 22 row stored and flagged (GEMM CTAs: phase 1 = all row flags seen)\n"
         "attn_decode phases: 0 start, 1 dependency wait passed, 2 scores in registers, 3 maxima exchanged, 5 P.V read, "
         "6 partial written, 7 merge begins (last CTA of a head), 63 merge done, 62 output quantised\n"
         "act_quant phases: 0 start, 1 dependency wait passed, 2 row rotated, 63 row stored\n" + DeviceTrace.summarize(recs, 400))

@@ -28,6 +28,29 @@ int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void* wq, const
 
 int b200_w8a8_gemm_decode_resident_clusters(int m, int splits);
 
+// Activation prologue carried inside a decode GEMM launch (quantiser CTAs of the same grid, see quant_row.cuh).
+// mode: 1 rotate + quantise x [M][K]; 2 RMSNorm(gamma, eps) first; 3 residual += x (bf16, in place) then RMSNorm of the
+// residual; 4 x is [M][2K] = gate | up and silu(gate) * up is quantised.  q [M][K] int8 and scale [M] are written by the
+// launch (and are what its GEMM CTAs consume); flags: M uint32 words; step: a device uint32 that the caller changes
+// between two replays of a captured launch (within one step every launch tags the flags with its own number).
+typedef struct b200_quant_prolog {
+  int mode;
+  const void* x; long long ldx;
+  void* residual; long long ldr;
+  const void* gamma; float eps;
+  void* q; float* scale;
+  void* flags; const void* step;
+} b200_quant_prolog;
+int b200_w8a8_gemm_decode_p(const b200_quant_prolog* prolog, const void* wq, const float* sw, void* y,
+                            const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status, int num_sms,
+                            cudaStream_t stream);
+int b200_w8a8_gemm_decode_ar_p(const b200_quant_prolog* prolog, const void* wq, const float* sw, void* y,
+                               const void* residual, int M, int N, int K, int ldy, int* status, int num_sms,
+                               void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
+                               size_t part_off0, size_t part_off1, void* words, int limit_ms, int ll,
+                               size_t recv_off0, size_t recv_off1, size_t recv_bytes, int two_hop, size_t recv2_off0,
+                               size_t recv2_off1, size_t recv2_bytes, cudaStream_t stream);
+
 // Same, fused with the tensor-parallel all-reduce over peer memory (one launch).  -20: grid not co-resident, use
 // b200_w8a8_gemm_decode followed by b200_peer_allreduce instead.  ll: low-latency {payload, epoch} words; two_hop
 // (with ll): partials go only to the rank owning the column slice, which sums and broadcasts them through a second

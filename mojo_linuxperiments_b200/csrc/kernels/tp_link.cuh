@@ -59,7 +59,7 @@ __device__ __forceinline__ void red_relaxed_sys_add(uint32_t* p, uint32_t v) {
   asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ void fence_acq_rel_sys() { asm volatile("fence.acq_rel.sys;" ::: "memory"); }
-// order generic-proxy observations (a flag another GPU wrote) before this thread's later TMA loads of global memory
-__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// fence_proxy_async_all (ptx.cuh) orders generic-proxy observations (a flag another GPU wrote) before this thread's
+// later TMA loads of global memory
 
 }  // namespace b200

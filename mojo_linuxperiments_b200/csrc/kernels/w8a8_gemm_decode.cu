@@ -22,6 +22,9 @@
 //     clusters doubles the latency of an op that is all latency.
 // All mbarrier waits are bounded; a CTA that gives up still reaches both cluster barriers, so peers never hang.
 //
+// Fused activation prologue (DecodeGemmParams::qp): residual add / RMSNorm / SwiGLU, Hadamard rotation and per-token
+// int8 run in quantiser CTAs of the same launch (quant_row.cuh), so a linear is one launch from bf16 in to bf16 out.
+//
 // Fused all-reduce (row-parallel layers under tensor parallelism): with an `ArTail` the CTAs write their bf16 tile of
 // the local partial product into this rank's symmetric buffer instead of y, the last CTA of the grid to finish
 // signals every peer, and then *all* CTAs (the host only fuses when the whole grid is co-resident) wait for the
@@ -33,6 +36,7 @@
 #include "gemm_common.cuh"
 #include "peer.cuh"
 #include "launch.cuh"
+#include "quant_row.cuh"
 #include <cstdlib>
 
 namespace b200 {
@@ -70,6 +74,10 @@ struct DecodeGemmParams {
   // of xq / y, its weights are rows [e*N, (e+1)*N) of wq / sw
   const int* grp_offsets;
   const int* grp_counts;
+  // Activation prologue inside the launch: the first qp.rows grid rows are quantiser CTAs (one token row each) that turn
+  // the bf16 input into the int8 operand and publish a flag per row; the GEMM CTAs prefetch their weights meanwhile
+  // and wait for the flags instead of for an earlier kernel.
+  QuantProlog qp;
 };
 
 // Where a finished output element goes.  A plain struct of scalars (not a capturing lambda: called from the epilogue
@@ -139,7 +147,24 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 
   const int S = p.splits;
   const int rank = static_cast<int>(cluster_ctarank());          // == blockIdx.x: position along K
-  const int n_tile = blockIdx.y;
+  const bool prolog = p.qp.mode != QR_NONE;
+  if (prolog && static_cast<int>(blockIdx.y) < p.qp.rows) {
+    // ---- quantiser CTA: one token row, then the row's flag ----
+    B200_TRACE_INIT();
+    if (threadIdx.x == 0) B200_TRACE(TK_GEMM_DECODE, 20);
+    pdl_wait();                                   // the bf16 rows are the previous kernel's output
+    if (threadIdx.x == 0) B200_TRACE(TK_GEMM_DECODE, 21);
+    const int qrow = blockIdx.y * p.splits + static_cast<int>(cluster_ctarank());
+    if (qrow < p.M) {
+      const uint32_t ticket = quant_ticket(p.qp);
+      quant_row_cta<GEMM_THREADS / 32>(p.qp, qrow, p.K, reinterpret_cast<float*>(smem), reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES));
+      __syncthreads();                            // the release below is cumulative over what this barrier orders
+      if (threadIdx.x == 0) { st_release_gpu(p.qp.flags + qrow, ticket); B200_TRACE(TK_GEMM_DECODE, 22); }
+    }
+    B200_TRACE_FLUSH(TK_GEMM_DECODE);
+    return;
+  }
+  const int n_tile = blockIdx.y - (prolog ? p.qp.rows : 0);
   int m0 = blockIdx.z * BN, rows_valid = min(BN, p.M - m0), w_base = 0;
   const bool grouped = p.grp_counts != nullptr;
   if (grouped) {
@@ -186,20 +211,40 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   const int cw = slice0(rank + 1) - slice0(rank);                       // channels this CTA finishes
   const int n_base = n_tile * TILE_N + slice0(rank);
   if (warp == 0) {
+    const uint64_t pol_w = policy_evict_first();       // weights are read exactly once per launch
+    int stage = 0; uint32_t phase = 0;
+    bool ok = true;
+    // Weights never change during inference, so the first ring-full of weight tiles is requested before waiting
+    // for the previous kernel; the activation tiles (its output) are requested after the wait.
+    const int pre = grouped ? 0 : min(STAGES, kb1 - kb0);
     if (lane == 0) {
       prefetch_tmap(&tmap_w);
       prefetch_tmap(&tmap_x);
-      const uint64_t pol_w = policy_evict_first();     // weights are read exactly once per launch
-      int stage = 0; uint32_t phase = 0;
-      bool ok = true;
-      // Weights never change during inference, so the first ring-full of weight tiles is requested before waiting
-      // for the previous kernel; the activation tiles (its output) are requested after the wait.
-      const int pre = grouped ? 0 : min(STAGES, kb1 - kb0);
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(full_bar(i), STAGE_BYTES);
         tma_load_2d_hint(smem_base + i * STAGE_BYTES, &tmap_w, full_bar(i), (kb0 + i) * BLOCK_K, w_base + n_tile * TILE_N, pol_w);
       }
-      if (!grouped) pdl_wait();
+    }
+    if (!grouped) pdl_wait();
+    if (prolog) {
+      // the whole warp watches the row flags of this launch's quantiser CTAs (lane l: rows l and l + 32)
+      const uint32_t ticket = quant_ticket(p.qp);
+      const uint64_t t_start = globaltimer_ns();
+      for (int r = lane; r < p.M; r += 32) {
+        uint32_t spins = 0;
+        while (*reinterpret_cast<const volatile uint32_t*>(p.qp.flags + r) != ticket) {
+          if ((++spins & 63u) == 0u && globaltimer_ns() - t_start > limit) {
+            if (p.status) atomicCAS(p.status, 0, (ST_TIMEOUT_PEER_FLAG | (2 << 8)));
+            ok = false;
+            break;
+          }
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      __threadfence();                            // acquire side of the row flags (they were polled with plain loads)
+      fence_proxy_async_all();                   // the rows were written with ordinary stores, TMA reads them
+    }
+    if (lane == 0 && ok) {
       B200_TRACE(TK_GEMM_DECODE, TP_DEPS);
       for (int i = 0; i < pre; ++i)
         tma_load_2d(smem_base + i * STAGE_BYTES + A_BYTES, &tmap_x, full_bar(i), (kb0 + i) * BLOCK_K, m0);
@@ -212,8 +257,8 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         tma_load_2d(a_dst + A_BYTES, &tmap_x, full_bar(stage), kb * BLOCK_K, m0);
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
-      if (!ok) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 2000000ull) { } }
     }
+    if (lane == 0 && !ok) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 2000000ull) { } }
     __syncwarp();
   } else if (warp == 1) {
     if (lane == 0) {
@@ -238,7 +283,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     __syncwarp();
   }
 
-  if (!grouped && !(warp == 0 && lane == 0)) pdl_wait();
+  if (!grouped && warp != 0) pdl_wait();
   if (fuse_ar) {
     // Every thread is past its dependency wait here, so all earlier launches of the stream (which advance the epoch
     // word when they finish) have completed.  The word is bumped again only after every CTA of this grid has exited.
@@ -256,9 +301,12 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   bool acc_ok = false;
   if (epi) {
     // token scales: the previous kernel's output, readable now that the dependency wait is behind us
-    if (et < BN) sx_s[et] = et < jmax ? p.sx[m0 + et] : 0.f;
+    if (!prolog && et < BN) sx_s[et] = et < jmax ? p.sx[m0 + et] : 0.f;
     acc_ok = (kb1 > kb0) && mbar_wait(tfull_bar, 0, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (2 << 8)), limit);
     tc_fence_after();
+    // fused prologue: the scales are written by this launch's quantiser CTAs; the accumulator can only be complete
+    // after the producer warp saw every row's flag, so they are there now (read past L1)
+    if (prolog && et < BN) sx_s[et] = et < jmax ? __ldcg(p.sx + m0 + et) : 0.f;
     if (et == 0) B200_TRACE(TK_GEMM_DECODE, 4);
   }
 
@@ -573,14 +621,16 @@ static int resident_clusters_reported(int bn, int s) {
 // Split along K: the largest cluster size (1..8, any value: slices need not divide the tile evenly) whose grid of
 // tiles x S CTAs (a) fits the SMs (two CTAs each for up to 32 tokens), (b) leaves every CTA at least two k-blocks, and (c) is resident at
 // once according to the occupancy query, with `margin` spare clusters.
-int decode_pick_splits(int tiles, int kblocks, int num_sms, int bn, int margin) {
+// quant_rows > 0: the launch also carries ceil(quant_rows / S) clusters of quantiser CTAs.
+int decode_pick_splits(int tiles, int kblocks, int num_sms, int bn, int margin, int quant_rows = 0) {
   static int limit_env = -1;
   if (limit_env < 0) { const char* e = std::getenv("B200RT_GEMM_MAX_CTAS"); limit_env = e ? std::atoi(e) : 0; }
   const int limit = limit_env > 0 ? limit_env : num_sms * ctas_per_sm(bn);
   int best = 1;
   for (int s = 2; s <= 8; ++s) {
-    if (tiles * s > limit || kblocks < 2 * s) break;
-    if (tiles + margin <= resident_clusters(bn, s)) best = s;
+    const int all = tiles + (quant_rows + s - 1) / s;
+    if (all * s > limit || kblocks < 2 * s) break;
+    if (all + margin <= resident_clusters(bn, s)) best = s;
   }
   return best;
 }
@@ -594,8 +644,17 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
                             const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
                             int num_sms, int force_splits, const ArTail* ar, cudaStream_t stream,
                             int groups = 0, const int* grp_offsets = nullptr, const int* grp_counts = nullptr,
-                            int x_rows = 0) {
+                            int x_rows = 0, const QuantProlog* qp = nullptr) {
   if (M <= 0 || M > SWAP_MAX_M || N <= 0 || K <= 0 || (K % 16) != 0) return -1;
+  if (qp) {
+    // the quantiser CTAs park a row as floats in the pipeline's stage memory and work in whole 128-blocks
+    if (groups > 0 || force_splits > 0 || (K % 128) || K * 4 > 80 * 1024 || qp->mode < QR_PLAIN || qp->mode > QR_SWIGLU) return -1;
+    if (!qp->x || !qp->q || !qp->scale || !qp->flags || !qp->step) return -1;
+    if ((qp->mode == QR_NORM || qp->mode == QR_ADD_NORM) && !qp->gamma) return -1;
+    if (qp->mode == QR_ADD_NORM && !qp->residual) return -1;
+    if ((qp->ldx % 4) || (qp->ldr % 4) || (reinterpret_cast<uintptr_t>(qp->x) & 7) || (reinterpret_cast<uintptr_t>(qp->residual) & 7) ||
+        (reinterpret_cast<uintptr_t>(qp->gamma) & 7)) return -2;
+  }
   if (groups > 0 && ((N % TILE_N) || !grp_offsets || !grp_counts || ar)) return -1;
   if ((reinterpret_cast<uintptr_t>(xq) & 15) || (reinterpret_cast<uintptr_t>(wq) & 15)) return -2;
   const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
@@ -605,7 +664,7 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
   const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = groups > 0 ? groups : (M + bn - 1) / bn;
   // A split whose clusters do not all fit on the GPU at once runs as two waves: twice the latency for an op that is
   // nothing but latency.  (Grouped launches have one grid row per expert and are multi-wave by nature.)
-  int s = force_splits > 0 ? force_splits : decode_pick_splits(n_tiles * m_tiles, p.kblocks, num_sms, bn, groups > 0 ? -100000 : 1);
+  int s = force_splits > 0 ? force_splits : decode_pick_splits(n_tiles * m_tiles, p.kblocks, num_sms, bn, groups > 0 ? -100000 : 1, qp ? M : 0);
   if (s < 1 || s > 8) return -1;
   p.splits = s;
   p.sx = sx; p.sw = sw; p.y = y; p.residual = static_cast<const __nv_bfloat16*>(residual);
@@ -620,15 +679,25 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
     // many clusters of this size fit (clusters are placed per GPC, so this is less than SMs x CTAs-per-SM / size)
     // and narrow the split until the grid fits, keeping a margin of one cluster.
     if ((N % 8) || (ldy % 8) || out_fp32) return -2;
-    while (s >= 1 && n_tiles * m_tiles + 1 > resident_clusters(bn, s)) --s;
+    while (s >= 1 && n_tiles * m_tiles + (qp ? (M + s - 1) / s : 0) + 1 > resident_clusters(bn, s)) --s;
     if (s < 1) return -20;
     p.splits = s;
     p.limit_ns = static_cast<unsigned long long>(ar->limit_ms > 0 ? ar->limit_ms : 2000) * 1000000ull;
   }
+  p.qp = QuantProlog{};
+  int q_rows = 0;
+  if (qp) {
+    static uint32_t launch_counter = 0;          // distinguishes the launches of one step (see quant_ticket)
+    p.qp = *qp;
+    p.qp.launch_id = ++launch_counter;
+    q_rows = (M + s - 1) / s;
+    p.qp.rows = q_rows;
+    if (m_tiles != 1) return -1;
+  }
   CUtensorMap tw, tx;
   if (make_tmap_2d_u8(&tw, wq, static_cast<uint64_t>(K), static_cast<uint64_t>(w_rows), static_cast<uint64_t>(K), TILE_N)) return -11;
   if (make_tmap_2d_u8(&tx, xq, static_cast<uint64_t>(K), static_cast<uint64_t>(xr), static_cast<uint64_t>(K), bn)) return -12;
-  dim3 grid(s, n_tiles, m_tiles);
+  dim3 grid(s, n_tiles + q_rows, m_tiles);
   switch (bn) {
     case 16: return launch_decode<16, 5>(tw, tx, p, grid, stream);
     case 32: return launch_decode<32, 4>(tw, tx, p, grid, stream);
@@ -667,6 +736,28 @@ extern "C" int b200_w8a8_gemm_decode_resident_clusters(int m, int splits) {
   return resident_clusters(m <= 16 ? 16 : (m <= 32 ? 32 : 64), splits);
 }
 
+static QuantProlog to_prolog(const b200_quant_prolog& c) {
+  QuantProlog q{};
+  q.mode = c.mode;
+  q.x = static_cast<const __nv_bfloat16*>(c.x); q.ldx = c.ldx;
+  q.residual = static_cast<__nv_bfloat16*>(c.residual); q.ldr = c.ldr;
+  q.gamma = static_cast<const __nv_bfloat16*>(c.gamma); q.eps = c.eps;
+  q.q = static_cast<int8_t*>(c.q); q.scale = c.scale;
+  q.flags = static_cast<uint32_t*>(c.flags); q.step = static_cast<const uint32_t*>(c.step);
+  return q;
+}
+
+// One launch from bf16 activations to the bf16 result: the prologue (prolog->mode: 1 rotate + quantise, 2 RMSNorm first,
+// 3 residual add + RMSNorm first, 4 SwiGLU of [M][2K] first) runs in quantiser CTAs of the same launch.
+extern "C" int b200_w8a8_gemm_decode_p(const b200_quant_prolog* prolog, const void* wq, const float* sw, void* y,
+                                       const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
+                                       int num_sms, cudaStream_t stream) {
+  if (!prolog) return -1;
+  const QuantProlog q = to_prolog(*prolog);
+  return decode_gemm_impl(q.q, q.scale, wq, sw, y, residual, M, N, K, ldy, out_fp32, status, num_sms, 0, nullptr, stream, 0, nullptr,
+                          nullptr, 0, &q);
+}
+
 extern "C" int b200_w8a8_gemm_decode(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
                                      const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status,
                                      int num_sms, int force_splits, cudaStream_t stream) {
@@ -687,12 +778,12 @@ extern "C" int b200_w8a8_gemm_decode_grouped(const void* xq, const float* sx, co
 // Row-parallel linear fused with its all-reduce: y[m,n] = sum over ranks of (xq_r . wq_r^T * sx_r * sw) (+ residual).
 // part_off0/1: byte offsets (same on every rank) of two [M][N] bf16 slots in the symmetric heap; words: >= 4 zeroed
 // device uint32 of this rank.  Returns -20 when the grid would not be co-resident (use the unfused path then).
-extern "C" int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
-                                        const void* residual, int M, int N, int K, int ldy, int* status, int num_sms,
-                                        void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
-                                        size_t part_off0, size_t part_off1, void* words, int limit_ms, int ll,
-                                        size_t recv_off0, size_t recv_off1, size_t recv_bytes, int two_hop,
-                                        size_t recv2_off0, size_t recv2_off1, size_t recv2_bytes, cudaStream_t stream) {
+static int decode_ar_impl(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
+                          const void* residual, int M, int N, int K, int ldy, int* status, int num_sms,
+                          void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
+                          size_t part_off0, size_t part_off1, void* words, int limit_ms, int ll,
+                          size_t recv_off0, size_t recv_off1, size_t recv_bytes, int two_hop,
+                          size_t recv2_off0, size_t recv2_off1, size_t recv2_bytes, cudaStream_t stream, const QuantProlog* qp) {
   if (world < 1 || world > MAX_RANKS) return -1;
   ArTail ar;
   for (int r = 0; r < MAX_RANKS; ++r) {
@@ -716,5 +807,30 @@ extern "C" int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const v
     if ((N + TILE_N - 1) / TILE_N < world) ar.two_hop = 0;
   }
   if ((part_off0 % 16) || (part_off1 % 16)) return -2;
-  return decode_gemm_impl(xq, sx, wq, sw, y, residual, M, N, K, ldy, 0, status, num_sms, 0, &ar, stream);
+  return decode_gemm_impl(xq, sx, wq, sw, y, residual, M, N, K, ldy, 0, status, num_sms, 0, &ar, stream, 0, nullptr, nullptr, 0, qp);
+}
+
+extern "C" int b200_w8a8_gemm_decode_ar(const void* xq, const float* sx, const void* wq, const float* sw, void* y,
+                                        const void* residual, int M, int N, int K, int ldy, int* status, int num_sms,
+                                        void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
+                                        size_t part_off0, size_t part_off1, void* words, int limit_ms, int ll,
+                                        size_t recv_off0, size_t recv_off1, size_t recv_bytes, int two_hop,
+                                        size_t recv2_off0, size_t recv2_off1, size_t recv2_bytes, cudaStream_t stream) {
+  return decode_ar_impl(xq, sx, wq, sw, y, residual, M, N, K, ldy, status, num_sms, peer_data, peer_flags, mc_base, world, rank,
+                        part_off0, part_off1, words, limit_ms, ll, recv_off0, recv_off1, recv_bytes, two_hop, recv2_off0,
+                        recv2_off1, recv2_bytes, stream, nullptr);
+}
+
+// The fused GEMM + all-reduce with the activation prologue in the same launch (see b200_w8a8_gemm_decode_p).
+extern "C" int b200_w8a8_gemm_decode_ar_p(const b200_quant_prolog* prolog, const void* wq, const float* sw, void* y,
+                                          const void* residual, int M, int N, int K, int ldy, int* status, int num_sms,
+                                          void* const* peer_data, void* const* peer_flags, void* mc_base, int world, int rank,
+                                          size_t part_off0, size_t part_off1, void* words, int limit_ms, int ll,
+                                          size_t recv_off0, size_t recv_off1, size_t recv_bytes, int two_hop,
+                                          size_t recv2_off0, size_t recv2_off1, size_t recv2_bytes, cudaStream_t stream) {
+  if (!prolog) return -1;
+  const QuantProlog q = to_prolog(*prolog);
+  return decode_ar_impl(q.q, q.scale, wq, sw, y, residual, M, N, K, ldy, status, num_sms, peer_data, peer_flags, mc_base, world, rank,
+                        part_off0, part_off1, words, limit_ms, ll, recv_off0, recv_off1, recv_bytes, two_hop, recv2_off0,
+                        recv2_off1, recv2_bytes, stream, &q);
 }

@@ -160,12 +160,14 @@ class Engine:
         nxt = self.model.forward(ids, positions, self.kv, mode="prefill", cu_seqlens=cu, max_len=S, seq_ids=seq_ids,
                                  last_idx=last)
         self.tokens[b0:b1].copy_(nxt)
+        default_workspace(self.device).next_step()
 
     def _decode_body(self) -> None:
         nxt = self.model.forward(self.tokens, self.positions, self.kv, mode="decode", max_len=self.rt.max_seq_len)
         self.tokens.copy_(nxt)
         self.positions.add_(1)
         self.kv.seq_lens.add_(1)
+        default_workspace(self.device).next_step()      # a launch replayed next step must not match this step's row flags
 
     def decode_step(self, use_graph: bool = True) -> torch.Tensor:
         """One greedy token for every sequence of the batch; returns the device tensor of new ids [B].

@@ -88,6 +88,11 @@ class Decoder:
         import os
         # decode attention with rope / KV append / output quantisation folded in (B200RT_FUSED_ATTN=0: three launches)
         self.fused_attention = os.environ.get("B200RT_FUSED_ATTN", "1") not in ("0", "false")
+        # decode linears that run their own activation prologue (norm / SwiGLU + rotation + int8) in quantiser CTAs of
+        # the GEMM launch.  Opt-in (B200RT_FUSED_QUANT=1): the hand-over of the int8 rows between CTAs of one launch (flag
+        # in L2, acquire, proxy fence) measured slower than the kernel boundary it replaces (programmatic dependent
+        # launch already overlaps that boundary): 5 instead of 8 launches per layer but +10..15 us per layer.
+        self.fused_quant = os.environ.get("B200RT_FUSED_QUANT", "0") not in ("0", "false")
 
     # -- building blocks ------------------------------------------------------------------------------------
     def _norm_quant(self, h, delta, gamma, want_normed=False):
@@ -136,6 +141,23 @@ class Decoder:
                             k_norm_w=W.get("k_norm"), eps=self.cfg.eps)
         return A.attn_decode(q, cache, kv.page_table, kv.seq_lens, scratch=sc, splits=splits, scale=self.scale)
 
+    def _fused_norm_linear(self, h, delta, gamma, lw):
+        """(residual add +) RMSNorm + rotation + int8 + column-parallel linear as one launch (decode, <= 64 tokens)."""
+        if delta is None:
+            return L.fused_linear(h, lw.qweight, lw.scale, mode=L.QR_NORM, gamma=gamma, eps=self.cfg.eps)
+        return L.fused_linear(delta, lw.qweight, lw.scale, mode=L.QR_ADD_NORM, gamma=gamma, eps=self.cfg.eps, residual=h)
+
+    def _fused_swiglu_down(self, gu, lw):
+        """SwiGLU + rotation + int8 + row-parallel down projection (+ all-reduce under tensor parallelism): one launch."""
+        if self.tp_ctx is not None:
+            y = self.tp_ctx.row_parallel_fused(gu, lw, L.QR_SWIGLU)
+            if y is not None:
+                return y
+        if self.comm.world > 1:
+            hq, sh = L.act_quant(gu, mode=L.AQ_SWIGLU)
+            return self._row_parallel(hq, sh, lw)
+        return L.fused_linear(gu, lw.qweight, lw.scale, mode=L.QR_SWIGLU)
+
     def _mlp(self, l, xq, sx, xn):
         W = self.w["layers"][l]
         if self.moe is not None:
@@ -159,13 +181,22 @@ class Decoder:
             return self._forward_prefill_sharded(token_ids, positions, kv, cu_seqlens, max_len, seq_ids, last_idx)
         h = A.embed_gather(token_ids, self.w["embed"])
         delta = None
+        d_ok = cfg.d_model % 128 == 0 and cfg.d_model <= L.FUSED_PROLOG_MAX_K
+        fq = self.fused_quant and mode == "decode" and token_ids.shape[0] <= L.DECODE_MAX_M and d_ok
         for l in range(cfg.n_layers):
             W = self.w["layers"][l]
-            xq, sx = self._norm_quant(h, delta, W["attn_norm"])
-            qkv = L.w8a8_gemm(xq, sx, W["qkv"].qweight, W["qkv"].scale)
+            if fq:
+                qkv = self._fused_norm_linear(h, delta, W["attn_norm"], W["qkv"])
+            else:
+                xq, sx = self._norm_quant(h, delta, W["attn_norm"])
+                qkv = L.w8a8_gemm(xq, sx, W["qkv"].qweight, W["qkv"].scale)
             attn = self._attention(l, qkv, positions, kv, mode, cu_seqlens, max_len, seq_ids)
             aq, sa = attn if isinstance(attn, tuple) else L.act_quant(attn.view(attn.shape[0], -1))
             delta = self._row_parallel(aq, sa, W["o"])
+            if fq and self.moe is None:
+                gu = self._fused_norm_linear(h, delta, W["mlp_norm"], W["gate_up"])
+                delta = self._fused_swiglu_down(gu, W["down"])
+                continue
             xq, sx = self._norm_quant(h, delta, W["mlp_norm"])      # the router, too, consumes the quantised rows
             delta = self._mlp(l, xq, sx, None)
         if last_idx is not None:

@@ -62,6 +62,8 @@ class _Sig:
     b200_w8a8_gemm = (I, [P, P, P, P, P, P, I, I, I, I, I, P, c_size_t, P, I, P, I, I, P])
     b200_w8a8_gemm_decode = (I, [P, P, P, P, P, P, I, I, I, I, I, P, I, I, P])
     b200_w8a8_gemm_decode_resident_clusters = (I, [I, I])
+    b200_w8a8_gemm_decode_p = (I, [P, P, P, P, P, I, I, I, I, I, P, I, P])
+    b200_w8a8_gemm_decode_ar_p = (I, [P, P, P, P, P, I, I, I, I, P, I, P, P, P, I, I, c_size_t, c_size_t, P, I, I, c_size_t, c_size_t, c_size_t, I, c_size_t, c_size_t, c_size_t, P])
     b200_peer_allreduce = (I, [P, P, P, I, I, c_size_t, c_size_t, P, P, c_size_t, I, I, P, P, I, I, I, P])
     b200_peer_argmax = (I, [P, P, I, I, c_size_t, P, P, I, I, P, P, P, I, P])
     b200_w8a8_gemm_ag = (I, [P, P, P, P, P, I, I, I, I, I, P, P, I, I, c_size_t, c_size_t, c_size_t, c_size_t, c_size_t, c_size_t, I, I, P, P, I, I, P, I, I, P])
@@ -99,6 +101,13 @@ class _Sig:
     b200_attn_prefill = (I, [P, LL, P, LL, P, LL, P, P, I, I, I, I, I, F, P, P])
     b200_attn_prefill_split = (I, [P, LL, P, LL, P, LL, P, P, I, I, I, I, I, F, I, P, P, P])
     b200_attn_prefill_split_scratch_floats = (c_size_t, [I, I, I, I])
+
+
+class QuantProlog(ctypes.Structure):
+    """``b200_quant_prolog`` of csrc/kernels/api.h: the activation prologue a decode GEMM launch carries itself."""
+    _fields_ = [("mode", c_int), ("x", c_void_p), ("ldx", c_longlong), ("residual", c_void_p), ("ldr", c_longlong),
+                ("gamma", c_void_p), ("eps", c_float), ("q", c_void_p), ("scale", c_void_p), ("flags", c_void_p),
+                ("step", c_void_p)]
 
 
 def ptr(t: torch.Tensor | None) -> int | None:

@@ -75,3 +75,48 @@ def w8a8_gemm(xq: torch.Tensor, sx: torch.Tensor, wq: torch.Tensor, sw: torch.Te
         _lib.num_sms(xq.device.index), force_mode, _lib.stream())
     _lib.check(rc, "w8a8_gemm")
     return out
+
+
+QR_PLAIN, QR_NORM, QR_ADD_NORM, QR_SWIGLU = 1, 2, 3, 4
+FUSED_PROLOG_MAX_K = 20480          # a row is parked as floats in the GEMM's stage memory (80 KiB)
+
+
+def make_prolog(x: torch.Tensor, mode: int, *, gamma: torch.Tensor | None = None, eps: float = 1e-5,
+                residual: torch.Tensor | None = None, workspace: Workspace | None = None):
+    """Describe the activation prologue a decode GEMM launch should run itself (see ``fused_linear``).
+
+    Returns ``(struct, keep)``: the ctypes struct for the C entry points and the tensors it points at (int8 rows,
+    scales), which the caller keeps alive until the launch has run."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    M = x.shape[0]
+    K = x.shape[1] // 2 if mode == QR_SWIGLU else x.shape[1]
+    assert M <= DECODE_MAX_M and K % 128 == 0 and K <= FUSED_PROLOG_MAX_K
+    w = workspace or default_workspace(x.device)
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.stride(1) == 1
+    st = _lib.QuantProlog(mode, x.data_ptr(), x.stride(0), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
+                          _lib.ptr(gamma), float(eps), q.data_ptr(), s.data_ptr(), w.qflags.data_ptr(), w.step.data_ptr())
+    return st, (q, s)
+
+
+def fused_linear(x: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor, *, mode: int = QR_PLAIN,
+                 gamma: torch.Tensor | None = None, eps: float = 1e-5, residual: torch.Tensor | None = None,
+                 out_dtype: torch.dtype = torch.bfloat16, workspace: Workspace | None = None) -> torch.Tensor:
+    """bf16 activations in, bf16 (or fp32) result out, in ONE launch for up to 64 tokens: the activation prologue
+    (``mode``: QR_PLAIN rotate + int8; QR_NORM RMSNorm first; QR_ADD_NORM ``residual += x`` in place, then RMSNorm of
+    the residual; QR_SWIGLU x = gate | up) runs in quantiser CTAs of the GEMM's own grid, which publish a flag per
+    token row; the GEMM CTAs stream their first weight tiles meanwhile and wait for the flags, not for a kernel."""
+    import ctypes
+    N, K = wq.shape
+    M = x.shape[0]
+    w = workspace or default_workspace(x.device)
+    st, keep = make_prolog(x, mode, gamma=gamma, eps=eps, residual=residual, workspace=w)
+    assert keep[0].shape[1] == K
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    rc = _lib.lib().b200_w8a8_gemm_decode_p(
+        ctypes.byref(st), wq.data_ptr(), sw.data_ptr(), out.data_ptr(), None, M, N, K, out.stride(0),
+        1 if out_dtype == torch.float32 else 0, w.status.data_ptr(), _lib.num_sms(x.device.index), _lib.stream())
+    _lib.check(rc, "w8a8_gemm_decode_p")
+    return out

@@ -20,7 +20,7 @@ class Workspace:
 
     @classmethod
     def nbytes(cls, ws_bytes: int | None = None, counters: int | None = None) -> int:
-        return (ws_bytes or cls.DEFAULT_WS_BYTES) + 4 * (counters or cls.DEFAULT_COUNTERS) + 16 + 3 * 1024
+        return (ws_bytes or cls.DEFAULT_WS_BYTES) + 4 * (counters or cls.DEFAULT_COUNTERS) + 16 + 256 + 16 + 5 * 1024
 
     def __init__(self, device: torch.device, ws_bytes: int = 64 << 20, counters: int = 1 << 16, alloc=None):
         """``alloc(shape, dtype) -> zeroed tensor`` places the buffers (e.g. in a rank's HBM arena); default torch."""
@@ -31,6 +31,14 @@ class Workspace:
         self.ws = alloc((ws_bytes // 4,), torch.int32)
         self.counters = alloc((counters,), torch.int32)
         self.status = alloc((4,), torch.int32)
+        # fused activation prologue of the decode GEMMs: one flag word per token row, and the step word whose change
+        # between two replays of a captured launch keeps a replay from mistaking last step's flags for its own
+        self.qflags = alloc((64,), torch.int32)
+        self.step = alloc((4,), torch.int32)
+
+    def next_step(self) -> None:
+        """Advance the step word (a tiny device-side add on the current stream): call once per forward pass."""
+        self.step.add_(1)
 
     @property
     def ws_bytes(self) -> int:

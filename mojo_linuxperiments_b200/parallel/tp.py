@@ -76,6 +76,31 @@ class TPContext:
             return want == "1"
         return True
 
+    def row_parallel_fused(self, x: torch.Tensor, lw, mode: int):
+        """Row-parallel linear from bf16 activations: activation prologue (``mode`` as in ``ops.linear.fused_linear``),
+        K-shard product and all-reduce in ONE launch.  Returns None when the grid would not be co-resident (the caller
+        then quantises with the stand-alone kernel and calls ``row_parallel``)."""
+        import ctypes
+        M = x.shape[0]
+        N, K = lw.qweight.shape
+        if M > FUSED_MAX_M or K % 128 or K > L.FUSED_PROLOG_MAX_K:
+            return None
+        h = self.heap
+        ws = default_workspace(x.device)
+        st, keep = L.make_prolog(x, mode, workspace=ws)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
+        rc = _lib.lib().b200_w8a8_gemm_decode_ar_p(
+            ctypes.byref(st), lw.qweight.data_ptr(), lw.scale.data_ptr(), out.data_ptr(), None, M, N, K, out.stride(0),
+            ws.status.data_ptr(), _lib.num_sms(x.device.index), h._c_data, h._c_flags,
+            (h.mc_data_ptr or None) if self.use_nvls else None, h.world, h.rank, self.part_off[0], self.part_off[1],
+            h.epoch_words.data_ptr(), self.limit_ms, 1 if self.low_latency else 0, self.recv_off[0], self.recv_off[1],
+            self.recv_bytes, 1 if (self.two_hop_min > 0 and M >= self.two_hop_min) else 0, self.recv2_off[0],
+            self.recv2_off[1], self.recv2_bytes, _lib.stream())
+        if rc == -20:
+            return None
+        _lib.check(rc, "w8a8_gemm_decode_ar_p")
+        return out
+
     def row_parallel(self, xq: torch.Tensor, sx: torch.Tensor, lw, residual: torch.Tensor | None = None) -> torch.Tensor:
         """Sum over ranks of this rank's K-shard product; returns the full [M, N] bf16 result on every rank."""
         M, K = xq.shape

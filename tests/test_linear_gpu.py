@@ -133,3 +133,66 @@ def test_w8a8_gemm_residual_and_full_op():
     exact = x.float() @ w.cuda().t() + res.float()
     rel = (y.float() - exact).norm() / exact.norm()
     assert rel.item() < 0.05
+
+
+@pytest.mark.parametrize("mode", ["plain", "norm", "add_norm", "swiglu"])
+@pytest.mark.parametrize("m,n,k", [(1, 768, 4096), (32, 6144, 4096), (17, 4096, 1792), (64, 1024, 512), (32, 4096, 14336)])
+def test_fused_linear_runs_its_own_activation_prologue(mode, m, n, k):
+    """One launch from bf16 rows to the linear's output: the quantiser CTAs inside the GEMM launch must produce what the
+    stand-alone prologue + GEMM produce (same int8 rows up to rare +-1 ties, so the outputs agree closely), update the
+    residual exactly, and keep doing so when the launch is replayed from a CUDA graph."""
+    from mojo_linuxperiments_b200.ops import linear as L
+    from mojo_linuxperiments_b200.ops.workspace import default_workspace
+    ws = default_workspace(torch.device("cuda", 0))
+    wq, sw = _mk_w(n, k)
+    gamma = (torch.rand(k) + 0.5).to(torch.bfloat16).cuda()
+    x = _mk_x(m, 2 * k if mode == "swiglu" else k, 21)
+    res = _mk_x(m, k, 22)
+
+    def unfused():
+        if mode == "plain":
+            q, s = L.act_quant(x)
+        elif mode == "norm":
+            q, s = L.act_quant(x, mode=L.AQ_NORM, gamma=gamma, eps=1e-5)
+        elif mode == "add_norm":
+            r = res.clone()
+            q, s = L.act_quant(x, mode=L.AQ_ADD_NORM, gamma=gamma, eps=1e-5, residual=r)
+            return L.w8a8_gemm(q, s, wq, sw, force_mode=2), r
+        else:
+            q, s = L.act_quant(x, mode=L.AQ_SWIGLU)
+        return L.w8a8_gemm(q, s, wq, sw, force_mode=2), None
+
+    def fused(r):
+        md = {"plain": L.QR_PLAIN, "norm": L.QR_NORM, "add_norm": L.QR_ADD_NORM, "swiglu": L.QR_SWIGLU}[mode]
+        return L.fused_linear(x, wq, sw, mode=md, gamma=gamma if mode in ("norm", "add_norm") else None, eps=1e-5,
+                              residual=r if mode == "add_norm" else None)
+
+    ref, ref_res = unfused()
+    r1 = res.clone()
+    y1 = fused(r1)
+    ws.next_step()
+    r2 = res.clone()
+    y2 = fused(r2)
+    torch.cuda.synchronize()
+    ws.check_status()
+    tol = 2e-2 * ref.float().abs().max().item()
+    assert torch.allclose(y1.float(), ref.float(), rtol=2e-2, atol=tol), (y1.float() - ref.float()).abs().max().item()
+    assert torch.equal(y1, y2)
+    if mode == "add_norm":
+        assert torch.equal(r1, ref_res) and torch.equal(r2, ref_res)
+    # replayed from a graph: the step word moves between replays, the row flags are told apart by it
+    rg = res.clone()
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(g, stream=s):
+            yg = fused(rg)
+            yg2 = fused(rg) if mode != "add_norm" else yg
+            ws.next_step()
+    for _ in range(3):
+        rg.copy_(res)
+        g.replay()
+    torch.cuda.synchronize()
+    ws.check_status()
+    assert torch.equal(yg, y1) and torch.equal(yg2, y1)
