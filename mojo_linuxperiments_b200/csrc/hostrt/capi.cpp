@@ -10,6 +10,7 @@
 #include "pool.hpp"
 #include "scenarios.hpp"
 #include "fabric/philox.h"
+#include "fabric/range_check.h"
 
 using namespace hostrt;
 
@@ -37,6 +38,14 @@ long hostrt_struct_size(const char* name) {
 }
 long hostrt_slot_total_size(unsigned long stack_bytes) { return static_cast<long>(slot_total_size(stack_bytes)); }
 long hostrt_gettid() { return sys_gettid(); }
+// The range check the debug build of the GPU kernels applies to heap offsets, run on the host: returns 1 when the
+// access may go ahead; otherwise 0, and report3 = {code, offset low, offset high} if it was still empty.
+int hostrt_range_check(unsigned long long off, unsigned long long len, unsigned long long extent, int* report3) {
+  b200::RangeReport rep{report3 ? report3[0] : 0, report3 ? static_cast<unsigned>(report3[1]) : 0u, report3 ? static_cast<unsigned>(report3[2]) : 0u};
+  const bool ok = b200::range_check_record(off, len, extent, &rep);
+  if (report3) { report3[0] = rep.code; report3[1] = static_cast<int>(rep.off_lo); report3[2] = static_cast<int>(rep.off_hi); }
+  return ok ? 1 : 0;
+}
 long hostrt_monotonic_ns() { return sys_clock_monotonic_ns(); }
 
 // ---- raw memory calls -----------------------------------------------------------------------------------

@@ -137,6 +137,8 @@ int b200_attn_prefill_split(const void* q, long long ld_q, const void* k, long l
                             float scale, int chunk, float* scratch, int* status, cudaStream_t stream);
 
 // ---- in-kernel time stamps (trace.cuh; only in the library variant built with -DB200RT_TRACE) -----------------------
+int b200_debug_compiled(void);
+int b200_debug_set_heap_extent(size_t bytes);
 int b200_trace_compiled(void);
 int b200_trace_set(void* ring, unsigned capacity);
 

@@ -5,6 +5,7 @@
 #include <cuda_runtime.h>
 #include <cstdlib>
 #include "trace.cuh"
+#include "debug_check.cuh"
 
 namespace b200 {
 
@@ -22,6 +23,7 @@ template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_ex(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster_x,
                              Args&&... args) {
   trace_refresh();
+  debug_refresh();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;
@@ -51,6 +53,7 @@ template <typename... KArgs, typename... Args>
 static inline cudaError_t launch_ex_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                             dim3 cluster, Args&&... args) {
   trace_refresh();
+  debug_refresh();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = block;

@@ -64,7 +64,12 @@ __global__ void __launch_bounds__(128) ep_dispatch_kernel(const EpDispatchParams
   }
   __syncthreads();
   const size_t grow = static_cast<size_t>(t.rank) * R + row;
-  if (ok_s) {
+  // debug build: every store of this row (int8 row, scale, routing lists) must land inside the peers' heaps
+  const bool heap_fine = B200_DBG_RANGE(g.q_off[par] + grow * p.K, static_cast<size_t>(p.K), g.status) &&
+                         B200_DBG_RANGE(g.s_off[par] + grow * 4, 4, g.status) &&
+                         B200_DBG_RANGE(p.ids_off[par] + grow * EP_KMAX * 4, EP_KMAX * 4, g.status) &&
+                         B200_DBG_RANGE(p.wts_off[par] + grow * EP_KMAX * 4, EP_KMAX * 4, g.status);
+  if (ok_s && heap_fine) {
     // routing list to every rank, padded to EP_KMAX with id -1
     if (tid < EP_KMAX) {
       const int id = tid < p.k ? p.ids_local[static_cast<size_t>(row) * p.k + tid] : -1;

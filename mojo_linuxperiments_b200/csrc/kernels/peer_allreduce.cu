@@ -48,6 +48,14 @@ __global__ void __launch_bounds__(256) peer_allreduce_kernel(const ArParams p) {
   pdl_wait();                // everything before this kernel in the stream has completed
 
   const PeerTable& t = p.t;
+  {
+    // debug build: the message and (low-latency form) the receive slots must lie inside the heap on every rank; a
+    // launch that would not is recorded and does nothing (its peers run into their bounded waits)
+    const size_t esz = p.dtype == 0 ? 2 : (p.dtype == 1 ? 4 : 8);
+    bool fine = B200_DBG_RANGE(p.in_off, p.n * esz, p.status);
+    if (p.algo == 5) fine = B200_DBG_RANGE(p.scratch_off, 2 * static_cast<size_t>(t.world) * (p.n / 2) * 8, p.status) && fine;
+    if (!fine) return;
+  }
   const uint32_t e0 = *reinterpret_cast<volatile uint32_t*>(p.epoch) + 1;     // same on every CTA: bumped only at exit
   const int tid = threadIdx.x;
   __shared__ int ok_s;
@@ -333,6 +341,7 @@ __global__ void __launch_bounds__(128) peer_argmax_kernel(const ArgmaxParams p) 
   const uint32_t e0 = *reinterpret_cast<volatile uint32_t*>(p.epoch) + 1;
   const size_t src_stride = static_cast<size_t>(p.rows) * 16;
   const size_t slot = p.val_off + static_cast<size_t>(e0 & 1) * t.world * src_stride;
+  if (!B200_DBG_RANGE(p.val_off, 2 * static_cast<size_t>(t.world) * src_stride, p.status)) return;
   const uint64_t t_start = globaltimer_ns();
   for (int r = threadIdx.x; r < p.rows; r += blockDim.x) {
     float best = -INFINITY;

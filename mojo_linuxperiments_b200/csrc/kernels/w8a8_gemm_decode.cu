@@ -421,12 +421,15 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     const size_t slot = p.ar.recv_off[ar_epoch & 1];
     const size_t src_stride = static_cast<size_t>(p.M) * (p.N / 2) * 8;          // bytes per source rank
     const bool two_hop = p.ar.two_hop != 0;
+    // debug build: both receive areas must lie inside the heap (a violation is recorded and the tail does nothing)
+    bool heap_fine = B200_DBG_RANGE(p.ar.recv_off[0], t.world * src_stride, p.status) && B200_DBG_RANGE(p.ar.recv_off[1], t.world * src_stride, p.status);
+    if (two_hop) heap_fine = B200_DBG_RANGE(p.ar.recv2_off[0], src_stride, p.status) && B200_DBG_RANGE(p.ar.recv2_off[1], src_stride, p.status) && heap_fine;
     // two-hop: who reduces this CTA's column slice
     const int unit = n_tile * S + rank;
     const int owner = two_hop ? unit % t.world : t.rank;
     const bool own = owner == t.rank;
     __syncthreads();                                                             // vals complete
-    if (epi) {
+    if (epi && heap_fine) {
       for (int w = et; w < words; w += 128) {
         const int j = w / half, c2 = w - j * half;
         const int n = n_base + 2 * c2;
@@ -513,6 +516,8 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     const PeerTable& t = p.ar.t;
     const unsigned total_ctas = gridDim.x * gridDim.y * gridDim.z;
     const unsigned cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+    const bool heap_fine = B200_DBG_RANGE(p.ar.part_off[0], static_cast<size_t>(p.M) * p.N * 2, p.status) &&
+                           B200_DBG_RANGE(p.ar.part_off[1], static_cast<size_t>(p.M) * p.N * 2, p.status);
     __shared__ int ar_ok;
     __threadfence_system();                       // this CTA's part of the partial product is visible to peers
     __syncthreads();
@@ -528,7 +533,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     __syncthreads();
     if (threadIdx.x < 32) { if (!wait_all(t, 0, ar_epoch, threadIdx.x, p.status, limit)) ar_ok = 0; }
     __syncthreads();
-    if (ar_ok) {
+    if (ar_ok && heap_fine) {
       const size_t nvec = static_cast<size_t>(p.M) * p.N / 8;            // N is a multiple of 8
       const size_t v0 = nvec * cta / total_ctas, v1 = nvec * (cta + 1) / total_ctas;
       const size_t off = p.ar.part_off[ar_epoch & 1];

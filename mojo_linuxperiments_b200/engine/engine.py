@@ -30,6 +30,11 @@ class Engine:
         self.comm = comm or Comm.single()
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         # where this rank runs (host thread pinned beside its GPU) and where its long-lived buffers live (HBM arena)
+        if self.rt.debug:
+            from ..ops import _lib
+            if not _lib.lib().b200_debug_compiled():
+                raise RuntimeError("RuntimeConfig.debug needs the range-checked kernel library: set B200RT_DEBUG=1 (or "
+                                   "B200RT_KERNELS=debug) before the first kernel is used")
         self.runtime = RankRuntime(self.device)
         self.heartbeat = None
         if weights is None:
@@ -56,6 +61,9 @@ class Engine:
 
     # ------------------------------------------------------------------------------------------------------
     def start_batch(self, batch: int, max_total_len: int) -> None:
+        """Open a batch of ``batch`` sequence slots whose sequences may grow to ``max_total_len`` tokens.  No KV page is
+        reserved here: ``prefill`` / ``admit_sequence`` take the pages a prompt needs, every decode step takes one more
+        page for the sequences that cross a page boundary, ``release_sequence`` gives them back."""
         if max_total_len > self.rt.max_seq_len:
             raise ValueError(f"{max_total_len} tokens exceed max_seq_len {self.rt.max_seq_len}")
         if self.kv is None or self.kv.seq_lens.numel() != batch or self.kv.max_pages * self.rt.page_size < max_total_len:
@@ -66,17 +74,20 @@ class Engine:
             self.kv = KVState(self.cfg, self.rt, self.device, batch, self.rt.max_seq_len, alloc=self.runtime.zeros)
             self.tokens = torch.zeros(batch, dtype=torch.int64, device=self.device)
             self.positions = torch.zeros(batch, dtype=torch.int32, device=self.device)
+            self.active = torch.zeros(batch, dtype=torch.int32, device=self.device)
         else:
             # same cache, same static tensors: the captured graphs stay valid
             for s in list(self.kv.owned):
                 self.kv.release(s)
             self.tokens.zero_()
             self.positions.zero_()
-        for s in range(batch):
-            self.kv.admit(s, max_total_len)
+            self.active.zero_()
+            self.kv.seq_lens.zero_()
+        self.kv.flush()
         self.batch = batch
         self._admitted = max_total_len
-        self._host_len = 0
+        self._lens = [0] * batch            # tokens per slot already in the cache (host mirror of ``positions``); 0: empty
+        self._host_len = 0                  # longest of them
 
     def _place_buffers(self, batch: int) -> None:
         """One arena per rank (the reference: one arena per node, test_linux_threading.mojo:237-250) for the KV cache of
@@ -103,21 +114,49 @@ class Engine:
 
     def memory_report(self) -> dict:
         """Placement of the rank (GPU, NUMA node, pinned CPUs) and the arena's counters (used / remaining / high water)."""
-        return self.runtime.report()
+        r = self.runtime.report()
+        if self.kv is not None:
+            r["kv_pages"] = {"total": self.kv.num_pages - 1, "in_use": self.kv.pages_in_use(), "high_water": self.kv.pages_high_water,
+                             "page_tokens": self.kv.page_size}
+        return r
 
-    def prefill(self, prompts: torch.Tensor, use_graph: bool = True) -> torch.Tensor:
-        """prompts int64 [B, S] (host or device; equal lengths).  Returns the first generated token per sequence
-        (device tensor) and leaves the engine ready for ``decode_step``.  Long batches are processed in groups of
-        whole sequences so that one call never carries more than ``rt.max_prefill_tokens`` tokens; each group's
-        forward pass is one CUDA graph (captured at first use)."""
+    def prefill(self, prompts, use_graph: bool = True) -> torch.Tensor:
+        """Prompts of the whole batch -> first generated token per sequence (device tensor); the engine is then ready
+        for ``decode_step``.  ``prompts`` is int64 [B, S] (host or device), or a list of B one-dimensional id tensors of
+        any lengths (a ragged batch: the kernels take cumulative sequence lengths).  Long batches are processed in
+        groups of whole sequences so that one call never carries more than ``rt.max_prefill_tokens`` tokens; for
+        equal lengths each group's forward pass is one CUDA graph (captured at first use)."""
         if self.heartbeat is not None:
             self.heartbeat.check_fast()
+        if isinstance(prompts, (list, tuple)):
+            lens = [int(p.numel()) for p in prompts]
+            if len(set(lens)) == 1:
+                prompts = torch.stack([p.reshape(-1) for p in prompts])
+            else:
+                return self._prefill_ragged(prompts, lens)
         B, S = prompts.shape
-        ids_all = prompts.to(self.device, non_blocking=True)
-        group = max(1, min(B, self.rt.max_prefill_tokens // S))
-        for b0 in range(0, B, group):
-            b1 = min(B, b0 + group)
-            ids = ids_all[b0:b1].reshape(-1)
+        if S + 1 > self._admitted:
+            raise ValueError(f"a prompt of {S} tokens leaves no room to decode within the {self._admitted} admitted")
+        for b in range(B):
+            self.kv.admit(b, S + 1)
+        self.kv.flush()
+        self._prefill_equal(prompts.to(self.device, non_blocking=True), 0, use_graph)
+        self.positions[:B].fill_(S)
+        self.kv.seq_lens[:B].fill_(S + 1)      # the next decode step attends to the prompt plus its own token
+        self.active[:B].fill_(1)
+        for b in range(B):
+            self._lens[b] = S
+        self._host_len = max(self._lens)
+        return self.tokens.clone()
+
+    def _prefill_equal(self, ids_all: torch.Tensor, slot0: int, use_graph: bool) -> None:
+        """ids_all [n, S] on the device: prefill slots slot0 .. slot0 + n - 1 (pages already admitted)."""
+        n, S = ids_all.shape
+        group = max(1, min(n, self.rt.max_prefill_tokens // S))
+        for g0 in range(0, n, group):
+            g1 = min(n, g0 + group)
+            b0, b1 = slot0 + g0, slot0 + g1
+            ids = ids_all[g0:g1].reshape(-1)
             if not use_graph:
                 self._prefill_body(ids, b0, b1, S, self._prefill_consts(b0, b1, S))
                 continue
@@ -142,10 +181,77 @@ class Engine:
                 self._prefill_graphs[key] = entry
             entry[1].copy_(ids, non_blocking=True)
             entry[0].replay()
-        self.positions.fill_(S)
-        self.kv.seq_lens.fill_(S + 1)      # the next decode step attends to the prompt plus its own token
-        self._host_len = S
+
+    def _prefill_ragged(self, prompts, lens) -> torch.Tensor:
+        """Prompts of different lengths in one call per group: ids are concatenated, every token carries its position
+        and its sequence slot, attention works on the cumulative lengths (eager launches: the shapes differ per call)."""
+        B = len(prompts)
+        if max(lens) + 1 > self._admitted or min(lens) < 1:
+            raise ValueError(f"prompt lengths {min(lens)}..{max(lens)} do not fit the {self._admitted} admitted tokens")
+        for b in range(B):
+            self.kv.admit(b, lens[b] + 1)
+        self.kv.flush()
+        dev = self.device
+        b0 = 0
+        while b0 < B:
+            b1, tokens = b0, 0
+            while b1 < B and (b1 == b0 or tokens + lens[b1] <= self.rt.max_prefill_tokens):
+                tokens += lens[b1]
+                b1 += 1
+            ids = torch.cat([prompts[b].reshape(-1).to(torch.int64) for b in range(b0, b1)]).to(dev, non_blocking=True)
+            pos = torch.cat([torch.arange(lens[b], dtype=torch.int32) for b in range(b0, b1)]).to(dev, non_blocking=True)
+            sid = torch.cat([torch.full((lens[b],), b, dtype=torch.int32) for b in range(b0, b1)]).to(dev, non_blocking=True)
+            cu_host = [0]
+            for b in range(b0, b1):
+                cu_host.append(cu_host[-1] + lens[b])
+            cu = torch.tensor(cu_host, dtype=torch.int32).to(dev, non_blocking=True)
+            last = torch.tensor([c - 1 for c in cu_host[1:]], dtype=torch.int64).to(dev, non_blocking=True)
+            nxt = self.model.forward(ids, pos, self.kv, mode="prefill", cu_seqlens=cu, max_len=max(lens[b0:b1]), seq_ids=sid,
+                                     last_idx=last)
+            self.tokens[b0:b1].copy_(nxt)
+            default_workspace(self.device).next_step()
+            b0 = b1
+        lt = torch.tensor(lens, dtype=torch.int32).to(dev, non_blocking=True)
+        self.positions[:B].copy_(lt)
+        self.kv.seq_lens[:B].copy_(lt + 1)
+        self.active[:B].fill_(1)
+        for b in range(B):
+            self._lens[b] = lens[b]
+        self._host_len = max(self._lens)
         return self.tokens.clone()
+
+    def admit_sequence(self, slot: int, prompt: torch.Tensor, use_graph: bool = True) -> torch.Tensor:
+        """Between two decode steps: put a new sequence into slot ``slot`` (empty, or whose sequence is finished) of the
+        running batch.  Its prompt is prefilled into freshly admitted pages, the slot's token / position / length are
+        set, and the captured decode graph keeps being replayed as it is (it reads those tensors, not their values
+        at capture time).  Returns the sequence's first generated token (one-element device tensor)."""
+        if not 0 <= slot < self.batch:
+            raise IndexError(slot)
+        S = int(prompt.numel())
+        if S < 1 or S + 1 > self._admitted:
+            raise ValueError(f"a prompt of {S} tokens does not fit the {self._admitted} admitted tokens")
+        self.kv.release(slot)
+        self.kv.admit(slot, S + 1)
+        self.kv.flush()
+        self._prefill_equal(prompt.reshape(1, S).to(torch.int64).to(self.device, non_blocking=True), slot, use_graph)
+        self.positions[slot:slot + 1].fill_(S)
+        self.kv.seq_lens[slot:slot + 1].fill_(S + 1)
+        self.active[slot:slot + 1].fill_(1)
+        self._lens[slot] = S
+        self._host_len = max(self._lens)
+        return self.tokens[slot:slot + 1].clone()
+
+    def release_sequence(self, slot: int) -> None:
+        """The sequence in ``slot`` is finished: its pages go back to the free list, and the slot stays in the batch as
+        an empty one (length 0, page-table row on the scratch page) until ``admit_sequence`` fills it again."""
+        self.kv.release(slot)
+        self.kv.flush()
+        self.positions[slot:slot + 1].zero_()
+        self.kv.seq_lens[slot:slot + 1].zero_()
+        self.active[slot:slot + 1].zero_()
+        self.tokens[slot:slot + 1].zero_()
+        self._lens[slot] = 0
+        self._host_len = max(self._lens)
 
     def _prefill_consts(self, b0: int, b1: int, S: int):
         n = b1 - b0
@@ -165,8 +271,8 @@ class Engine:
     def _decode_body(self) -> None:
         nxt = self.model.forward(self.tokens, self.positions, self.kv, mode="decode", max_len=self.rt.max_seq_len)
         self.tokens.copy_(nxt)
-        self.positions.add_(1)
-        self.kv.seq_lens.add_(1)
+        self.positions.add_(self.active)        # empty slots stay at position 0, length 0
+        self.kv.seq_lens.add_(self.active)
         default_workspace(self.device).next_step()      # a launch replayed next step must not match this step's row flags
 
     def decode_step(self, use_graph: bool = True) -> torch.Tensor:
@@ -179,6 +285,13 @@ class Engine:
         if self._host_len + 1 > self._admitted:
             raise RuntimeError(f"decode step at position {self._host_len} exceeds the {self._admitted} tokens per "
                                f"sequence admitted by start_batch")
+        # this step writes token number len + 1 of every running sequence: take the page it lands on if the sequence
+        # does not own it yet (once per page_size steps and sequence), and push the page table if a row changed
+        for b, n in enumerate(self._lens):
+            if n > 0:
+                self.kv.admit(b, n + 1)
+                self._lens[b] = n + 1
+        self.kv.flush()
         self._host_len += 1
         if not use_graph:
             self._decode_body()

@@ -70,6 +70,7 @@ def lib() -> ctypes.CDLL:
         "hostrt_chain_reduce": (c_long, [c_void_p, c_int, c_long, POINTER(c_longlong)]),
         "hostrt_butterfly_allreduce": (c_long, [c_void_p, c_int, POINTER(c_longlong), c_long]),
         "hostrt_fabric_allreduce": (c_long, [c_void_p, c_int, POINTER(c_double), POINTER(c_double), c_int, c_long, c_int]),
+        "hostrt_range_check": (c_int, [c_ulonglong, c_ulonglong, c_ulonglong, c_void_p]),
         "hostrt_team_create": (c_void_p, [c_void_p, c_int]), "hostrt_team_destroy": (None, [c_void_p]),
         "hostrt_team_size": (c_int, [c_void_p]), "hostrt_team_jobs_run": (c_ulonglong, [c_void_p]),
         "hostrt_team_valid": (c_int, [c_void_p]), "hostrt_team_stragglers": (c_int, [c_void_p]),

@@ -25,40 +25,67 @@ class KVState:
         """Device bytes of a cache for ``num_seqs`` sequences of up to ``max_seq_len`` tokens (storage + tables)."""
         max_pages = (max_seq_len + rt.page_size - 1) // rt.page_size
         hkv = kv_heads_per_rank(cfg, rt.tp)
-        return (cfg.n_layers * num_seqs * max_pages * 2 * hkv * rt.page_size * cfg.head_dim * 2
+        return (cfg.n_layers * (num_seqs * max_pages + 1) * 2 * hkv * rt.page_size * cfg.head_dim * 2
                 + num_seqs * max_pages * 4 + num_seqs * 4 + 3 * 1024)
 
     def __init__(self, cfg: ModelConfig, rt: RuntimeConfig, device, num_seqs: int, max_seq_len: int, alloc=None):
-        """``alloc(shape, dtype) -> zeroed tensor``: where the cache lives (the rank's HBM arena); default torch.zeros."""
+        """``alloc(shape, dtype) -> zeroed tensor``: where the cache lives (the rank's HBM arena); default torch.zeros.
+
+        Pages are handed out on demand (``admit`` as a sequence grows) from a host-side free list.  The last page is
+        a scratch page no sequence owns: the page-table rows of empty slots point at it, so a kernel that runs over
+        an empty slot of the batch has somewhere harmless to write."""
         if alloc is None:
             def alloc(shape, dtype):
                 return torch.zeros(shape, dtype=dtype, device=device)
         self.page_size = rt.page_size
         self.max_pages = (max_seq_len + rt.page_size - 1) // rt.page_size
-        self.num_pages = num_seqs * self.max_pages
+        self.num_pages = num_seqs * self.max_pages + 1
+        self.scratch_page = self.num_pages - 1
         hkv = kv_heads_per_rank(cfg, rt.tp)
         self.storage = alloc((cfg.n_layers, self.num_pages, 2, hkv, rt.page_size, cfg.head_dim), torch.bfloat16)
         self.layers = [A.PagedKVCache(self.num_pages, hkv, rt.page_size, device, storage=self.storage[l])
                        for l in range(cfg.n_layers)]
         self.page_table = alloc((num_seqs, self.max_pages), torch.int32)
         self.seq_lens = alloc((num_seqs,), torch.int32)
-        self.free_pages = list(range(self.num_pages - 1, -1, -1))
+        self.free_pages = list(range(self.num_pages - 2, -1, -1))
         self.owned: dict[int, list[int]] = {}
+        # host mirror of the page table (pinned where possible): rows are edited here and copied over when they changed
+        self.table_host = torch.full((num_seqs, self.max_pages), self.scratch_page, dtype=torch.int32)
+        if torch.cuda.is_available() and torch.device(device).type == "cuda":
+            self.table_host = self.table_host.pin_memory()
+        self._dirty = True
+        self.pages_high_water = 0
 
     def admit(self, seq: int, n_tokens: int) -> None:
-        """Reserve pages for ``n_tokens`` tokens of sequence slot ``seq`` (host-side free list)."""
+        """Make sure sequence slot ``seq`` owns pages for ``n_tokens`` tokens (grows, never shrinks)."""
         need = (n_tokens + self.page_size - 1) // self.page_size
+        if need > self.max_pages:
+            raise RuntimeError(f"{n_tokens} tokens exceed the {self.max_pages * self.page_size} a page-table row can describe")
         have = self.owned.setdefault(seq, [])
         if need - len(have) > len(self.free_pages):
             raise RuntimeError("KV cache exhausted")
         while len(have) < need:
+            self.table_host[seq, len(have)] = self.free_pages[-1]
             have.append(self.free_pages.pop())
-        row = torch.zeros(self.max_pages, dtype=torch.int32)
-        row[: len(have)] = torch.tensor(have, dtype=torch.int32)
-        self.page_table[seq].copy_(row, non_blocking=True)
+            self._dirty = True
+        self.pages_high_water = max(self.pages_high_water, self.num_pages - 1 - len(self.free_pages))
 
     def release(self, seq: int) -> None:
-        self.free_pages.extend(reversed(self.owned.pop(seq, [])))
+        """Give the pages of slot ``seq`` back; its page-table row points at the scratch page again."""
+        pages = self.owned.pop(seq, [])
+        if pages:
+            self.free_pages.extend(reversed(pages))
+            self.table_host[seq].fill_(self.scratch_page)
+            self._dirty = True
+
+    def flush(self) -> None:
+        """Copy the page table to the device if a row changed since the last flush (asynchronous, stream-ordered)."""
+        if self._dirty:
+            self.page_table.copy_(self.table_host, non_blocking=True)
+            self._dirty = False
+
+    def pages_in_use(self) -> int:
+        return self.num_pages - 1 - len(self.free_pages)
 
 
 def own_last_rows(last_idx: torch.Tensor, a: int, b: int):

@@ -76,6 +76,8 @@ class _Sig:
     b200_ag_sync = (I, [P, I, I, c_size_t, c_size_t, I, I, I, P, I, I, P, I, P])
     b200_w8a8_gemm_decode_ar = (I, [P, P, P, P, P, P, I, I, I, I, P, I, P, P, P, I, I, c_size_t, c_size_t, P, I, I, c_size_t, c_size_t, c_size_t, I, c_size_t, c_size_t, c_size_t, P])
     b200_where_am_i = (I, [P, I, I, P])
+    b200_debug_compiled = (I, [])
+    b200_debug_set_heap_extent = (I, [c_size_t])
     b200_trace_compiled = (I, [])
     b200_trace_set = (I, [P, ctypes.c_uint])
     b200_fill_uniform_reduce = (I, [P, c_uint64, c_uint64, c_uint64, P, I, P, P, P])

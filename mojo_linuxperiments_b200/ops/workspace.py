@@ -46,7 +46,12 @@ class Workspace:
 
     def check_status(self) -> None:
         """Synchronising read of the status word; raises if any kernel recorded a bounded-wait timeout."""
-        code = int(self.status[0].item())
+        st = self.status.tolist()
+        code = st[0]
+        if st[1] != 0:
+            self.status.zero_()
+            raise RuntimeError(f"range-checked kernel refused heap offset {(st[3] & 0xffffffff) << 32 | (st[2] & 0xffffffff)}: "
+                               "the access was skipped")
         if code != 0:
             self.status.zero_()
             kernel = {0: "?", 1: "w8a8_gemm", 2: "w8a8_gemm_decode", 3: "attn_prefill", 4: "attn_decode_tma", 5: "attn_decode_tc",

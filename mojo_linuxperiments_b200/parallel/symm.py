@@ -17,6 +17,8 @@ import torch.distributed as dist
 from ..ops import _lib
 
 FLAG_BYTES = 4096
+CANARY_BYTES = 64                      # debug mode: guard words before and after every allocation
+CANARY_WORD = 0x5AFEC0DE
 AR_ONE_SHOT_P2P, AR_ONE_SHOT_NVLS, AR_TWO_SHOT_NVLS, AR_CHAIN, AR_BUTTERFLY, AR_LOW_LATENCY = 0, 1, 2, 3, 4, 5
 _DTYPES = {torch.bfloat16: 0, torch.float32: 1, torch.float64: 2}
 
@@ -41,6 +43,14 @@ class SymmetricHeap:
         self._c_data = (ctypes.c_void_p * self.world)(*self.data_ptrs)
         self._c_flags = (ctypes.c_void_p * self.world)(*self.flag_ptrs)
         self.offset = 0
+        # Debug mode (B200RT_DEBUG=1 / the range-checked kernel library): every allocation is fenced by canary words
+        # that check_status() verifies - the reference's guard pages (threading/linux_threading.mojo:148,419-420)
+        # for a heap that cannot have any - and the kernels are told the heap's extent so they can refuse offsets
+        # beyond it.
+        self.debug = bool(_lib.lib().b200_debug_compiled()) if torch.cuda.is_available() else False
+        self._canaries: list[int] = []
+        if self.debug:
+            _lib.lib().b200_debug_set_heap_extent(self.nbytes)
         # device-resident epoch words of this rank: [epoch, exit counter, stage counters...]
         self.epoch_words = torch.zeros(8, dtype=torch.int32, device=self.device)
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
@@ -53,16 +63,36 @@ class SymmetricHeap:
 
     # -- bump allocation: same offsets on every rank as long as every rank makes the same calls ----------------
     def alloc(self, nbytes: int, align: int = 256) -> int:
+        if self.debug:
+            # [canary][allocation][canary]; every rank makes the same calls, so the offsets still agree
+            lead = (self.offset + CANARY_BYTES + align - 1) // align * align
+            end = lead + nbytes + CANARY_BYTES
+            if end > self.nbytes:
+                raise MemoryError(f"symmetric heap exhausted ({end} > {self.nbytes})")
+            for off in (lead - CANARY_BYTES, lead + nbytes):
+                self.tensor(off, (CANARY_BYTES // 4,), torch.int32).fill_(CANARY_WORD)
+                self._canaries.append(off)
+            self.offset = end
+            return lead
         start = (self.offset + align - 1) // align * align
         if start + nbytes > self.nbytes:
             raise MemoryError(f"symmetric heap exhausted ({start + nbytes} > {self.nbytes})")
         self.offset = start + nbytes
         return start
 
+    def check_canaries(self) -> list[int]:
+        """Offsets of the guard blocks that no longer hold the canary pattern (debug mode; synchronises)."""
+        bad = []
+        for off in self._canaries:
+            if off + CANARY_BYTES <= self.offset and not bool((self.tensor(off, (CANARY_BYTES // 4,), torch.int32) == CANARY_WORD).all().item()):
+                bad.append(off)
+        return bad
+
     def mark(self) -> int: return self.offset
     def reset_to(self, w: int):
         if w <= self.offset:
             self.offset = w
+            self._canaries = [c for c in self._canaries if c + CANARY_BYTES <= w]
     def remaining(self) -> int: return self.nbytes - self.offset
     def used(self) -> int: return self.offset
 
@@ -82,10 +112,18 @@ class SymmetricHeap:
         return off, self.tensor(off, shape, dtype)
 
     def check_status(self):
-        code = int(self.status[0].item())
-        if code != 0:
+        st = self.status.tolist()
+        if st[1] != 0:
             self.status.zero_()
-            raise RuntimeError(f"peer kernel status {code} (5 = a flag from a peer never arrived)")
+            raise RuntimeError(f"range-checked kernel refused heap offset {(st[3] & 0xffffffff) << 32 | (st[2] & 0xffffffff)} "
+                               f"(heap of {self.nbytes} bytes): the access was skipped")
+        if st[0] != 0:
+            self.status.zero_()
+            raise RuntimeError(f"peer kernel status {st[0]} (5 = a flag from a peer never arrived)")
+        if self.debug:
+            bad = self.check_canaries()
+            if bad:
+                raise RuntimeError(f"symmetric heap canaries overwritten at offsets {bad[:8]}: a kernel wrote outside its allocation")
 
     # -- collectives --------------------------------------------------------------------------------------------
     def all_reduce(self, offset: int, n: int, dtype: torch.dtype, out: torch.Tensor | None, *, algo: int | None = None,

@@ -465,3 +465,24 @@ def test_fabric_protocols_are_race_free_under_the_thread_sanitizer():
     assert "ThreadSanitizer" not in p.stderr, p.stderr[-3000:]
     assert p.returncode == 0, p.stdout[-2000:] + p.stderr[-2000:]
     assert p.stdout.count("[PASS]") == 8
+
+
+def test_heap_range_check_reports_and_refuses_out_of_range_offsets():
+    """The check the range-checked ("debug") GPU kernels apply before touching a symmetric heap, exercised on the host
+    with bad offsets (on a GPU only valid cases ever run): in range passes, anything else is refused and the first
+    violation is what the report keeps."""
+    RC = 0x52430001
+    rep = (ctypes.c_int * 3)()
+    chk = H.lib().hostrt_range_check
+    ext = 1 << 20
+    assert chk(0, 16, ext, rep) == 1 and chk(ext - 16, 16, ext, rep) == 1 and chk(123, 0, ext, rep) == 1
+    assert list(rep) == [0, 0, 0]
+    assert chk(ext - 15, 16, ext, rep) == 0                       # one byte past the end
+    assert list(rep) == [RC, (ext - 15) & 0xffffffff, 0]
+    assert chk((5 << 32) + 8, 8, ext, rep) == 0                   # far outside: refused, first report kept
+    assert list(rep) == [RC, (ext - 15) & 0xffffffff, 0]
+    rep2 = (ctypes.c_int * 3)()
+    assert chk((5 << 32) + 8, 8, ext, rep2) == 0 and list(rep2) == [RC, 8, 5]
+    assert chk(2**64 - 8, 16, ext, rep2) == 0                     # offset + length would wrap around
+    assert chk(0, ext + 1, ext, rep2) == 0
+    assert chk(1 << 40, 1 << 40, 0, rep2) == 1                    # extent 0 = unknown: nothing is checked

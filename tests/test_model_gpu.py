@@ -79,3 +79,62 @@ def test_decode_past_the_admitted_length_is_refused_on_the_host():
         eng.decode_step()
     torch.cuda.synchronize()
     eng.check_status()               # and nothing on the device went out of range either
+
+
+def test_ragged_prefill_on_demand_pages_and_admission_between_steps():
+    """Prompts of different lengths in one prefill call, KV pages taken as the sequences grow, a finished sequence
+    released and a new one admitted into its slot between two replays of the same decode graph: every sequence must
+    produce the tokens it produces when it is run alone."""
+    from mojo_linuxperiments_b200.engine.engine import Engine
+    cfg = C.tiny_dense()
+    rt = C.RuntimeConfig(max_seq_len=256)
+    ck, ck_dev = _setup(cfg, 6)
+    eng = Engine(cfg, rt, weights=Wt.shard_from_checkpoint(cfg, ck, 1, 0, "cuda"))
+    g = torch.Generator().manual_seed(7)
+    lens = [5, 40, 17, 33]
+    prompts = [torch.randint(0, cfg.vocab, (n,), generator=g) for n in lens]
+    late = torch.randint(0, cfg.vocab, (23,), generator=g)
+    NEW = 20
+
+    def alone(p, n):
+        e = Engine(cfg, rt, weights=eng.model.w)
+        return e.generate(p.view(1, -1), n)[0].tolist()
+
+    want = [alone(p, NEW) for p in prompts]
+    want_late = alone(late, NEW - 7)       # its first token at step 8, then one per remaining step
+
+    eng.start_batch(4, 80)
+    assert eng.kv.pages_in_use() == 0
+    first = eng.prefill(prompts).tolist()
+    # pages for prompt + 1 tokens only, not for the 80 tokens the batch may grow to
+    assert eng.kv.pages_in_use() == sum((n + 1 + 15) // 16 for n in lens)
+    got = [[t] for t in first]
+    late_got = []
+    for step in range(1, NEW):
+        if step == 8:
+            # sequence 0 is declared finished; a new prompt takes its slot; the decode graph is not re-captured
+            graphs = dict(eng._graphs)
+            eng.release_sequence(0)
+            late_got.append(int(eng.admit_sequence(0, late)[0]))
+            assert eng._graphs == graphs
+        toks = eng.decode_step().tolist()
+        for b in range(4):
+            if b == 0 and step >= 8:
+                late_got.append(toks[0])
+            else:
+                got[b].append(toks[b])
+    torch.cuda.synchronize()
+    eng.check_status()
+    assert got[0] == want[0][:8]
+    for b in (1, 2, 3):
+        assert got[b] == want[b], (b, got[b], want[b])
+    assert late_got == want_late, (late_got, want_late)
+    rep = eng.memory_report()["kv_pages"]
+    assert rep["in_use"] == eng.kv.pages_in_use() and rep["high_water"] >= rep["in_use"]
+    # an empty slot stays empty while the others decode
+    eng.release_sequence(2)
+    before = eng.kv.pages_in_use()
+    eng.decode_step()
+    torch.cuda.synchronize()
+    assert int(eng.kv.seq_lens[2].item()) == 0 and int(eng.positions[2].item()) == 0
+    assert eng.kv.pages_in_use() <= before + 3
