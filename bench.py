@@ -415,6 +415,8 @@ def run(args):
                 gb = torch.Generator().manual_seed(1234)
                 torch.randint(0, cfg.vocab, (B, S), generator=gb)
                 base = measure(beng, cfg, args, world, local, rank, prompts, gb, ours=False, extras=not args.skip_extra)
+                beng._graphs.clear()             # graphs with NCCL work in them must not outlive the process group
+                del beng
             except Exception as e:  # the product's own line must survive a failing comparison arm
                 base = {"error": f"{type(e).__name__}: {e}"[:300]}
         if base and "value" in base:
@@ -446,12 +448,28 @@ def run(args):
     if rank == 0:
         print(json.dumps(result), flush=True)
     if world > 1:
-        # Leave without tearing down NCCL / symmetric-memory state: destroying a communicator whose collectives sit in
-        # live CUDA graphs has been seen to block for minutes.  Every rank has passed the last barrier and flushed.
+        # Orderly teardown: first everything that pins the communicator (captured graphs with NCCL / symmetric-memory
+        # work in them, the symmetric heaps), then the process group.  Destroying the group while such graphs were alive
+        # has blocked for minutes; should the orderly path ever block too, a watchdog ends the process (the result
+        # line is already out and every rank is past the last barrier).
+        import threading
         barrier(world)
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        threading.Timer(30.0, lambda: os._exit(0)).start()
+        try:
+            if hasattr(eng, "close"):
+                eng.close()
+            del eng
+            import gc
+            gc.collect()
+            torch.cuda.synchronize()
+            import torch.distributed as dist
+            dist.destroy_process_group()
+            if rank == 0:
+                print("teardown: process group destroyed after the graphs and heaps were released", file=sys.stderr, flush=True)
+        finally:
+            os._exit(0)
 
 
 def main():

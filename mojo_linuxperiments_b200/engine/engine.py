@@ -318,6 +318,29 @@ class Engine:
         g.replay()
         return self.tokens
 
+    def close(self) -> None:
+        """Release what has to go before the process group does: the captured graphs (they hold symmetric-memory
+        tensors and NCCL work of the communicator), the heartbeat thread, the symmetric heap, the KV cache.  After
+        ``close()`` the rank can call ``torch.distributed.destroy_process_group()`` without a graph still pinning
+        the communicator's resources."""
+        if self.heartbeat is not None:
+            self.heartbeat.stop()
+            self.heartbeat = None
+        torch.cuda.synchronize(self.device)
+        self._graphs.clear()
+        self._prefill_graphs.clear()
+        self._prefill_pool = None
+        self.model._decode_scratch.clear()
+        if self.tp_ctx is not None:
+            self.tp_ctx.sp = None
+            self.tp_ctx.heap = None
+            self.tp_ctx = None
+            self.model.tp_ctx = None
+            if self.model.moe is not None:
+                self.model.moe.tp_ctx = None
+        self.kv = None
+        torch.cuda.synchronize(self.device)
+
     def check_status(self) -> None:
         """Synchronising read of the kernels' status words; raises if a device-side wait timed out."""
         default_workspace(self.device).check_status()

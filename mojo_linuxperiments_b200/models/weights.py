@@ -117,6 +117,72 @@ def load_checkpoint(path: str):
     return ModelConfig.from_json(meta["config"]), tensors
 
 
+class _LazyTensor:
+    """A tensor of an open safetensors file that is only read where it is sliced: ``t[a:b]`` / ``t[:, a:b]`` read
+    those rows / columns, ``t.to(device)`` reads all of it."""
+
+    def __init__(self, reader: "ShardReader", name: str):
+        self.reader, self.name = reader, name
+
+    def _count(self, t: torch.Tensor) -> torch.Tensor:
+        self.reader.bytes_read += t.numel() * t.element_size()
+        return t
+
+    def __getitem__(self, idx) -> torch.Tensor:
+        return self._count(self.reader.file.get_slice(self.name)[idx])
+
+    def full(self) -> torch.Tensor:
+        return self._count(self.reader.file.get_tensor(self.name))
+
+    def to(self, *args, **kw) -> torch.Tensor:
+        return self.full().to(*args, **kw)
+
+
+class ShardReader:
+    """Dict-like view of a checkpoint file whose tensors are read slice by slice (``shard_from_checkpoint`` then pulls
+    only this rank's rows / columns of every linear from the file instead of materialising the whole model per rank)."""
+
+    def __init__(self, path: str):
+        from safetensors import safe_open
+        self._ctx = safe_open(path, framework="pt")
+        self.file = self._ctx.__enter__()
+        self.meta = self.file.metadata()
+        self.names = set(self.file.keys())
+        self.bytes_read = 0
+        if self.meta.get("rotated") != "true" or int(self.meta.get("hadamard_block", "0")) != 128:
+            self.close()
+            raise ValueError("checkpoint is not in the rotated block-128 W8A8 layout")
+
+    def __getitem__(self, name: str) -> _LazyTensor:
+        if name not in self.names:
+            raise KeyError(name)
+        return _LazyTensor(self, name)
+
+    def config(self) -> ModelConfig:
+        return ModelConfig.from_json(self.meta["config"])
+
+    def close(self) -> None:
+        if self._ctx is not None:
+            self._ctx.__exit__(None, None, None)
+            self._ctx = None
+
+
+def load_shard(path: str, tp: int, rank: int, device):
+    """(config, this rank's weights) read from a checkpoint file without loading the other ranks' shards."""
+    rd = ShardReader(path)
+    try:
+        cfg = rd.config()
+        w = shard_from_checkpoint(cfg, rd, tp, rank, device)
+        w["checkpoint_bytes_read"] = rd.bytes_read
+        return cfg, w
+    finally:
+        rd.close()
+
+
+def _full(t):
+    return t.full() if isinstance(t, _LazyTensor) else t
+
+
 # ---------------------------------------------------------------------------------------------------------
 # per-rank model weights
 # ---------------------------------------------------------------------------------------------------------
@@ -129,11 +195,11 @@ def _rows(lw: LinearW, a: int, b: int) -> LinearW:
 
 
 def _cols(lw: LinearW, a: int, b: int) -> LinearW:
-    return LinearW(lw.qweight[:, a:b], lw.scale)
+    return LinearW(lw.qweight[:, a:b], _full(lw.scale))
 
 
 def _cat_rows(*ls: LinearW) -> LinearW:
-    return LinearW(torch.cat([l.qweight for l in ls], 0), torch.cat([l.scale for l in ls], 0))
+    return LinearW(torch.cat([_full(l.qweight) for l in ls], 0), torch.cat([_full(l.scale) for l in ls], 0))
 
 
 def shard_from_checkpoint(cfg: ModelConfig, ck: dict, tp: int, rank: int, device) -> dict:
@@ -166,8 +232,8 @@ def shard_from_checkpoint(cfg: ModelConfig, ck: dict, tp: int, rank: int, device
                 dn.append(_lin(ck, p + f"experts.{e}.down"))
             L["experts_gate_up"] = LinearW(torch.stack([x.qweight for x in gu]).to(device).contiguous(),
                                            torch.stack([x.scale for x in gu]).to(device).contiguous())
-            L["experts_down"] = LinearW(torch.stack([x.qweight for x in dn]).to(device).contiguous(),
-                                        torch.stack([x.scale for x in dn]).to(device).contiguous())
+            L["experts_down"] = LinearW(torch.stack([_full(x.qweight) for x in dn]).to(device).contiguous(),
+                                        torch.stack([_full(x.scale) for x in dn]).to(device).contiguous())
         else:
             fs = cfg.ffn // tp
             L["gate_up"] = _cat_rows(_rows(_lin(ck, p + "gate"), rank * fs, (rank + 1) * fs),

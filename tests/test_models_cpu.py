@@ -142,3 +142,45 @@ def test_last_token_rows_of_a_token_sharded_prefill_sum_to_the_replicated_rows()
             if b > a:
                 total += torch.where(mine, h[a:b].index_select(0, loc), torch.zeros(()))
         assert torch.equal(owners, torch.ones(len(lens))) and torch.equal(total, h[last])
+
+
+@pytest.mark.parametrize("kind", ["dense", "moe"])
+def test_load_shard_reads_only_this_ranks_part_of_the_file(tmp_path, kind):
+    """``load_shard`` cuts a rank's rows / columns out of the checkpoint file slice by slice: the result equals sharding
+    a fully loaded checkpoint, and what was read from the file is well below the whole model."""
+    import os
+
+    def same(a, b):
+        if isinstance(a, Wt.LinearW):
+            return torch.equal(a.qweight, b.qweight) and torch.equal(a.scale, b.scale)
+        return torch.equal(a, b) if isinstance(a, torch.Tensor) else a == b
+
+    if kind == "dense":
+        cfg = C.tiny_dense(n_layers=2, d_model=256, n_heads=4, n_kv_heads=2, ffn=512, vocab=512)
+    else:
+        cfg = C.tiny_moe(n_layers=1, d_model=256, n_heads=4, n_kv_heads=2, n_experts=8, top_k=2, moe_ffn=128, vocab=512)
+    ck = Wt.quantize_master(Wt.init_master(cfg, 1))
+    path = str(tmp_path / "m.safetensors")
+    Wt.save_checkpoint(path, cfg, ck)
+    size = os.path.getsize(path)
+    tp = 4 if kind == "moe" else 2
+    total_read = 0
+    for rank in range(tp):
+        cfg2, w = Wt.load_shard(path, tp, rank, "cpu")
+        ref = Wt.shard_from_checkpoint(cfg, ck, tp, rank, "cpu")
+        assert cfg2 == cfg
+        read = w.pop("checkpoint_bytes_read")
+        total_read += read
+        for k in ("embed", "final_norm", "lm_head", "vocab_offset"):
+            assert same(w[k], ref[k]), k
+        for La, Lb in zip(w["layers"], ref["layers"]):
+            assert set(La) == set(Lb)
+            for k in La:
+                assert same(La[k], Lb[k]), k
+        # the linears are sharded; only the replicated tensors (embedding, norms, router) are read by every rank
+        assert read < 0.8 * size
+    with pytest.raises(ValueError):
+        from safetensors.torch import save_file
+        bad = str(tmp_path / "bad.safetensors")
+        save_file({"x": torch.zeros(1)}, bad, metadata={"config": cfg.to_json(), "rotated": "false", "hadamard_block": "128"})
+        Wt.load_shard(bad, 2, 0, "cpu")
