@@ -38,6 +38,9 @@ struct Driver {
   CUresult (*MemUnmap)(CUdeviceptr, size_t) = nullptr;
   CUresult (*MemSetAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
   CUresult (*PointerGetAttribute)(void*, CUpointer_attribute, CUdeviceptr) = nullptr;
+  // optional (symmetric segments): sharing an allocation with other processes through a POSIX file descriptor
+  CUresult (*MemExportToShareableHandle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType, unsigned long long) = nullptr;
+  CUresult (*MemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType) = nullptr;
 };
 
 template <class F>
@@ -83,6 +86,8 @@ Driver& driver() {
   ok &= load(d.lib, d.MemUnmap, "cuMemUnmap");
   ok &= load(d.lib, d.MemSetAccess, "cuMemSetAccess");
   ok &= load(d.lib, d.PointerGetAttribute, "cuPointerGetAttribute");
+  load(d.lib, d.MemExportToShareableHandle, "cuMemExportToShareableHandle");
+  load(d.lib, d.MemImportFromShareableHandle, "cuMemImportFromShareableHandle");
   if (ok && d.Init(0) == CUDA_SUCCESS) d.ok = true;
   return d;
 }
@@ -232,6 +237,73 @@ uint64_t HbmArena::alloc_bytes(size_t bytes) {
   return base_ + start;
 }
 
+// ---- SymmSegment -------------------------------------------------------------------------------------------------
+SymmSegment::SymmSegment(int device, size_t bytes, int world, int rank) : device_(device), world_(world), rank_(rank) {
+  Driver& d = driver();
+  if (!d.ok) { status_ = DEVRT_NO_DRIVER; return; }
+  if (bytes == 0 || device < 0 || world < 1 || world > 64 || rank < 0 || rank >= world) { status_ = DEVRT_BAD_ARG; return; }
+  if (!d.MemExportToShareableHandle || !d.MemImportFromShareableHandle) { status_ = DEVRT_NO_DRIVER; return; }
+  CtxScope cs(d, device);
+  if (!cs.pushed) { status_ = DEVRT_BAD_ARG; return; }
+  CUmemAllocationProp prop{};
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = device;
+  prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  size_t gran = 0;
+  if (d.MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS || gran == 0) { status_ = DEVRT_NO_MEM; return; }
+  stride_ = (bytes + gran - 1) / gran * gran;
+  CUdeviceptr va = 0;
+  if (d.MemAddressReserve(&va, stride_ * world, gran, 0, 0) != CUDA_SUCCESS) { status_ = DEVRT_NO_MEM; return; }
+  CUmemGenericAllocationHandle h = 0;
+  if (d.MemCreate(&h, stride_, &prop, 0) != CUDA_SUCCESS) { d.MemAddressFree(va, stride_ * world); status_ = DEVRT_NO_MEM; return; }
+  base_ = va;
+  handles_.assign(world, 0);
+  mapped_.assign(world, false);
+  handles_[rank] = h;
+  if (!map_at(rank, h)) { d.MemRelease(h); d.MemAddressFree(va, stride_ * world); base_ = 0; status_ = DEVRT_NO_MEM; return; }
+  int fd = -1;
+  if (d.MemExportToShareableHandle(&fd, h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0) != CUDA_SUCCESS) { status_ = DEVRT_NO_MEM; fd = -1; }
+  fd_ = fd;
+}
+
+bool SymmSegment::map_at(int r, uint64_t handle) {
+  Driver& d = driver();
+  const CUdeviceptr at = base_ + stride_ * static_cast<size_t>(r);
+  if (d.MemMap(at, stride_, 0, handle, 0) != CUDA_SUCCESS) return false;
+  CUmemAccessDesc acc{};
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = device_;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  if (d.MemSetAccess(at, stride_, &acc, 1) != CUDA_SUCCESS) { d.MemUnmap(at, stride_); return false; }
+  mapped_[r] = true;
+  return true;
+}
+
+int SymmSegment::map_peer(int peer, int fd) {
+  Driver& d = driver();
+  if (!base_ || peer < 0 || peer >= world_ || peer == rank_ || mapped_[peer] || fd < 0) return DEVRT_BAD_ARG;
+  CtxScope cs(d, device_);
+  if (!cs.pushed) return DEVRT_BAD_ARG;
+  CUmemGenericAllocationHandle h = 0;
+  if (d.MemImportFromShareableHandle(&h, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)), CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) != CUDA_SUCCESS)
+    return DEVRT_NO_MEM;
+  if (!map_at(peer, h)) { d.MemRelease(h); return DEVRT_NO_MEM; }
+  handles_[peer] = h;
+  return 0;
+}
+
+SymmSegment::~SymmSegment() {
+  if (!base_) return;
+  Driver& d = driver();
+  CtxScope cs(d, device_);
+  for (int r = 0; r < world_; ++r) {
+    if (mapped_[r]) d.MemUnmap(base_ + stride_ * static_cast<size_t>(r), stride_);
+    if (handles_[r]) d.MemRelease(handles_[r]);
+  }
+  d.MemAddressFree(base_, stride_ * world_);
+}
+
 bool HbmArena::verify_placement() const {
   if (!base_) return false;
   Driver& d = driver();
@@ -286,4 +358,18 @@ unsigned long long devrt_arena_size(void* a) { return static_cast<HbmArena*>(a)-
 unsigned long long devrt_arena_high_water(void* a) { return static_cast<HbmArena*>(a)->high_water(); }
 unsigned long long devrt_arena_base(void* a) { return static_cast<HbmArena*>(a)->base(); }
 int devrt_arena_verify_placement(void* a) { return static_cast<HbmArena*>(a)->verify_placement() ? 1 : 0; }
+
+// symmetric segment: create -> export_fd -> (descriptors cross processes) -> map_peer for every other rank
+void* devrt_symm_create(int device, unsigned long long bytes, int world, int rank) {
+  auto* s = new (std::nothrow) SymmSegment(device, static_cast<size_t>(bytes), world, rank);
+  if (s && !*s) { delete s; return nullptr; }
+  return s;
+}
+void devrt_symm_destroy(void* s) { delete static_cast<SymmSegment*>(s); }
+int devrt_symm_export_fd(void* s) { return static_cast<SymmSegment*>(s)->export_fd(); }
+int devrt_symm_map_peer(void* s, int peer, int fd) { return static_cast<SymmSegment*>(s)->map_peer(peer, fd); }
+unsigned long long devrt_symm_base(void* s) { return static_cast<SymmSegment*>(s)->base(); }
+unsigned long long devrt_symm_stride(void* s) { return static_cast<SymmSegment*>(s)->stride(); }
+unsigned long long devrt_symm_peer_ptr(void* s, int r) { return static_cast<SymmSegment*>(s)->peer_ptr(r); }
+int devrt_symm_mapped(void* s, int r) { return static_cast<SymmSegment*>(s)->mapped(r) ? 1 : 0; }
 }

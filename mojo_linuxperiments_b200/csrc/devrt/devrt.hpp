@@ -93,4 +93,34 @@ class HbmArena {
   int device_ = -1, status_ = 0;
 };
 
+// One rank's share of a symmetric heap, built on the virtual-memory API alone: an HBM block that can be handed to other
+// processes as a POSIX file descriptor, and one address range of world x stride bytes in which this rank's block and,
+// once their descriptors arrived, every peer's block are mapped at rank * stride.  peer_ptr(r) + off then addresses
+// byte `off` of rank r's block from this GPU (NVLink peer access), with the same `off` on every rank - the GPU form
+// of the reference's one shared arena that every worker addresses (test_linux_threading.mojo:426-435), bound to its
+// owner like mbind binds an arena to a node (threading/numa_arena.mojo:93-137).  The descriptors travel between the
+// rank processes over a unix socket (parallel/symm_native.py); nothing here talks to another process.
+class SymmSegment {
+ public:
+  SymmSegment(int device, size_t bytes, int world, int rank);
+  SymmSegment(const SymmSegment&) = delete;
+  SymmSegment& operator=(const SymmSegment&) = delete;
+  ~SymmSegment();
+  explicit operator bool() const { return base_ != 0 && fd_ >= 0; }
+  int status() const { return status_; }
+  int export_fd() const { return fd_; }               // descriptor of this rank's block (owned by the caller's process)
+  int map_peer(int peer, int fd);                     // 0, or a negative status
+  uint64_t base() const { return base_; }
+  size_t stride() const { return stride_; }
+  uint64_t peer_ptr(int r) const { return base_ + stride_ * static_cast<size_t>(r); }
+  bool mapped(int r) const { return r >= 0 && r < world_ && mapped_[r]; }
+ private:
+  bool map_at(int r, uint64_t handle);
+  uint64_t base_ = 0;
+  size_t stride_ = 0;
+  std::vector<uint64_t> handles_;
+  std::vector<bool> mapped_;
+  int device_ = -1, world_ = 0, rank_ = 0, fd_ = -1, status_ = 0;
+};
+
 }  // namespace devrt

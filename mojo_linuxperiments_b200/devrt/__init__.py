@@ -39,6 +39,10 @@ def lib() -> ctypes.CDLL:
         "devrt_arena_remaining": (U, [c_void_p]), "devrt_arena_used": (U, [c_void_p]),
         "devrt_arena_size": (U, [c_void_p]), "devrt_arena_high_water": (U, [c_void_p]),
         "devrt_arena_base": (U, [c_void_p]), "devrt_arena_verify_placement": (c_int, [c_void_p]),
+        "devrt_symm_create": (c_void_p, [c_int, U, c_int, c_int]), "devrt_symm_destroy": (None, [c_void_p]),
+        "devrt_symm_export_fd": (c_int, [c_void_p]), "devrt_symm_map_peer": (c_int, [c_void_p, c_int, c_int]),
+        "devrt_symm_base": (U, [c_void_p]), "devrt_symm_stride": (U, [c_void_p]),
+        "devrt_symm_peer_ptr": (U, [c_void_p, c_int]), "devrt_symm_mapped": (c_int, [c_void_p, c_int]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -149,3 +153,98 @@ class HbmArena:
             return None
         raw = torch.as_tensor(_ArenaView(p, n, self), device=torch.device("cuda", self.device))
         return raw.view(dtype).view(*shape)
+
+
+class SymmSegment:
+    """This rank's block of a symmetric heap and the mappings of its peers' blocks (``csrc/devrt`` ``SymmSegment``).
+
+    ``export_fd()`` is a POSIX descriptor of the local block; once a peer's descriptor has reached this process
+    (``exchange_fds``), ``map_peer`` maps that peer's block at ``peer_ptr(peer)``.  The reference's workers share one
+    mmap'd arena by address (test_linux_threading.mojo:426-435); processes that own one GPU each share HBM this way.
+    """
+
+    def __init__(self, device: int, nbytes: int, world: int, rank: int):
+        self.device, self.world, self.rank = device, world, rank
+        self._h = lib().devrt_symm_create(device, nbytes, world, rank)
+        if not self._h:
+            raise RuntimeError(f"symmetric segment of {nbytes} bytes on device {device}: the driver refused it "
+                               "(no driver, no virtual-memory support, or no shareable handles)")
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().devrt_symm_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def export_fd(self) -> int: return lib().devrt_symm_export_fd(self._h)
+    def map_peer(self, peer: int, fd: int) -> int: return lib().devrt_symm_map_peer(self._h, peer, fd)
+    def mapped(self, r: int) -> bool: return bool(lib().devrt_symm_mapped(self._h, r))
+    @property
+    def base(self) -> int: return lib().devrt_symm_base(self._h)
+    @property
+    def stride(self) -> int: return lib().devrt_symm_stride(self._h)
+    def peer_ptr(self, r: int) -> int: return lib().devrt_symm_peer_ptr(self._h, r)
+
+    def local_tensor(self):
+        """The local block as a uint8 torch tensor (no copy; the segment must outlive it)."""
+        import torch
+        view = _ArenaView(self.peer_ptr(self.rank), self.stride, self)
+        return torch.as_tensor(view, device=torch.device("cuda", self.device))
+
+
+def exchange_fds(fd: int, rank: int, world: int, all_gather_names, timeout_s: float = 60.0) -> dict[int, int]:
+    """Hand ``fd`` to every other rank process of this host and collect theirs: {peer rank: descriptor}.
+
+    Descriptors cross processes as SCM_RIGHTS ancillary data on unix sockets in the abstract namespace (nothing is
+    left in the file system).  ``all_gather_names(name) -> list[str]`` publishes this rank's socket name and returns
+    everybody's (``torch.distributed.all_gather_object`` in practice; any out-of-band channel works).  The caller
+    owns the returned descriptors and closes them after mapping.
+    """
+    import os
+    import socket
+    import threading
+    name = f"\0b200rt-symm-{os.getpid()}-{rank}-{os.urandom(6).hex()}"
+    srv = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+    srv.bind(name)
+    srv.listen(world)
+    srv.settimeout(timeout_s)
+    errors: list[BaseException] = []
+
+    def serve():
+        try:
+            for _ in range(world - 1):
+                c, _addr = srv.accept()
+                with c:
+                    c.settimeout(timeout_s)
+                    c.recv(8)                                    # the requester's rank (kept for the log of a failure)
+                    socket.send_fds(c, [rank.to_bytes(4, "little")], [fd])
+        except BaseException as e:                               # noqa: BLE001 - reported to the caller's thread
+            errors.append(e)
+
+    th = threading.Thread(target=serve, daemon=True)
+    th.start()
+    names = all_gather_names(name)
+    got: dict[int, int] = {}
+    try:
+        for r in range(world):
+            if r == rank:
+                continue
+            with socket.socket(socket.AF_UNIX, socket.SOCK_STREAM) as c:
+                c.settimeout(timeout_s)
+                c.connect(names[r])
+                c.sendall(rank.to_bytes(8, "little"))
+                msg, fds, _flags, _addr = socket.recv_fds(c, 4, 1)
+                if len(fds) != 1 or int.from_bytes(msg, "little") != r:
+                    raise RuntimeError(f"rank {r} answered the descriptor request with {len(fds)} descriptors")
+                got[r] = fds[0]
+        th.join(timeout_s)
+        if th.is_alive() or errors:
+            raise RuntimeError(f"descriptor exchange: serving side failed ({errors[:1] or 'timed out'})")
+    except BaseException:
+        for f in got.values():
+            os.close(f)
+        raise
+    finally:
+        srv.close()
+    return got

@@ -17,6 +17,7 @@ from ..models.decoder import Decoder, KVState
 from ..models import weights as Wt
 from ..ops.workspace import Workspace, default_workspace, has_default_workspace, install_default_workspace
 from ..parallel.comm import Comm
+from ..utils.trace import op_range
 from .runtime import RankRuntime
 
 
@@ -315,7 +316,8 @@ class Engine:
             self.kernels_per_step = _lib.LAUNCHES[0] - n0      # this library's kernels inside one replay
             self.tokens.copy_(saved[0]); self.positions.copy_(saved[1]); self.kv.seq_lens.copy_(saved[2])
             self._graphs[self.batch] = g
-        g.replay()
+        with op_range(f"decode_step.bs{self.batch}"):
+            g.replay()
         return self.tokens
 
     def close(self) -> None:

@@ -14,6 +14,7 @@ import torch
 from ..ops import attention as A
 from ..ops import linear as L
 from ..parallel.comm import Comm
+from ..utils.trace import op_range
 from .config import ModelConfig, RuntimeConfig, kv_heads_per_rank
 
 
@@ -217,15 +218,18 @@ class Decoder:
             else:
                 xq, sx = self._norm_quant(h, delta, W["attn_norm"])
                 qkv = L.w8a8_gemm(xq, sx, W["qkv"].qweight, W["qkv"].scale)
-            attn = self._attention(l, qkv, positions, kv, mode, cu_seqlens, max_len, seq_ids)
+            with op_range(f"layer{l}.attention.{mode}"):
+                attn = self._attention(l, qkv, positions, kv, mode, cu_seqlens, max_len, seq_ids)
             aq, sa = attn if isinstance(attn, tuple) else L.act_quant(attn.view(attn.shape[0], -1))
-            delta = self._row_parallel(aq, sa, W["o"])
+            with op_range(f"layer{l}.o_proj+allreduce"):
+                delta = self._row_parallel(aq, sa, W["o"])
             if fq and self.moe is None:
                 gu = self._fused_norm_linear(h, delta, W["mlp_norm"], W["gate_up"])
                 delta = self._fused_swiglu_down(gu, W["down"])
                 continue
             xq, sx = self._norm_quant(h, delta, W["mlp_norm"])      # the router, too, consumes the quantised rows
-            delta = self._mlp(l, xq, sx, None)
+            with op_range(f"layer{l}.mlp"):
+                delta = self._mlp(l, xq, sx, None)
         if last_idx is not None:
             h = h.index_select(0, last_idx)
             delta = delta.index_select(0, last_idx)
@@ -268,6 +272,10 @@ class Decoder:
         return self._sample(both[:, :d].contiguous(), both[:, d:].contiguous())
 
     def _sample(self, h, delta):
+        with op_range("lm_head+argmax"):
+            return self._sample_body(h, delta)
+
+    def _sample_body(self, h, delta):
         xq, sx = self._norm_quant(h, delta, self.w["final_norm"])
         lm = self.w["lm_head"]
         logits = L.w8a8_gemm(xq, sx, lm.qweight, lm.scale)

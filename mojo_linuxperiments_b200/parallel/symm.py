@@ -4,12 +4,20 @@ can address (test_linux_threading.mojo:426-435) and of its futex gates (threadin
 Every rank allocates the same number of bytes; after the rendezvous each rank holds a pointer to every other rank's
 block (NVLink / NVSwitch peer mapping) and, where the fabric supports it, one NVLS multicast pointer that addresses all
 copies at once.  The first ``FLAG_BYTES`` of the block are the rank's flag words (epochs written by peers); the rest is
-a bump-allocated data heap whose offsets are identical on every rank.  Allocation and mapping come from
-``torch.distributed._symmetric_memory``; the kernels that read and write peers are this package's own.
+a bump-allocated data heap whose offsets are identical on every rank.  The kernels that read and write peers are this
+package's own.  Allocation and mapping have two backends, chosen by ``B200RT_SYMM``:
+
+* ``torch`` (default): ``torch.distributed._symmetric_memory`` - peer pointers and, where the fabric has it, the NVLS
+  multicast pointer the ``multimem`` kernels use.
+* ``native``: this package's device runtime (``devrt.SymmSegment``: a virtual-memory block per rank, exported as a
+  POSIX descriptor, handed to the peers over unix sockets and mapped by each of them).  Peer pointers only - no
+  multicast object is bound, so the kernels take their peer-store paths; a rank that dies therefore leaves no
+  multicast binding behind.
 """
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.distributed as dist
@@ -32,13 +40,18 @@ class SymmetricHeap:
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.nbytes = (nbytes + 4095) // 4096 * 4096
         total = FLAG_BYTES + self.nbytes
-        self.block = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
-        self.block.zero_()
-        self.handle = symm_mem.rendezvous(self.block, group=self.group.group_name)
-        ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.backend = os.environ.get("B200RT_SYMM", "torch").lower()
+        self.segment = None
+        if self.backend == "native":
+            ptrs, mc = self._native_rendezvous(total)
+        else:
+            self.block = symm_mem.empty(total, dtype=torch.uint8, device=self.device)
+            self.block.zero_()
+            self.handle = symm_mem.rendezvous(self.block, group=self.group.group_name)
+            ptrs = [int(p) for p in self.handle.buffer_ptrs]
+            mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.flag_ptrs = ptrs
         self.data_ptrs = [p + FLAG_BYTES for p in ptrs]
-        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
         self.mc_data_ptr = mc + FLAG_BYTES if mc else 0
         self._c_data = (ctypes.c_void_p * self.world)(*self.data_ptrs)
         self._c_flags = (ctypes.c_void_p * self.world)(*self.flag_ptrs)
@@ -56,6 +69,34 @@ class SymmetricHeap:
         self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)
+
+    def _native_rendezvous(self, total: int):
+        """Own block through the device runtime, peers' blocks mapped from the descriptors they hand over."""
+        from .. import devrt
+        dev = self.device.index if self.device.index is not None else torch.cuda.current_device()
+        torch.cuda.init()
+        torch.zeros(1, device=self.device)                       # the primary context exists before the driver calls
+        self.segment = devrt.SymmSegment(dev, total, self.world, self.rank)
+
+        def gather(name):
+            names = [None] * self.world
+            dist.all_gather_object(names, name, group=self.group)
+            return names
+
+        fds = devrt.exchange_fds(self.segment.export_fd(), self.rank, self.world, gather)
+        try:
+            for r, fd in fds.items():
+                rc = self.segment.map_peer(r, fd)
+                if rc != 0:
+                    raise RuntimeError(f"mapping rank {r}'s block failed with status {rc}")
+        finally:
+            for fd in fds.values():
+                os.close(fd)
+            os.close(self.segment.export_fd())
+        self.block = self.segment.local_tensor()[:total]
+        self.block.zero_()
+        self.handle = None
+        return [self.segment.peer_ptr(r) for r in range(self.world)], 0
 
     @property
     def has_multicast(self) -> bool:

@@ -44,6 +44,15 @@ def nvtx_range(name: str):
             torch.cuda.nvtx.range_pop()
 
 
+_NVTX_ON = os.environ.get("B200RT_NVTX", "0") not in ("0", "", "false")
+
+
+def op_range(name: str):
+    """NVTX range around a fused op / layer when B200RT_NVTX=1, else a no-op context: the engine and the decoder wrap
+    their steps in these, so a timeline capture shows which launches belong to which layer and phase."""
+    return nvtx_range(name) if _NVTX_ON else contextlib.nullcontext()
+
+
 class MetricsLog:
     """Append-only JSON-lines file; one dict per record plus a wall-clock stamp."""
 

@@ -1,9 +1,12 @@
 /* Host-memory stand-in for the handful of CUDA driver entry points the device runtime uses, so that topology and
  * arena logic can be tested on a machine without a GPU.  FAKE_CUDA_DEVICES (default 2) sets the device count,
  * FAKE_CUDA_NO_PEER=1 removes peer access, FAKE_CUDA_FAIL_CREATE=1 makes physical allocation fail. */
+#define _GNU_SOURCE
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
+#include <sys/mman.h>
+#include <unistd.h>
 
 typedef int CUresult;
 typedef int CUdevice;
@@ -61,6 +64,22 @@ CUresult cuMemCreate(CUmemGenericAllocationHandle* h, size_t size, const void* p
   return 0;
 }
 CUresult cuMemRelease(CUmemGenericAllocationHandle h) { (void)h; return 0; }
+/* A shareable handle is a memfd that holds the handle's value: it survives SCM_RIGHTS to another process. */
+CUresult cuMemExportToShareableHandle(void* out, CUmemGenericAllocationHandle h, int type, unsigned long long fl) {
+  (void)fl;
+  if (type != 1 || flag("FAKE_CUDA_FAIL_EXPORT")) return 801;
+  int fd = memfd_create("fake_cuda_handle", 0);
+  if (fd < 0) return 2;
+  if (write(fd, &h, sizeof h) != (ssize_t)sizeof h) { close(fd); return 2; }
+  *(int*)out = fd;
+  return 0;
+}
+CUresult cuMemImportFromShareableHandle(CUmemGenericAllocationHandle* h, void* os_handle, int type) {
+  if (type != 1) return 801;
+  int fd = (int)(long)os_handle;
+  if (pread(fd, h, sizeof *h, 0) != (ssize_t)sizeof *h) return 1;
+  return 0;
+}
 CUresult cuMemMap(CUdeviceptr p, size_t size, size_t off, CUmemGenericAllocationHandle h, unsigned long long fl) {
   (void)off; (void)fl;
   if (nmaps >= 64) return 2;

@@ -81,6 +81,7 @@ def main():
     if rank == 0:
         for k, v in timing.items():
             print("TIMING two_hop_min=%d M=%d K_shard=%d: %.2f us per fused GEMM+all-reduce" % (*k, v))
+        print("symm backend", tp.heap.backend, "multicast", tp.heap.has_multicast)
         print("FAILURES", int(bad.item()), failures)
     else:
         if failures:

@@ -91,6 +91,7 @@ def main():
     dist.all_reduce(bad)
     if rank == 0:
         print("MULTICAST", heap.has_multicast)
+        print("symm backend", heap.backend, "multicast", heap.has_multicast)
         print("FAILURES", int(bad.item()), failures)
     dist.barrier()
     sys.stdout.flush()

@@ -101,3 +101,48 @@ def test_real_topology_and_arena_tensor():
     del x, y
     if t.num_devices > 1:
         assert t.fully_connected() and t.distance(0, 1) == 1
+
+
+def test_symmetric_segments_on_fake_driver(fake_driver):
+    """Two ranks' segments: each exports a descriptor, maps the other's block at rank * stride, refuses repeats."""
+    import threading
+    fake_driver.setenv("FAKE_CUDA_DEVICES", "2")
+    world = 2
+    segs = [D.SymmSegment(r, (3 << 20) + 5, world, r) for r in range(world)]
+    assert all(s.stride == 4 << 20 for s in segs)                       # rounded up to the 2 MiB granularity
+    for r, s in enumerate(segs):
+        assert s.mapped(r) and not s.mapped(1 - r) and s.peer_ptr(1) - s.peer_ptr(0) == s.stride and s.export_fd() >= 0
+    names, got, bar = [None] * world, [None] * world, threading.Barrier(world)
+
+    def gather_for(r):
+        def gather(name):
+            names[r] = name
+            bar.wait(10)
+            return list(names)
+        return gather
+
+    def run(r):
+        got[r] = D.exchange_fds(segs[r].export_fd(), r, world, gather_for(r), timeout_s=10)
+
+    ths = [threading.Thread(target=run, args=(r,)) for r in range(world)]
+    [t.start() for t in ths]
+    [t.join(20) for t in ths]
+    assert got[0] is not None and set(got[0]) == {1} and set(got[1]) == {0}
+    for r, s in enumerate(segs):
+        fd = got[r][1 - r]
+        assert fd != segs[1 - r].export_fd()                              # a descriptor of its own, not the sender's
+        assert s.map_peer(1 - r, fd) == 0 and s.mapped(1 - r)
+        assert s.map_peer(1 - r, fd) != 0                                 # already mapped
+        assert s.map_peer(r, fd) != 0 and s.map_peer(7, fd) != 0          # own slot, out of range
+        os.close(fd)
+    [s.close() for s in segs]
+
+
+def test_symmetric_segment_refusals(fake_driver):
+    fake_driver.setenv("FAKE_CUDA_FAIL_EXPORT", "1")
+    with pytest.raises(RuntimeError):
+        D.SymmSegment(0, 1 << 20, 2, 0)
+    fake_driver.delenv("FAKE_CUDA_FAIL_EXPORT")
+    for args in [(0, 0, 2, 0), (0, 1 << 20, 2, 2), (0, 1 << 20, 0, 0), (0, 1 << 20, 65, 0)]:
+        with pytest.raises(RuntimeError):
+            D.SymmSegment(*args)

@@ -77,3 +77,17 @@ def test_fused_gemm_allreduce_one_trip_and_two_hop(nproc):
     p = _run("mp_fused_ar.py", nproc)
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     assert "FAILURES 0" in p.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu(2)
+@pytest.mark.parametrize("script", ["mp_peer_allreduce.py", "mp_fused_ar.py"])
+def test_native_symmetric_heap_backend(script):
+    """The same peer kernels over this package's own heap (virtual-memory blocks shared as POSIX descriptors and
+    mapped by every rank) instead of torch's symmetric memory: peer pointers only, no multicast object."""
+    if NGPU < 2:
+        pytest.skip(f"needs 2 GPUs, found {NGPU}")
+    p = _run(script, 2, env={"B200RT_SYMM": "native"})
+    assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
+    assert "FAILURES 0" in p.stdout
+    assert "symm backend native" in p.stdout
