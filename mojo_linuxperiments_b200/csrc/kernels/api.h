@@ -40,6 +40,10 @@ typedef struct b200_quant_prolog {
   const void* gamma; float eps;
   void* q; float* scale;
   void* flags; const void* step;
+  void* residual_out; long long ldro;   // mode 3: where residual + x is written (NULL: in place, which rules out the
+                                        // inline form)
+  int allow_inline;                     // up to four tokens: let the GEMM CTAs quantise their own operand (no quantiser
+                                        // CTAs, row statistics exchanged inside the split-K cluster) when the shape allows
 } b200_quant_prolog;
 int b200_w8a8_gemm_decode_p(const b200_quant_prolog* prolog, const void* wq, const float* sw, void* y,
                             const void* residual, int M, int N, int K, int ldy, int out_fp32, int* status, int num_sms,

@@ -131,8 +131,13 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   pdl_launch_dependents();
   B200_TRACE_INIT();
   if (threadIdx.x == 0) B200_TRACE(TK_ATTN_DECODE, TP_START);
-  pdl_wait();
-  if (threadIdx.x == 0) B200_TRACE(TK_ATTN_DECODE, TP_DEPS);
+  // Fused form: only the new token's q / k / v come from the previous kernel.  Lengths, positions and page table were
+  // settled before this step began and the cached tokens were written by earlier steps, so the first two K / V tiles are
+  // requested before the dependency wait (below) and stream in while the previous kernel finishes.
+  if constexpr (!FUSED) {
+    pdl_wait();
+    if (threadIdx.x == 0) B200_TRACE(TK_ATTN_DECODE, TP_DEPS);
+  }
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -194,6 +199,21 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   // Page ids are fetched once, in parallel, so the producer never waits on a global load between two TMA issues;
   // pages past the end of the sequence are replaced by its last page (already in L2) and masked in the softmax.
   if (tid < ADC_NB * 8 && total_pages > 0) page_s[tid] = pt[min(blk0 * 8 + tid, total_pages - 1)];
+  // tile i of this CTA's stream (K blocks first, then V blocks) into ring stage i & 1
+  auto issue_tile = [&](int i) {
+    const int st = i & 1;
+    const int blk = i < nb ? i : i - nb;
+    const int kv = i < nb ? 0 : 1;
+    mbar_expect_tx(bar(B_FULL + st), ADC_TILE);
+    const uint32_t dst = sRing + st * ADC_TILE;
+#pragma unroll 1
+    for (int j = 0; j < 8; ++j) {
+      const int page = page_s[blk * 8 + j];
+      const int row = ((page * 2 + kv) * p.hkv + kvh) * 16;  // first token row of the block in the [rows][2][64] view
+      tma_load_3d(dst + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 0, row);
+      tma_load_3d(dst + ADC_HALF + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 1, row);
+    }
+  };
   if constexpr (!FUSED) {
     for (int i = tid; i < G * 16; i += ADC_THREADS) {
       const int g = i >> 4, c = i & 15;
@@ -201,6 +221,13 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
       *reinterpret_cast<uint4*>(pQ + (c >> 3) * 2048 + (g >> 3) * 1024 + (g & 7) * 128 + (((c & 7) ^ (g & 7)) << 4)) = v;
     }
   } else {
+    __syncthreads();                                 // barriers initialised, page ids in shared memory
+    if (tid == 0 && nb > 0) {
+      prefetch_tmap(&tmap_kv);
+      for (int i = 0; i < 2; ++i) issue_tile(i);     // first use of both ring stages: nothing to wait for (nb >= 1: 2 nb >= 2)
+    }
+    pdl_wait();
+    if (tid == 0) B200_TRACE(TK_ATTN_DECODE, TP_DEPS);
     // ---- rotate q (every CTA), and in the CTA that owns the new token: rotate k, append k and v to the cache, score ----
     const int pos = p.f.positions[b];
     const bool pos_ok = pos >= 0 && pos < p.f.max_pos;
@@ -284,23 +311,13 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
 
   if (warp == 0) {
     if (lane == 0 && nb > 0) {
-      prefetch_tmap(&tmap_kv);
+      if constexpr (!FUSED) prefetch_tmap(&tmap_kv);
       bool ok = true;
-      for (int i = 0; i < 2 * nb && ok; ++i) {
+      for (int i = FUSED ? 2 : 0; i < 2 * nb && ok; ++i) {            // fused: tiles 0 and 1 are already on their way
         const int st = i & 1;
         const uint32_t ph = (i >> 1) & 1u;
-        const int blk = i < nb ? i : i - nb;
-        const int kv = i < nb ? 0 : 1;
         if (!mbar_wait(bar(B_EMPTY + st), ph ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (5 << 8)), limit)) { ok = false; break; }
-        mbar_expect_tx(bar(B_FULL + st), ADC_TILE);
-        const uint32_t dst = sRing + st * ADC_TILE;
-#pragma unroll 1
-        for (int j = 0; j < 8; ++j) {
-          const int page = page_s[blk * 8 + j];
-          const int row = ((page * 2 + kv) * p.hkv + kvh) * 16;  // first token row of the block in the [rows][2][64] view
-          tma_load_3d(dst + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 0, row);
-          tma_load_3d(dst + ADC_HALF + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 1, row);
-        }
+        issue_tile(i);
       }
       if (!ok) { const uint64_t t0 = globaltimer_ns(); while (globaltimer_ns() - t0 < 2000000ull) { } }
     }

@@ -29,7 +29,12 @@ struct QuantProlog {
   uint32_t* flags;                 // [M] one word per row: holds `ticket` once the row is complete
   const uint32_t* step;            // device word that changes between replays of a captured launch
   uint32_t launch_id;              // differs between the launches of one step
-  int rows;                        // grid rows (blockIdx.y values) taken by quantiser CTAs
+  int rows;                        // grid rows (blockIdx.y values) taken by quantiser CTAs; 0 with a mode set: the inline
+                                   // form (a few tokens) - every GEMM CTA quantises its own K slice of the rows straight
+                                   // into its operand stages, the cluster exchanges the row statistics
+  __nv_bfloat16* residual_out;     // QR_ADD_NORM: where bf16(residual + x) goes (may equal residual with quantiser CTAs;
+  long long ldro;                  // must differ for the inline form, where every cluster reads the old residual)
+  int allow_inline;                // host only: the caller accepts the inline form
 };
 
 __device__ __forceinline__ uint32_t quant_ticket(const QuantProlog& q) {
@@ -88,7 +93,7 @@ __device__ void quant_row_cta(const QuantProlog& p, int row, int K, float* buf, 
         uint2 raw;
         raw.x = *reinterpret_cast<const uint32_t*>(&lo);
         raw.y = *reinterpret_cast<const uint32_t*>(&hi);
-        *reinterpret_cast<uint2*>(p.residual + static_cast<size_t>(row) * p.ldr + k) = raw;
+        *reinterpret_cast<uint2*>(p.residual_out + static_cast<size_t>(row) * p.ldro + k) = raw;
       }
       if (norm) {
 #pragma unroll

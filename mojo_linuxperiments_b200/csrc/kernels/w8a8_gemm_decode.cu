@@ -109,9 +109,19 @@ __device__ __forceinline__ void emit2(const OutSink& k, int m, int n, float v0, 
   *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(k.y) + o) = __floats2bfloat162_rn(v0, v1);
 }
 
+// u / m for the handful of values the inline prologue meets (u < 8 unrolled, m = 1..4)
+__device__ __forceinline__ int inl_div(int u, int m) {
+  return m == 1 ? u : (m == 2 ? (u >> 1) : (m == 3 ? ((u * 11) >> 5) : (u >> 2)));
+}
+
+// inline prologue: [4 warps][4 rows][2] partial statistics of this CTA + [8 senders][4 rows][4] of the cluster
+constexpr int STAT_BYTES = (32 + 128) * 4;
+constexpr int INL_MAX_ROWS = 4;       // token rows the inline prologue handles
+constexpr int INL_UNITS = 8;          // (k-block, row) pairs per quantising warp: their rotated values stay in registers
+
 // dynamic shared memory: pipeline stages, split-K exchange buffer, channel / token scales, barriers, alignment slack
 constexpr int decode_smem_bytes(int bn, int stages) {
-  return stages * (TILE_N * BLOCK_K + bn * BLOCK_K) + (TILE_N + 16) * (bn + 4) * 4 + (TILE_N + 64) * 4 + 1024 + 256;
+  return stages * (TILE_N * BLOCK_K + bn * BLOCK_K) + (TILE_N + 16) * (bn + 4) * 4 + (TILE_N + 64) * 4 + STAT_BYTES + 1024 + 256;
 }
 
 template <int BN, int STAGES>
@@ -134,7 +144,8 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   int32_t* ex = reinterpret_cast<int32_t*>(smem + STAGES * STAGE_BYTES);          // split-K exchange buffer
   float* sw_s = reinterpret_cast<float*>(smem + STAGES * STAGE_BYTES + EX_BYTES);  // [128] channel scales of this tile
   float* sx_s = sw_s + TILE_N;                                                     // [BN] token scales
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sx_s + 64);                         // full[S], empty[S], tfull
+  float* stat_s = sx_s + 64;                                                       // inline prologue: row statistics
+  uint64_t* bars = reinterpret_cast<uint64_t*>(stat_s + STAT_BYTES / 4);           // full[S], empty[S], tfull
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -148,6 +159,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   const int S = p.splits;
   const int rank = static_cast<int>(cluster_ctarank());          // == blockIdx.x: position along K
   const bool prolog = p.qp.mode != QR_NONE;
+  const bool inl = BN == 16 && prolog && p.qp.rows == 0;     // a few tokens: this CTA quantises its own operand (below)
   if (prolog && static_cast<int>(blockIdx.y) < p.qp.rows) {
     // ---- quantiser CTA: one token row, then the row's flag ----
     B200_TRACE_INIT();
@@ -179,7 +191,8 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   const uint64_t limit = p.limit_ns;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    // inline prologue: a stage is full when the weight tile has landed and a quantising warp has stored the rows
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), inl ? 2 : 1); mbar_init(empty_bar(s), 1); }
     mbar_init(tfull_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -210,6 +223,143 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   auto slice0 = [S](int r) { return 2 * ((64 * r + S - 1) / S); };
   const int cw = slice0(rank + 1) - slice0(rank);                       // channels this CTA finishes
   const int n_base = n_tile * TILE_N + slice0(rank);
+
+  // ---------------- inline activation prologue (up to INL_MAX_ROWS tokens) ----------------
+  // Warps 2..5 turn rows [0, M) x this CTA's k-blocks of the bf16 input into the int8 B operand themselves.  A k-block
+  // is one 128-block of the Hadamard rotation; k-block kb0 + i belongs to warp 2 + (i & 3), a lane holds four
+  // consecutive elements, the rotated values stay in registers.  What a row needs from the other k-blocks - the sum of
+  // squares for the norm, the maximum for the scale - is exchanged once through distributed shared memory: the
+  // rotation is linear, so the values are rotated *before* the norm's scalar 1/rms is known and the maximum is scaled
+  // afterwards.  Every cluster repeats the work for its own tile (a few thousand elements), which removes the
+  // activation kernel and its boundary from the chain.  The weight tiles are requested before the dependency wait.
+  uint32_t qw[INL_UNITS];
+  const int nkb = kb1 - kb0, w4 = warp - 2, Mr = p.M;
+  if (inl) {
+    if (warp == 0 && lane == 0) {
+      const uint64_t pol = policy_evict_first();
+      prefetch_tmap(&tmap_w);
+      const int pre = min(STAGES, nkb);
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(full_bar(i), A_BYTES);
+        tma_load_2d_hint(smem_base + i * STAGE_BYTES, &tmap_w, full_bar(i), (kb0 + i) * BLOCK_K, w_base + n_tile * TILE_N, pol);
+      }
+    }
+    pdl_wait();
+    if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 21);
+    const int mode = p.qp.mode;
+    const bool norm = mode == QR_NORM || mode == QR_ADD_NORM;
+    const int eti = threadIdx.x - 64;
+    float v[INL_UNITS][4];
+    float st_a = 0.f, st_b = 0.f;
+    if (warp >= 2) {
+      uint2 ra[INL_UNITS], rb[INL_UNITS], rg[INL_UNITS];
+#pragma unroll
+      for (int u = 0; u < INL_UNITS; ++u) {
+        const int ib = inl_div(u, Mr), m = u - ib * Mr, i = 4 * ib + w4;
+        ra[u] = make_uint2(0u, 0u); rb[u] = make_uint2(0u, 0u); rg[u] = make_uint2(0u, 0u);
+        if (i < nkb) {
+          const int k = (kb0 + i) * BLOCK_K + lane * 4;
+          const __nv_bfloat16* xr = p.qp.x + static_cast<size_t>(m) * p.qp.ldx;
+          ra[u] = *reinterpret_cast<const uint2*>(xr + k);
+          if (mode == QR_SWIGLU) rb[u] = *reinterpret_cast<const uint2*>(xr + p.K + k);
+          if (mode == QR_ADD_NORM) rb[u] = *reinterpret_cast<const uint2*>(p.qp.residual + static_cast<size_t>(m) * p.qp.ldr + k);
+          if (norm) rg[u] = __ldg(reinterpret_cast<const uint2*>(p.qp.gamma + k));
+        }
+      }
+      const bool keeper = n_tile == 0 && blockIdx.z == 0;       // one cluster writes the updated residual stream
+      float ssr[INL_MAX_ROWS] = {0.f, 0.f, 0.f, 0.f}, amr[INL_MAX_ROWS] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int u = 0; u < INL_UNITS; ++u) {
+        const int ib = inl_div(u, Mr), m = u - ib * Mr, i = 4 * ib + w4;
+        if (i < nkb) {
+          unpack4_bf16(ra[u], v[u]);
+          if (mode == QR_SWIGLU) {
+            float up[4];
+            unpack4_bf16(rb[u], up);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[u][j] = __fdividef(v[u][j], 1.f + __expf(-v[u][j])) * up[j];
+          } else if (mode == QR_ADD_NORM) {
+            float r[4];
+            unpack4_bf16(rb[u], r);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[u][j] = __bfloat162float(__float2bfloat16(__fadd_rn(v[u][j], r[j])));
+            if (keeper) {
+              const __nv_bfloat162 lo = __floats2bfloat162_rn(v[u][0], v[u][1]), hi = __floats2bfloat162_rn(v[u][2], v[u][3]);
+              uint2 raw;
+              raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+              raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+              *reinterpret_cast<uint2*>(p.qp.residual_out + static_cast<size_t>(m) * p.qp.ldro + (kb0 + i) * BLOCK_K + lane * 4) = raw;
+            }
+          }
+          float ss = 0.f;
+          if (norm) {
+            float g[4];
+            unpack4_bf16(rg[u], g);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { ss += v[u][j] * v[u][j]; v[u][j] *= g[j]; }
+          }
+          fwht128_lane4(v[u], lane);
+          float am = 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) am = fmaxf(am, fabsf(v[u][j]));
+#pragma unroll
+          for (int mm = 0; mm < INL_MAX_ROWS; ++mm)
+            if (m == mm) { ssr[mm] += ss; amr[mm] = fmaxf(amr[mm], am); }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) v[u][j] = 0.f;
+        }
+      }
+#pragma unroll
+      for (int mm = 0; mm < INL_MAX_ROWS; ++mm) {
+        ssr[mm] = warp_sum(ssr[mm]);
+        amr[mm] = warp_max(amr[mm]);
+        if (lane == 0) { stat_s[(w4 * 4 + mm) * 2] = ssr[mm]; stat_s[(w4 * 4 + mm) * 2 + 1] = amr[mm]; }
+      }
+      named_bar_sync(1, 128);
+      if (eti < INL_MAX_ROWS) {                  // thread `eti` owns row `eti`: this CTA's share of its statistics
+#pragma unroll
+        for (int w = 0; w < 4; ++w) { st_a += stat_s[(w * 4 + eti) * 2]; st_b = fmaxf(st_b, stat_s[(w * 4 + eti) * 2 + 1]); }
+        if (S == 1) { stat_s[32 + eti * 4] = st_a; stat_s[32 + eti * 4 + 1] = st_b; }
+      }
+    }
+    if (S > 1) {
+      cluster_wait_acquire();                    // every CTA of the cluster runs (pairs with the arrival at kernel start)
+      if (warp >= 2 && eti < INL_MAX_ROWS) {
+        const uint32_t mine = smem_u32(stat_s + 32 + (rank * 4 + eti) * 4);
+        for (int dst = 0; dst < S; ++dst)
+          st_shared_cluster_v4(mapa_shared(mine, static_cast<uint32_t>(dst)), __float_as_uint(st_a), __float_as_uint(st_b), 0u, 0u);
+      }
+      cluster_arrive_release();
+      cluster_wait_acquire();
+      cluster_arrive_relaxed();                  // re-arms the barrier that the split-K exchange waits on
+    } else if (warp >= 2) {
+      named_bar_sync(1, 128);
+    }
+    if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 22);
+    if (warp >= 2) {
+      float inv[INL_MAX_ROWS], my_scale = 0.f;
+#pragma unroll
+      for (int mm = 0; mm < INL_MAX_ROWS; ++mm) {
+        float tss = 0.f, tam = 0.f;
+        for (int r = 0; r < S; ++r) { tss += stat_s[32 + (r * 4 + mm) * 4]; tam = fmaxf(tam, stat_s[32 + (r * 4 + mm) * 4 + 1]); }
+        const float rstd = norm ? rsqrtf(tss / static_cast<float>(p.K) + p.qp.eps) : 1.f;
+        const float sc = quant_scale_from_amax(tam * rstd);
+        inv[mm] = rstd * quant_inv_scale(sc);
+        if (eti == mm && mm < Mr) my_scale = sc;
+      }
+      if (eti < BN) sx_s[eti] = my_scale;         // token scales of the epilogue (rows beyond M: 0)
+#pragma unroll
+      for (int u = 0; u < INL_UNITS; ++u) {
+        const int ib = inl_div(u, Mr), m = u - ib * Mr;
+        float iv = inv[0];
+#pragma unroll
+        for (int mm = 1; mm < INL_MAX_ROWS; ++mm) if (m == mm) iv = inv[mm];
+        qw[u] = quant_pack4(v[u], iv);
+      }
+    }
+  }
+
   if (warp == 0) {
     const uint64_t pol_w = policy_evict_first();       // weights are read exactly once per launch
     int stage = 0; uint32_t phase = 0;
@@ -217,7 +367,8 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     // Weights never change during inference, so the first ring-full of weight tiles is requested before waiting
     // for the previous kernel; the activation tiles (its output) are requested after the wait.
     const int pre = grouped ? 0 : min(STAGES, kb1 - kb0);
-    if (lane == 0) {
+    const uint32_t stage_tx = inl ? A_BYTES : STAGE_BYTES;     // inline prologue: the token rows are stored, not loaded
+    if (lane == 0 && !inl) {
       prefetch_tmap(&tmap_w);
       prefetch_tmap(&tmap_x);
       for (int i = 0; i < pre; ++i) {
@@ -225,8 +376,8 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         tma_load_2d_hint(smem_base + i * STAGE_BYTES, &tmap_w, full_bar(i), (kb0 + i) * BLOCK_K, w_base + n_tile * TILE_N, pol_w);
       }
     }
-    if (!grouped) pdl_wait();
-    if (prolog) {
+    if (!grouped && !inl) pdl_wait();
+    if (prolog && !inl) {
       // the whole warp watches the row flags of this launch's quantiser CTAs (lane l: rows l and l + 32)
       const uint32_t ticket = quant_ticket(p.qp);
       const uint64_t t_start = globaltimer_ns();
@@ -246,15 +397,15 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     }
     if (lane == 0 && ok) {
       B200_TRACE(TK_GEMM_DECODE, TP_DEPS);
-      for (int i = 0; i < pre; ++i)
+      for (int i = 0; i < pre && !inl; ++i)
         tma_load_2d(smem_base + i * STAGE_BYTES + A_BYTES, &tmap_x, full_bar(i), (kb0 + i) * BLOCK_K, m0);
       if (pre == STAGES) phase = 1u; else stage = pre;
       for (int kb = kb0 + pre; kb < kb1; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (2 << 8)), limit)) { ok = false; break; }
-        mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+        mbar_expect_tx(full_bar(stage), stage_tx);
         const uint32_t a_dst = smem_base + stage * STAGE_BYTES;
         tma_load_2d_hint(a_dst, &tmap_w, full_bar(stage), kb * BLOCK_K, w_base + n_tile * TILE_N, pol_w);
-        tma_load_2d(a_dst + A_BYTES, &tmap_x, full_bar(stage), kb * BLOCK_K, m0);
+        if (!inl) tma_load_2d(a_dst + A_BYTES, &tmap_x, full_bar(stage), kb * BLOCK_K, m0);
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
@@ -281,6 +432,28 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       B200_TRACE(TK_GEMM_DECODE, 3);
     }
     __syncwarp();
+  } else if (inl) {
+    // warps 2..5: the quantised rows of their k-blocks go into the B half of the stages (128-byte rows, 16-byte chunk c
+    // of row r stored at chunk c ^ (r & 7): the layout a swizzled TMA load would have produced)
+    bool ok = true;
+#pragma unroll
+    for (int u = 0; u < INL_UNITS; ++u) {
+      const int ib = inl_div(u, Mr), m = u - ib * Mr, i = 4 * ib + w4;
+      if (i < nkb && ok) {
+        const int stage = i % STAGES, use = i / STAGES;
+        if (m == 0 && use > 0)
+          ok = mbar_wait(empty_bar(stage), static_cast<uint32_t>(use - 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (2 << 8)), limit);
+        if (ok) {
+          const uint32_t dst = smem_base + stage * STAGE_BYTES + A_BYTES + m * 128 + ((((lane >> 2) ^ m) & 7) << 4) + ((lane & 3) << 2);
+          asm volatile("st.shared.u32 [%0], %1;" ::"r"(dst), "r"(qw[u]) : "memory");
+          if (m == Mr - 1) {
+            fence_proxy_async_smem();              // generic-proxy stores, read by the tensor core's async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full_bar(stage));
+          }
+        }
+      }
+    }
   }
 
   if (!grouped && warp != 0) pdl_wait();
@@ -301,12 +474,12 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   bool acc_ok = false;
   if (epi) {
     // token scales: the previous kernel's output, readable now that the dependency wait is behind us
-    if (!prolog && et < BN) sx_s[et] = et < jmax ? p.sx[m0 + et] : 0.f;
+    if (!prolog && et < BN) sx_s[et] = et < jmax ? p.sx[m0 + et] : 0.f;       // (inline prologue: already there)
     acc_ok = (kb1 > kb0) && mbar_wait(tfull_bar, 0, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (2 << 8)), limit);
     tc_fence_after();
     // fused prologue: the scales are written by this launch's quantiser CTAs; the accumulator can only be complete
     // after the producer warp saw every row's flag, so they are there now (read past L1)
-    if (prolog && et < BN) sx_s[et] = et < jmax ? __ldcg(p.sx + m0 + et) : 0.f;
+    if (prolog && !inl && et < BN) sx_s[et] = et < jmax ? __ldcg(p.sx + m0 + et) : 0.f;
     if (et == 0) B200_TRACE(TK_GEMM_DECODE, 4);
   }
 
@@ -657,6 +830,7 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
     if (!qp->x || !qp->q || !qp->scale || !qp->flags || !qp->step) return -1;
     if ((qp->mode == QR_NORM || qp->mode == QR_ADD_NORM) && !qp->gamma) return -1;
     if (qp->mode == QR_ADD_NORM && !qp->residual) return -1;
+    if (qp->residual_out && ((qp->ldro % 4) || (reinterpret_cast<uintptr_t>(qp->residual_out) & 7))) return -2;
     if ((qp->ldx % 4) || (qp->ldr % 4) || (reinterpret_cast<uintptr_t>(qp->x) & 7) || (reinterpret_cast<uintptr_t>(qp->residual) & 7) ||
         (reinterpret_cast<uintptr_t>(qp->gamma) & 7)) return -2;
   }
@@ -669,7 +843,16 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
   const int n_tiles = (N + TILE_N - 1) / TILE_N, m_tiles = groups > 0 ? groups : (M + bn - 1) / bn;
   // A split whose clusters do not all fit on the GPU at once runs as two waves: twice the latency for an op that is
   // nothing but latency.  (Grouped launches have one grid row per expert and are multi-wave by nature.)
-  int s = force_splits > 0 ? force_splits : decode_pick_splits(n_tiles * m_tiles, p.kblocks, num_sms, bn, groups > 0 ? -100000 : 1, qp ? M : 0);
+  // Up to INL_MAX_ROWS tokens the GEMM CTAs quantise their own operand (inline prologue) when a warp's share of
+  // (k-block, row) pairs fits its registers; otherwise the launch carries quantiser CTAs.
+  bool inl = false;
+  int s = 0;
+  if (qp && M <= INL_MAX_ROWS && qp->allow_inline && !(qp->mode == QR_ADD_NORM && (!qp->residual_out || qp->residual_out == qp->residual))) {
+    s = decode_pick_splits(n_tiles * m_tiles, p.kblocks, num_sms, bn, 1, 0);
+    if (ar) while (s >= 1 && n_tiles * m_tiles + 1 > resident_clusters(bn, s)) --s;
+    if (s >= 1 && (((p.kblocks + s - 1) / s + 3) / 4) * M <= INL_UNITS) inl = true;
+  }
+  if (!inl) s = force_splits > 0 ? force_splits : decode_pick_splits(n_tiles * m_tiles, p.kblocks, num_sms, bn, groups > 0 ? -100000 : 1, qp ? M : 0);
   if (s < 1 || s > 8) return -1;
   p.splits = s;
   p.sx = sx; p.sw = sw; p.y = y; p.residual = static_cast<const __nv_bfloat16*>(residual);
@@ -684,7 +867,7 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
     // many clusters of this size fit (clusters are placed per GPC, so this is less than SMs x CTAs-per-SM / size)
     // and narrow the split until the grid fits, keeping a margin of one cluster.
     if ((N % 8) || (ldy % 8) || out_fp32) return -2;
-    while (s >= 1 && n_tiles * m_tiles + (qp ? (M + s - 1) / s : 0) + 1 > resident_clusters(bn, s)) --s;
+    while (s >= 1 && n_tiles * m_tiles + ((qp && !inl) ? (M + s - 1) / s : 0) + 1 > resident_clusters(bn, s)) --s;
     if (s < 1) return -20;
     p.splits = s;
     p.limit_ns = static_cast<unsigned long long>(ar->limit_ms > 0 ? ar->limit_ms : 2000) * 1000000ull;
@@ -695,8 +878,9 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
     static uint32_t launch_counter = 0;          // distinguishes the launches of one step (see quant_ticket)
     p.qp = *qp;
     p.qp.launch_id = ++launch_counter;
-    q_rows = (M + s - 1) / s;
+    q_rows = inl ? 0 : (M + s - 1) / s;
     p.qp.rows = q_rows;
+    if (!p.qp.residual_out) { p.qp.residual_out = p.qp.residual; p.qp.ldro = p.qp.ldr; }
     if (m_tiles != 1) return -1;
   }
   CUtensorMap tw, tx;
@@ -749,6 +933,8 @@ static QuantProlog to_prolog(const b200_quant_prolog& c) {
   q.gamma = static_cast<const __nv_bfloat16*>(c.gamma); q.eps = c.eps;
   q.q = static_cast<int8_t*>(c.q); q.scale = c.scale;
   q.flags = static_cast<uint32_t*>(c.flags); q.step = static_cast<const uint32_t*>(c.step);
+  q.residual_out = static_cast<__nv_bfloat16*>(c.residual_out); q.ldro = c.ldro;
+  q.allow_inline = c.allow_inline;
   return q;
 }
 

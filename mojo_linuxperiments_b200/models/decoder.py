@@ -121,6 +121,12 @@ class Decoder:
         # in L2, acquire, proxy fence) measured slower than the kernel boundary it replaces (programmatic dependent
         # launch already overlaps that boundary): 5 instead of 8 launches per layer but +10..15 us per layer.
         self.fused_quant = os.environ.get("B200RT_FUSED_QUANT", "0") not in ("0", "false")
+        # Up to four tokens the GEMM CTAs can quantise their own K slice of the rows (no extra CTAs, no flags: the row
+        # statistics cross the split-K cluster through distributed shared memory).  Opt-in as well: 5 launches per layer
+        # instead of 8, but measured slower at batch 1 (4 layers of the 1/8 shard: 227 us against 177 us) - the
+        # prologue's serial steps (load, two reductions, cluster exchange, pack, proxy fence) run on four warps of every
+        # CTA and cost more than the stand-alone kernel plus its boundary.
+        self.inline_quant = os.environ.get("B200RT_INLINE_QUANT", "0") not in ("0", "false")
 
     # -- building blocks ------------------------------------------------------------------------------------
     def _norm_quant(self, h, delta, gamma, want_normed=False):
@@ -169,22 +175,24 @@ class Decoder:
                             k_norm_w=W.get("k_norm"), eps=self.cfg.eps)
         return A.attn_decode(q, cache, kv.page_table, kv.seq_lens, scratch=sc, splits=splits, scale=self.scale)
 
-    def _fused_norm_linear(self, h, delta, gamma, lw):
-        """(residual add +) RMSNorm + rotation + int8 + column-parallel linear as one launch (decode, <= 64 tokens)."""
+    def _fused_norm_linear(self, h, delta, gamma, lw, h_out=None):
+        """(residual add +) RMSNorm + rotation + int8 + column-parallel linear as one launch (decode, <= 64 tokens).
+        With ``h_out`` the updated residual stream ``h + delta`` is written there instead of in place."""
         if delta is None:
-            return L.fused_linear(h, lw.qweight, lw.scale, mode=L.QR_NORM, gamma=gamma, eps=self.cfg.eps)
-        return L.fused_linear(delta, lw.qweight, lw.scale, mode=L.QR_ADD_NORM, gamma=gamma, eps=self.cfg.eps, residual=h)
+            return L.fused_linear(h, lw.qweight, lw.scale, mode=L.QR_NORM, gamma=gamma, eps=self.cfg.eps, inline=self.inline_quant)
+        return L.fused_linear(delta, lw.qweight, lw.scale, mode=L.QR_ADD_NORM, gamma=gamma, eps=self.cfg.eps, residual=h,
+                              residual_out=h_out, inline=self.inline_quant)
 
     def _fused_swiglu_down(self, gu, lw):
         """SwiGLU + rotation + int8 + row-parallel down projection (+ all-reduce under tensor parallelism): one launch."""
         if self.tp_ctx is not None:
-            y = self.tp_ctx.row_parallel_fused(gu, lw, L.QR_SWIGLU)
+            y = self.tp_ctx.row_parallel_fused(gu, lw, L.QR_SWIGLU, inline=self.inline_quant)
             if y is not None:
                 return y
         if self.comm.world > 1:
             hq, sh = L.act_quant(gu, mode=L.AQ_SWIGLU)
             return self._row_parallel(hq, sh, lw)
-        return L.fused_linear(gu, lw.qweight, lw.scale, mode=L.QR_SWIGLU)
+        return L.fused_linear(gu, lw.qweight, lw.scale, mode=L.QR_SWIGLU, inline=self.inline_quant)
 
     def _mlp(self, l, xq, sx, xn):
         W = self.w["layers"][l]
@@ -210,11 +218,18 @@ class Decoder:
         h = A.embed_gather(token_ids, self.w["embed"])
         delta = None
         d_ok = cfg.d_model % 128 == 0 and cfg.d_model <= L.FUSED_PROLOG_MAX_K
-        fq = self.fused_quant and mode == "decode" and token_ids.shape[0] <= L.DECODE_MAX_M and d_ok
+        M = token_ids.shape[0]
+        # a few tokens: the linears quantise their own operand inside the GEMM CTAs (always on); more: quantiser CTAs
+        # in the launch (opt-in)
+        fq = ((self.fused_quant and M <= L.DECODE_MAX_M) or (self.inline_quant and M <= L.INLINE_PROLOG_MAX_M)) and mode == "decode" and d_ok
+        # The inline form reads the old residual in every cluster, so the sum goes to a second buffer and the two swap.
+        h_alt = torch.empty_like(h) if fq else None
         for l in range(cfg.n_layers):
             W = self.w["layers"][l]
             if fq:
-                qkv = self._fused_norm_linear(h, delta, W["attn_norm"], W["qkv"])
+                qkv = self._fused_norm_linear(h, delta, W["attn_norm"], W["qkv"], h_alt)
+                if delta is not None:
+                    h, h_alt = h_alt, h
             else:
                 xq, sx = self._norm_quant(h, delta, W["attn_norm"])
                 qkv = L.w8a8_gemm(xq, sx, W["qkv"].qweight, W["qkv"].scale)
@@ -224,7 +239,8 @@ class Decoder:
             with op_range(f"layer{l}.o_proj+allreduce"):
                 delta = self._row_parallel(aq, sa, W["o"])
             if fq and self.moe is None:
-                gu = self._fused_norm_linear(h, delta, W["mlp_norm"], W["gate_up"])
+                gu = self._fused_norm_linear(h, delta, W["mlp_norm"], W["gate_up"], h_alt)
+                h, h_alt = h_alt, h
                 delta = self._fused_swiglu_down(gu, W["down"])
                 continue
             xq, sx = self._norm_quant(h, delta, W["mlp_norm"])      # the router, too, consumes the quantised rows

@@ -109,7 +109,7 @@ class QuantProlog(ctypes.Structure):
     """``b200_quant_prolog`` of csrc/kernels/api.h: the activation prologue a decode GEMM launch carries itself."""
     _fields_ = [("mode", c_int), ("x", c_void_p), ("ldx", c_longlong), ("residual", c_void_p), ("ldr", c_longlong),
                 ("gamma", c_void_p), ("eps", c_float), ("q", c_void_p), ("scale", c_void_p), ("flags", c_void_p),
-                ("step", c_void_p)]
+                ("step", c_void_p), ("residual_out", c_void_p), ("ldro", c_longlong), ("allow_inline", c_int)]
 
 
 def ptr(t: torch.Tensor | None) -> int | None:

@@ -81,8 +81,12 @@ QR_PLAIN, QR_NORM, QR_ADD_NORM, QR_SWIGLU = 1, 2, 3, 4
 FUSED_PROLOG_MAX_K = 20480          # a row is parked as floats in the GEMM's stage memory (80 KiB)
 
 
+INLINE_PROLOG_MAX_M = 4             # up to this many tokens the GEMM CTAs quantise their own operand (no quantiser CTAs)
+
+
 def make_prolog(x: torch.Tensor, mode: int, *, gamma: torch.Tensor | None = None, eps: float = 1e-5,
-                residual: torch.Tensor | None = None, workspace: Workspace | None = None):
+                residual: torch.Tensor | None = None, residual_out: torch.Tensor | None = None,
+                inline: bool = False, workspace: Workspace | None = None):
     """Describe the activation prologue a decode GEMM launch should run itself (see ``fused_linear``).
 
     Returns ``(struct, keep)``: the ctypes struct for the C entry points and the tensors it points at (int8 rows,
@@ -96,23 +100,34 @@ def make_prolog(x: torch.Tensor, mode: int, *, gamma: torch.Tensor | None = None
     s = torch.empty((M,), dtype=torch.float32, device=x.device)
     if residual is not None:
         assert residual.dtype == torch.bfloat16 and residual.stride(1) == 1
+    if residual_out is not None:
+        assert residual is not None and residual_out.dtype == torch.bfloat16 and residual_out.stride(1) == 1
+        assert residual_out.shape == residual.shape
     st = _lib.QuantProlog(mode, x.data_ptr(), x.stride(0), _lib.ptr(residual), residual.stride(0) if residual is not None else 0,
-                          _lib.ptr(gamma), float(eps), q.data_ptr(), s.data_ptr(), w.qflags.data_ptr(), w.step.data_ptr())
+                          _lib.ptr(gamma), float(eps), q.data_ptr(), s.data_ptr(), w.qflags.data_ptr(), w.step.data_ptr(),
+                          _lib.ptr(residual_out), residual_out.stride(0) if residual_out is not None else 0,
+                          1 if inline else 0)
     return st, (q, s)
 
 
 def fused_linear(x: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor, *, mode: int = QR_PLAIN,
                  gamma: torch.Tensor | None = None, eps: float = 1e-5, residual: torch.Tensor | None = None,
+                 residual_out: torch.Tensor | None = None, inline: bool = False,
                  out_dtype: torch.dtype = torch.bfloat16, workspace: Workspace | None = None) -> torch.Tensor:
     """bf16 activations in, bf16 (or fp32) result out, in ONE launch for up to 64 tokens: the activation prologue
     (``mode``: QR_PLAIN rotate + int8; QR_NORM RMSNorm first; QR_ADD_NORM ``residual += x`` in place, then RMSNorm of
     the residual; QR_SWIGLU x = gate | up) runs in quantiser CTAs of the GEMM's own grid, which publish a flag per
-    token row; the GEMM CTAs stream their first weight tiles meanwhile and wait for the flags, not for a kernel."""
+    token row; the GEMM CTAs stream their first weight tiles meanwhile and wait for the flags, not for a kernel.
+
+    With ``inline`` and up to ``INLINE_PROLOG_MAX_M`` tokens there are no quantiser CTAs: every GEMM CTA quantises its own K slice of the
+    rows into its operand stages and the cluster exchanges the row statistics (sum of squares, maximum) through
+    distributed shared memory.  Because every cluster then reads the old residual, QR_ADD_NORM needs ``residual_out``
+    (a second buffer that receives ``residual + x``; without it the sum is written in place and quantiser CTAs run)."""
     import ctypes
     N, K = wq.shape
     M = x.shape[0]
     w = workspace or default_workspace(x.device)
-    st, keep = make_prolog(x, mode, gamma=gamma, eps=eps, residual=residual, workspace=w)
+    st, keep = make_prolog(x, mode, gamma=gamma, eps=eps, residual=residual, residual_out=residual_out, inline=inline, workspace=w)
     assert keep[0].shape[1] == K
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     rc = _lib.lib().b200_w8a8_gemm_decode_p(

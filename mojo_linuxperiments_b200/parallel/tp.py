@@ -76,7 +76,7 @@ class TPContext:
             return want == "1"
         return True
 
-    def row_parallel_fused(self, x: torch.Tensor, lw, mode: int):
+    def row_parallel_fused(self, x: torch.Tensor, lw, mode: int, inline: bool = False):
         """Row-parallel linear from bf16 activations: activation prologue (``mode`` as in ``ops.linear.fused_linear``),
         K-shard product and all-reduce in ONE launch.  Returns None when the grid would not be co-resident (the caller
         then quantises with the stand-alone kernel and calls ``row_parallel``)."""
@@ -87,7 +87,7 @@ class TPContext:
             return None
         h = self.heap
         ws = default_workspace(x.device)
-        st, keep = L.make_prolog(x, mode, workspace=ws)
+        st, keep = L.make_prolog(x, mode, inline=inline, workspace=ws)
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
         rc = _lib.lib().b200_w8a8_gemm_decode_ar_p(
             ctypes.byref(st), lw.qweight.data_ptr(), lw.scale.data_ptr(), out.data_ptr(), None, M, N, K, out.stride(0),

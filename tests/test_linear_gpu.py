@@ -196,3 +196,55 @@ def test_fused_linear_runs_its_own_activation_prologue(mode, m, n, k):
     torch.cuda.synchronize()
     ws.check_status()
     assert torch.equal(yg, y1) and torch.equal(yg2, y1)
+
+
+@pytest.mark.parametrize("mode", ["plain", "norm", "add_norm", "swiglu"])
+@pytest.mark.parametrize("m", [1, 2, 3, 4])
+@pytest.mark.parametrize("n,k", [(768, 4096), (6144, 4096), (4096, 1792), (28672, 4096), (4096, 14336), (512, 128), (1000, 640)])
+def test_fused_linear_inline_prologue_for_a_few_tokens(mode, m, n, k):
+    """Up to four tokens the GEMM CTAs quantise their own operand (row statistics exchanged inside the split-K cluster).
+    The result must match stand-alone prologue + GEMM (the rotation runs before the norm's 1/rms is applied, so single
+    int8 values may differ by one step), the residual sum goes to the second buffer bit-exactly and the input residual
+    stays untouched; shapes whose K slice does not fit a warp's registers fall back to quantiser CTAs and must agree too."""
+    from mojo_linuxperiments_b200.ops import linear as L
+    from mojo_linuxperiments_b200.ops.workspace import default_workspace
+    ws = default_workspace(torch.device("cuda", 0))
+    wq, sw = _mk_w(n, k)
+    gamma = (torch.rand(k) + 0.5).to(torch.bfloat16).cuda()
+    x = _mk_x(m, 2 * k if mode == "swiglu" else k, 31)
+    res = _mk_x(m, k, 32)
+    md = {"plain": L.QR_PLAIN, "norm": L.QR_NORM, "add_norm": L.QR_ADD_NORM, "swiglu": L.QR_SWIGLU}[mode]
+    aq = {"plain": L.AQ_PLAIN, "norm": L.AQ_NORM, "add_norm": L.AQ_ADD_NORM, "swiglu": L.AQ_SWIGLU}[mode]
+    r_ref = res.clone()
+    q, s = L.act_quant(x, mode=aq, gamma=gamma if mode in ("norm", "add_norm") else None, eps=1e-5,
+                       residual=r_ref if mode == "add_norm" else None)
+    ref = L.w8a8_gemm(q, s, wq, sw, force_mode=2)
+    r_in, r_out = res.clone(), torch.full_like(res, 7.0)
+
+    def fused():
+        return L.fused_linear(x, wq, sw, mode=md, gamma=gamma if mode in ("norm", "add_norm") else None, eps=1e-5,
+                              residual=r_in if mode == "add_norm" else None, residual_out=r_out if mode == "add_norm" else None,
+                              inline=True)
+
+    y1 = fused()
+    ws.next_step()
+    y2 = fused()
+    torch.cuda.synchronize()
+    ws.check_status()
+    rel = ((y1.float() - ref.float()).norm() / ref.float().norm()).item()
+    assert rel < 1e-2, rel
+    assert torch.equal(y1, y2)
+    if mode == "add_norm":
+        assert torch.equal(r_out, r_ref) and torch.equal(r_in, res)
+    g = torch.cuda.CUDAGraph()
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        with torch.cuda.graph(g, stream=st):
+            yg = fused()
+            ws.next_step()
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    ws.check_status()
+    assert torch.equal(yg, y1)
