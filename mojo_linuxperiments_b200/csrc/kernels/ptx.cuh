@@ -321,6 +321,12 @@ __device__ __forceinline__ void st_shared_cluster_v4(uint32_t addr, uint32_t a, 
 }
 // The two halves of the cluster barrier, for hiding its latency: every thread of every CTA arrives once and later
 // waits once per phase.  The relaxed arrive orders nothing (use it for "every CTA of the cluster has started").
+// 16 bytes into another CTA's shared memory, counted on an mbarrier of that CTA (complete_tx): the receiver waits on its
+// own barrier for the bytes it expects instead of on a barrier of the whole cluster
+__device__ __forceinline__ void st_async_cluster_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t mbar) {
+  asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.b32 [%0], {%1, %2, %3, %4}, [%5];"
+               ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d), "r"(mbar) : "memory");
+}
 __device__ __forceinline__ void cluster_arrive_relaxed() {
   asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
 }

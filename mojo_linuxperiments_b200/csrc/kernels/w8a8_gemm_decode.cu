@@ -78,6 +78,10 @@ struct DecodeGemmParams {
   // the bf16 input into the int8 operand and publish a flag per row; the GEMM CTAs prefetch their weights meanwhile
   // and wait for the flags instead of for an earlier kernel.
   QuantProlog qp;
+  // split-K exchange: 1 = partials travel as st.async counted on an mbarrier of the receiving CTA (it proceeds as soon
+  // as its own bytes are there), 0 = plain distributed-shared-memory stores followed by a barrier of the whole cluster
+  int async_x;
+  int narrow_epi;      // diagnostics: 1 = the unsplit epilogue stores 2 bytes per thread and token (the older form)
 };
 
 // Where a finished output element goes.  A plain struct of scalars (not a capturing lambda: called from the epilogue
@@ -146,7 +150,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   float* sx_s = sw_s + TILE_N;                                                     // [BN] token scales
   float* stat_s = sx_s + 64;                                                       // inline prologue: row statistics
   uint64_t* bars = reinterpret_cast<uint64_t*>(stat_s + STAT_BYTES / 4);           // full[S], empty[S], tfull
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -155,6 +159,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
   const uint32_t tfull_bar = bar_base + 8u * (2 * STAGES);
+  const uint32_t xch_bar = bar_base + 8u * (2 * STAGES + 1);     // split-K exchange: bytes the other CTAs send to this one
 
   const int S = p.splits;
   const int rank = static_cast<int>(cluster_ctarank());          // == blockIdx.x: position along K
@@ -194,6 +199,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
     // inline prologue: a stage is full when the weight tile has landed and a quantising warp has stored the rows
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), inl ? 2 : 1); mbar_init(empty_bar(s), 1); }
     mbar_init(tfull_bar, 1);
+    mbar_init(xch_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
     B200_TRACE_INIT();
@@ -209,6 +215,14 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool async_x = S > 1 && p.async_x != 0;
+  if (async_x && threadIdx.x == 0) {
+    // every CTA of the cluster (this one included) sends its partial of this CTA's slice: whole token chunks, 4 bytes
+    // each.  Expected before this CTA announces that it runs, so no sender's bytes can come first.
+    constexpr int CHX = (BN >= 32) ? 32 : 16;
+    const int my_cw = 2 * ((64 * (rank + 1) + S - 1) / S) - 2 * ((64 * rank + S - 1) / S);
+    mbar_expect_tx(xch_bar, static_cast<uint32_t>(S * my_cw * ((rows_valid + CHX - 1) / CHX) * CHX * 4));
+  }
   if (S > 1) cluster_arrive_relaxed();          // "this CTA runs": waited for just before the exchange
 
   // where a finished output element goes: y, or (fused all-reduce) this rank's slot of the symmetric partial buffer
@@ -490,7 +504,59 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
 
   if (S == 1) {
     if (epi) asm volatile("bar.sync 1, 128;" ::: "memory");          // sx_s is complete (epilogue warps only)
-    if (epi && acc_ok) {
+    if (epi) {
+      // a wait gave up somewhere: one thread reads the flag, so all four warps take the same path below (they meet at
+      // a barrier there)
+      volatile int* verdict = abort_flag + 1;
+      if (et == 0) *verdict = *abort_flag;
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (*verdict) acc_ok = false;
+    }
+    // Whole tile inside N, bf16 out, 16-byte aligned rows: the tile is turned through shared memory (the pipeline
+    // stages are idle now) so that every thread stores 16 bytes of one token row instead of 2 bytes of BN rows.
+    __nv_bfloat16* const wdst = sink.mode == 2 ? part : reinterpret_cast<__nv_bfloat16*>(p.y);
+    const int wld = sink.mode == 2 ? p.N : p.ldy;
+    const __nv_bfloat16* const wres = sink.mode == 0 ? p.residual : nullptr;
+    const bool wide = !p.narrow_epi && sink.mode != 1 && !p.out_fp32 && n_tile * TILE_N + TILE_N <= p.N && (wld % 8) == 0 &&
+                      (reinterpret_cast<uintptr_t>(wdst) & 15) == 0 && (reinterpret_cast<uintptr_t>(wres) & 15) == 0;
+    if (epi && acc_ok && wide) {
+      constexpr int TP = TILE_N + 4;                       // floats per token row of the turned tile
+      float* tile_f = reinterpret_cast<float*>(smem);
+      const float swn = sw_s[row];
+      const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / CH; ++c) {
+        if (c * CH >= jmax) break;
+        uint32_t r[CH];
+        if constexpr (CH == 32) tmem_ld_x32(t_addr + c * CH, r); else tmem_ld_x16(t_addr + c * CH, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < CH; ++j)
+          tile_f[(c * CH + j) * TP + row] = static_cast<float>(static_cast<int32_t>(r[j])) * swn * sx_s[c * CH + j];
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const size_t col0 = static_cast<size_t>(n_tile) * TILE_N;
+      for (int ch = et; ch < jmax * (TILE_N / 8); ch += 128) {
+        const int j = ch >> 4, c8 = ch & 15;
+        const float4 lo = *reinterpret_cast<const float4*>(tile_f + j * TP + c8 * 8);
+        const float4 hi = *reinterpret_cast<const float4*>(tile_f + j * TP + c8 * 8 + 4);
+        float f[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        const size_t o = static_cast<size_t>(m0 + j) * wld + col0 + c8 * 8;
+        if (wres) {
+          const uint4 rv = *reinterpret_cast<const uint4*>(wres + o);
+          const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { f[2 * e] += __uint_as_float(rw[e] << 16); f[2 * e + 1] += __uint_as_float(rw[e] & 0xffff0000u); }
+        }
+        uint4 out;
+        __nv_bfloat162 b2;
+        b2 = __floats2bfloat162_rn(f[0], f[1]); out.x = *reinterpret_cast<uint32_t*>(&b2);
+        b2 = __floats2bfloat162_rn(f[2], f[3]); out.y = *reinterpret_cast<uint32_t*>(&b2);
+        b2 = __floats2bfloat162_rn(f[4], f[5]); out.z = *reinterpret_cast<uint32_t*>(&b2);
+        b2 = __floats2bfloat162_rn(f[6], f[7]); out.w = *reinterpret_cast<uint32_t*>(&b2);
+        *reinterpret_cast<uint4*>(wdst + o) = out;
+      }
+    } else if (epi && acc_ok) {
       const int n = n_tile * TILE_N + row;
       const bool n_ok = n < p.N;
       const float swn = sw_s[row];
@@ -517,6 +583,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       const int cw_owner = slice0(owner + 1) - slice0(owner);
       const uint32_t remote = mapa_shared(smem_u32(ex), static_cast<uint32_t>(owner)) +
                               4u * static_cast<uint32_t>((rank * cw_owner + row_in) * XS);
+      const uint32_t remote_bar = mapa_shared(xch_bar, static_cast<uint32_t>(owner));
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / CH; ++c) {
@@ -530,16 +597,25 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         }
         if (c * CH < jmax) {                                // token rows beyond the batch are never read back
 #pragma unroll
-          for (int j = 0; j < CH; j += 4)
-            st_shared_cluster_v4(remote + 4u * (c * CH + j), r[j], r[j + 1], r[j + 2], r[j + 3]);
+          for (int j = 0; j < CH; j += 4) {
+            if (async_x) st_async_cluster_v4(remote + 4u * (c * CH + j), r[j], r[j + 1], r[j + 2], r[j + 3], remote_bar);
+            else st_shared_cluster_v4(remote + 4u * (c * CH + j), r[j], r[j + 1], r[j + 2], r[j + 3]);
+          }
         }
       }
     }
     if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 10);
     tc_fence_before();
-    cluster_sync_all();
+    bool x_ok = true;
+    if (async_x) {
+      cluster_arrive_relaxed();      // "my stores are issued": waited for just before this CTA leaves (below), so that no
+                                     // CTA exits while a peer may still write into it
+      x_ok = mbar_wait(xch_bar, 0, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (2 << 8)), limit);
+    } else {
+      cluster_sync_all();
+    }
     if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 6);
-    {
+    if (x_ok) {
       // All six warps finish blocks of 4 tokens x 8 channel pairs: shared-memory reads spread over the banks (2-way
       // conflicts at worst) and every token row gets 32 contiguous bytes, i.e. whole sectors.  With one warp per
       // scheduler every instruction's latency is exposed, so the loop avoids integer division and works on two
@@ -549,26 +625,37 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       const uint32_t inv_jt = (65536u + jt_n - 1) / jt_n;            // blk / jt_n == (blk * inv_jt) >> 16 for blk < 4096
       const int lj = lane & 3, lp = lane >> 2;
       constexpr int NWARP = GEMM_THREADS / 32;
-      for (int blk0 = warp; blk0 < blocks; blk0 += 2 * NWARP) {
-        int32_t a[2][2] = {{0, 0}, {0, 0}};
-        int jj[2], rr[2];
-        bool on[2];
+      constexpr int UB = 3;                       // blocks per round: with the sender loop unrolled, all their loads fly together
+      for (int blk0 = warp; blk0 < blocks; blk0 += UB * NWARP) {
+        int32_t a[UB][2];
+        int jj[UB], rr[UB];
+        bool on[UB];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < UB; ++u) {
           const int blk = blk0 + u * NWARP;
           const int pt = static_cast<int>((static_cast<uint32_t>(blk) * inv_jt) >> 16), jt = blk - pt * jt_n;
           jj[u] = 4 * jt + lj;
           rr[u] = 2 * (8 * pt + lp);
           on[u] = blk < blocks && jj[u] < jmax && rr[u] < cw;
-          if (on[u]) {
-            for (int s = 0; s < S; ++s) {
-              a[u][0] += ex[(s * cw + rr[u]) * XS + jj[u]];
-              a[u][1] += ex[(s * cw + rr[u] + 1) * XS + jj[u]];
+          a[u][0] = 0; a[u][1] = 0;
+        }
+        int32_t ld[UB][8][2];
+#pragma unroll
+        for (int u = 0; u < UB; ++u)
+#pragma unroll
+          for (int sdr = 0; sdr < 8; ++sdr) {
+            ld[u][sdr][0] = 0; ld[u][sdr][1] = 0;
+            if (on[u] && sdr < S) {
+              ld[u][sdr][0] = ex[(sdr * cw + rr[u]) * XS + jj[u]];
+              ld[u][sdr][1] = ex[(sdr * cw + rr[u] + 1) * XS + jj[u]];
             }
           }
-        }
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < UB; ++u)
+#pragma unroll
+          for (int sdr = 0; sdr < 8; ++sdr) { a[u][0] += ld[u][sdr][0]; a[u][1] += ld[u][sdr][1]; }
+#pragma unroll
+        for (int u = 0; u < UB; ++u) {
           if (!on[u]) continue;
           const int n = n_base + rr[u];
           const float sxj = sx_s[jj[u]];
@@ -580,6 +667,7 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
       }
       if (threadIdx.x == 64) B200_TRACE(TK_GEMM_DECODE, 11);
     }
+    if (async_x) cluster_wait_acquire();
   }
 
   tc_fence_before();
@@ -872,6 +960,12 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
     p.splits = s;
     p.limit_ns = static_cast<unsigned long long>(ar->limit_ms > 0 ? ar->limit_ms : 2000) * 1000000ull;
   }
+  static int async_env = -1;
+  if (async_env < 0) { const char* e = std::getenv("B200RT_GEMM_ASYNC_X"); async_env = (e && e[0] == '0') ? 0 : 1; }
+  p.async_x = async_env;
+  static int narrow_env = -1;
+  if (narrow_env < 0) { const char* e = std::getenv("B200RT_GEMM_NARROW_EPI"); narrow_env = (e && e[0] == '1') ? 1 : 0; }
+  p.narrow_epi = narrow_env;
   p.qp = QuantProlog{};
   int q_rows = 0;
   if (qp) {
