@@ -75,6 +75,7 @@ struct DecodeTcParams {
   // 1: the splits of a (sequence, kv head) are one thread-block cluster (cluster dims 1 x 1 x splits) and their partials
   // meet in the shared memory of the cluster's first CTA, which merges them: no global scratch, no counter, no fence
   int cluster_merge;
+  int early_tiles;     // fused form: request the first two K / V tiles before the dependency wait
   DecodeFuse f;
 };
 
@@ -222,7 +223,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
     }
   } else {
     __syncthreads();                                 // barriers initialised, page ids in shared memory
-    if (tid == 0 && nb > 0) {
+    if (tid == 0 && nb > 0 && p.early_tiles) {
       prefetch_tmap(&tmap_kv);
       for (int i = 0; i < 2; ++i) issue_tile(i);     // first use of both ring stages: nothing to wait for (nb >= 1: 2 nb >= 2)
     }
@@ -311,9 +312,10 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
 
   if (warp == 0) {
     if (lane == 0 && nb > 0) {
-      if constexpr (!FUSED) prefetch_tmap(&tmap_kv);
+      const bool early = FUSED && p.early_tiles;
+      if (!early) prefetch_tmap(&tmap_kv);
       bool ok = true;
-      for (int i = FUSED ? 2 : 0; i < 2 * nb && ok; ++i) {            // fused: tiles 0 and 1 are already on their way
+      for (int i = early ? 2 : 0; i < 2 * nb && ok; ++i) {            // fused: tiles 0 and 1 are already on their way
         const int st = i & 1;
         const uint32_t ph = (i >> 1) & 1u;
         if (!mbar_wait(bar(B_EMPTY + st), ph ^ 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_EMPTY | (5 << 8)), limit)) { ok = false; break; }
@@ -1147,6 +1149,9 @@ static int attn_decode_tc_common(const void* q, const void* cache, int num_pages
   // per four layers), while a one-wave grid saves the fence, the counter and the L2 round trips of that merge.
   static int sm_count = 0;
   if (!sm_count) { int dev = 0; cudaGetDevice(&dev); cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev); }
+  static int early_env = -1;
+  if (early_env < 0) { const char* e = std::getenv("B200RT_ATTN_EARLY_TILES"); early_env = (e && e[0] == '0') ? 0 : 1; }
+  p.early_tiles = early_env;
   p.cluster_merge = (!persistent && cluster_env && G <= ADC_ZONE_MAX_G && splits >= 2 && splits <= ADC_ZONE_MAX_SPLITS &&
                      static_cast<long long>(B) * hkv * splits <= 2ll * sm_count) ? 1 : 0;
   if (splits > 1 && !p.cluster_merge && (!scratch || !counters)) return -1;

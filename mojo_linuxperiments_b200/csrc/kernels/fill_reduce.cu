@@ -2,7 +2,7 @@
 // the *global* element index (any split of the index space over GPUs produces the same elements), and reduce them.
 //   fill_uniform_reduce   grid-stride fill (16-byte stores) with per-thread double accumulation, warp shuffle and
 //                         shared-memory block reduction, one double per CTA; the last CTA to finish adds the CTA
-//                         partials in index order (deterministic) into the result
+//                         partials (exact in double, so any order gives the same bits) into the result
 // The op is bound by the 4 bytes per element written to HBM; Philox costs ~25 integer ops per element.
 #include "ptx.cuh"
 #include "api.h"
@@ -55,12 +55,24 @@ __global__ void __launch_bounds__(256) fill_uniform_reduce_kernel(float* out, un
     last = (old == gridDim.x - 1) ? 1 : 0;
   }
   __syncthreads();
-  if (last && threadIdx.x == 0) {
+  if (last) {
+    // The CTA partials are integer multiples of 2^-23 far below 2^53 in magnitude, so their double sum is exact and
+    // does not depend on the order: the whole CTA adds them (one thread walking a thousand L2 loads one by one
+    // cost several microseconds of a 40 us kernel).
     __threadfence();
     double t = 0.0;
-    for (unsigned c = 0; c < gridDim.x; ++c) t += *reinterpret_cast<volatile double*>(partials + c);
-    *result = t;
-    *counter = 0;
+    for (unsigned c = threadIdx.x; c < gridDim.x; c += blockDim.x) t += *reinterpret_cast<volatile double*>(partials + c);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    __syncthreads();                       // red[] of the first reduction has been read
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = t;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      double r = 0.0;
+      for (int w = 0; w < 8; ++w) r += red[w];
+      *result = r;
+      *counter = 0;
+    }
   }
 }
 

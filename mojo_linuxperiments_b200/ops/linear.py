@@ -1,6 +1,8 @@
 """W8A8 Hadamard linear: activation prologue (rotate + per-token int8) and the tcgen05 int8 GEMM."""
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -58,7 +60,7 @@ def w8a8_gemm(xq: torch.Tensor, sx: torch.Tensor, wq: torch.Tensor, sw: torch.Te
         assert residual.dtype == torch.bfloat16 and residual.stride(0) == out.stride(0) and residual.stride(1) == 1
     w = workspace or default_workspace(xq.device)
     n_tiles = (N + 127) // 128
-    use_cluster = M <= DECODE_MAX_M and (force_mode == 2 or (force_mode == -1 and n_tiles < 4 * _lib.num_sms(xq.device.index)))
+    use_cluster = M <= DECODE_MAX_M and (force_mode == 2 or (force_mode == -1 and n_tiles < _DECODE_TILE_WAVES * _lib.num_sms(xq.device.index)))
     if use_cluster:
         rc = _lib.lib().b200_w8a8_gemm_decode(
             xq.data_ptr(), sx.data_ptr(), wq.data_ptr(), sw.data_ptr(), out.data_ptr(), _lib.ptr(residual),
@@ -76,6 +78,9 @@ def w8a8_gemm(xq: torch.Tensor, sx: torch.Tensor, wq: torch.Tensor, sw: torch.Te
     _lib.check(rc, "w8a8_gemm")
     return out
 
+
+# up to this many 128-channel tiles per SM a small-M GEMM goes to the weight-streaming cluster kernel
+_DECODE_TILE_WAVES = int(os.environ.get("B200RT_DECODE_TILE_WAVES", "4"))
 
 QR_PLAIN, QR_NORM, QR_ADD_NORM, QR_SWIGLU = 1, 2, 3, 4
 FUSED_PROLOG_MAX_K = 20480          # a row is parked as floats in the GEMM's stage memory (80 KiB)
