@@ -73,6 +73,17 @@ def main():
             t = graph_time(lambda i: A.attn_decode(q, caches[i % n_layers], pt, lens, scratch=sc, splits=splits, out=out, impl=impl))
             print(json.dumps({"op": "attn_decode", "impl": impl, "case": tag, "splits": splits, "us": t * 1e6,
                               "gbs": byts / t / 1e9, "frac_of_measured_hbm": byts / t / 1e9 / hbm}), flush=True)
+        # the fused form the decoder runs (RoPE + KV append + attention + rotate / quantise of the output in one launch);
+        # `lens` counts the new token, so the cached part is ctx - 1 tokens
+        qkv = torch.randn((B, (hq + 2 * hkv) * 128), device=dev).to(torch.bfloat16)
+        pos = (lens - 1).contiguous()
+        cos, sin = A.rope_tables(ctx + 64, 500000.0, dev)
+        for long_form in (True, False):
+            splits = A.pick_decode_splits_tc(B, hkv, max_pages * ps, fused=long_form)
+            sc = A.DecodeAttnScratch(B, hq, hkv, splits, dev)
+            t = graph_time(lambda i: A.attn_decode_fused(qkv, pos, cos, sin, hq, hkv, caches[i % n_layers], pt, lens, scratch=sc, splits=splits))
+            print(json.dumps({"op": "attn_decode_fused", "blocks_per_cta": 9 if long_form else 4, "case": tag, "splits": splits,
+                              "us": t * 1e6, "gbs": byts / t / 1e9, "frac_of_measured_hbm": byts / t / 1e9 / hbm}), flush=True)
         if os.environ.get("SWEEP_SPLITS"):
             for splits in range(A.tc_min_splits(max_pages * ps), 10):
                 sc = A.DecodeAttnScratch(B, hq, hkv, splits, dev)

@@ -27,6 +27,7 @@ namespace b200 {
 
 constexpr int ADC_THREADS = 192;
 constexpr int ADC_NB = 4;                       // token blocks (of 128) per CTA
+constexpr int ADC_NB_LONG = 9;                  // fused form without a merge zone: up to 1,152 cached tokens per CTA
 constexpr int ADC_D = 128;
 constexpr int ADC_HALF = 128 * 128;             // bytes: 128 tokens x 64 dims bf16
 constexpr int ADC_TILE = 2 * ADC_HALF;          // 32 KiB
@@ -126,9 +127,12 @@ __device__ __forceinline__ void head_norm_rope(float (&lo)[8], float (&hi)[8], c
   }
 }
 
-template <int G, bool FUSED>
+template <int G, bool FUSED, int NB>
 __global__ void __launch_bounds__(ADC_THREADS, 2)
 attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeTcParams p) {
+  // score columns of the NB blocks, then 16 columns of output; allocations are powers of two
+  constexpr int O_COL_K = NB * ADC_NH;
+  constexpr int TMEM_COLS_K = (NB * ADC_NH + ADC_NH <= 128) ? 128 : 256;
   pdl_launch_dependents();
   B200_TRACE_INIT();
   if (threadIdx.x == 0) B200_TRACE(TK_ATTN_DECODE, TP_START);
@@ -142,19 +146,19 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // [ring 2 x 32K][P ADC_NB x 4K][Q 4K][exchange floats][barriers]
+  // [ring 2 x 32K][P NB x 4K][Q 4K][exchange floats][barriers]
   uint8_t* pP = smem + 2 * ADC_TILE;
-  uint8_t* pQ = pP + ADC_NB * ADC_P_TILE;
+  uint8_t* pQ = pP + NB * ADC_P_TILE;
   float* xch = reinterpret_cast<float*>(pQ + ADC_Q_TILE);          // [2][4 warps][8]: per-warp max, then sum
   float* ml_s = xch + 64;                                          // [8][2]: final (m, l) per head
   uint64_t* bars = reinterpret_cast<uint64_t*>(ml_s + 16);
-  enum { B_FULL = 0, B_EMPTY = 2, B_SFULL = 4, B_PFULL = 4 + ADC_NB, B_OFULL = 4 + 2 * ADC_NB, B_XCH = 5 + 2 * ADC_NB, B_COUNT = 6 + 2 * ADC_NB };
+  enum { B_FULL = 0, B_EMPTY = 2, B_SFULL = 4, B_PFULL = 4 + NB, B_OFULL = 4 + 2 * NB, B_XCH = 5 + 2 * NB, B_COUNT = 6 + 2 * NB };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* last_flag = const_cast<int*>(abort_flag) + 1;
-  int* page_s = last_flag + 1;                     // [ADC_NB * 8] page ids of this CTA's blocks
+  int* page_s = last_flag + 1;                     // [NB * 8] page ids of this CTA's blocks
   // fused form only: the finished (bf16-rounded) output rows of this CTA's heads, v and the scores of the new token
-  float* row_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(page_s + ADC_NB * 8) + 15) & ~uintptr_t(15));   // [G][128]
+  float* row_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(page_s + NB * 8) + 15) & ~uintptr_t(15));   // [G][128]
   float* vnew_s = row_s + G * ADC_D;               // [128]
   float* snew_s = vnew_s + ADC_D;                  // [8]
   float* amax_s = snew_s + 8;                      // [8]
@@ -181,25 +185,25 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   const int blk0 = split * per;
   int nb = min(total_blocks, blk0 + per) - blk0;
   if (nb < 0) nb = 0;
-  if (nb > ADC_NB) {                       // the host sized `splits` for a shorter maximum length
+  if (nb > NB) {                       // the host sized `splits` for a shorter maximum length
     if (tid == 0 && p.status) atomicCAS(p.status, 0, (int)ST_BAD_ARGUMENT | (5 << 8));
-    nb = ADC_NB;
+    nb = NB;
   }
   const int* pt = p.page_table + static_cast<size_t>(b) * p.max_pages;
   const uint64_t limit = p.limit_ns;
 
   if (tid == 0) {
-    for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i >= B_PFULL && i < B_PFULL + ADC_NB) || i == B_XCH ? 4 : 1);
+    for (int i = 0; i < B_COUNT; ++i) mbar_init(bar(i), (i >= B_PFULL && i < B_PFULL + NB) || i == B_XCH ? 4 : 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), ADC_TMEM_COLS); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(smem_u32(tmem_slot), TMEM_COLS_K); tmem_relinquish(); }
   // Q^T operand: rows = heads, K-major, two 64-dim halves of [16 rows x 128 B], 128-byte swizzle.  Only the first G
   // rows of Q^T and of the P tiles are ever written: row n of a B operand feeds column n of the accumulator alone,
   // and the columns >= G of S^T and O^T are never read, so whatever the other rows hold is harmless.
   // Page ids are fetched once, in parallel, so the producer never waits on a global load between two TMA issues;
   // pages past the end of the sequence are replaced by its last page (already in L2) and masked in the softmax.
-  if (tid < ADC_NB * 8 && total_pages > 0) page_s[tid] = pt[min(blk0 * 8 + tid, total_pages - 1)];
+  if (tid < NB * 8 && total_pages > 0) page_s[tid] = pt[min(blk0 * 8 + tid, total_pages - 1)];
   // tile i of this CTA's stream (K blocks first, then V blocks) into ring stage i & 1
   auto issue_tile = [&](int i) {
     const int st = i & 1;
@@ -349,7 +353,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
         if (!mbar_wait(bar(B_PFULL + blk), 0, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (5 << 8)), limit)) { ok = false; break; }
         if (!mbar_wait(bar(B_FULL + st), (i >> 1) & 1u, abort_flag, p.status, (ST_TIMEOUT_SMEM_FULL | (5 << 8)), limit)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t d = tmem_base + ADC_O_COL;
+        const uint32_t d = tmem_base + O_COL_K;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
           const uint64_t a = umma_desc_mn_sw128(sRing + st * ADC_TILE + kk * 2048, ADC_HALF, 1024);
@@ -367,13 +371,13 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
     const int r = qd * 32 + lane;                    // token inside a block, later output dim: the TMEM lane
     const int wi = warp - 2;
     const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(qd * 32) << 16);
-    float s[ADC_NB][G];
+    float s[NB][G];
     float mx[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) mx[g] = -INFINITY;
     bool ok = nb > 0;
 #pragma unroll
-    for (int blk = 0; blk < ADC_NB; ++blk) {
+    for (int blk = 0; blk < NB; ++blk) {
       if (blk < nb && ok) {
         if (!mbar_wait(bar(B_SFULL + blk), 0, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (5 << 8)), limit)) { ok = false; }
         else {
@@ -421,7 +425,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
     }
     // ---- probabilities with the final maximum -> bf16 -> P tiles (K-major rows = heads, swizzled) ----
 #pragma unroll
-    for (int blk = 0; blk < ADC_NB; ++blk) {
+    for (int blk = 0; blk < NB; ++blk) {
       if (blk < nb && ok) {
         uint8_t* pt_blk = pP + blk * ADC_P_TILE + (r >> 6) * 2048;
         const int c = (r & 63) >> 3, e = (r & 7) * 2;
@@ -461,7 +465,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
       else {
         tc_fence_after();
         uint32_t v[16];
-        tmem_ld_x16(t_lane + ADC_O_COL, v);
+        tmem_ld_x16(t_lane + O_COL_K, v);
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < G; ++g) o[g] = __uint_as_float(v[g]);
@@ -514,7 +518,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, ADC_TMEM_COLS); }
+  if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, TMEM_COLS_K); }
   if (tid == 0) B200_TRACE(TK_ATTN_DECODE, 6);
   if (p.splits == 1 && !(FUSED && p.f.xq)) { B200_TRACE_FLUSH(TK_ATTN_DECODE); return; }
 
@@ -1049,26 +1053,30 @@ typedef CUresult (*EncodeTiledFn3)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-template <int G, bool FUSED>
+// NB: 128-token blocks a CTA can hold.  4 with the merge zone (clusters of splits), 9 without it for a CTA that takes a
+// whole sequence of up to 1,152 tokens - both sized for two CTAs per SM.
+template <int G, bool FUSED, int NB>
 static int launch_adc(const CUtensorMap& tm, const DecodeTcParams& p, dim3 grid, cudaStream_t stream) {
   // rows of the CTA's heads, the new token's value row, a few scalars, and (groups of up to four heads) the merge zone
-  constexpr int SMEM = 2 * ADC_TILE + ADC_NB * ADC_P_TILE + ADC_Q_TILE + (64 + 16) * 4 + (6 + 2 * ADC_NB) * 8 + 64 + ADC_NB * 8 * 4 + 1024 +
+  constexpr int SMEM = 2 * ADC_TILE + NB * ADC_P_TILE + ADC_Q_TILE + (64 + 16) * 4 + (6 + 2 * NB) * 8 + 64 + NB * 8 * 4 + 1024 +
                        (G * ADC_D + ADC_D + 16) * 4 + 16 +
-                       (G <= ADC_ZONE_MAX_G ? ADC_ZONE_MAX_SPLITS * G * ADC_ZONE_ROW * 4 : 0);
+                       ((G <= ADC_ZONE_MAX_G && NB <= ADC_NB) ? ADC_ZONE_MAX_SPLITS * G * ADC_ZONE_ROW * 4 : 0);
+  static_assert(2 * (SMEM + 1024) <= 228 * 1024, "two CTAs per SM");
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<G, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_tc_kernel<G, FUSED, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     // ask for the largest shared-memory carveout: with the default preference the occupancy calculator (and the
     // launch) may settle for a split of the L1 / shared array that holds fewer CTAs per SM than the kernel was sized for
-    cudaFuncSetAttribute(attn_decode_tc_kernel<G, FUSED>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(attn_decode_tc_kernel<G, FUSED, NB>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     if (e != cudaSuccess) return -1000 - static_cast<int>(e);
     configured = true;
   }
-  if (p.cluster_merge) launch_ex_cluster(attn_decode_tc_kernel<G, FUSED>, dim3(grid), dim3(ADC_THREADS), SMEM, stream, dim3(1, 1, grid.z), tm, p);
-  else launch_ex(attn_decode_tc_kernel<G, FUSED>, dim3(grid), dim3(ADC_THREADS), SMEM, stream, 0, tm, p);
+  if (p.cluster_merge) launch_ex_cluster(attn_decode_tc_kernel<G, FUSED, NB>, dim3(grid), dim3(ADC_THREADS), SMEM, stream, dim3(1, 1, grid.z), tm, p);
+  else launch_ex(attn_decode_tc_kernel<G, FUSED, NB>, dim3(grid), dim3(ADC_THREADS), SMEM, stream, 0, tm, p);
   cudaError_t e = cudaGetLastError();
   return e == cudaSuccess ? 0 : -2000 - static_cast<int>(e);
 }
+
 
 template <int G>
 static int launch_adcp(const CUtensorMap& tm, const DecodeTcParams& p, int num_items, int num_sms, cudaStream_t stream) {
@@ -1097,6 +1105,9 @@ extern "C" int b200_attn_decode_tc_min_splits(int max_len) {
   const int blocks = (max_len + 127) / 128;
   return (blocks + ADC_NB - 1) / ADC_NB > 0 ? (blocks + ADC_NB - 1) / ADC_NB : 1;
 }
+// 128-token blocks one CTA can hold: 4, or 9 in the fused form (b200_attn_decode_fused) when the splits do not merge
+// as a cluster
+extern "C" int b200_attn_decode_tc_blocks_per_cta(int fused) { return fused ? ADC_NB_LONG : ADC_NB; }
 
 static int attn_decode_tc_common(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,
                                  void* out, float* scratch, unsigned* counters, int B, int hq, int hkv, int page_size,
@@ -1152,7 +1163,11 @@ static int attn_decode_tc_common(const void* q, const void* cache, int num_pages
   static int early_env = -1;
   if (early_env < 0) { const char* e = std::getenv("B200RT_ATTN_EARLY_TILES"); early_env = (e && e[0] == '0') ? 0 : 1; }
   p.early_tiles = early_env;
-  p.cluster_merge = (!persistent && cluster_env && G <= ADC_ZONE_MAX_G && splits >= 2 && splits <= ADC_ZONE_MAX_SPLITS &&
+  // blocks a CTA may meet: the page-table row bounds the sequence length
+  const int blocks_max = (max_pages * 16 + 127) / 128, per_max = (blocks_max + splits - 1) / splits;
+  const bool long_form = fuse && !persistent && per_max > ADC_NB;        // whole (or half) sequences per CTA: no merge zone
+  if (per_max > (long_form ? ADC_NB_LONG : ADC_NB)) return -1;
+  p.cluster_merge = (!persistent && !long_form && cluster_env && G <= ADC_ZONE_MAX_G && splits >= 2 && splits <= ADC_ZONE_MAX_SPLITS &&
                      static_cast<long long>(B) * hkv * splits <= 2ll * sm_count) ? 1 : 0;
   if (splits > 1 && !p.cluster_merge && (!scratch || !counters)) return -1;
   if (persistent) {
@@ -1165,19 +1180,27 @@ static int attn_decode_tc_common(const void* q, const void* cache, int num_pages
     }
   }
   dim3 grid(hkv, B, splits);
+  if (long_form) {
+    switch (G) {
+      case 1: return launch_adc<1, true, ADC_NB_LONG>(tm, p, grid, stream);
+      case 2: return launch_adc<2, true, ADC_NB_LONG>(tm, p, grid, stream);
+      case 4: return launch_adc<4, true, ADC_NB_LONG>(tm, p, grid, stream);
+      default: return launch_adc<8, true, ADC_NB_LONG>(tm, p, grid, stream);
+    }
+  }
   if (fuse) {
     switch (G) {
-      case 1: return launch_adc<1, true>(tm, p, grid, stream);
-      case 2: return launch_adc<2, true>(tm, p, grid, stream);
-      case 4: return launch_adc<4, true>(tm, p, grid, stream);
-      default: return launch_adc<8, true>(tm, p, grid, stream);
+      case 1: return launch_adc<1, true, ADC_NB>(tm, p, grid, stream);
+      case 2: return launch_adc<2, true, ADC_NB>(tm, p, grid, stream);
+      case 4: return launch_adc<4, true, ADC_NB>(tm, p, grid, stream);
+      default: return launch_adc<8, true, ADC_NB>(tm, p, grid, stream);
     }
   }
   switch (G) {
-    case 1: return launch_adc<1, false>(tm, p, grid, stream);
-    case 2: return launch_adc<2, false>(tm, p, grid, stream);
-    case 4: return launch_adc<4, false>(tm, p, grid, stream);
-    default: return launch_adc<8, false>(tm, p, grid, stream);
+    case 1: return launch_adc<1, false, ADC_NB>(tm, p, grid, stream);
+    case 2: return launch_adc<2, false, ADC_NB>(tm, p, grid, stream);
+    case 4: return launch_adc<4, false, ADC_NB>(tm, p, grid, stream);
+    default: return launch_adc<8, false, ADC_NB>(tm, p, grid, stream);
   }
 }
 
@@ -1205,10 +1228,10 @@ extern "C" int b200_attn_decode_fused(const void* qkv, long long ld_qkv, const i
 // CTAs of the tensor-core decode attention (group size 4, plain form) one SM holds at once.
 extern "C" int b200_attn_decode_tc_ctas_per_sm() {
   constexpr int SMEM = 2 * ADC_TILE + ADC_NB * ADC_P_TILE + ADC_Q_TILE + (64 + 16) * 4 + (6 + 2 * ADC_NB) * 8 + 64 + ADC_NB * 8 * 4 + 1024;
-  cudaFuncSetAttribute(attn_decode_tc_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-  cudaFuncSetAttribute(attn_decode_tc_kernel<4, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  cudaFuncSetAttribute(attn_decode_tc_kernel<4, false, ADC_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+  cudaFuncSetAttribute(attn_decode_tc_kernel<4, false, ADC_NB>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   int blocks = 0;
-  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attn_decode_tc_kernel<4, false>, ADC_THREADS, SMEM);
+  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, attn_decode_tc_kernel<4, false, ADC_NB>, ADC_THREADS, SMEM);
   return blocks;
 }
 

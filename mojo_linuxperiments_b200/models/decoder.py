@@ -116,6 +116,8 @@ class Decoder:
         import os
         # decode attention with rope / KV append / output quantisation folded in (B200RT_FUSED_ATTN=0: three launches)
         self.fused_attention = os.environ.get("B200RT_FUSED_ATTN", "1") not in ("0", "false")
+        # fused decode attention may give a CTA up to 9 blocks of 128 cached tokens (no KV split at batch 32 x 1,024)
+        self.long_attention = os.environ.get("B200RT_ATTN_LONG", "1") not in ("0", "false")
         # decode linears that run their own activation prologue (norm / SwiGLU + rotation + int8) in quantiser CTAs of
         # the GEMM launch.  Opt-in (B200RT_FUSED_QUANT=1): the hand-over of the int8 rows between CTAs of one launch (flag
         # in L2, acquire, proxy fence) measured slower than the kernel boundary it replaces (programmatic dependent
@@ -154,7 +156,8 @@ class Decoder:
             return A.attn_prefill(q, k_rot, v, cu_seqlens, max_len, scale=self.scale)
         impl = A.decode_impl(cache.page_size, self.hq // self.hkv)
         if impl in ("tc", "tcp"):
-            splits = A.pick_decode_splits_tc(M, self.hkv, kv.page_table.shape[1] * cache.page_size)
+            splits = A.pick_decode_splits_tc(M, self.hkv, kv.page_table.shape[1] * cache.page_size,
+                                             fused=impl == "tc" and self.fused_attention and self.long_attention)
         else:
             splits = A.pick_decode_splits(M, self.hkv, max_len)
         fused = impl == "tc" and self.fused_attention

@@ -117,12 +117,13 @@ class DecodeAttnScratch:
 
 
 TC_BLOCKS_PER_CTA = 4          # the tensor-core decode kernel holds at most 4 x 128 cached tokens per CTA
+TC_BLOCKS_PER_CTA_FUSED = 9    # its fused form has a variant without the cluster-merge zone that holds 9 x 128
 
 
-def tc_min_splits(max_len: int) -> int:
+def tc_min_splits(max_len: int, fused: bool = False) -> int:
     """Fewest KV splits the tensor-core decode kernel accepts for sequences of up to ``max_len`` tokens."""
     blocks = (max_len + 127) // 128
-    return max(1, -(-blocks // TC_BLOCKS_PER_CTA))
+    return max(1, -(-blocks // (TC_BLOCKS_PER_CTA_FUSED if fused else TC_BLOCKS_PER_CTA)))
 
 
 def decode_impl(page_size: int, group: int) -> str:
@@ -134,12 +135,13 @@ def decode_impl(page_size: int, group: int) -> str:
     return "simple"
 
 
-def pick_decode_splits_tc(B: int, hkv: int, max_len: int, num_sms: int = 148) -> int:
+def pick_decode_splits_tc(B: int, hkv: int, max_len: int, num_sms: int = 148, fused: bool = False) -> int:
     """KV splits for the tensor-core decode kernel.  Measured on B200 its time is close to
     waves x (128-token blocks per CTA + 1.6) x 2.7 us with two CTAs per SM (the 1.6 is the per-CTA set-up, softmax
     exchange and partial write), plus a little per split for the merge: few, long CTAs win once the grid fills the GPU."""
     blocks = max(1, (max_len + 127) // 128)
-    smin = tc_min_splits(max_len)
+    smin = tc_min_splits(max_len, fused)     # fused: a CTA may take a whole sequence (one wave of long CTAs beats three
+                                             # of short ones: every CTA pays ~1.6 blocks' worth of set-up and epilogue)
     slots = 2 * num_sms
     best, best_cost = smin, None
     # up to eight splits are one thread-block cluster that merges in shared memory: stay there when that is possible
@@ -224,7 +226,7 @@ def attn_decode_fused(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Ten
     assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape[1] == (hq + 2 * hkv) * d
     assert positions.dtype == torch.int32 and page_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
     assert cache.page_size == 16 and cache.kv_heads == hkv and hq // hkv in (1, 2, 4, 8)
-    splits = max(splits, tc_min_splits(page_table.shape[1] * cache.page_size))
+    splits = max(splits, tc_min_splits(page_table.shape[1] * cache.page_size, fused=True))
     if scratch is None or scratch.splits != splits:
         scratch = DecodeAttnScratch(B, hq, hkv, splits, qkv.device)
     out = torch.empty((B, hq, d), dtype=torch.bfloat16, device=qkv.device) if (want_out or not quantize) else None

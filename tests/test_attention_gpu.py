@@ -204,15 +204,17 @@ def test_attn_decode_clamps_lengths_beyond_the_page_table_row(impl):
 
 
 @pytest.mark.parametrize("hq,hkv,qk_norm", [(32, 8, False), (4, 1, False), (8, 1, True), (8, 4, True), (2, 2, False)])
-@pytest.mark.parametrize("splits", [1, 4])
-def test_attn_decode_fused_matches_the_three_kernels_it_replaces(hq, hkv, qk_norm, splits):
+@pytest.mark.parametrize("splits,longest", [(1, 1280), (4, 1280), (1, 1150), (2, 1025)])
+def test_attn_decode_fused_matches_the_three_kernels_it_replaces(hq, hkv, qk_norm, splits, longest):
     """rope_kv_write + attn_decode + act_quant in one launch: same cache contents, same attention output (against the
     fp32 oracle), and exactly the int8 rows / scales the stand-alone prologue makes of that output."""
     from mojo_linuxperiments_b200.ops import attention as A
     from mojo_linuxperiments_b200.ops import linear as L
     from mojo_linuxperiments_b200.ops.workspace import default_workspace
     ps, theta = 16, 500000.0
-    lens = [1, 17, 300, 1280, 64, 128, 513]                # tokens per sequence including the new one
+    # tokens per sequence including the new one; up to 1,152 a CTA of the fused kernel may take a whole sequence (nine
+    # blocks of 128, no split), beyond that the splits merge through global memory, with four splits as a cluster
+    lens = [1, 17, 300, longest, 64, 128, 513, 1024, min(longest, 1025)]
     B = len(lens)
     max_pages = (max(lens) + ps - 1) // ps
     n_pages = B * max_pages
@@ -232,7 +234,7 @@ def test_attn_decode_fused_matches_the_three_kernels_it_replaces(hq, hkv, qk_nor
     ws.status.zero_()
     # the three separate kernels
     q = A.rope_kv_write(qkv, pos, cos, sin, hq, hkv, cache=cache_a, page_table=page_table, q_norm_w=qw, k_norm_w=kw, eps=1e-6)
-    ref_out = A.attn_decode(q, cache_a, page_table, seq_lens, splits=splits, impl="tc")
+    ref_out = A.attn_decode(q, cache_a, page_table, seq_lens, splits=max(splits, 3), impl="tc")
     # the fused kernel, twice (its counters must reset themselves)
     xq, sx, out = A.attn_decode_fused(qkv, pos, cos, sin, hq, hkv, cache_b, page_table, seq_lens, splits=splits,
                                       q_norm_w=qw, k_norm_w=kw, eps=1e-6, want_out=True)
