@@ -123,7 +123,8 @@ int b200_attn_decode_fused(const void* qkv, long long ld_qkv, const int* positio
                            void* cache, int num_pages, const int* page_table, const int* seq_lens, void* out, void* xq,
                            long long ldq, float* sx, float* scratch, unsigned* counters, float* rot_scratch,
                            float* blk_amax, unsigned* seq_counters, int B, int hq, int hkv, int page_size, int max_pages,
-                           int splits, float scale, int* status, cudaStream_t stream);
+                           int splits, float scale, int* status, const void* next_weights,
+                           unsigned long long next_weights_bytes, cudaStream_t stream);
 // Persistent form: two CTAs per SM walk the (kv head, sequence, split) items, loads of the next item overlap the
 // softmax / output phase of the current one.
 int b200_attn_decode_tcp(const void* q, const void* cache, int num_pages, const int* page_table, const int* seq_lens,

@@ -59,6 +59,10 @@ struct DecodeFuse {
   float* rot_scratch;              // [B][hq][128] rotated rows, used when a token's heads span several CTAs (hkv > 1)
   float* blk_amax;                 // [B][hkv]
   unsigned* seq_counters;          // [B], zero between launches
+  // Constant bytes that the next kernel streams (the o-projection's weights): its CTAs cannot be resident while this
+  // kernel fills the SMs, so this kernel's CTAs ask for one slice each to be brought into L2 while HBM has slack.
+  const uint8_t* next_w;
+  unsigned long long next_w_bytes;
 };
 
 struct DecodeTcParams {
@@ -211,12 +215,14 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
     const int kv = i < nb ? 0 : 1;
     mbar_expect_tx(bar(B_FULL + st), ADC_TILE);
     const uint32_t dst = sRing + st * ADC_TILE;
+    const uint64_t pol = policy_evict_first();               // cached tokens are read once per step: they should not push
+                                                             // the next kernels' weights out of L2
 #pragma unroll 1
     for (int j = 0; j < 8; ++j) {
       const int page = page_s[blk * 8 + j];
       const int row = ((page * 2 + kv) * p.hkv + kvh) * 16;  // first token row of the block in the [rows][2][64] view
-      tma_load_3d(dst + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 0, row);
-      tma_load_3d(dst + ADC_HALF + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 1, row);
+      tma_load_3d_hint(dst + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 0, row, pol);
+      tma_load_3d_hint(dst + ADC_HALF + j * 2048, &tmap_kv, bar(B_FULL + st), 0, 1, row, pol);
     }
   };
   if constexpr (!FUSED) {
@@ -230,6 +236,16 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
     if (tid == 0 && nb > 0 && p.early_tiles) {
       prefetch_tmap(&tmap_kv);
       for (int i = 0; i < 2; ++i) issue_tile(i);     // first use of both ring stages: nothing to wait for (nb >= 1: 2 nb >= 2)
+    }
+    if (tid == 32 && p.f.next_w) {
+      const unsigned long long ctas = static_cast<unsigned long long>(gridDim.x) * gridDim.y * gridDim.z;
+      const unsigned long long me = blockIdx.x + gridDim.x * (blockIdx.y + static_cast<unsigned long long>(gridDim.y) * blockIdx.z);
+      const unsigned long long chunk = ((p.f.next_w_bytes + ctas - 1) / ctas + 15) & ~15ull;
+      const unsigned long long lo = me * chunk;
+      if (lo < p.f.next_w_bytes) {
+        const unsigned long long n = min(chunk, p.f.next_w_bytes - lo) & ~15ull;
+        if (n) bulk_prefetch_l2(p.f.next_w + lo, static_cast<uint32_t>(n));
+      }
     }
     pdl_wait();
     if (tid == 0) B200_TRACE(TK_ATTN_DECODE, TP_DEPS);
@@ -1215,12 +1231,18 @@ extern "C" int b200_attn_decode_fused(const void* qkv, long long ld_qkv, const i
                                       void* cache, int num_pages, const int* page_table, const int* seq_lens, void* out,
                                       void* xq, long long ldq, float* sx, float* scratch, unsigned* counters,
                                       float* rot_scratch, float* blk_amax, unsigned* seq_counters, int B, int hq, int hkv,
-                                      int page_size, int max_pages, int splits, float scale, int* status, cudaStream_t stream) {
+                                      int page_size, int max_pages, int splits, float scale, int* status,
+                                      const void* next_weights, unsigned long long next_weights_bytes, cudaStream_t stream) {
   DecodeFuse f;
   f.qkv = static_cast<const __nv_bfloat16*>(qkv); f.ld_qkv = ld_qkv; f.positions = positions; f.cos_tab = cos_tab; f.sin_tab = sin_tab;
   f.max_pos = max_pos; f.q_norm_w = static_cast<const __nv_bfloat16*>(q_norm_w); f.k_norm_w = static_cast<const __nv_bfloat16*>(k_norm_w);
   f.eps = eps; f.cache = static_cast<__nv_bfloat16*>(cache); f.num_pages = num_pages;
   f.xq = static_cast<int8_t*>(xq); f.ldq = ldq; f.sx = sx; f.rot_scratch = rot_scratch; f.blk_amax = blk_amax; f.seq_counters = seq_counters;
+  static int l2_env = -1;
+  if (l2_env < 0) { const char* e = std::getenv("B200RT_ATTN_NEXT_W"); l2_env = (e && e[0] == '1') ? 1 : 0; }
+  const bool pf = l2_env && next_weights && next_weights_bytes >= 16 && (reinterpret_cast<uintptr_t>(next_weights) & 15) == 0;
+  f.next_w = pf ? static_cast<const uint8_t*>(next_weights) : nullptr;
+  f.next_w_bytes = pf ? next_weights_bytes : 0;
   return attn_decode_tc_common(nullptr, cache, num_pages, page_table, seq_lens, out, scratch, counters, B, hq, hkv, page_size,
                                max_pages, splits, scale, status, 0, 0, stream, &f);
 }

@@ -81,6 +81,7 @@ struct DecodeGemmParams {
   // split-K exchange: 1 = partials travel as st.async counted on an mbarrier of the receiving CTA (it proceeds as soon
   // as its own bytes are there), 0 = plain distributed-shared-memory stores followed by a barrier of the whole cluster
   int async_x;
+  int l2_prefetch;     // this many weight tiles beyond the shared-memory ring are requested into L2 before the dependency wait
   int narrow_epi;      // diagnostics: 1 = the unsplit epilogue stores 2 bytes per thread and token (the older form)
 };
 
@@ -389,6 +390,10 @@ w8a8_gemm_decode_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid
         mbar_expect_tx(full_bar(i), STAGE_BYTES);
         tma_load_2d_hint(smem_base + i * STAGE_BYTES, &tmap_w, full_bar(i), (kb0 + i) * BLOCK_K, w_base + n_tile * TILE_N, pol_w);
       }
+      // The ring holds the first STAGES tiles; the rest of this CTA's weights are pulled into L2 meanwhile, so that once
+      // the input is there the stream runs from L2 for as far as HBM got ahead while the previous kernel finished.
+      if (p.l2_prefetch > 0)
+        for (int kb = kb0 + pre; kb < min(kb1, kb0 + pre + p.l2_prefetch); ++kb) tma_prefetch_2d(&tmap_w, kb * BLOCK_K, w_base + n_tile * TILE_N);
     }
     if (!grouped && !inl) pdl_wait();
     if (prolog && !inl) {
@@ -963,6 +968,9 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
   static int async_env = -1;
   if (async_env < 0) { const char* e = std::getenv("B200RT_GEMM_ASYNC_X"); async_env = (e && e[0] == '0') ? 0 : 1; }
   p.async_x = async_env;
+  static int l2_env = -1;
+  if (l2_env < 0) { const char* e = std::getenv("B200RT_L2_PREFETCH_TILES"); l2_env = e ? std::atoi(e) : 0; }
+  p.l2_prefetch = (groups > 0) ? 0 : l2_env;
   static int narrow_env = -1;
   if (narrow_env < 0) { const char* e = std::getenv("B200RT_GEMM_NARROW_EPI"); narrow_env = (e && e[0] == '1') ? 1 : 0; }
   p.narrow_epi = narrow_env;

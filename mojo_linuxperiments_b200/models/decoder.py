@@ -171,7 +171,8 @@ class Decoder:
             # one launch: per-head norm + rotary embedding + KV append + attention + rotation / int8 of the output
             xq, sx, _ = A.attn_decode_fused(qkv, positions, self.cos, self.sin, self.hq, self.hkv, cache, kv.page_table,
                                             kv.seq_lens, scratch=sc, splits=splits, scale=self.scale,
-                                            q_norm_w=W.get("q_norm"), k_norm_w=W.get("k_norm"), eps=self.cfg.eps)
+                                            q_norm_w=W.get("q_norm"), k_norm_w=W.get("k_norm"), eps=self.cfg.eps,
+                                            next_weights=W["o"].qweight)
             return xq, sx
         q = A.rope_kv_write(qkv, positions, self.cos, self.sin, self.hq, self.hkv, cache=cache,
                             page_table=kv.page_table, seq_ids=None, q_norm_w=W.get("q_norm"),

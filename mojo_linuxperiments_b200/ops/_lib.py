@@ -98,7 +98,7 @@ class _Sig:
     b200_attn_decode_tma = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
     b200_attn_decode_tc = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
     b200_attn_decode_tc_min_splits = (I, [I])
-    b200_attn_decode_fused = (I, [P, LL, P, P, P, I, P, P, F, P, I, P, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, I, I, F, P, P])
+    b200_attn_decode_fused = (I, [P, LL, P, P, P, I, P, P, F, P, I, P, P, P, P, LL, P, P, P, P, P, P, I, I, I, I, I, I, F, P, P, c_uint64, P])
     b200_attn_decode_tcp = (I, [P, P, I, P, P, P, P, P, I, I, I, I, I, I, F, P, I, P])
     b200_attn_prefill = (I, [P, LL, P, LL, P, LL, P, P, I, I, I, I, I, F, P, P])
     b200_attn_prefill_split = (I, [P, LL, P, LL, P, LL, P, P, I, I, I, I, I, F, I, P, P, P])

@@ -215,12 +215,15 @@ def attn_decode(q: torch.Tensor, cache: PagedKVCache, page_table: torch.Tensor, 
 def attn_decode_fused(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, hq: int, hkv: int,
                       cache: PagedKVCache, page_table: torch.Tensor, seq_lens: torch.Tensor, *,
                       scratch: DecodeAttnScratch | None = None, splits: int = 1, scale: float | None = None,
-                      q_norm_w=None, k_norm_w=None, eps: float = 1e-6, quantize: bool = True, want_out: bool = False):
+                      q_norm_w=None, k_norm_w=None, eps: float = 1e-6, quantize: bool = True, want_out: bool = False,
+                      next_weights: torch.Tensor | None = None):
     """One launch for rope_kv_write + decode attention + the activation prologue of o_proj.
 
     qkv bf16 [B, (hq + 2 hkv) * 128]: the new token's raw projections; ``positions[b]`` is where it goes in the cache and
     ``seq_lens[b]`` counts it.  Returns ``(xq int8 [B, hq*128], sx fp32 [B], out bf16 [B, hq, 128] or None)``; with
-    ``quantize=False`` only ``out``.  Needs page size 16 and a group size of 1/2/4/8 (the tcgen05 kernel)."""
+    ``quantize=False`` only ``out``.  Needs page size 16 and a group size of 1/2/4/8 (the tcgen05 kernel).
+    ``next_weights``: a constant tensor the following kernel streams (the o-projection's int8 weights); the kernel's CTAs
+    ask for it to be brought into L2 meanwhile."""
     B = qkv.shape[0]
     d = HEAD_DIM
     assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape[1] == (hq + 2 * hkv) * d
@@ -238,7 +241,9 @@ def attn_decode_fused(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Ten
         seq_lens.data_ptr(), _lib.ptr(out), _lib.ptr(xq), xq.stride(0) if xq is not None else 0, _lib.ptr(sx),
         scratch.buf.data_ptr(), scratch.counters.data_ptr(), _lib.ptr(scratch.rot), _lib.ptr(scratch.blk_amax),
         _lib.ptr(scratch.seq_counters), B, hq, hkv, cache.page_size, page_table.shape[1], splits,
-        float(scale if scale is not None else 1.0 / math.sqrt(d)), default_workspace(qkv.device).status.data_ptr(), _lib.stream())
+        float(scale if scale is not None else 1.0 / math.sqrt(d)), default_workspace(qkv.device).status.data_ptr(),
+        _lib.ptr(next_weights), next_weights.numel() * next_weights.element_size() if next_weights is not None else 0,
+        _lib.stream())
     _lib.check(rc, "attn_decode_fused")
     return (xq, sx, out) if quantize else out
 
