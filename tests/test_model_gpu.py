@@ -36,7 +36,8 @@ def test_tiny_dense_prefill_logits_and_greedy_decode():
     agree = 0
     for b in range(B):
         ref = OM.forward_sequence(cfg, ck_dev, prompts[b].cuda())[-1]
-        assert torch.allclose(got[b], ref, rtol=5e-2, atol=5e-2 * ref.abs().max().item()), (got[b] - ref).abs().max().item()
+        # measured: 1.4-2.0 % of the largest logit (int8 activations on both sides, different summation orders)
+        assert (got[b] - ref).abs().max().item() <= 3e-2 * ref.abs().max().item(), (got[b] - ref).abs().max().item()
         toks, logs = OM.greedy_generate(cfg, ck_dev, prompts[b].cuda(), NEW)
         # token-for-token unless the oracle's own top-2 margin is within rounding noise
         for t in range(NEW):
