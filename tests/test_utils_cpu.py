@@ -32,6 +32,13 @@ def test_decode_attention_split_policy_and_sp_layout():
         assert s >= A.tc_min_splits(max_len) and s <= max(A.tc_min_splits(max_len), min(32, (max_len + 127) // 128))
     assert A.pick_decode_splits_tc(32, 8, 1088) == 3            # a full GPU prefers few, long CTAs
     assert A.pick_decode_splits_tc(1, 1, 1088) > 3              # a nearly empty one prefers many short ones
+    # the fused form may hold 9 x 128 tokens per CTA: whole sequences when that makes one wave of CTAs
+    assert [A.tc_min_splits(n, fused=True) for n in (1, 1152, 1153, 2304, 4096)] == [1, 1, 2, 2, 4]
+    assert A.pick_decode_splits_tc(32, 8, 1152, fused=True) == 1   # 256 CTAs of nine blocks: one wave
+    assert A.pick_decode_splits_tc(32, 8, 1280, fused=True) == 2   # ten blocks do not fit one CTA
+    # a 1/8 shard keeps its many short CTAs (they merge as a cluster)
+    assert A.pick_decode_splits_tc(32, 1, 1152, fused=True) == A.pick_decode_splits_tc(32, 1, 1152) > 1
+    assert A.pick_decode_splits_tc(32, 2, 1152, fused=True) * 64 <= 296
     assert A.decode_impl(16, 4) in ("tc", "tcp", "tma", "simple") and A.decode_impl(32, 4) == "simple"
     assert A.decode_impl(16, 16) == "simple"
     # exchange layout: every area aligned, nothing overlaps, rows per rank cover the tokens
