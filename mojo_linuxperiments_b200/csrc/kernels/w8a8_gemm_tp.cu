@@ -69,8 +69,15 @@ __global__ void __launch_bounds__(TP_THREADS, 1)
 w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_constant__ CUtensorMap tmap_a1,
                     const __grid_constant__ CUtensorMap tmap_loc, const __grid_constant__ CUtensorMap tmap_b,
                     const TpGemmParams p) {
+  // Stamps of the trace build (TK_GEMM_TP): 0 start, 1 dependency wait passed, 2 this rank's rows pushed to the peers,
+  // 3 producer met a tile whose rows had not arrived (once per CTA, first time), 4 ... and they were there, 5 first tile's
+  // accumulator complete, 6 last tile stored / scattered, 7 scatter tail: all partial rows have arrived, 8 tail summed,
+  // 63 leaving.  Together they show how much of the exchange hides behind the tensor-core work.
   pdl_launch_dependents();
+  B200_TRACE_INIT();
+  if (threadIdx.x == 0) B200_TRACE(TK_GEMM_TP, TP_START);
   pdl_wait();
+  if (threadIdx.x == 0) B200_TRACE(TK_GEMM_TP, TP_DEPS);
 
   constexpr int A_BYTES = TILE_N * BLOCK_K;
   constexpr int B_BYTES = BN * BLOCK_K;
@@ -135,6 +142,7 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
       const uint64_t pol_w = policy_evict_last();
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
+      bool stamped_wait = false;
       for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
         int m_tile, n_tile;
         tp_tile_coords(p, tile, m_tile, n_tile);
@@ -151,6 +159,7 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
             for (int blk = a >> 7; ok && blk <= (b >> 7); ++blk) {
               const int i = s * p.ag.blk_cap + blk;
               if (ready[i]) continue;
+              if (!stamped_wait) B200_TRACE(TK_GEMM_TP, 3);
               const uint64_t t0 = globaltimer_ns();
               uint32_t spins = 0;
               while (!ready[i]) {
@@ -166,6 +175,7 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
             }
           }
           if (!ok) break;
+          if (!stamped_wait) { B200_TRACE(TK_GEMM_TP, 4); stamped_wait = true; }
           __threadfence_block();
           fence_proxy_async_all();
         }
@@ -227,6 +237,7 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
       tp_tile_coords(p, tile, m_tile, n_tile);
       if (!mbar_wait(tfull_bar(a), aphase, abort_flag, p.status, (ST_TIMEOUT_TMEM_FULL | (3 << 8)), limit)) { ok = false; break; }
       tc_fence_after();
+      if (seg_idx == 0 && threadIdx.x == 64) B200_TRACE(TK_GEMM_TP, 5);
       const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + a * BN;
       const int m = m_tile * TILE_N + q * 32 + lane;
       const bool m_ok = m < p.M;
@@ -380,6 +391,7 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
             }
           }
         }
+        if (ct == 0) B200_TRACE(TK_GEMM_TP, 2);
       }
       if (do_tiles) {
         // ---- watch the arrival flags (sources visited starting with this rank) and mirror them into shared memory ----
@@ -435,6 +447,7 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
 
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) B200_TRACE(TK_GEMM_TP, 6);
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
@@ -452,6 +465,7 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
       if (good && my_rows > 0)
         good = wait_flag_ge(reinterpret_cast<const uint32_t*>(t.data[t.rank] + s.ctr_off) + rs_par, expected, p.status, limit) ? 1 : 0;
       misc_slot[1] = good;
+      B200_TRACE(TK_GEMM_TP, 7);
     }
     __syncthreads();
     if (misc_slot[1]) {
@@ -491,6 +505,7 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
 
   // ------------------------------ last CTA out: advance the epochs ------------------------------
   __syncthreads();
+  if (threadIdx.x == 0 && p.scatter && (p.phase & 2)) B200_TRACE(TK_GEMM_TP, 8);
   if (threadIdx.x == 0) {
     uint32_t* exit_ctr = p.gather ? p.ag.words + 1 : p.rs.words + 1;
     __threadfence();
@@ -510,7 +525,9 @@ w8a8_gemm_tp_kernel(const __grid_constant__ CUtensorMap tmap_a0, const __grid_co
       }
       __threadfence();
     }
+    B200_TRACE(TK_GEMM_TP, TP_EXIT);
   }
+  B200_TRACE_FLUSH(TK_GEMM_TP);
 }
 
 // Ends an epoch of the gather buffer without a consuming GEMM of this file (its readers were other kernels launched
