@@ -27,7 +27,7 @@ def main():
     timing = {}
     for two_hop_min in (0, 1):
         tp.two_hop_min = two_hop_min
-        for M, K in [(1, 512), (3, 1792), (8, 512), (32, 1792), (64, 512), (32, 128)]:
+        for M, K in [(1, 512), (3, 1792), (8, 512), (32, 1792), (32, 512), (64, 512), (32, 128)]:
             g = torch.Generator().manual_seed(100 * rank + M + K)
             xq = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8).cuda()
             sx = (torch.rand(M, generator=g) * 0.01 + 0.001).cuda()
