@@ -38,6 +38,7 @@
 #include "launch.cuh"
 #include "quant_row.cuh"
 #include <cstdlib>
+#include <algorithm>
 
 namespace b200 {
 
@@ -893,14 +894,15 @@ static int resident_clusters_reported(int bn, int s) {
 // tiles x S CTAs (a) fits the SMs (two CTAs each for up to 32 tokens), (b) leaves every CTA at least two k-blocks, and (c) is resident at
 // once according to the occupancy query, with `margin` spare clusters.
 // quant_rows > 0: the launch also carries ceil(quant_rows / S) clusters of quantiser CTAs.
-int decode_pick_splits(int tiles, int kblocks, int num_sms, int bn, int margin, int quant_rows = 0) {
+// min_kb: fewest k-blocks a CTA should keep.
+int decode_pick_splits(int tiles, int kblocks, int num_sms, int bn, int margin, int quant_rows = 0, int min_kb = 2) {
   static int limit_env = -1;
   if (limit_env < 0) { const char* e = std::getenv("B200RT_GEMM_MAX_CTAS"); limit_env = e ? std::atoi(e) : 0; }
   const int limit = limit_env > 0 ? limit_env : num_sms * ctas_per_sm(bn);
   int best = 1;
   for (int s = 2; s <= 8; ++s) {
     const int all = tiles + (quant_rows + s - 1) / s;
-    if (all * s > limit || kblocks < 2 * s) break;
+    if (all * s > limit || kblocks < min_kb * s) break;
     if (all + margin <= resident_clusters(bn, s)) best = s;
   }
   return best;
@@ -945,7 +947,12 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
     if (ar) while (s >= 1 && n_tiles * m_tiles + 1 > resident_clusters(bn, s)) --s;
     if (s >= 1 && (((p.kblocks + s - 1) / s + 3) / 4) * M <= INL_UNITS) inl = true;
   }
-  if (!inl) s = force_splits > 0 ? force_splits : decode_pick_splits(n_tiles * m_tiles, p.kblocks, num_sms, bn, groups > 0 ? -100000 : 1, qp ? M : 0);
+  // With the all-reduce tail every CTA also pushes, polls and sums its slice of the output: a launch of few CTAs (the
+  // o-projection's 1/8 shard has four k-blocks) is bound by that tail, so there a CTA may keep a single k-block.
+  static int ar_min_kb = -1;
+  if (ar_min_kb < 0) { const char* e = std::getenv("B200RT_AR_MIN_KBLOCKS"); ar_min_kb = e ? std::max(1, std::atoi(e)) : 1; }
+  if (!inl) s = force_splits > 0 ? force_splits : decode_pick_splits(n_tiles * m_tiles, p.kblocks, num_sms, bn, groups > 0 ? -100000 : 1, qp ? M : 0,
+                                                                     ar ? ar_min_kb : 2);
   if (s < 1 || s > 8) return -1;
   p.splits = s;
   p.sx = sx; p.sw = sw; p.y = y; p.residual = static_cast<const __nv_bfloat16*>(residual);
