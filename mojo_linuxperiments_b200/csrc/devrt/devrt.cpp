@@ -41,6 +41,12 @@ struct Driver {
   // optional (symmetric segments): sharing an allocation with other processes through a POSIX file descriptor
   CUresult (*MemExportToShareableHandle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType, unsigned long long) = nullptr;
   CUresult (*MemImportFromShareableHandle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType) = nullptr;
+  // optional (multicast object over the blocks of all ranks: one address that NVSwitch fans out to every GPU)
+  CUresult (*MulticastCreate)(CUmemGenericAllocationHandle*, const CUmulticastObjectProp*) = nullptr;
+  CUresult (*MulticastAddDevice)(CUmemGenericAllocationHandle, CUdevice) = nullptr;
+  CUresult (*MulticastBindMem)(CUmemGenericAllocationHandle, size_t, CUmemGenericAllocationHandle, size_t, size_t, unsigned long long) = nullptr;
+  CUresult (*MulticastUnbind)(CUmemGenericAllocationHandle, CUdevice, size_t, size_t) = nullptr;
+  CUresult (*MulticastGetGranularity)(size_t*, const CUmulticastObjectProp*, CUmulticastGranularity_flags) = nullptr;
 };
 
 template <class F>
@@ -88,6 +94,11 @@ Driver& driver() {
   ok &= load(d.lib, d.PointerGetAttribute, "cuPointerGetAttribute");
   load(d.lib, d.MemExportToShareableHandle, "cuMemExportToShareableHandle");
   load(d.lib, d.MemImportFromShareableHandle, "cuMemImportFromShareableHandle");
+  load(d.lib, d.MulticastCreate, "cuMulticastCreate");
+  load(d.lib, d.MulticastAddDevice, "cuMulticastAddDevice");
+  load(d.lib, d.MulticastBindMem, "cuMulticastBindMem");
+  load(d.lib, d.MulticastUnbind, "cuMulticastUnbind");
+  load(d.lib, d.MulticastGetGranularity, "cuMulticastGetGranularity");
   if (ok && d.Init(0) == CUDA_SUCCESS) d.ok = true;
   return d;
 }
@@ -252,7 +263,17 @@ SymmSegment::SymmSegment(int device, size_t bytes, int world, int rank) : device
   prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
   size_t gran = 0;
   if (d.MemGetAllocationGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS || gran == 0) { status_ = DEVRT_NO_MEM; return; }
+  // a block that may later be bound to a multicast object has to be a multiple of that object's granularity too
+  if (d.MulticastGetGranularity) {
+    CUmulticastObjectProp mp{};
+    mp.numDevices = static_cast<unsigned>(world);
+    mp.size = gran;
+    mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+    size_t mg = 0;
+    if (world > 1 && d.MulticastGetGranularity(&mg, &mp, CU_MULTICAST_GRANULARITY_RECOMMENDED) == CUDA_SUCCESS && mg > gran && mg % gran == 0) gran = mg;
+  }
   stride_ = (bytes + gran - 1) / gran * gran;
+  gran_ = gran;
   CUdeviceptr va = 0;
   if (d.MemAddressReserve(&va, stride_ * world, gran, 0, 0) != CUDA_SUCCESS) { status_ = DEVRT_NO_MEM; return; }
   CUmemGenericAllocationHandle h = 0;
@@ -293,10 +314,70 @@ int SymmSegment::map_peer(int peer, int fd) {
   return 0;
 }
 
+int SymmSegment::mc_create() {
+  Driver& d = driver();
+  if (!base_ || mc_handle_ || !d.MulticastCreate) return DEVRT_NO_DRIVER;
+  CtxScope cs(d, device_);
+  if (!cs.pushed) return DEVRT_BAD_ARG;
+  CUmulticastObjectProp mp{};
+  mp.numDevices = static_cast<unsigned>(world_);
+  mp.size = stride_;
+  mp.handleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  CUmemGenericAllocationHandle h = 0;
+  if (d.MulticastCreate(&h, &mp) != CUDA_SUCCESS) return DEVRT_NO_MEM;
+  int fd = -1;
+  if (d.MemExportToShareableHandle(&fd, h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0) != CUDA_SUCCESS) { d.MemRelease(h); return DEVRT_NO_MEM; }
+  mc_handle_ = h;
+  return fd;
+}
+
+int SymmSegment::mc_import(int fd) {
+  Driver& d = driver();
+  if (!base_ || mc_handle_ || fd < 0 || !d.MulticastAddDevice) return DEVRT_BAD_ARG;
+  CtxScope cs(d, device_);
+  if (!cs.pushed) return DEVRT_BAD_ARG;
+  CUmemGenericAllocationHandle h = 0;
+  if (d.MemImportFromShareableHandle(&h, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)), CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) != CUDA_SUCCESS)
+    return DEVRT_NO_MEM;
+  mc_handle_ = h;
+  return 0;
+}
+
+int SymmSegment::mc_add_device() {
+  Driver& d = driver();
+  if (!mc_handle_ || !d.MulticastAddDevice) return DEVRT_BAD_ARG;
+  CtxScope cs(d, device_);
+  CUdevice dev;
+  if (!cs.pushed || d.DeviceGet(&dev, device_) != CUDA_SUCCESS) return DEVRT_BAD_ARG;
+  return d.MulticastAddDevice(mc_handle_, dev) == CUDA_SUCCESS ? 0 : DEVRT_NO_MEM;
+}
+
+int SymmSegment::mc_bind() {
+  Driver& d = driver();
+  if (!mc_handle_ || mc_base_ || !d.MulticastBindMem) return DEVRT_BAD_ARG;
+  CtxScope cs(d, device_);
+  if (!cs.pushed) return DEVRT_BAD_ARG;
+  if (d.MulticastBindMem(mc_handle_, 0, handles_[rank_], 0, stride_, 0) != CUDA_SUCCESS) return DEVRT_NO_MEM;
+  mc_bound_ = true;
+  CUdeviceptr va = 0;
+  if (d.MemAddressReserve(&va, stride_, gran_, 0, 0) != CUDA_SUCCESS) return DEVRT_NO_MEM;
+  if (d.MemMap(va, stride_, 0, mc_handle_, 0) != CUDA_SUCCESS) { d.MemAddressFree(va, stride_); return DEVRT_NO_MEM; }
+  CUmemAccessDesc acc{};
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = device_;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  if (d.MemSetAccess(va, stride_, &acc, 1) != CUDA_SUCCESS) { d.MemUnmap(va, stride_); d.MemAddressFree(va, stride_); return DEVRT_NO_MEM; }
+  mc_base_ = va;
+  return 0;
+}
+
 SymmSegment::~SymmSegment() {
   if (!base_) return;
   Driver& d = driver();
   CtxScope cs(d, device_);
+  if (mc_base_) { d.MemUnmap(mc_base_, stride_); d.MemAddressFree(mc_base_, stride_); }
+  if (mc_bound_ && d.MulticastUnbind) { CUdevice dev; if (d.DeviceGet(&dev, device_) == CUDA_SUCCESS) d.MulticastUnbind(mc_handle_, dev, 0, stride_); }
+  if (mc_handle_) d.MemRelease(mc_handle_);
   for (int r = 0; r < world_; ++r) {
     if (mapped_[r]) d.MemUnmap(base_ + stride_ * static_cast<size_t>(r), stride_);
     if (handles_[r]) d.MemRelease(handles_[r]);
@@ -372,4 +453,11 @@ unsigned long long devrt_symm_base(void* s) { return static_cast<SymmSegment*>(s
 unsigned long long devrt_symm_stride(void* s) { return static_cast<SymmSegment*>(s)->stride(); }
 unsigned long long devrt_symm_peer_ptr(void* s, int r) { return static_cast<SymmSegment*>(s)->peer_ptr(r); }
 int devrt_symm_mapped(void* s, int r) { return static_cast<SymmSegment*>(s)->mapped(r) ? 1 : 0; }
+// multicast object over all ranks' blocks: rank 0 creates (-> descriptor for the others), the others import, everybody
+// adds its device, (barrier), everybody binds its block and maps the object, (barrier), mc_ptr() addresses all copies
+int devrt_symm_mc_create(void* s) { return static_cast<SymmSegment*>(s)->mc_create(); }
+int devrt_symm_mc_import(void* s, int fd) { return static_cast<SymmSegment*>(s)->mc_import(fd); }
+int devrt_symm_mc_add_device(void* s) { return static_cast<SymmSegment*>(s)->mc_add_device(); }
+int devrt_symm_mc_bind(void* s) { return static_cast<SymmSegment*>(s)->mc_bind(); }
+unsigned long long devrt_symm_mc_ptr(void* s) { return static_cast<SymmSegment*>(s)->mc_ptr(); }
 }

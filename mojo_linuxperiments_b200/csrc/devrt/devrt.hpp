@@ -114,13 +114,23 @@ class SymmSegment {
   size_t stride() const { return stride_; }
   uint64_t peer_ptr(int r) const { return base_ + stride_ * static_cast<size_t>(r); }
   bool mapped(int r) const { return r >= 0 && r < world_ && mapped_[r]; }
+  // Multicast object (NVSwitch fans a store to mc_ptr() + off out to byte `off` of every rank's block; multimem loads
+  // reduce over them).  Order across the ranks: rank 0 mc_create() -> descriptor; others mc_import(fd); all
+  // mc_add_device(); barrier; all mc_bind(); barrier.  Each returns 0 (mc_create: the descriptor) or a negative status.
+  int mc_create();
+  int mc_import(int fd);
+  int mc_add_device();
+  int mc_bind();
+  uint64_t mc_ptr() const { return mc_base_; }
  private:
   bool map_at(int r, uint64_t handle);
   uint64_t base_ = 0;
-  size_t stride_ = 0;
+  size_t stride_ = 0, gran_ = 0;
   std::vector<uint64_t> handles_;
   std::vector<bool> mapped_;
   int device_ = -1, world_ = 0, rank_ = 0, fd_ = -1, status_ = 0;
+  uint64_t mc_handle_ = 0, mc_base_ = 0;
+  bool mc_bound_ = false;
 };
 
 }  // namespace devrt

@@ -43,6 +43,9 @@ def lib() -> ctypes.CDLL:
         "devrt_symm_export_fd": (c_int, [c_void_p]), "devrt_symm_map_peer": (c_int, [c_void_p, c_int, c_int]),
         "devrt_symm_base": (U, [c_void_p]), "devrt_symm_stride": (U, [c_void_p]),
         "devrt_symm_peer_ptr": (U, [c_void_p, c_int]), "devrt_symm_mapped": (c_int, [c_void_p, c_int]),
+        "devrt_symm_mc_create": (c_int, [c_void_p]), "devrt_symm_mc_import": (c_int, [c_void_p, c_int]),
+        "devrt_symm_mc_add_device": (c_int, [c_void_p]), "devrt_symm_mc_bind": (c_int, [c_void_p]),
+        "devrt_symm_mc_ptr": (U, [c_void_p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(L, name)
@@ -185,6 +188,15 @@ class SymmSegment:
     @property
     def stride(self) -> int: return lib().devrt_symm_stride(self._h)
     def peer_ptr(self, r: int) -> int: return lib().devrt_symm_peer_ptr(self._h, r)
+
+    # Multicast object over all ranks' blocks.  Order across ranks: rank 0 ``mc_create()`` (returns a descriptor for the
+    # others) / the others ``mc_import(fd)``; all ``mc_add_device()``; barrier; all ``mc_bind()``; barrier; ``mc_ptr``.
+    def mc_create(self) -> int: return lib().devrt_symm_mc_create(self._h)
+    def mc_import(self, fd: int) -> int: return lib().devrt_symm_mc_import(self._h, fd)
+    def mc_add_device(self) -> int: return lib().devrt_symm_mc_add_device(self._h)
+    def mc_bind(self) -> int: return lib().devrt_symm_mc_bind(self._h)
+    @property
+    def mc_ptr(self) -> int: return lib().devrt_symm_mc_ptr(self._h)
 
     def local_tensor(self):
         """The local block as a uint8 torch tensor (no copy; the segment must outlive it)."""

@@ -10,9 +10,10 @@ package's own.  Allocation and mapping have two backends, chosen by ``B200RT_SYM
 * ``torch`` (default): ``torch.distributed._symmetric_memory`` - peer pointers and, where the fabric has it, the NVLS
   multicast pointer the ``multimem`` kernels use.
 * ``native``: this package's device runtime (``devrt.SymmSegment``: a virtual-memory block per rank, exported as a
-  POSIX descriptor, handed to the peers over unix sockets and mapped by each of them).  Peer pointers only - no
-  multicast object is bound, so the kernels take their peer-store paths; a rank that dies therefore leaves no
-  multicast binding behind.
+  POSIX descriptor, handed to the peers over unix sockets and mapped by each of them).  Peer pointers only by
+  default, so the kernels take their peer-store paths and a rank that dies leaves no multicast binding behind;
+  ``B200RT_SYMM_MC=1`` also creates a multicast object over the blocks (``cuMulticastCreate`` on rank 0, every rank
+  adds its device and binds its block) and maps it, which gives the ``multimem`` kernels their pointer.
 """
 from __future__ import annotations
 
@@ -96,7 +97,35 @@ class SymmetricHeap:
         self.block = self.segment.local_tensor()[:total]
         self.block.zero_()
         self.handle = None
-        return [self.segment.peer_ptr(r) for r in range(self.world)], 0
+        mc = 0
+        if os.environ.get("B200RT_SYMM_MC", "0") not in ("0", "") and self.world > 1:
+            mc = self._native_multicast(gather)
+        return [self.segment.peer_ptr(r) for r in range(self.world)], mc
+
+    def _native_multicast(self, gather) -> int:
+        """Bind every rank's block to one multicast object and map it; every rank learns of a failure on any rank."""
+        from .. import devrt
+        seg = self.segment
+
+        def agree(rc: int, what: str):
+            codes = [None] * self.world
+            dist.all_gather_object(codes, rc, group=self.group)
+            if any(c < 0 for c in codes):
+                raise RuntimeError(f"multicast object: {what} failed with status {codes} (one entry per rank)")
+
+        own = seg.mc_create() if self.rank == 0 else os.open(os.devnull, os.O_RDONLY)
+        agree(min(own, 0), "cuMulticastCreate / export on rank 0")
+        fds = devrt.exchange_fds(own, self.rank, self.world, gather)
+        try:
+            rc = seg.mc_import(fds[0]) if self.rank != 0 else 0
+        finally:
+            for fd in fds.values():
+                os.close(fd)
+            os.close(own)
+        agree(rc, "import of the multicast handle")
+        agree(seg.mc_add_device(), "cuMulticastAddDevice")          # also the barrier: every device is in before any bind
+        agree(seg.mc_bind(), "cuMulticastBindMem / map")
+        return seg.mc_ptr
 
     @property
     def has_multicast(self) -> bool:

@@ -74,6 +74,24 @@ CUresult cuMemExportToShareableHandle(void* out, CUmemGenericAllocationHandle h,
   *(int*)out = fd;
   return 0;
 }
+/* Multicast objects: a handle in its own number range; devices added and blocks bound are only counted. */
+typedef struct { unsigned numDevices; size_t size; unsigned long long handleTypes, flags; } FakeMcProp;
+static int mc_added = 0, mc_bound = 0;
+CUresult cuMulticastGetGranularity(size_t* g, const void* prop, int opt) { (void)prop; (void)opt; *g = 4u << 20; return 0; }
+CUresult cuMulticastCreate(CUmemGenericAllocationHandle* h, const void* prop) {
+  const FakeMcProp* p = (const FakeMcProp*)prop;
+  if (flag("FAKE_CUDA_NO_MULTICAST") || p->numDevices < 2 || (p->size % (4u << 20))) return 801;
+  *h = 5000 + p->numDevices;
+  return 0;
+}
+CUresult cuMulticastAddDevice(CUmemGenericAllocationHandle h, CUdevice d) { if (h < 5000 || d < 0 || d >= ndev()) return 1; ++mc_added; return 0; }
+CUresult cuMulticastBindMem(CUmemGenericAllocationHandle mc, size_t mo, CUmemGenericAllocationHandle mem, size_t o, size_t size, unsigned long long fl) {
+  (void)mo; (void)o; (void)fl;
+  if (mc < 5000 || mem < 1000 || mem >= 5000 || (size % (4u << 20)) || mc_added < (int)(mc - 5000)) return 1;   /* every device first */
+  ++mc_bound;
+  return 0;
+}
+CUresult cuMulticastUnbind(CUmemGenericAllocationHandle mc, CUdevice d, size_t mo, size_t size) { (void)mc; (void)d; (void)mo; (void)size; --mc_bound; return 0; }
 CUresult cuMemImportFromShareableHandle(CUmemGenericAllocationHandle* h, void* os_handle, int type) {
   if (type != 1) return 801;
   int fd = (int)(long)os_handle;
@@ -83,7 +101,7 @@ CUresult cuMemImportFromShareableHandle(CUmemGenericAllocationHandle* h, void* o
 CUresult cuMemMap(CUdeviceptr p, size_t size, size_t off, CUmemGenericAllocationHandle h, unsigned long long fl) {
   (void)off; (void)fl;
   if (nmaps >= 64) return 2;
-  maps[nmaps].va = p; maps[nmaps].size = size; maps[nmaps].device = (int)(h - 1000); ++nmaps;
+  maps[nmaps].va = p; maps[nmaps].size = size; maps[nmaps].device = h >= 5000 ? -2 : (int)(h - 1000); ++nmaps;
   return 0;
 }
 CUresult cuMemUnmap(CUdeviceptr p, size_t size) {

@@ -146,3 +146,25 @@ def test_symmetric_segment_refusals(fake_driver):
     for args in [(0, 0, 2, 0), (0, 1 << 20, 2, 2), (0, 1 << 20, 0, 0), (0, 1 << 20, 65, 0)]:
         with pytest.raises(RuntimeError):
             D.SymmSegment(*args)
+
+
+def test_symmetric_segment_multicast_object_on_fake_driver(fake_driver):
+    """Order of the multicast calls: create on rank 0, import elsewhere, every device added before any block is bound."""
+    fake_driver.setenv("FAKE_CUDA_DEVICES", "2")
+    segs = [D.SymmSegment(r, 1 << 20, 2, r) for r in range(2)]
+    assert all(s.stride == 4 << 20 for s in segs)            # rounded to the multicast granularity of the fake (4 MiB)
+    assert segs[1].mc_bind() != 0 and segs[1].mc_add_device() != 0      # nothing to bind / add to yet
+    fd = segs[0].mc_create()
+    assert fd >= 0 and segs[0].mc_create() < 0                           # one object per segment
+    assert segs[1].mc_import(fd) == 0
+    os.close(fd)
+    assert segs[0].mc_add_device() == 0
+    assert segs[0].mc_bind() != 0                                        # the other device has not been added
+    assert segs[1].mc_add_device() == 0
+    assert segs[0].mc_bind() == 0 and segs[1].mc_bind() == 0
+    assert segs[0].mc_ptr != 0 and segs[0].mc_ptr != segs[0].base and segs[0].mc_bind() != 0
+    [s.close() for s in segs]
+    fake_driver.setenv("FAKE_CUDA_NO_MULTICAST", "1")
+    s = D.SymmSegment(0, 1 << 20, 2, 0)
+    assert s.mc_create() < 0 and s.mc_ptr == 0
+    s.close()

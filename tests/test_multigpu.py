@@ -81,13 +81,15 @@ def test_fused_gemm_allreduce_one_trip_and_two_hop(nproc):
 
 @pytest.mark.gpu
 @pytest.mark.multigpu(2)
+@pytest.mark.parametrize("multicast", ["0", "1"])
 @pytest.mark.parametrize("script", ["mp_peer_allreduce.py", "mp_fused_ar.py"])
-def test_native_symmetric_heap_backend(script):
+def test_native_symmetric_heap_backend(script, multicast):
     """The same peer kernels over this package's own heap (virtual-memory blocks shared as POSIX descriptors and
-    mapped by every rank) instead of torch's symmetric memory: peer pointers only, no multicast object."""
+    mapped by every rank) instead of torch's symmetric memory: with peer pointers only, and with its own multicast
+    object bound over the blocks (the multimem kernels then run through it)."""
     if NGPU < 2:
         pytest.skip(f"needs 2 GPUs, found {NGPU}")
-    p = _run(script, 2, env={"B200RT_SYMM": "native"})
+    p = _run(script, 2, env={"B200RT_SYMM": "native", "B200RT_SYMM_MC": multicast})
     assert p.returncode == 0, p.stdout[-3000:] + p.stderr[-3000:]
     assert "FAILURES 0" in p.stdout
-    assert "symm backend native" in p.stdout
+    assert f"symm backend native multicast {multicast == '1'}" in p.stdout
