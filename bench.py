@@ -42,7 +42,7 @@ def parse():
     ap.add_argument("--skip-extra", action="store_true", help="only the headline number (no bs-1 / TTFT / e2e runs)")
     ap.add_argument("--skip-baseline", action="store_true", help="do not run the stock-PyTorch comparison arm after the product's own measurement")
     ap.add_argument("--skip-self-check", action="store_true", help="do not decode the miniature model against the oracle before timing")
-    ap.add_argument("--metrics-log", default="gpurun_out/bench_metrics.jsonl",
+    ap.add_argument("--metrics-log", default=os.path.join(tempfile.gettempdir(), "b200rt_bench_metrics.jsonl"),
                     help="append the result record to this JSON-lines file (empty: do not)")
     ap.add_argument("--layers", type=int, default=0, help="smoke runs only: override the layer count (the line is then marked invalid)")
     return ap.parse_args()
@@ -435,7 +435,7 @@ def run(args):
             rec = RECORDED_BASELINE_TOK_S.get(world)
             if rec and args.model == "llama3-8b" and B == 32:
                 result["vs_baseline"] = value / rec
-                result["baseline"] = {"impl": "torch_baseline, recorded earlier on this pool (BASELINE.md)",
+                result["baseline"] = {"impl": "torch_baseline, recorded earlier on this pool",
                                       "decode_tokens_per_sec_bs32": rec, **({"live_run": base} if base else {})}
             elif base:
                 result["baseline"] = base
