@@ -971,6 +971,11 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
     while (s >= 1 && n_tiles * m_tiles + ((qp && !inl) ? (M + s - 1) / s : 0) + 1 > resident_clusters(bn, s)) --s;
     if (s < 1) return -20;
     p.splits = s;
+    // The two-hop tail pays for its second NVLink trip by spreading the owner's work over many CTAs; a launch split
+    // into fewer CTAs than this per tile keeps the one-trip tail (B200RT_AR_TWO_HOP_MIN_SPLITS, default 1: no limit).
+    static int th_min_s = -1;
+    if (th_min_s < 0) { const char* e = std::getenv("B200RT_AR_TWO_HOP_MIN_SPLITS"); th_min_s = e ? std::max(1, std::atoi(e)) : 1; }
+    if (s < th_min_s) p.ar.two_hop = 0;
     p.limit_ns = static_cast<unsigned long long>(ar->limit_ms > 0 ? ar->limit_ms : 2000) * 1000000ull;
   }
   static int async_env = -1;
