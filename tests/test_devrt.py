@@ -168,3 +168,44 @@ def test_symmetric_segment_multicast_object_on_fake_driver(fake_driver):
     s = D.SymmSegment(0, 1 << 20, 2, 0)
     assert s.mc_create() < 0 and s.mc_ptr == 0
     s.close()
+
+
+def _fd_exchange_worker(rank, world, q_names, q_out):
+    """One process of the descriptor exchange: owns an anonymous file, hands it to the peers, reads theirs."""
+    import os as _os
+    from mojo_linuxperiments_b200 import devrt as _D
+    mine = _os.memfd_create(f"rank{rank}")
+    _os.write(mine, f"from-{rank}".encode())
+
+    def gather(name):
+        q_names.put((rank, name))
+        names = {}
+        while len(names) < world:            # every process reads the full set (each entry is put back for the others)
+            k, v = q_names.get()
+            names[k] = v
+            q_names.put((k, v))
+        return [names[i] for i in range(world)]
+
+    got = _D.exchange_fds(mine, rank, world, gather, timeout_s=20)
+    seen = {}
+    for peer, fd in got.items():
+        seen[peer] = _os.pread(fd, 64, 0).decode()
+        _os.close(fd)
+    q_out.put((rank, seen))
+
+
+def test_descriptors_cross_real_processes():
+    """SCM_RIGHTS over abstract unix sockets between separate processes: each receives working descriptors of the
+    others' anonymous files (what carries the exported HBM handles between rank processes)."""
+    import multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    world = 3
+    q_names, q_out = ctx.Queue(), ctx.Queue()
+    ps = [ctx.Process(target=_fd_exchange_worker, args=(r, world, q_names, q_out)) for r in range(world)]
+    [p.start() for p in ps]
+    results = [q_out.get(timeout=60) for _ in range(world)]
+    [p.join(30) for p in ps]
+    assert all(p.exitcode == 0 for p in ps)
+    reads = {r: v for r, v in results if isinstance(v, dict)}
+    for r in range(world):
+        assert reads[r] == {p: f"from-{p}" for p in range(world) if p != r}
