@@ -153,9 +153,9 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   // [ring 2 x 32K][P NB x 4K][Q 4K][exchange floats][barriers]
   uint8_t* pP = smem + 2 * ADC_TILE;
   uint8_t* pQ = pP + NB * ADC_P_TILE;
-  float* xch = reinterpret_cast<float*>(pQ + ADC_Q_TILE);          // [2][4 warps][8]: per-warp max, then sum
-  float* ml_s = xch + 64;                                          // [8][2]: final (m, l) per head
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ml_s + 16);
+  float* xch = reinterpret_cast<float*>(pQ + ADC_Q_TILE);          // [2][4 warps][16]: per-warp max, then sum
+  float* ml_s = xch + 128;                                         // [16][2]: final (m, l) per head
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ml_s + 32);
   enum { B_FULL = 0, B_EMPTY = 2, B_SFULL = 4, B_PFULL = 4 + NB, B_OFULL = 4 + 2 * NB, B_XCH = 5 + 2 * NB, B_COUNT = 6 + 2 * NB };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + B_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -164,8 +164,8 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
   // fused form only: the finished (bf16-rounded) output rows of this CTA's heads, v and the scores of the new token
   float* row_s = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(page_s + NB * 8) + 15) & ~uintptr_t(15));   // [G][128]
   float* vnew_s = row_s + G * ADC_D;               // [128]
-  float* snew_s = vnew_s + ADC_D;                  // [8]
-  float* amax_s = snew_s + 8;                      // [8]
+  float* snew_s = vnew_s + ADC_D;                  // [16]
+  float* amax_s = snew_s + 16;                     // [8]
   float* zone = amax_s + 8;                        // cluster merge: [splits][G][ADC_ZONE_ROW] (G <= 4 only)
   const uint32_t sRing = smem_u32(smem);
   const uint32_t sP = smem_u32(pP), sQ = smem_u32(pQ);
@@ -428,7 +428,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
     }
     if (lane == 0) {
 #pragma unroll
-      for (int g = 0; g < G; ++g) xch[wi * 8 + g] = mx[g];
+      for (int g = 0; g < G; ++g) xch[wi * 16 + g] = mx[g];
       mbar_arrive(bar(B_XCH));
     }
     if (ok && !mbar_wait(bar(B_XCH), 0, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (5 << 8)), limit)) ok = false;
@@ -436,7 +436,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
     float m[G], sum[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) {
-      m[g] = fmaxf(fmaxf(xch[g], xch[8 + g]), fmaxf(xch[16 + g], xch[24 + g]));
+      m[g] = fmaxf(fmaxf(xch[g], xch[16 + g]), fmaxf(xch[32 + g], xch[48 + g]));
       sum[g] = 0.f;
     }
     // ---- probabilities with the final maximum -> bf16 -> P tiles (K-major rows = heads, swizzled) ----
@@ -465,13 +465,13 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
     }
     if (lane == 0) {
 #pragma unroll
-      for (int g = 0; g < G; ++g) xch[32 + wi * 8 + g] = sum[g];
+      for (int g = 0; g < G; ++g) xch[64 + wi * 16 + g] = sum[g];
       mbar_arrive(bar(B_XCH));
     }
     if (ok && !mbar_wait(bar(B_XCH), 1, abort_flag, p.status, (ST_TIMEOUT_PEER_FLAG | (5 << 8)), limit)) ok = false;
     float l[G];
 #pragma unroll
-    for (int g = 0; g < G; ++g) l[g] = xch[32 + g] + xch[40 + g] + xch[48 + g] + xch[56 + g];
+    for (int g = 0; g < G; ++g) l[g] = xch[64 + g] + xch[80 + g] + xch[96 + g] + xch[112 + g];
     // ---- output: thread <-> dim ----
     float o[G];
 #pragma unroll
@@ -619,10 +619,11 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
     // ---- epilogue: block-128 Hadamard rotation (one head = one block) + per-token int8 of the output row ----
     __syncthreads();                                   // row_s of all heads of this CTA is complete
     constexpr int NW = ADC_THREADS / 32;
-    float v[2][4];
+    constexpr int GI = (G + NW - 1) / NW;               // heads per warp in the rotation (16 heads on 6 warps: 3)
+    float v[GI < 2 ? 2 : GI][4];
     float am = 0.f;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < (GI < 2 ? 2 : GI); ++i) {
       const int g = warp + i * NW;
       if (g < G) {
         const float4 x = *reinterpret_cast<const float4*>(row_s + g * ADC_D + 4 * lane);
@@ -641,7 +642,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
       for (int w = 0; w < NW; ++w) row_amax = fmaxf(row_amax, amax_s[w]);
       const float scale = quant_scale_from_amax(row_amax), inv = quant_inv_scale(scale);
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < (GI < 2 ? 2 : GI); ++i) {
         const int g = warp + i * NW;
         if (g < G) *reinterpret_cast<uint32_t*>(p.f.xq + static_cast<size_t>(b) * p.f.ldq + g * ADC_D + 4 * lane) = quant_pack4(v[i], inv);
       }
@@ -649,7 +650,7 @@ attn_decode_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const DecodeT
     } else {
       // the token's heads are spread over hkv CTAs: park the rotated rows, the last CTA to arrive quantises the token
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
+      for (int i = 0; i < (GI < 2 ? 2 : GI); ++i) {
         const int g = warp + i * NW;
         if (g < G)
           *reinterpret_cast<float4*>(p.f.rot_scratch + (static_cast<size_t>(b) * p.hq + kvh * G + g) * ADC_D + 4 * lane) =
@@ -1074,8 +1075,8 @@ typedef CUresult (*EncodeTiledFn3)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 template <int G, bool FUSED, int NB>
 static int launch_adc(const CUtensorMap& tm, const DecodeTcParams& p, dim3 grid, cudaStream_t stream) {
   // rows of the CTA's heads, the new token's value row, a few scalars, and (groups of up to four heads) the merge zone
-  constexpr int SMEM = 2 * ADC_TILE + NB * ADC_P_TILE + ADC_Q_TILE + (64 + 16) * 4 + (6 + 2 * NB) * 8 + 64 + NB * 8 * 4 + 1024 +
-                       (G * ADC_D + ADC_D + 16) * 4 + 16 +
+  constexpr int SMEM = 2 * ADC_TILE + NB * ADC_P_TILE + ADC_Q_TILE + (128 + 32) * 4 + (6 + 2 * NB) * 8 + 64 + NB * 8 * 4 + 1024 +
+                       (G * ADC_D + ADC_D + 32) * 4 + 16 +
                        ((G <= ADC_ZONE_MAX_G && NB <= ADC_NB) ? ADC_ZONE_MAX_SPLITS * G * ADC_ZONE_ROW * 4 : 0);
   static_assert(2 * (SMEM + 1024) <= 228 * 1024, "two CTAs per SM");
   static bool configured = false;
@@ -1132,7 +1133,8 @@ static int attn_decode_tc_common(const void* q, const void* cache, int num_pages
   if (B <= 0) return 0;
   if (page_size != 16 || (hq % hkv)) return -3;
   const int G = hq / hkv;
-  if (G != 1 && G != 2 && G != 4 && G != 8) return -3;
+  if (G != 1 && G != 2 && G != 4 && G != 8 && G != 16) return -3;
+  if (G == 16 && persistent) return -3;               // sixteen heads per KV head: the one-item kernel only
   if (splits < 1) splits = 1;
   if (reinterpret_cast<uintptr_t>(cache) & 127) return -2;
   if (!fuse && (reinterpret_cast<uintptr_t>(q) & 15)) return -2;
@@ -1181,7 +1183,7 @@ static int attn_decode_tc_common(const void* q, const void* cache, int num_pages
   p.early_tiles = early_env;
   // blocks a CTA may meet: the page-table row bounds the sequence length
   const int blocks_max = (max_pages * 16 + 127) / 128, per_max = (blocks_max + splits - 1) / splits;
-  const bool long_form = fuse && !persistent && per_max > ADC_NB;        // whole (or half) sequences per CTA: no merge zone
+  const bool long_form = fuse && !persistent && per_max > ADC_NB && G <= 8;   // (sixteen heads: the scores of nine blocks would not fit the registers)        // whole (or half) sequences per CTA: no merge zone
   if (per_max > (long_form ? ADC_NB_LONG : ADC_NB)) return -1;
   p.cluster_merge = (!persistent && !long_form && cluster_env && G <= ADC_ZONE_MAX_G && splits >= 2 && splits <= ADC_ZONE_MAX_SPLITS &&
                      static_cast<long long>(B) * hkv * splits <= 2ll * sm_count) ? 1 : 0;
@@ -1209,14 +1211,16 @@ static int attn_decode_tc_common(const void* q, const void* cache, int num_pages
       case 1: return launch_adc<1, true, ADC_NB>(tm, p, grid, stream);
       case 2: return launch_adc<2, true, ADC_NB>(tm, p, grid, stream);
       case 4: return launch_adc<4, true, ADC_NB>(tm, p, grid, stream);
-      default: return launch_adc<8, true, ADC_NB>(tm, p, grid, stream);
+      case 8: return launch_adc<8, true, ADC_NB>(tm, p, grid, stream);
+      default: return launch_adc<16, true, ADC_NB>(tm, p, grid, stream);
     }
   }
   switch (G) {
     case 1: return launch_adc<1, false, ADC_NB>(tm, p, grid, stream);
     case 2: return launch_adc<2, false, ADC_NB>(tm, p, grid, stream);
     case 4: return launch_adc<4, false, ADC_NB>(tm, p, grid, stream);
-    default: return launch_adc<8, false, ADC_NB>(tm, p, grid, stream);
+    case 8: return launch_adc<8, false, ADC_NB>(tm, p, grid, stream);
+    default: return launch_adc<16, false, ADC_NB>(tm, p, grid, stream);
   }
 }
 
@@ -1249,7 +1253,7 @@ extern "C" int b200_attn_decode_fused(const void* qkv, long long ld_qkv, const i
 
 // CTAs of the tensor-core decode attention (group size 4, plain form) one SM holds at once.
 extern "C" int b200_attn_decode_tc_ctas_per_sm() {
-  constexpr int SMEM = 2 * ADC_TILE + ADC_NB * ADC_P_TILE + ADC_Q_TILE + (64 + 16) * 4 + (6 + 2 * ADC_NB) * 8 + 64 + ADC_NB * 8 * 4 + 1024;
+  constexpr int SMEM = 2 * ADC_TILE + ADC_NB * ADC_P_TILE + ADC_Q_TILE + (128 + 32) * 4 + (6 + 2 * ADC_NB) * 8 + 64 + ADC_NB * 8 * 4 + 1024;
   cudaFuncSetAttribute(attn_decode_tc_kernel<4, false, ADC_NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
   cudaFuncSetAttribute(attn_decode_tc_kernel<4, false, ADC_NB>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   int blocks = 0;

@@ -157,7 +157,8 @@ class Decoder:
         impl = A.decode_impl(cache.page_size, self.hq // self.hkv)
         if impl in ("tc", "tcp"):
             splits = A.pick_decode_splits_tc(M, self.hkv, kv.page_table.shape[1] * cache.page_size,
-                                             fused=impl == "tc" and self.fused_attention and self.long_attention)
+                                             fused=(impl == "tc" and self.fused_attention and self.long_attention
+                                                    and self.hq // self.hkv <= 8))
         else:
             splits = A.pick_decode_splits(M, self.hkv, max_len)
         fused = impl == "tc" and self.fused_attention

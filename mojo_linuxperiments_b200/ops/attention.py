@@ -130,7 +130,7 @@ def decode_impl(page_size: int, group: int) -> str:
     """Which decode-attention kernel "auto" means: the tcgen05 one where it applies (B200RT_ATTN=tma|simple overrides)."""
     import os
     want = os.environ.get("B200RT_ATTN", "tc")
-    if page_size == 16 and group in (1, 2, 4, 8):
+    if page_size == 16 and group in (1, 2, 4, 8, 16):
         return want if want in ("tc", "tcp", "tma", "simple") else "tc"
     return "simple"
 
@@ -173,7 +173,7 @@ def attn_decode(q: torch.Tensor, cache: PagedKVCache, page_table: torch.Tensor, 
                 out: torch.Tensor | None = None, impl: str = "auto") -> torch.Tensor:
     """q [B, hq, 128] against the first seq_lens[b] cached tokens of sequence b.
 
-    impl "tc" (page size 16, group size 1/2/4/8): tcgen05 MMAs for Q.K^T and P.V, scores in TMEM, pages by TMA
+    impl "tc" (page size 16, group size 1/2/4/8/16): tcgen05 MMAs for Q.K^T and P.V, scores in TMEM, pages by TMA
     (raises ``splits`` to what the longest representable sequence needs); "tcp": the same as a persistent grid whose
     producer runs ahead into the next work item; "tma": TMA-fed ring with CUDA-core dot
     products; "simple": the general kernel; "auto" picks the first that applies."""
@@ -221,15 +221,16 @@ def attn_decode_fused(qkv: torch.Tensor, positions: torch.Tensor, cos: torch.Ten
 
     qkv bf16 [B, (hq + 2 hkv) * 128]: the new token's raw projections; ``positions[b]`` is where it goes in the cache and
     ``seq_lens[b]`` counts it.  Returns ``(xq int8 [B, hq*128], sx fp32 [B], out bf16 [B, hq, 128] or None)``; with
-    ``quantize=False`` only ``out``.  Needs page size 16 and a group size of 1/2/4/8 (the tcgen05 kernel).
+    ``quantize=False`` only ``out``.  Needs page size 16 and a group size of 1/2/4/8/16 (the tcgen05 kernel).
     ``next_weights``: a constant tensor the following kernel streams (the o-projection's int8 weights); the kernel's CTAs
     ask for it to be brought into L2 meanwhile."""
     B = qkv.shape[0]
     d = HEAD_DIM
     assert qkv.dtype == torch.bfloat16 and qkv.stride(1) == 1 and qkv.shape[1] == (hq + 2 * hkv) * d
     assert positions.dtype == torch.int32 and page_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
-    assert cache.page_size == 16 and cache.kv_heads == hkv and hq // hkv in (1, 2, 4, 8)
-    splits = max(splits, tc_min_splits(page_table.shape[1] * cache.page_size, fused=True))
+    assert cache.page_size == 16 and cache.kv_heads == hkv and hq // hkv in (1, 2, 4, 8, 16)
+    # nine blocks per CTA only up to eight heads per KV head (the scores stay in registers)
+    splits = max(splits, tc_min_splits(page_table.shape[1] * cache.page_size, fused=hq // hkv <= 8))
     if scratch is None or scratch.splits != splits:
         scratch = DecodeAttnScratch(B, hq, hkv, splits, qkv.device)
     out = torch.empty((B, hq, d), dtype=torch.bfloat16, device=qkv.device) if (want_out or not quantize) else None

@@ -111,8 +111,8 @@ def test_attn_prefill_reads_strided_qkv():
 @pytest.mark.parametrize("impl", ["simple", "tma", "tc", "tcp"])
 def test_attn_decode_paged(hq, hkv, splits, impl):
     from mojo_linuxperiments_b200.ops import attention as A
-    if impl in ("tma", "tc", "tcp") and hq // hkv == 16:
-        pytest.skip("the TMA-fed forms cover group sizes up to 8")
+    if impl in ("tma", "tcp") and hq // hkv == 16:
+        pytest.skip("these forms cover group sizes up to 8 (the one-item tcgen05 kernel takes 16)")
     ps = 16
     lens = [1, 17, 300, 1280, 64]
     B = len(lens)
@@ -203,7 +203,8 @@ def test_attn_decode_clamps_lengths_beyond_the_page_table_row(impl):
     assert torch.equal(ok, over)                             # the over-long sequence was read as its 128 admitted tokens
 
 
-@pytest.mark.parametrize("hq,hkv,qk_norm", [(32, 8, False), (4, 1, False), (8, 1, True), (8, 4, True), (2, 2, False)])
+@pytest.mark.parametrize("hq,hkv,qk_norm", [(32, 8, False), (4, 1, False), (8, 1, True), (8, 4, True), (2, 2, False),
+                                            (16, 1, True), (32, 2, False)])
 @pytest.mark.parametrize("splits,longest", [(1, 1280), (4, 1280), (1, 1150), (2, 1025)])
 def test_attn_decode_fused_matches_the_three_kernels_it_replaces(hq, hkv, qk_norm, splits, longest):
     """rope_kv_write + attn_decode + act_quant in one launch: same cache contents, same attention output (against the
