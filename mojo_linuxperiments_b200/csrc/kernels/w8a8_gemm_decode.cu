@@ -918,7 +918,11 @@ static int decode_gemm_impl(const void* xq, const float* sx, const void* wq, con
                             int num_sms, int force_splits, const ArTail* ar, cudaStream_t stream,
                             int groups = 0, const int* grp_offsets = nullptr, const int* grp_counts = nullptr,
                             int x_rows = 0, const QuantProlog* qp = nullptr) {
-  if (M <= 0 || M > SWAP_MAX_M || N <= 0 || K <= 0 || (K % 16) != 0) return -1;
+  // Plain calls may bring several token tiles of 64 (one grid layer each; every layer streams the weights again, so this
+  // is for narrow outputs such as a router); the grouped, fused-prologue and all-reduce forms take one tile.
+  constexpr int MULTI_TILE_MAX_M = 4 * SWAP_MAX_M;
+  if (M <= 0 || N <= 0 || K <= 0 || (K % 16) != 0) return -1;
+  if (M > ((groups > 0 || qp || ar) ? SWAP_MAX_M : MULTI_TILE_MAX_M)) return -1;
   if (qp) {
     // the quantiser CTAs park a row as floats in the pipeline's stage memory and work in whole 128-blocks
     if (groups > 0 || force_splits > 0 || (K % 128) || K * 4 > 80 * 1024 || qp->mode < QR_PLAIN || qp->mode > QR_SWIGLU) return -1;

@@ -61,6 +61,10 @@ def w8a8_gemm(xq: torch.Tensor, sx: torch.Tensor, wq: torch.Tensor, sw: torch.Te
     w = workspace or default_workspace(xq.device)
     n_tiles = (N + 127) // 128
     use_cluster = M <= DECODE_MAX_M and (force_mode == 2 or (force_mode == -1 and n_tiles < _DECODE_TILE_WAVES * _lib.num_sms(xq.device.index)))
+    # a narrow output (a router: one or two channel tiles) for up to 256 tokens is still a weight stream: the persistent
+    # kernel would walk its whole K loop on one or two CTAs, the cluster kernel splits K and takes 64 tokens per grid layer
+    if not use_cluster and force_mode in (-1, 2) and M <= 4 * DECODE_MAX_M and (force_mode == 2 or n_tiles * ((M + 63) // 64) <= 8):
+        use_cluster = True
     if use_cluster:
         rc = _lib.lib().b200_w8a8_gemm_decode(
             xq.data_ptr(), sx.data_ptr(), wq.data_ptr(), sw.data_ptr(), out.data_ptr(), _lib.ptr(residual),

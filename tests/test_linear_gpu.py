@@ -65,6 +65,7 @@ def test_act_quant_fused_modes(mode):
 
 
 GEMM_SHAPES = [
+    (128, 128, 4096), (200, 256, 2048), (256, 128, 512), (65, 100, 640),      # narrow outputs: several 64-token tiles on the cluster kernel
     (16, 128, 128), (1, 128, 128), (1, 256, 512), (7, 384, 1024), (32, 4096, 4096), (32, 6144, 4096),
     (33, 1024, 512), (100, 4096, 1792), (128, 3584, 4096), (200, 1000, 768), (1024, 3584, 4096),
     (4096, 1792, 4096), (777, 16032, 1024),
