@@ -27,7 +27,7 @@ class MoEBlock:
     def forward(self, W: dict, xq: torch.Tensor, sx: torch.Tensor, xn=None) -> torch.Tensor:
         cfg = self.cfg
         M = xq.shape[0]
-        logits = L.w8a8_gemm(xq, sx, W["router"].qweight, W["router"].scale, out_dtype=torch.float32)
+        logits = L.w8a8_gemm(xq, sx, W["router"].qweight, W["router"].scale, out_dtype=torch.float32, narrow=True)
         ids, wts = MO.router_topk(logits, cfg.top_k, cfg.norm_topk_prob)
         work = MO.moe_align(ids, self.e0, self.n_local)
         xp, sp = MO.moe_gather(xq, sx, work)

@@ -42,7 +42,7 @@ DECODE_MAX_M = 64
 def w8a8_gemm(xq: torch.Tensor, sx: torch.Tensor, wq: torch.Tensor, sw: torch.Tensor, *,
               residual: torch.Tensor | None = None, out: torch.Tensor | None = None,
               out_dtype: torch.dtype = torch.bfloat16, workspace: Workspace | None = None,
-              force_mode: int = -1, force_splits: int = 0) -> torch.Tensor:
+              force_mode: int = -1, force_splits: int = 0, narrow: bool = False) -> torch.Tensor:
     """y[m,n] = (sum_k xq[m,k] wq[n,k]) * sx[m] * sw[n] (+ residual); int8 operands, int32 accumulate in TMEM.
 
     Up to 64 tokens the cluster split-K weight-streaming kernel runs (``force_mode`` -1) unless the problem has
@@ -61,9 +61,13 @@ def w8a8_gemm(xq: torch.Tensor, sx: torch.Tensor, wq: torch.Tensor, sw: torch.Te
     w = workspace or default_workspace(xq.device)
     n_tiles = (N + 127) // 128
     use_cluster = M <= DECODE_MAX_M and (force_mode == 2 or (force_mode == -1 and n_tiles < _DECODE_TILE_WAVES * _lib.num_sms(xq.device.index)))
-    # a narrow output (a router: one or two channel tiles) for up to 256 tokens is still a weight stream: the persistent
+    # a narrow output (a router: one channel tile) for up to 256 tokens is still a weight stream: the persistent
     # kernel would walk its whole K loop on one or two CTAs, the cluster kernel splits K and takes 64 tokens per grid layer
-    if not use_cluster and force_mode in (-1, 2) and M <= 4 * DECODE_MAX_M and (force_mode == 2 or n_tiles * ((M + 63) // 64) <= 8):
+    # (one channel tile only: wider outputs stay on the persistent kernel, whose results the token-sharded paths are
+    # compared with bit for bit - the two kernels multiply the scales in a different order)
+    # The caller asks for it (``narrow=True``) because the two kernels multiply the scales in a different order and
+    # other callers compare this function's persistent-kernel results bit for bit with the token-sharded paths.
+    if not use_cluster and force_mode in (-1, 2) and M <= 4 * DECODE_MAX_M and (force_mode == 2 or (narrow and n_tiles == 1)):
         use_cluster = True
     if use_cluster:
         rc = _lib.lib().b200_w8a8_gemm_decode(
